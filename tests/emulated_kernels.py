@@ -1,0 +1,124 @@
+"""Stand-ins for the CUDA kernels, written with torch on the CPU, for tests only.
+
+The engine has no CPU path. To check the host side of the engine on a machine without
+a GPU (batch building, block tables, page reuse, the scheduler's loop), the `-m "not gpu"`
+tests swap the functions of `tgo_b200.kernels.ops` for these through `install(monkeypatch)`.
+They mirror the kernels' contracts (in-place writes, strided views, the cache layout
+[page, kv_head, offset, head_dim]) and nothing of this file is importable from the
+package itself.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+
+def embed(table, ids, out):
+    out.copy_(table[ids.long()].float())
+
+
+def add_rmsnorm(h, delta, gain, eps, out, rows=None):
+    if rows is None:
+        if delta is not None:
+            h += delta.float()
+        x = h
+    else:
+        x = h[rows.long()]
+        if delta is not None:
+            x = x + delta[rows.long()].float()
+    scale = torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)
+    out.copy_(((x * scale) * gain).to(out.dtype))
+
+
+def residual_add(h, delta):
+    h += delta.float()
+
+
+def swiglu(gate_up, out):
+    f = out.shape[1]
+    g, u = gate_up[:, :f].float(), gate_up[:, f:].float()
+    out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
+
+
+def qk_norm_rope_cache(q, k, v, num_heads, num_kv_heads, head_dim, q_gain, k_gain, eps, positions,
+                       inv_freq, rotary_dim, slots, k_cache, v_cache, page_size):
+    T = q.shape[0]
+
+    def treat(x, heads, gain):
+        y = x.reshape(T, heads, head_dim).float()
+        if gain is not None:
+            y = (y * torch.rsqrt((y * y).mean(-1, keepdim=True) + eps)) * gain
+        if inv_freq is not None:
+            half = rotary_dim // 2
+            ang = positions.double()[:, None] * inv_freq[None, :]
+            cos, sin = ang.cos().float()[:, None, :], ang.sin().float()[:, None, :]
+            lo, hi = y[..., :half].clone(), y[..., half:rotary_dim].clone()
+            y[..., :half] = lo * cos - hi * sin
+            y[..., half:rotary_dim] = lo * sin + hi * cos
+        return y
+
+    q.copy_(treat(q, num_heads, q_gain).reshape(T, -1).to(q.dtype))
+    if k is not None:
+        kk = treat(k, num_kv_heads, k_gain)
+        if k_cache is None:
+            k.copy_(kk.reshape(T, -1).to(k.dtype))
+    if k_cache is not None:
+        vv = v.reshape(T, num_kv_heads, head_dim)
+        for t in range(T):
+            s = int(slots[t])
+            if s < 0:
+                continue
+            page, off = s // page_size, s % page_size
+            k_cache[page, :, off, :] = kk[t].to(k_cache.dtype)
+            v_cache[page, :, off, :] = vv[t]
+
+
+def attention_generic(q, out, num_heads, num_kv_heads, head_dim, k_cache, v_cache, page_size,
+                      block_tables, seq_ids, positions, scale, window):
+    T = q.shape[0]
+    group = num_heads // num_kv_heads
+    scale = float(torch.tensor(scale, dtype=torch.float32))
+    for t in range(T):
+        p, b = int(positions[t]), int(seq_ids[t])
+        lo = max(0, p - window + 1) if window > 0 else 0
+        idx = torch.arange(lo, p + 1)
+        pages = block_tables[b].long()[idx // page_size]
+        offs = idx % page_size
+        for h in range(num_heads):
+            g = h // group
+            K = k_cache[pages, g, offs, :].float()
+            V = v_cache[pages, g, offs, :].float()
+            qv = q[t, h * head_dim:(h + 1) * head_dim].float()
+            s = (K @ qv) * scale
+            w = torch.softmax(s, dim=0)
+            out[t, h * head_dim:(h + 1) * head_dim] = (w @ V).to(out.dtype)
+
+
+def paged_attention(q, out, num_heads, num_kv_heads, head_dim, cache, ctx, scale, window):
+    attention_generic(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
+                      cache.page_size, cache.block_tables, ctx.seq_ids, ctx.positions, scale,
+                      window)
+
+
+def linear(x, w, out_dtype=None, out=None):
+    y = (x.float() @ w.float().t()).to(out_dtype or x.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def sgemm_tn(x, w, out):
+    out.copy_(x @ w.t())
+
+
+NAMES = ["embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",
+         "attention_generic", "paged_attention", "linear", "sgemm_tn"]
+
+
+def install(monkeypatch):
+    from tgo_b200.kernels import ops
+    here = globals()
+    for name in NAMES:
+        monkeypatch.setattr(ops, name, here[name])

@@ -1,0 +1,324 @@
+// Memory-bound kernels between the matrix products: embedding gather, residual add
+// fused with RMSNorm (and with the row selection before the head), the SiLU gate, and
+// per-head q/k RMSNorm fused with the rotation and the write into the paged cache.
+// Sums of squares, the rotation and the residual are float32 whatever the storage.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+// out[t, :] = table[ids[t], :] widened to float32 (the residual stream's type).
+// An id outside [0, V) writes zeros; the host refuses such ids before the launch.
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int d, int V) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < V;
+    const T* row = table + (size_t)(ok ? id : 0) * d;
+    float* o = out + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? to_f32(row[i]) : 0.f;
+}
+
+TGO_API int tgo_embed(const void* table, int dtype, const int* ids, float* out, int T, int d,
+                      int V, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (dtype == TGO_BF16)
+        embed_kernel<bf16><<<T, threads, 0, stream>>>((const bf16*)table, ids, out, d, V);
+    else if (dtype == TGO_F32)
+        embed_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, d, V);
+    else
+        return TGO_E_BAD_ARG;
+    return launch_status();
+}
+
+// ------------------------------------------------------- residual add + RMSNorm
+// For output row i: r = rows ? rows[i] : i;  x = h[r] (+ delta[r]);  if rows is null the
+// sum is written back to h (the residual stream moves on);  out[i] = x * rsqrt(mean x^2
+// + eps) * gain, computed as (x * scale) * gain.  One block per row; the row is held in
+// registers when it fits (d <= blockDim * 4 * CHUNKS), else read a second time.
+template <typename TD, typename TO, int CHUNKS>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                   const float* __restrict__ gain, float eps,
+                                   TO* __restrict__ out, const int* __restrict__ rows, int d) {
+    __shared__ float scratch[33];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    float* hr = h + (size_t)r * d;
+    const TD* dr = delta ? delta + (size_t)r * d : nullptr;
+    TO* o = out + (size_t)i * d;
+    float x[CHUNKS > 0 ? CHUNKS : 1];
+    float ss = 0.f;
+    if (CHUNKS > 0) {
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int j = threadIdx.x + c * blockDim.x;
+            float v = 0.f;
+            if (j < d) {
+                v = hr[j];
+                if (dr) v += to_f32(dr[j]);
+                if (dr && !rows) hr[j] = v;
+            }
+            x[c] = v;
+            ss += v * v;
+        }
+    } else {
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            float v = hr[j];
+            if (dr) v += to_f32(dr[j]);
+            if (dr && !rows) hr[j] = v;
+            ss += v * v;
+        }
+    }
+    const float total = block_sum(ss, scratch);
+    const float scale = rsqrtf(total / (float)d + eps);
+    if (CHUNKS > 0) {
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int j = threadIdx.x + c * blockDim.x;
+            if (j < d) o[j] = from_f32<TO>((x[c] * scale) * gain[j]);
+        }
+    } else {
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            float v = hr[j];
+            if (dr && rows) v += to_f32(dr[j]);
+            o[j] = from_f32<TO>((v * scale) * gain[j]);
+        }
+    }
+}
+
+template <typename TD, typename TO>
+static int add_rmsnorm_launch(float* h, const void* delta, const float* gain, float eps, void* out,
+                              const int* rows, int n, int d, cudaStream_t s) {
+    const TD* dl = (const TD*)delta;
+    TO* o = (TO*)out;
+    int threads = 256;
+    if (d > 2048) threads = 512;
+    if (d > 4096) threads = 1024;
+    const int chunks = (d + threads - 1) / threads;
+    if (chunks <= 4)
+        add_rmsnorm_kernel<TD, TO, 4><<<n, threads, 0, s>>>(h, dl, gain, eps, o, rows, d);
+    else if (chunks <= 8)
+        add_rmsnorm_kernel<TD, TO, 8><<<n, threads, 0, s>>>(h, dl, gain, eps, o, rows, d);
+    else if (chunks <= 16)
+        add_rmsnorm_kernel<TD, TO, 16><<<n, threads, 0, s>>>(h, dl, gain, eps, o, rows, d);
+    else
+        add_rmsnorm_kernel<TD, TO, 0><<<n, threads, 0, s>>>(h, dl, gain, eps, o, rows, d);
+    return launch_status();
+}
+
+TGO_API int tgo_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* gain,
+                            float eps, void* out, int out_dtype, const int* rows, int n, int d,
+                            cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (d <= 0) return TGO_E_BAD_ARG;
+    if (out_dtype == TGO_BF16 && (delta_dtype == TGO_BF16 || !delta))
+        return add_rmsnorm_launch<bf16, bf16>(h, delta, gain, eps, out, rows, n, d, stream);
+    if (out_dtype == TGO_F32 && (delta_dtype == TGO_F32 || !delta))
+        return add_rmsnorm_launch<float, float>(h, delta, gain, eps, out, rows, n, d, stream);
+    if (out_dtype == TGO_BF16 && delta_dtype == TGO_F32)
+        return add_rmsnorm_launch<float, bf16>(h, delta, gain, eps, out, rows, n, d, stream);
+    if (out_dtype == TGO_F32 && delta_dtype == TGO_BF16)
+        return add_rmsnorm_launch<bf16, float>(h, delta, gain, eps, out, rows, n, d, stream);
+    return TGO_E_BAD_ARG;
+}
+
+// h[r] += delta[r] for every row, nothing else (the add a block leaves pending when
+// no norm follows it).
+template <typename TD>
+__global__ void residual_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) h[i] += to_f32(delta[i]);
+}
+
+TGO_API int tgo_residual_add(float* h, const void* delta, int dtype, long long n,
+                             cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)((n + threads - 1) / threads < 65535 ? (n + threads - 1) / threads : 65535);
+    if (dtype == TGO_BF16)
+        residual_add_kernel<bf16><<<blocks, threads, 0, stream>>>(h, (const bf16*)delta, (size_t)n);
+    else if (dtype == TGO_F32)
+        residual_add_kernel<float><<<blocks, threads, 0, stream>>>(h, (const float*)delta, (size_t)n);
+    else
+        return TGO_E_BAD_ARG;
+    return launch_status();
+}
+
+// ------------------------------------------------------------------- SiLU gate
+// out[t, j] = silu(gu[t, j]) * gu[t, f + j];  gu is [T, 2f] (gate columns, then up).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int f) {
+    const size_t t = blockIdx.y;
+    const T* g = gu + t * 2 * (size_t)f;
+    const T* u = g + f;
+    T* o = out + t * (size_t)f;
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < f; j += gridDim.x * blockDim.x) {
+        const float a = to_f32(g[j]);
+        const float s = a / (1.f + expf(-a));
+        o[j] = from_f32<T>(s * to_f32(u[j]));
+    }
+}
+
+// bf16, 8 values per thread when f is a multiple of 8 (16-byte loads and stores).
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int f) {
+    const size_t t = blockIdx.y;
+    const uint4* g = (const uint4*)(gu + t * 2 * (size_t)f);
+    const uint4* u = (const uint4*)(gu + t * 2 * (size_t)f + f);
+    uint4* o = (uint4*)(out + t * (size_t)f);
+    const int n8 = f / 8;
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n8; j += gridDim.x * blockDim.x) {
+        uint4 gv = g[j], uv = u[j], ov;
+        const __nv_bfloat162* gp = (const __nv_bfloat162*)&gv;
+        const __nv_bfloat162* up = (const __nv_bfloat162*)&uv;
+        __nv_bfloat162* op = (__nv_bfloat162*)&ov;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 a = __bfloat1622float2(gp[k]);
+            const float2 b = __bfloat1622float2(up[k]);
+            float2 r;
+            r.x = a.x / (1.f + expf(-a.x)) * b.x;
+            r.y = a.y / (1.f + expf(-a.y)) * b.y;
+            op[k] = __float22bfloat162_rn(r);
+        }
+        o[j] = ov;
+    }
+}
+
+TGO_API int tgo_swiglu(const void* gate_up, void* out, int dtype, int T, int f,
+                       cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (f <= 0 || T > 65535 * 32) return TGO_E_BAD_ARG;
+    // grid.y is limited to 65535 rows: larger batches go in slices.
+    for (int t0 = 0; t0 < T; t0 += 65535) {
+        const int rows = T - t0 < 65535 ? T - t0 : 65535;
+        if (dtype == TGO_BF16 && f % 8 == 0) {
+            const int bx = (f / 8 + 255) / 256;
+            swiglu_bf16x8_kernel<<<dim3(bx, rows), 256, 0, stream>>>(
+                (const bf16*)gate_up + (size_t)t0 * 2 * f, (bf16*)out + (size_t)t0 * f, f);
+        } else if (dtype == TGO_BF16) {
+            swiglu_kernel<bf16><<<dim3((f + 255) / 256, rows), 256, 0, stream>>>(
+                (const bf16*)gate_up + (size_t)t0 * 2 * f, (bf16*)out + (size_t)t0 * f, f);
+        } else if (dtype == TGO_F32) {
+            swiglu_kernel<float><<<dim3((f + 255) / 256, rows), 256, 0, stream>>>(
+                (const float*)gate_up + (size_t)t0 * 2 * f, (float*)out + (size_t)t0 * f, f);
+        } else {
+            return TGO_E_BAD_ARG;
+        }
+    }
+    return launch_status();
+}
+
+// --------------------------------- per-head q/k RMSNorm + rotation + cache write
+// One block per token. Heads of q are normalised (if q_gain), rotated (if inv_freq) and
+// written back in place; heads of k likewise and then stored at the token's slot of the
+// paged cache; v is copied to its slot. The rotation pairs channel i with i + rot/2
+// (half-split), angle = position * inv_freq[i] evaluated in float64, the rotation itself
+// in float32. slot < 0 stores nothing. k or v may be null (a layer that reads another
+// layer's cache computes q only); with k given and k_cache null, k is written back in
+// place like q (used when another position encoding runs between the norm and the store).
+//
+// Cache layout of one layer: [page][kv_head][offset in page][head_dim]; slot = page *
+// page_size + offset.
+#define QKR_MAX_DH 512
+template <typename T>
+__global__ void qk_norm_rope_cache_kernel(
+    T* __restrict__ q, long long q_stride, T* __restrict__ k, long long k_stride,
+    const T* __restrict__ v, long long v_stride, int H, int Hkv, int dh,
+    const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+    const int* __restrict__ positions, const double* __restrict__ inv_freq, int rot,
+    const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
+    int page_size) {
+    extern __shared__ float smem[];
+    const int t = blockIdx.x;
+    const int half = rot / 2;
+    float* cs = smem;                 // [half] cos, [half] sin
+    const int nwarps = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* buf = smem + 2 * half + warp * dh;
+    if (inv_freq) {
+        const double pos = (double)positions[t];
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            double s, c;
+            sincos(pos * inv_freq[i], &s, &c);
+            cs[i] = (float)c;
+            cs[half + i] = (float)s;
+        }
+    }
+    __syncthreads();
+    const int slot = slots ? slots[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+    const int n_heads = H + (k ? Hkv : 0);
+    for (int hh = warp; hh < n_heads; hh += nwarps) {
+        const bool is_q = hh < H;
+        const int head = is_q ? hh : hh - H;
+        T* vec = is_q ? q + (size_t)t * q_stride + (size_t)head * dh
+                      : k + (size_t)t * k_stride + (size_t)head * dh;
+        const float* gain = is_q ? q_gain : k_gain;
+        float ss = 0.f;
+        for (int i = lane; i < dh; i += 32) {
+            const float x = to_f32(vec[i]);
+            buf[i] = x;
+            ss += x * x;
+        }
+        if (gain) {
+            ss = warp_sum(ss);
+            const float scale = rsqrtf(ss / (float)dh + eps);
+            for (int i = lane; i < dh; i += 32) buf[i] = (buf[i] * scale) * gain[i];
+        }
+        __syncwarp();
+        T* dst = vec;
+        if (!is_q && k_cache) {
+            dst = slot >= 0 ? k_cache + (((size_t)page * Hkv + head) * page_size + off) * dh
+                            : nullptr;
+        }
+        if (dst) {
+            for (int i = lane; i < dh; i += 32) {
+                float y;
+                if (inv_freq && i < half)
+                    y = buf[i] * cs[i] - buf[i + half] * cs[half + i];
+                else if (inv_freq && i < rot)
+                    y = buf[i - half] * cs[half + i - half] + buf[i] * cs[i - half];
+                else
+                    y = buf[i];
+                dst[i] = from_f32<T>(y);
+            }
+        }
+        __syncwarp();
+    }
+    if (v && slot >= 0) {
+        for (int i = threadIdx.x; i < Hkv * dh; i += blockDim.x) {
+            const int head = i / dh, c = i % dh;
+            v_cache[(((size_t)page * Hkv + head) * page_size + off) * dh + c] =
+                v[(size_t)t * v_stride + i];
+        }
+    }
+}
+
+TGO_API int tgo_qk_norm_rope_cache(void* q, long long q_stride, void* k, long long k_stride,
+                                   const void* v, long long v_stride, int dtype, int T, int H,
+                                   int Hkv, int dh, const float* q_gain, const float* k_gain,
+                                   float eps, const int* positions, const double* inv_freq,
+                                   int rot, const int* slots, void* k_cache, void* v_cache,
+                                   int page_size, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (dh <= 0 || dh > QKR_MAX_DH || rot < 0 || rot > dh || (rot & 1) || H <= 0) return TGO_E_BAD_ARG;
+    if ((k || v) && Hkv <= 0) return TGO_E_BAD_ARG;
+    if ((k_cache || v) && (page_size <= 0 || !slots)) return TGO_E_BAD_ARG;
+    if ((v && !v_cache) || (k_cache && !k)) return TGO_E_BAD_ARG;
+    if (inv_freq && !positions) return TGO_E_BAD_ARG;
+    const int warps = 4;
+    const size_t smem = (size_t)(rot + warps * dh) * sizeof(float);
+    if (dtype == TGO_BF16)
+        qk_norm_rope_cache_kernel<bf16><<<T, warps * 32, smem, stream>>>(
+            (bf16*)q, q_stride, (bf16*)k, k_stride, (const bf16*)v, v_stride, H, Hkv, dh, q_gain,
+            k_gain, eps, positions, inv_freq, rot, slots, (bf16*)k_cache, (bf16*)v_cache, page_size);
+    else if (dtype == TGO_F32)
+        qk_norm_rope_cache_kernel<float><<<T, warps * 32, smem, stream>>>(
+            (float*)q, q_stride, (float*)k, k_stride, (const float*)v, v_stride, H, Hkv, dh,
+            q_gain, k_gain, eps, positions, inv_freq, rot, slots, (float*)k_cache,
+            (float*)v_cache, page_size);
+    else
+        return TGO_E_BAD_ARG;
+    return launch_status();
+}

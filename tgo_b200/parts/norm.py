@@ -1,0 +1,38 @@
+"""RMSNorm over the last axis, with the residual add (and the row selection before the
+head) fused into the same kernel: y = (x * rsqrt(mean x^2 + eps)) * gain, eps inside
+the root, sums in float32 (nn/blocks.go:53-55; internal/oracle/oracle.go:31-67)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..config.spec import NormSpec
+from ..kernels import ops
+from ..registry import NORMS
+from ..weights.binder import WeightSpec
+from .base import Part
+
+
+class RMSNorm(Part):
+    def __init__(self, spec: NormSpec, width: int, name: str):
+        self.eps = float(spec.eps)
+        self.width = width
+        self.name = name
+        self.gain: Optional[torch.Tensor] = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.name, (self.width,), "gain")]
+
+    def bind(self, weights):
+        self.gain = weights[self.name].contiguous()
+
+    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n = h.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.width), dtype=out_dtype, device=h.device)
+        ops.add_rmsnorm(h, delta, self.gain, self.eps, out, rows)
+        return out
+
+
+NORMS.register("rmsnorm", RMSNorm)
