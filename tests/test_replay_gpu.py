@@ -1,0 +1,56 @@
+"""Replay on the GPU: the same requests whole, with the last 32 tokens one by one, in
+portions of changing size, and mixed with page reuse, in float32 and in bfloat16, through
+bin/trace_run (a subprocess, as a user runs it) and compared with the plain implementation."""
+import numpy as np
+import pytest
+
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [5, 17, 33, 70, 100, 64], "B": [1, 9, 40, 70, 129, 48]}
+FAMILIES = {"whole": tiny.trace_whole, "tail": tiny.trace_tail, "portions": tiny.trace_portions,
+            "mixed": tiny.trace_mixed}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for name, (cfg, run) in tiny.TINIES.items():
+        d = tiny.make_model_dir(tmp_path_factory.mktemp(f"tiny{name}"), cfg, run["seed"],
+                                run["sigma"])
+        reqs = tiny.random_requests(cfg["vocab_size"], LENGTHS[name], seed=10 + run["seed"])
+        out[name] = (d, cfg, run, reqs, tiny.plain_logits(d, reqs))
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("family", list(FAMILIES))
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_replay_matches_plain(models, tmp_path, name, family, dtype):
+    d, cfg, run, reqs, want = models[name]
+    trace = FAMILIES[family](reqs)
+    got = tiny.run_trace_program(d, dtype, trace, tmp_path / "out", cfg["vocab_size"],
+                                 extra=["--page-size", str(run["page_size"])])
+    assert len(got) == sum(len(t) for t in reqs.values())
+    worst, where, tol = tiny.compare(got, want, cfg, dtype)
+    assert worst <= tol, f"{name}/{family}/{dtype}: error {worst:.3e} at {where}, allowed {tol:.3e}"
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_float32_cuts_agree_bit_for_bit(models, name):
+    """In float32 every sum's order depends on the position alone, so the four ways of
+    cutting give the same bits, not just close values."""
+    import tgo_b200
+    d, cfg, run, reqs, _ = models[name]
+    model = tgo_b200.open(d, dtype="float32")
+    results = {}
+    for fam, make in FAMILIES.items():
+        trace = make(reqs)
+        eng = model.new_engine(page_size=run["page_size"], max_tokens=tiny.max_tokens_of(trace),
+                               num_slots=4)
+        results[fam] = tiny.run_trace_engine(eng, trace)
+    base = results["whole"]
+    for fam, got in results.items():
+        for k, row in got.items():
+            assert np.array_equal(row, base[k]), f"{name}: {fam} differs from whole at {k}"
