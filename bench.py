@@ -1,0 +1,199 @@
+#!/usr/bin/env python3
+"""Headline measurement: decode tokens a second of a Qwen3-8B-shaped model with random
+bfloat16 weights at batch 8 (1,024-token prompts), on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step. Prints one JSON line: `value` is decoded tokens a second timed
+on the device over exactly K steps; `e2e` is the same through the Python entry point
+(scheduler, sampling, host tokens in and out); `prefill` a 2,048-token prompt; `roofline`
+the bytes a decode step must read over its time against the measured copy bandwidth;
+`points` decoding at batch 1 and 64.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# configs[2] of the baseline record: the Qwen3-8B shape
+CONFIG_8B = dict(architectures=["Qwen3ForCausalLM"], hidden_size=4096, num_hidden_layers=36,
+                 num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                 intermediate_size=12288, vocab_size=151936, rms_norm_eps=1e-6,
+                 rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=40960,
+                 attention_bias=False, sliding_window=None, use_sliding_window=False)
+SEED = 8
+PROMPT = 1024
+CONTEXT_CAP = 8192
+PAGE = 16
+PREFILL_TOKENS = 2048
+
+
+class ClockSampler:
+    """nvidia-smi in the background during the timed region (reads only)."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(index), "-lms", "200"], stdout=subprocess.PIPE,
+                stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm():
+    """The reference is a Go program (go.mod wants Go 1.27, and its device layer is an
+    external Go module); there is no Go toolchain here and pip cannot install it."""
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "latere-ai/tgo is Go (no setup.py/pyproject; needs Go 1.27 and the "
+                      "external golang.design/x/accel module, neither present offline); "
+                      "pip install of /root/reference fails"}))
+    return 0
+
+
+def e2e_decode(model, batch, steps, warmup):
+    """Decode tokens a second through the public entry point: new_scheduler, admit, then
+    Runner steps (plan, pack inputs in pinned memory, copy, run, sample on the device,
+    read the ids back, feed). Timed with the host clock around exactly `steps` steps."""
+    import torch
+
+    from tgo_b200.engine.measure import random_prompts, round_up
+    from tgo_b200.engine.scheduler import Request, Runner
+    from tgo_b200.sampling.policy import Policy
+    from tgo_b200.sampling.sampler import sample_rows
+    total = warmup + steps + 2
+    sched = model.new_scheduler(batch, chunk=PREFILL_TOKENS, reserve=total,
+                                pool_tokens=batch * round_up(PROMPT + total, 64), page_size=PAGE,
+                                max_batched_tokens=8192)
+    runner = Runner(sched, sample_rows)
+    prompts = random_prompts(model.spec.vocab_size, batch, PROMPT, SEED + 1)
+    reqs = [Request(p, Policy(max_tokens=total), request_id=i) for i, p in enumerate(prompts)]
+    for r in reqs:
+        runner.submit(r)
+    while min(len(r.output) for r in reqs) < warmup + 1:
+        runner.run_step()
+    torch.cuda.synchronize()
+    before = sum(len(r.output) for r in reqs)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        runner.run_step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    made = sum(len(r.output) for r in reqs) - before
+    h2d = sched.engine.h2d_bytes_last
+    for slot in list(runner.by_slot):
+        sched.finish(slot)
+    return {"value": made / dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": 4 * batch, "ms_per_step": dt / steps * 1e3}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the 36 (0: all)")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64, and prefill")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        print("bench: this engine runs on one GPU; --gpus must be 1")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+
+    import tgo_b200
+    from tgo_b200.engine.measure import load_peaks, measure_decode, measure_prefill
+
+    config = dict(CONFIG_8B)
+    if args.layers:
+        config["num_hidden_layers"] = args.layers
+    model = tgo_b200.open_random(config, seed=SEED, dtype="bfloat16", sigma=0.02, gain_sigma=0.05)
+    peaks = load_peaks()
+
+    clocks = ClockSampler()
+    main_run = measure_decode(model, args.batch, PROMPT, args.steps, warmup=warmup, seed=SEED,
+                              page_size=PAGE)
+    clock_record = clocks.stop()
+    e2e = e2e_decode(model, args.batch, args.steps, warmup)
+    points, prefill = {}, None
+    if not args.no_points:
+        for b in (1, 64):
+            r = measure_decode(model, b, PROMPT, min(args.steps, 128), warmup=warmup, seed=SEED,
+                               page_size=PAGE)
+            points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
+            points[f"decode_b{b}_hbm_frac"] = round(r["gbs"] / peaks["hbm_gbs"], 3)
+        pre = measure_prefill(model, PREFILL_TOKENS, warmup=3, steps=3, seed=SEED, page_size=PAGE)
+        prefill = {"value": round(pre["tokens_per_s"], 1), "tokens": PREFILL_TOKENS,
+                   "ms": round(pre["ms"], 3),
+                   "frac": round(pre["tflops"] / peaks["bf16_tflops"], 4)}
+    line = {
+        "metric": "decode tokens/s, Qwen3-8B shape, batch 8, 1024-token prompts",
+        "value": round(main_run["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded uniform-random token ids, random N(0,0.02) weights",
+        "config": {"model": "Qwen3-8B shape", "layers": config["num_hidden_layers"],
+                   "layers_of_full_model": 36, "hidden": 4096, "heads": 32, "kv_heads": 8,
+                   "head_dim": 128, "intermediate": 12288, "vocab": 151936,
+                   "global_batch": args.batch, "seq_len": PROMPT, "context_cap": CONTEXT_CAP,
+                   "page_size": PAGE, "prefill_tokens": PREFILL_TOKENS, "seed": SEED,
+                   "parallelism": "1 GPU",
+                   "l2": "inputs larger than L2: every step streams all weights from HBM",
+                   "peaks": peaks["source"]},
+        "clocks": clock_record, "e2e": {k: (round(v, 2) if isinstance(v, float) else v)
+                                        for k, v in e2e.items()},
+        "gpu_launches": main_run["gpu_launches"],
+        "roofline": {"bound": "hbm", "achieved": round(main_run["gbs"], 1),
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(main_run["gbs"] / peaks["hbm_gbs"], 4)},
+        "points": points,
+    }
+    if prefill is not None:
+        line["prefill"] = prefill
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

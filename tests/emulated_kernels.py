@@ -113,7 +113,35 @@ def sgemm_tn(x, w, out):
     out.copy_(x @ w.t())
 
 
-NAMES = ["embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",
+def argmax(logits, out):
+    import plain_qwen3 as plain
+    for r in range(logits.shape[0]):
+        out[r] = plain.argmax_lowest(logits[r].numpy())
+
+
+def sample(logits, temperature, top_k, top_p, draws, out):
+    import plain_qwen3 as plain
+    for r in range(logits.shape[0]):
+        ids, w, total = plain.policy_distribution(
+            logits[r].numpy(), temperature=float(temperature[r]), top_k=int(top_k[r]),
+            top_p=float(top_p[r]))
+        out[r] = plain.walk(ids, w, total, float(draws[r]))
+
+
+def logits_adjust(row, bias_ids, bias, ids, counts, repetition, presence, frequency):
+    if bias_ids is not None:
+        for i, b in zip(bias_ids.tolist(), bias.tolist()):
+            row[i] += b
+    if ids is not None:
+        for i, c in zip(ids.tolist(), counts.tolist()):
+            x = float(row[i])
+            if repetition not in (0.0, 1.0):
+                x = x / repetition if x > 0 else x * repetition
+            x -= presence + frequency * c
+            row[i] = x
+
+
+NAMES = ["argmax", "sample", "logits_adjust", "embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",
          "attention_generic", "paged_attention", "linear", "sgemm_tn"]
 
 

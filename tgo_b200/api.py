@@ -77,13 +77,57 @@ class LoadedModel:
         from .engine.step import Engine
         return Engine(self.model, page_size, max_tokens, num_pages, num_slots)
 
-    def new_scheduler(self, slots: int, chunk: int = 0, reserve: int = 512, **kw):
-        from .engine.scheduler import Scheduler
-        return Scheduler(self, slots, chunk=chunk, reserve=reserve, **kw)
+    def new_scheduler(self, slots: int, chunk: int = 0, reserve: int = 512,
+                      pool_tokens: Optional[int] = None, page_size: int = 16,
+                      max_batched_tokens: Optional[int] = None):
+        """A continuous-batching scheduler over a pool of `pool_tokens` cache positions
+        (default: every slot can hold chunk + reserve... at least 4096 positions)."""
+        from .engine.scheduler import DEFAULT_CHUNK, Scheduler
+        from .engine.step import Engine
+        if pool_tokens is None:
+            pool_tokens = slots * max(4096, (chunk or DEFAULT_CHUNK) + reserve)
+        engine = Engine(self.model, page_size=page_size, max_tokens=pool_tokens, num_slots=slots)
+        return Scheduler(engine, slots, chunk=chunk, reserve=reserve,
+                         max_batched_tokens=max_batched_tokens)
 
     def new_session(self, context: int = 4096, **kw):
         from .engine.session import Session
         return Session(self, context, **kw)
+
+    def generate(self, prompts, policy=None, slots: Optional[int] = None, chunk: int = 0,
+                 pool_tokens: Optional[int] = None, page_size: int = 16, stop_ids=(),
+                 max_batched_tokens: Optional[int] = None, scheduler=None,
+                 reserve: Optional[int] = None):
+        """Run every prompt (lists of token ids) to completion with continuous batching;
+        returns the generated ids per prompt, in order. `policy` is one Policy for all or
+        one per prompt; its max_tokens must be positive."""
+        from .engine.scheduler import Request, Runner
+        from .sampling.policy import Policy
+        from .sampling.sampler import sample_rows
+        prompts = [list(map(int, p)) for p in prompts]
+        policies = policy if isinstance(policy, (list, tuple)) else [policy or Policy(
+            max_tokens=16)] * len(prompts)
+        V = self.spec.vocab_size
+        for pol in policies:
+            pol.check(V)
+            if pol.max_tokens <= 0:
+                raise ValueError("generate: give every policy a positive max_tokens")
+        slots = slots or min(len(prompts), 64)
+        if scheduler is None:
+            need = max(len(p) + pol.max_tokens for p, pol in zip(prompts, policies))
+            if pool_tokens is None:
+                pool_tokens = slots * ((need + 63) // 64 * 64)
+            scheduler = self.new_scheduler(slots, chunk=chunk, reserve=reserve or max(
+                pol.max_tokens for pol in policies), pool_tokens=pool_tokens,
+                page_size=page_size, max_batched_tokens=max_batched_tokens)
+        runner = Runner(scheduler, sample_rows, stop_ids)
+        requests = [Request(p, pol, request_id=i) for i, (p, pol) in
+                    enumerate(zip(prompts, policies))]
+        for r in requests:
+            runner.submit(r)
+        runner.run()
+        self.last_runner = runner
+        return [r.output for r in requests]
 
 
 def open(model_dir: str, dtype="bfloat16", device="cuda:0", log=None) -> LoadedModel:  # noqa: A001

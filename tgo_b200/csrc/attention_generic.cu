@@ -24,7 +24,7 @@ __global__ void attention_generic_kernel(
     if (h >= H) return;
     float* qs = smem + warp * dh;
     const int p = positions[t];
-    const int b = seq_ids[t];
+    const int b = p >= 0 ? seq_ids[t] : 0;
     const int kvh = h / (H / Hkv);
     const int* bt = block_tables + (size_t)b * max_blocks;
     const T* qv = q + (size_t)t * q_stride + (size_t)h * dh;
@@ -68,7 +68,7 @@ __global__ void attention_generic_kernel(
         m = m_new;
     }
     T* o = out + (size_t)t * out_stride + (size_t)h * dh;
-    const float inv = 1.f / l;
+    const float inv = l > 0.f ? 1.f / l : 0.f;     // position < 0: no keys, zeros out
 #pragma unroll
     for (int i = 0; i < AG_MAX_DH / 32; ++i) {
         const int d = lane + 32 * i;

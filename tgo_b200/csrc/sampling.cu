@@ -1,0 +1,331 @@
+// Sampling on the device, one block per row of float32 logits, so that a step reads back
+// token ids instead of [rows, vocab] floats.
+//
+// The order of the stages is the reference's (sample/sample.go:16-24, sample/stages.go:
+// 74-146): bias -> penalties -> (temperature 0: argmax, ties to the lowest id) -> divide by
+// the temperature -> top-k on the softmax weights by (weight, lower id) -> top-p (smallest
+// prefix of the descending candidates whose weight reaches p of the total; at most 128
+// candidates) -> walk the kept ids in ascending order and return the first whose running
+// sum exceeds u * total, or the last kept id if rounding never gets there.
+//
+// Sums over the vocabulary are formed per thread over a contiguous range and then over the
+// threads in order, which is not the reference's single ascending sum: totals can differ
+// in their last bits and so can a draw that lands within rounding of a boundary.
+#include "common.cuh"
+
+#define SM_THREADS 1024
+#define SM_MAXC 128          // most candidates a truncation stage keeps (sample.go:47)
+
+// ---------------------------------------------------------------- bias and penalties
+// Sparse edits of one row: logits[bias_ids[i]] += bias[i]; then for each distinct history
+// token (ids, counts): repetition (divide a positive logit, multiply otherwise), then
+// subtract presence + frequency * count (sample/stages.go:152-190).
+__global__ void adjust_kernel(float* __restrict__ row, const int* __restrict__ bias_ids,
+                              const float* __restrict__ bias, int n_bias,
+                              const int* __restrict__ ids, const int* __restrict__ counts, int n_ids,
+                              float rep, float presence, float frequency, int V) {
+    for (int i = threadIdx.x; i < n_bias; i += blockDim.x)
+        if (bias_ids[i] >= 0 && bias_ids[i] < V) row[bias_ids[i]] += bias[i];
+    __syncthreads();
+    const bool use_rep = rep != 0.f && rep != 1.f;
+    const bool use_add = presence != 0.f || frequency != 0.f;
+    for (int i = threadIdx.x; i < n_ids; i += blockDim.x) {
+        const int id = ids[i];
+        if (id < 0 || id >= V) continue;
+        float x = row[id];
+        if (use_rep) x = x > 0.f ? x / rep : x * rep;
+        if (use_add) x -= presence + frequency * (float)counts[i];
+        row[id] = x;
+    }
+}
+
+TGO_API int tgo_logits_adjust(float* row, const int* bias_ids, const float* bias, int n_bias,
+                              const int* ids, const int* counts, int n_ids, float rep,
+                              float presence, float frequency, int V, cudaStream_t stream) {
+    if (n_bias <= 0 && n_ids <= 0) return 0;
+    adjust_kernel<<<1, 256, 0, stream>>>(row, bias_ids, bias, n_bias, ids, counts, n_ids, rep,
+                                         presence, frequency, V);
+    return launch_status();
+}
+
+// ------------------------------------------------------------------------- helpers
+struct Best { float v; int i; };
+
+__device__ __forceinline__ Best better(Best a, Best b) {   // larger value, then lower id
+    return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+
+// argmax of f(row[i]) over the row with the lowest-id tie rule; every thread gets it.
+__device__ Best block_argmax(const float* __restrict__ row, int V, float inv_t, Best* scratch) {
+    Best b = {-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = inv_t == 1.f ? row[i] : row[i] / inv_t;
+        if (v > b.v || (v == b.v && i < b.i)) { b.v = v; b.i = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other;
+        other.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+        other.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+        b = better(b, other);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = b;
+    __syncthreads();
+    if (warp == 0) {
+        Best t = lane < (blockDim.x >> 5) ? scratch[lane] : Best{-INFINITY, 0x7fffffff};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            Best other;
+            other.v = __shfl_xor_sync(0xffffffffu, t.v, o);
+            other.i = __shfl_xor_sync(0xffffffffu, t.i, o);
+            t = better(t, other);
+        }
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__global__ void __launch_bounds__(SM_THREADS)
+argmax_kernel(const float* __restrict__ logits, long long stride, int V, int* __restrict__ out) {
+    __shared__ Best scratch[33];
+    const float* row = logits + (size_t)blockIdx.x * stride;
+    const Best b = block_argmax(row, V, 1.f, scratch);
+    if (threadIdx.x == 0) out[blockIdx.x] = b.i;
+}
+
+TGO_API int tgo_argmax(const float* logits, long long stride, int n, int V, int* out,
+                       cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (V <= 0) return TGO_E_BAD_ARG;
+    argmax_kernel<<<n, SM_THREADS, 0, stream>>>(logits, stride, V, out);
+    return launch_status();
+}
+
+// Exclusive prefix of per-thread values (float), in thread order; total in *total.
+// part[] has blockDim.x + 1 floats of shared memory. The order of additions is fixed.
+__device__ void block_prefix_f(float mine, float* part, float* seg, float* total) {
+    const int t = threadIdx.x;
+    part[t] = mine;
+    __syncthreads();
+    if (t < 32) {
+        float s = 0.f;
+        for (int j = 0; j < 32; ++j) s += part[t * 32 + j];
+        seg[t] = s;
+    }
+    __syncthreads();
+    if (t == 0) {
+        float s = 0.f;
+        for (int j = 0; j < 32; ++j) { const float x = seg[j]; seg[j] = s; s += x; }
+        *total = s;
+    }
+    __syncthreads();
+    if (t < 32) {
+        float s = seg[t];
+        for (int j = 0; j < 32; ++j) { const float x = part[t * 32 + j]; part[t * 32 + j] = s; s += x; }
+    }
+    __syncthreads();
+}
+
+__device__ void block_prefix_i(int mine, int* part, int* seg, int* total) {
+    const int t = threadIdx.x;
+    part[t] = mine;
+    __syncthreads();
+    if (t < 32) {
+        int s = 0;
+        for (int j = 0; j < 32; ++j) s += part[t * 32 + j];
+        seg[t] = s;
+    }
+    __syncthreads();
+    if (t == 0) {
+        int s = 0;
+        for (int j = 0; j < 32; ++j) { const int x = seg[j]; seg[j] = s; s += x; }
+        *total = s;
+    }
+    __syncthreads();
+    if (t < 32) {
+        int s = seg[t];
+        for (int j = 0; j < 32; ++j) { const int x = part[t * 32 + j]; part[t * 32 + j] = s; s += x; }
+    }
+    __syncthreads();
+}
+
+// ------------------------------------------------------------------------- sampler
+__global__ void __launch_bounds__(SM_THREADS)
+sample_kernel(const float* __restrict__ logits, long long stride, int V,
+              const float* __restrict__ temperature, const int* __restrict__ top_k,
+              const float* __restrict__ top_p, const float* __restrict__ draws,
+              int* __restrict__ out) {
+    __shared__ Best bscratch[33];
+    __shared__ float part[SM_THREADS];
+    __shared__ float seg[32];
+    __shared__ int ipart[SM_THREADS];
+    __shared__ int iseg[32];
+    __shared__ float total_s;
+    __shared__ int itotal_s;
+    __shared__ int result_s;
+    __shared__ unsigned hist[256];
+    __shared__ unsigned sel_prefix, sel_remaining;
+    __shared__ float cw[SM_MAXC], sw[SM_MAXC];
+    __shared__ int cid[SM_MAXC], sid[SM_MAXC];
+    __shared__ int n_cand, n_kept;
+
+    const int r = blockIdx.x, t = threadIdx.x;
+    const float* row = logits + (size_t)r * stride;
+    const float T = temperature[r];
+    const float u = draws[r];
+    if (T == 0.f) {
+        const Best b = block_argmax(row, V, 1.f, bscratch);
+        if (t == 0) out[r] = b.i;
+        return;
+    }
+    const float m = block_argmax(row, V, T, bscratch).v;     // max of logits / T
+    const int chunk = (V + SM_THREADS - 1) / SM_THREADS;
+    const int c0 = t * chunk < V ? t * chunk : V;
+    const int c1 = c0 + chunk < V ? c0 + chunk : V;
+    const int k_req = top_k[r];
+    const float p_req = top_p[r];
+
+    // total of exp(l/T - m) over the vocabulary, ascending within a thread, threads in order
+    float mine = 0.f;
+    for (int i = c0; i < c1; ++i) mine += expf(row[i] / T - m);
+    block_prefix_f(mine, part, seg, &total_s);
+    const float total_all = total_s;
+
+    if (k_req <= 0 && p_req <= 0.f) {
+        if (t == 0) result_s = V - 1;
+        __syncthreads();
+        const float target = u * total_all;
+        const float before = part[t];
+        const float after = t + 1 < SM_THREADS ? part[t + 1] : total_all;
+        if (c0 < c1 && before <= target && after > target) {
+            float acc = before;
+            int pick = c1 - 1;
+            for (int i = c0; i < c1; ++i) {
+                acc += expf(row[i] / T - m);
+                if (acc > target) { pick = i; break; }
+            }
+            result_s = pick;
+        }
+        __syncthreads();
+        if (t == 0) out[r] = result_s;
+        return;
+    }
+
+    // ---- the k largest weights by (weight, lower id): radix select on the float bits
+    const int k = k_req > 0 ? (k_req < V ? k_req : V) : (SM_MAXC < V ? SM_MAXC : V);
+    if (t == 0) { sel_prefix = 0u; sel_remaining = (unsigned)k; }
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        for (int i = t; i < 256; i += SM_THREADS) hist[i] = 0u;
+        __syncthreads();
+        const unsigned prefix = sel_prefix;
+        for (int i = t; i < V; i += SM_THREADS) {
+            const unsigned bits = __float_as_uint(expf(row[i] / T - m));
+            if (pass == 0 || (bits >> (shift + 8)) == (prefix >> (shift + 8)))
+                atomicAdd(&hist[(bits >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (t == 0) {
+            unsigned rem = sel_remaining;
+            int b = 255;
+            for (; b > 0; --b) {
+                if (hist[b] >= rem) break;
+                rem -= hist[b];
+            }
+            sel_prefix = prefix | ((unsigned)b << shift);
+            sel_remaining = rem;
+        }
+        __syncthreads();
+    }
+    const unsigned thr = sel_prefix;            // bits of the k-th largest weight
+    const int need_equal = (int)sel_remaining;  // how many of the ties at thr are kept
+    if (t == 0) n_cand = 0;
+    __syncthreads();
+    int eq = 0;
+    for (int i = c0; i < c1; ++i) {
+        const float w = expf(row[i] / T - m);
+        const unsigned bits = __float_as_uint(w);
+        if (bits > thr) {
+            const int at = atomicAdd(&n_cand, 1);
+            if (at < SM_MAXC) { cw[at] = w; cid[at] = i; }
+        } else if (bits == thr) {
+            ++eq;
+        }
+    }
+    block_prefix_i(eq, ipart, iseg, &itotal_s);
+    {
+        int rank = ipart[t];                    // ties before this thread's range, by id
+        for (int i = c0; i < c1 && rank < need_equal; ++i) {
+            const float w = expf(row[i] / T - m);
+            if (__float_as_uint(w) == thr) {
+                const int at = atomicAdd(&n_cand, 1);
+                if (at < SM_MAXC) { cw[at] = w; cid[at] = i; }
+                ++rank;
+            }
+        }
+    }
+    __syncthreads();
+    const int nc = n_cand < SM_MAXC ? n_cand : SM_MAXC;
+    // descending by (weight, lower id)
+    if (t < nc) {
+        int rank = 0;
+        for (int j = 0; j < nc; ++j)
+            if (cw[j] > cw[t] || (cw[j] == cw[t] && cid[j] < cid[t])) ++rank;
+        sw[rank] = cw[t];
+        sid[rank] = cid[t];
+    }
+    __syncthreads();
+    if (t == 0) {
+        float total;
+        if (k_req > 0) {
+            total = 0.f;
+            for (int j = 0; j < nc; ++j) total += sw[j];
+        } else {
+            total = total_all;
+        }
+        int kept = nc;
+        if (p_req > 0.f) {
+            const float target = total * p_req;
+            float acc = 0.f;
+            kept = 0;
+            while (kept < nc && acc < target) { acc += sw[kept]; ++kept; }
+            total = acc;
+        }
+        n_kept = kept;
+        total_s = total;
+    }
+    __syncthreads();
+    const int kept = n_kept;
+    // ascending by id
+    if (t < kept) {
+        int rank = 0;
+        for (int j = 0; j < kept; ++j)
+            if (sid[j] < sid[t]) ++rank;
+        cw[rank] = sw[t];
+        cid[rank] = sid[t];
+    }
+    __syncthreads();
+    if (t == 0) {
+        const float target = u * total_s;
+        float acc = 0.f;
+        int pick = kept > 0 ? cid[kept - 1] : 0;
+        for (int j = 0; j < kept; ++j) {
+            acc += cw[j];
+            if (acc > target) { pick = cid[j]; break; }
+        }
+        out[r] = pick;
+    }
+}
+
+TGO_API int tgo_sample(const float* logits, long long stride, int n, int V,
+                       const float* temperature, const int* top_k, const float* top_p,
+                       const float* draws, int* out, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (V <= 0) return TGO_E_BAD_ARG;
+    sample_kernel<<<n, SM_THREADS, 0, stream>>>(logits, stride, V, temperature, top_k, top_p,
+                                                draws, out);
+    return launch_status();
+}

@@ -1,0 +1,202 @@
+"""Timing of the two workloads the reference's `tgo bench` reports (cmd/tgo/bench.go:
+168-246: warm up, reset, measure; prefill of a synthetic prompt, then decode steps), on
+the device with CUDA events, plus the arithmetic for roofline fractions.
+
+Prompts are seeded uniform-random token ids. A decode step of a model larger than the L2
+cache reads its weights from HBM every time, so no flush is needed between steps; for
+small models `flush_l2` writes a buffer larger than L2 between timed steps.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kernels import ops
+from .step import Engine, StepEntry
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def round_up(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+def model_flops(model, n_tokens: int, first_position: int = 0, n_logit_rows: int = 1) -> float:
+    """Floating-point operations of one step that runs `n_tokens` tokens of one request
+    starting at `first_position`: 2 per multiply-add of every matrix product, and of
+    q.K and w.V over the keys each token may read."""
+    spec = model.spec
+    d = spec.hidden_size
+    total = 0.0
+    for call in spec.run_order:
+        ls = spec.layers[call.layer]
+        m, f = ls.mixer, ls.feed_forward
+        H, Hkv, dh = m.num_heads, m.num_kv_heads, m.head_dim
+        kv = 0 if call.cache_from is not None else 2 * Hkv * dh
+        total += 2.0 * n_tokens * d * (H * dh + kv) + 2.0 * n_tokens * H * dh * d
+        total += 2.0 * n_tokens * d * 2 * f.intermediate_size + 2.0 * n_tokens * \
+            f.intermediate_size * d
+        keys = 0
+        for t in range(n_tokens):
+            p = first_position + t
+            keys += min(p + 1, m.window) if m.window else p + 1
+        total += 4.0 * H * dh * keys
+    total += 2.0 * n_logit_rows * d * spec.vocab_size
+    return total
+
+
+def decode_bytes(model, context_lens) -> float:
+    """Bytes a decode step has to read: every weight it uses once, and the cached keys
+    and values of the live requests (window layers: at most the window)."""
+    width = 4 if model.dtype == torch.float32 else 2
+    kv = 0.0
+    for g in model.groups:
+        per_tok = 2 * len(g.calls) * g.num_kv_heads * g.head_dim * width
+        for c in context_lens:
+            kv += per_tok * (min(c, g.window) if g.kind == "window" else c)
+    return model.weight_bytes() + kv
+
+
+def load_peaks(path: Optional[str] = None) -> Dict[str, object]:
+    """Measured peaks of this pool if the driver wrote them, else the stated fallback."""
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = path or os.path.join(here, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+           "source": "fallback"}
+    try:
+        with open(path) as f:
+            raw = json.load(f)
+
+        def find(d, key):
+            if isinstance(d, dict):
+                if key in d and isinstance(d[key], (int, float)):
+                    return float(d[key])
+                for v in d.values():
+                    r = find(v, key)
+                    if r is not None:
+                        return r
+            return None
+        for key in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+            v = find(raw, key)
+            if v:
+                out[key] = v
+        out["source"] = "measured"
+    except (OSError, ValueError):
+        pass
+    return out
+
+
+class L2Flusher:
+    def __init__(self, device):
+        self.buf = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
+
+    def __call__(self):
+        self.buf.fill_(1)
+
+
+def random_prompts(vocab: int, n: int, length: int, seed: int) -> List[List[int]]:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n, length), generator=g).tolist()
+
+
+def measure_prefill(loaded, tokens: int, warmup: int = 3, steps: int = 3, seed: int = 0,
+                    page_size: int = 16) -> dict:
+    """One request of `tokens` prompt tokens in one step, logits of its last token."""
+    model = loaded.model
+    eng = Engine(model, page_size=page_size, max_tokens=round_up(tokens, 64), num_slots=1,
+                 graphs=False)
+    prompt = random_prompts(model.spec.vocab_size, 1, tokens, seed)[0]
+    flush = L2Flusher(model.device)
+    times = []
+    for i in range(warmup + steps):
+        eng.admit("p")
+        flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        eng.step([StepEntry("p", prompt, [tokens - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        eng.finish("p")
+        if i >= warmup:
+            times.append(a.elapsed_time(b))
+    ms = sum(times) / len(times)
+    flops = model_flops(model, tokens)
+    return {"tokens": tokens, "ms": ms, "tokens_per_s": tokens / ms * 1e3, "flops": flops,
+            "tflops": flops / ms / 1e9, "steps": steps}
+
+
+def measure_decode(loaded, batch: int, prompt_len: int, tokens: int, warmup: int = 8,
+                   seed: int = 0, page_size: int = 16, prefill_budget: int = 8192,
+                   flush_l2: bool = False) -> dict:
+    """`batch` requests with `prompt_len`-token prompts decode `tokens` steps greedily.
+    Each step: copy the step's inputs to the device, run the step, pick the argmax on the
+    device, read the ids back (they are the next step's inputs). Timed as a whole with
+    CUDA events around the `tokens` steps, and per step for the percentiles."""
+    model = loaded.model
+    V = model.spec.vocab_size
+    per_req = round_up(prompt_len + warmup + tokens + 1, 64)
+    eng = Engine(model, page_size=page_size, max_tokens=batch * per_req, num_slots=batch)
+    prompts = random_prompts(V, batch, prompt_len, seed)
+    ids = [f"d{i}" for i in range(batch)]
+    for r in ids:
+        eng.admit(r, prompt_len + warmup + tokens + 1)
+    out_ids = torch.empty(batch, dtype=torch.int32, device=model.device)
+    feed = [0] * batch
+    # prompts, several requests a step within the token budget
+    i = 0
+    while i < batch:
+        group, used = [], 0
+        while i < batch and (not group or used + prompt_len <= prefill_budget):
+            group.append(i)
+            used += prompt_len
+            i += 1
+        logits = eng.step([StepEntry(ids[j], prompts[j], [prompt_len - 1]) for j in group])
+        tmp = torch.empty(len(group), dtype=torch.int32, device=model.device)
+        ops.argmax(logits, tmp)
+        for j, t in zip(group, tmp.tolist()):
+            feed[j] = t
+    flush = L2Flusher(model.device) if flush_l2 else None
+    step_ms, events = [], []
+    launches0 = 0
+    for s in range(warmup + tokens):
+        if s == warmup:
+            torch.cuda.synchronize()
+            launches0 = ops.LAUNCHES[0]
+            start = torch.cuda.Event(enable_timing=True)
+            start.record()
+        if flush is not None:
+            flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        logits = eng.step([StepEntry(ids[j], [feed[j]], [0]) for j in range(batch)])
+        ops.argmax(logits, out_ids)
+        b.record()
+        feed = out_ids.tolist()
+        if s >= warmup:
+            events.append((a, b))
+    end = torch.cuda.Event(enable_timing=True)
+    end.record()
+    torch.cuda.synchronize()
+    total_ms = start.elapsed_time(end)
+    step_ms = sorted(a.elapsed_time(b) for a, b in events)
+    launches = ops.LAUNCHES[0] - launches0
+    ctx = [eng.length(r) for r in ids]
+    mean_ctx = [c - tokens / 2 for c in ctx]
+    nbytes = decode_bytes(model, mean_ctx)
+    ms_per_step = total_ms / tokens
+    dev_ms = sum(step_ms) / len(step_ms)
+
+    def rank(p):
+        return step_ms[min(len(step_ms) - 1, max(0, int(p * len(step_ms) + 0.999999) - 1))]
+    for r in ids:
+        eng.finish(r)
+    return {"batch": batch, "prompt_tokens": prompt_len, "tokens": tokens,
+            "ms_per_step": ms_per_step, "device_ms_per_step": dev_ms,
+            "tokens_per_s": batch * 1e3 / ms_per_step, "p50_ms": rank(0.5), "p90_ms": rank(0.9),
+            "p99_ms": rank(0.99), "bytes_per_step": nbytes,
+            "gbs": nbytes / (ms_per_step * 1e-3) / 1e9, "gpu_launches": launches,
+            "h2d_bytes_per_step": 0, "final_context": ctx[0]}

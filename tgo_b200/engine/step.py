@@ -16,6 +16,7 @@ import torch
 
 from ..cache.pages import NULL_PAGE, CacheManager
 from ..cache.storage import CacheStorage
+from ..kernels import ops
 from ..parts.base import StepContext
 from .model import Model
 
@@ -33,9 +34,11 @@ class Engine:
     """Model + cache storage + cache bookkeeping on one device."""
 
     def __init__(self, model: Model, page_size: int = 16, max_tokens: Optional[int] = None,
-                 num_pages: Optional[int] = None, num_slots: int = 4):
+                 num_pages: Optional[int] = None, num_slots: int = 4, graphs: bool = True):
         """The pool of every group holds `num_pages` pages, or enough for `max_tokens`
-        tokens (each live request's count rounded up to whole pages)."""
+        tokens (each live request's count rounded up to whole pages). With `graphs`, steps
+        in which every request brings one token are captured once per batch-size bucket
+        as a CUDA graph and replayed."""
         if page_size <= 0:
             raise ValueError(f"engine: page size {page_size}")
         if num_pages is None:
@@ -50,6 +53,9 @@ class Engine:
         self.storage = CacheStorage(model.groups, page_size, pages, num_slots, model.dtype,
                                     model.device, model.state_shapes)
         self.steps_run = 0
+        self.use_graphs = graphs and self.device.type == "cuda"
+        self.h2d_bytes_last = 0       # bytes of the last step's inputs copied to the device
+        self._graphs = {}
 
     # ------------------------------------------------------------------ requests
     def admit(self, request_id, reserve_tokens: int = 0):
@@ -84,8 +90,12 @@ class Engine:
                     raise ValueError(f"step: request {e.request_id!r} wants the logits of "
                                      f"place {w} among {len(e.tokens)} tokens")
 
-    def build_context(self, entries: List[StepEntry]):
-        """Host lists -> one pinned buffer -> one copy -> device views."""
+    def _pack(self, entries: List[StepEntry], pad_to: int = 0, width_quantum: int = 1,
+              all_rows: bool = False):
+        """Host lists of one step, laid out as one flat int32 array:
+        ids[T] pos[T] seq[T] q_start[B+1] ctx[B] state_slot[B] rows[n] then, per group,
+        slots[T] table[B*width]. With pad_to > B, requests that bring nothing fill the batch:
+        one token each at position -1 (the kernels read and write nothing for it)."""
         cm = self.cache
         reqs = [cm.requests[e.request_id] for e in entries]
         ids, pos, seq, q_start, ctx_lens, slots_state, rows = [], [], [], [0], [], [], []
@@ -102,27 +112,43 @@ class Engine:
             rows += [base + int(w) for w in e.want]
             extents.append(n)
             firsts.append(r.length)
-        T, B = len(ids), len(entries)
+        n_pad = max(0, pad_to - len(entries))
+        for k in range(n_pad):
+            ids.append(0)
+            pos.append(-1)
+            seq.append(len(entries) + k)
+            q_start.append(len(ids))
+            ctx_lens.append(0)
+            slots_state.append(-1)
+        T, B = len(ids), len(entries) + n_pad
+        if all_rows:
+            rows = list(range(T))
         group_slots, group_tables, widths = [], [], []
         for g in range(len(cm.groups)):
             sl = []
             for e, r in zip(entries, reqs):
                 for p in range(r.length, r.length + len(e.tokens)):
                     sl.append(cm.slot_of(r, g, p))
+            sl += [-1] * n_pad
             group_slots.append(sl)
             width = max(1, max(len(r.tables[g]) for r in reqs))
+            width = (width + width_quantum - 1) // width_quantum * width_quantum
             widths.append(width)
             tb = []
             for r in reqs:
                 tb += r.tables[g] + [NULL_PAGE] * (width - len(r.tables[g]))
+            tb += [NULL_PAGE] * (width * n_pad)
             group_tables.append(tb)
         flat = ids + pos + seq + q_start + ctx_lens + slots_state + rows
         for sl, tb in zip(group_slots, group_tables):
             flat += sl + tb
-        host = torch.tensor(flat, dtype=torch.int32)
-        if self.device.type == "cuda":
-            host = host.pin_memory()
-        dev = host.to(self.device, non_blocking=True)
+        meta = dict(T=T, B=B, n_rows=len(rows), widths=widths, extents=extents, firsts=firsts,
+                    max_context=max(ctx_lens))
+        return flat, meta
+
+    def _views(self, dev: torch.Tensor, meta: dict):
+        """Device views into a flat buffer laid out by `_pack`."""
+        T, B, widths = meta["T"], meta["B"], meta["widths"]
         o = 0
 
         def take(n):
@@ -130,17 +156,28 @@ class Engine:
             t = dev[o:o + n]
             o += n
             return t
+        extents = meta["extents"] + [1] * (B - len(meta["extents"]))
         ctx = StepContext(
             num_tokens=T, num_seqs=B, token_ids=take(T), positions=take(T), seq_ids=take(T),
             q_start=take(B + 1), context_lens=take(B), state_slots=take(B),
-            logit_rows=take(len(rows)), act_dtype=self.model.dtype, extents=extents,
-            first_positions=firsts, max_extent=max(extents), max_context=max(ctx_lens),
-            decode_only=all(x == 1 for x in extents))
+            logit_rows=take(meta["n_rows"]), act_dtype=self.model.dtype, extents=extents,
+            first_positions=meta["firsts"], max_extent=max(extents),
+            max_context=meta["max_context"], decode_only=all(x == 1 for x in extents))
         dev_slots, dev_tables = [], []
-        for sl, width in zip(group_slots, widths):
+        for width in widths:
             dev_slots.append(take(T))
             dev_tables.append(take(B * width).view(B, width))
         return ctx, dev_tables, dev_slots
+
+    def build_context(self, entries: List[StepEntry]):
+        """Host lists -> one pinned buffer -> one copy -> device views."""
+        flat, meta = self._pack(entries)
+        host = torch.tensor(flat, dtype=torch.int32)
+        if self.device.type == "cuda":
+            host = host.pin_memory()
+        dev = host.to(self.device, non_blocking=True)
+        self.h2d_bytes_last = len(flat) * 4
+        return self._views(dev, meta)
 
     def step(self, entries: List[StepEntry]) -> torch.Tensor:
         """Run one batch; returns logits [number of wanted places, vocab], float32, on the
@@ -152,10 +189,66 @@ class Engine:
         for e in entries:
             r = self.cache.requests[e.request_id]
             self.cache.grow(e.request_id, r.length + len(e.tokens))
-        ctx, tables, slots = self.build_context(entries)
-        logits = self.model.forward(ctx, self.storage, tables, slots)
+        if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
+            logits = self._graph_step(entries)
+        else:
+            ctx, tables, slots = self.build_context(entries)
+            logits = self.model.forward(ctx, self.storage, tables, slots)
         for e in entries:
             r = self.cache.requests[e.request_id]
             self.cache.commit(e.request_id, r.length + len(e.tokens))
         self.steps_run += 1
         return logits
+
+    # ------------------------------------------------------------- decode graphs
+    BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+    WIDTH_QUANTUM = 64          # block-table columns per graph variant
+
+    def _graph_step(self, entries: List[StepEntry]) -> torch.Tensor:
+        """A decode-only step through a captured graph. The batch is padded to a bucket
+        with requests that bring nothing; logits are computed for every row and the wanted
+        ones are returned (a view when they are the first rows in order). The result is
+        valid until the next step of the same bucket."""
+        B = len(entries)
+        bucket = next((b for b in self.BUCKETS if b >= B), B)
+        flat, meta = self._pack(entries, pad_to=bucket, width_quantum=self.WIDTH_QUANTUM,
+                                all_rows=True)
+        key = (bucket, tuple(meta["widths"]))
+        entry = self._graphs.get(key)
+        if entry is None:
+            entry = self._capture(flat, meta)
+            self._graphs[key] = entry
+        graph, host, dev, logits, launches = entry
+        host.copy_(torch.tensor(flat, dtype=torch.int32))
+        dev.copy_(host, non_blocking=True)
+        self.h2d_bytes_last = len(flat) * 4
+        graph.replay()
+        ops.LAUNCHES[0] += launches
+        want = [b for b, e in enumerate(entries) for _ in e.want]
+        if want == list(range(B)):
+            return logits[:B]
+        if not want:
+            return logits[:0]
+        return logits[torch.tensor(want, device=self.device)]
+
+    def _capture(self, flat, meta):
+        host = torch.tensor(flat, dtype=torch.int32).pin_memory()
+        dev = torch.empty(len(flat), dtype=torch.int32, device=self.device)
+        dev.copy_(host)
+        meta = dict(meta)
+        meta["max_context"] = max(meta["widths"]) * self.page_size if meta["widths"] else 0
+        ctx, tables, slots = self._views(dev, meta)
+        ctx.aux["graph"] = True
+        # one eager run first: libraries initialise and kernels compile outside the capture.
+        # The cache rows it writes are the ones the replay writes again.
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self.model.forward(ctx, self.storage, tables, slots)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.LAUNCHES[0]
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx, self.storage, tables, slots)
+        return graph, host, dev, logits, ops.LAUNCHES[0] - before

@@ -31,6 +31,7 @@ LIBRARIES = {
     "elementwise": (["elementwise.cu"], []),
     "attention_generic": (["attention_generic.cu"], []),
     "sgemm": (["sgemm.cu"], []),
+    "sampling": (["sampling.cu"], []),
 }
 
 _loaded = {}

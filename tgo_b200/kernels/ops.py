@@ -46,8 +46,12 @@ def _need_cuda(*tensors) -> None:
                               f"{t.device}. There is no CPU path.")
 
 
+LAUNCHES = [0]        # kernels of this package launched so far (graph replays add theirs)
+
+
 def _check(status: int, name: str, detail: str = "") -> None:
     if status == 0:
+        LAUNCHES[0] += 1
         return
     if status == E_BAD_ARG:
         raise KernelError(f"{name}: refused these sizes or types {detail}")
@@ -209,3 +213,48 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
     attention_generic(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
                       cache.page_size, cache.block_tables, ctx.seq_ids, ctx.positions, scale,
                       window)
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = index of the largest logit of row r, ties to the lowest id."""
+    _need_cuda(logits, out)
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert out.dtype == torch.int32 and out.numel() == n
+    lib = load_library("sampling")
+    _check(lib.tgo_argmax(_ptr(logits), c_ll(logits.stride(0)), c_int(n), c_int(V), _ptr(out),
+                          _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, draws: torch.Tensor, out: torch.Tensor) -> None:
+    """Per row: temperature 0 -> argmax; else the softmax of logits / temperature, cut to the
+    top_k largest (0: no cut) and to the top_p nucleus (0: no cut), walked in ascending id
+    order to draws[r] * total."""
+    _need_cuda(logits, temperature, top_k, top_p, draws, out)
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32
+    assert draws.dtype == torch.float32 and top_k.dtype == torch.int32 and out.dtype == torch.int32
+    assert temperature.numel() == top_k.numel() == top_p.numel() == draws.numel() == n
+    lib = load_library("sampling")
+    _check(lib.tgo_sample(_ptr(logits), c_ll(logits.stride(0)), c_int(n), c_int(V),
+                          _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(draws), _ptr(out),
+                          _stream()), "sample")
+
+
+def logits_adjust(row: torch.Tensor, bias_ids: Optional[torch.Tensor],
+                  bias: Optional[torch.Tensor], ids: Optional[torch.Tensor],
+                  counts: Optional[torch.Tensor], repetition: float, presence: float,
+                  frequency: float) -> None:
+    """Edit one row of logits in place: add the biases, then apply the penalties to the
+    distinct history tokens `ids` with their `counts`."""
+    _need_cuda(row, bias_ids, bias, ids, counts)
+    assert row.dtype == torch.float32 and row.dim() == 1 and row.is_contiguous()
+    nb = 0 if bias_ids is None else bias_ids.numel()
+    ni = 0 if ids is None else ids.numel()
+    lib = load_library("sampling")
+    _check(lib.tgo_logits_adjust(_ptr(row), _ptr(bias_ids), _ptr(bias), c_int(nb), _ptr(ids),
+                                 _ptr(counts), c_int(ni), c_float(repetition), c_float(presence),
+                                 c_float(frequency), c_int(row.numel()), _stream()),
+           "logits_adjust")
