@@ -1,0 +1,382 @@
+// Paged causal attention on the tensor cores for bfloat16 storage, prefill and decode.
+//
+// One CTA takes a tile of query rows of one request and one kv head: the rows are the
+// (token, query head of the group) pairs of up to 16*NW/G consecutive tokens, G = H/Hkv,
+// so every row of the tile reads the same keys and values. Keys and values come from the
+// paged cache [page][kv_head][offset][DH] through the request's block table, 64 at a time,
+// by cp.async into shared memory (two buffers: the next tile loads while this one is
+// computed). S = Q K^T and O += P V are mma.sync m16n8k16 with float32 accumulators; the
+// running maximum, the sum of exponentials and the rescaling are float32 in registers.
+// A query at position p reads keys max(0, p - window + 1) .. p (window 0: from 0).
+//
+// Decode steps may cut each request's keys into `n_splits` ranges, one CTA each; the
+// partial results (unnormalised O, maximum, sum) go to scratch and `flash_combine_kernel`
+// joins them. Tiles are given by arrays (first token, token count) or, when those are
+// null, tile t is the single token t (decode).
+//
+// mma.sync is the legacy tensor path on sm_100a; attention is a few percent of the
+// model's flops, and this kernel is bound by the cache's bandwidth in decode.
+#include "common.cuh"
+
+#define FL_BN 64                 // keys per tile
+#define FL_PAD 8                 // bf16 of padding per shared-memory row (keeps ldmatrix conflict-free)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;    // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *(uint32_t*)&v;
+}
+
+template <int DH, int NW>
+__global__ void __launch_bounds__(NW * 32)
+flash_paged_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                   long long out_stride, const bf16* __restrict__ k_cache,
+                   const bf16* __restrict__ v_cache, int page_size,
+                   const int* __restrict__ block_tables, int max_blocks,
+                   const int* __restrict__ positions, const int* __restrict__ seq_ids,
+                   const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok, int H,
+                   int Hkv, float scale_log2, int window, int n_splits,
+                   float* __restrict__ part_o, float* __restrict__ part_ml) {
+    constexpr int BM = 16 * NW;
+    constexpr int LD = DH + FL_PAD;            // shared-memory row stride in bf16
+    constexpr int KS = DH / 16;                // k-steps of Q K^T
+    constexpr int CH = DH / 8;                 // 16-byte chunks per row
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sq = (bf16*)smem_raw;                // [BM][LD]
+    bf16* sk = sq + BM * LD;                   // [2][FL_BN][LD]
+    bf16* sv = sk + 2 * FL_BN * LD;            // [2][FL_BN][LD]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int G = H / Hkv;
+    const int tok0 = tile_tok0 ? tile_tok0[tile] : tile;
+    const int ntok = tile_ntok ? tile_ntok[tile] : 1;
+    const int n_rows = ntok * G;
+    const int p0 = positions[tok0];            // position of the tile's first token
+    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+
+    if (p0 < 0) {                              // a request that brings nothing: zeros out
+        if (n_splits == 1) {
+            for (int i = tid; i < n_rows * DH; i += NW * 32) {
+                const int r = i / DH, d = i % DH;
+                out[(size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * DH + d] =
+                    __float2bfloat16_rn(0.f);
+            }
+        } else {
+            for (int r = tid; r < n_rows; r += NW * 32) {
+                const size_t at = ((size_t)(tok0 + r / G) * H + kvh * G + r % G) * n_splits + split;
+                part_ml[at * 2] = -INFINITY;
+                part_ml[at * 2 + 1] = 0.f;
+            }
+        }
+        return;
+    }
+    const int b = seq_ids[tok0];
+    const int* bt = block_tables + (size_t)b * max_blocks;
+    const int p_last = p0 + ntok - 1;
+    // keys any row of the tile may read: [key_lo, key_hi)
+    const int key_lo = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+    const int key_hi = p_last + 1;
+    const int t_first = key_lo / FL_BN, t_end = (key_hi + FL_BN - 1) / FL_BN;
+    int t_lo = t_first, t_hi = t_end;
+    if (n_splits > 1) {
+        const int per = (t_end - t_first + n_splits - 1) / n_splits;
+        t_lo = t_first + split * per;
+        t_hi = t_lo + per < t_end ? t_lo + per : t_end;
+    }
+
+    // ---- Q tile -> shared memory (rows beyond n_rows are zeros)
+    for (int i = tid; i < BM * CH; i += NW * 32) {
+        const int r = i / CH, c = i % CH;
+        const bool ok = r < n_rows;
+        const bf16* src = ok ? q + (size_t)(tok0 + r / G) * q_stride + (size_t)(kvh * G + r % G) * DH + c * 8 : q;
+        cp_async16(sq + r * LD + c * 8, src, ok);
+    }
+    auto load_kv = [&](int t, int buf) {
+        bf16* dk = sk + buf * FL_BN * LD;
+        bf16* dv = sv + buf * FL_BN * LD;
+        for (int i = tid; i < FL_BN * CH; i += NW * 32) {
+            const int r = i / CH, c = i % CH;
+            const int j = t * FL_BN + r;
+            const bool ok = j >= key_lo && j < key_hi;
+            size_t off = 0;
+            if (ok) {
+                const int page = bt[j / page_size];
+                off = (((size_t)page * Hkv + kvh) * page_size + (j % page_size)) * DH + c * 8;
+            }
+            cp_async16(dk + r * LD + c * 8, k_cache + off, ok);
+            cp_async16(dv + r * LD + c * 8, v_cache + off, ok);
+        }
+    };
+    if (t_lo < t_hi) load_kv(t_lo, 0);
+    cp_async_commit();
+
+    float o[DH / 8][4];
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    // positions of this lane's two rows (rows beyond the tile read nothing)
+    const int pos_lo = r_lo < n_rows ? p0 + r_lo / G : -1;
+    const int pos_hi = r_hi < n_rows ? p0 + r_hi / G : -1;
+    const int vis_lo_lo = (window > 0 && pos_lo - window + 1 > 0) ? pos_lo - window + 1 : 0;
+    const int vis_lo_hi = (window > 0 && pos_hi - window + 1 > 0) ? pos_hi - window + 1 : 0;
+    const bool warp_active = warp * 16 < n_rows;
+
+    uint32_t qa[KS][4];
+    bool q_loaded = false;
+
+    for (int t = t_lo; t < t_hi; ++t) {
+        const int buf = (t - t_lo) & 1;
+        if (t + 1 < t_hi) load_kv(t + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (warp_active) {
+            if (!q_loaded) {
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks)
+                    ldmatrix_x4(qa[ks], sq + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD +
+                                            ks * 16 + (lane >> 4) * 8);
+                q_loaded = true;
+            }
+            const bf16* kt = sk + buf * FL_BN * LD;
+            const bf16* vt = sv + buf * FL_BN * LD;
+            float s[FL_BN / 8][4];
+#pragma unroll
+            for (int i = 0; i < FL_BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+                for (int np = 0; np < FL_BN / 16; ++np) {       // two n-tiles (16 keys) at a time
+                    uint32_t kb[4];
+                    ldmatrix_x4(kb, kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * LD + ks * 16 +
+                                        ((lane >> 3) & 1) * 8);
+                    mma_bf16(s[2 * np], qa[ks], kb[0], kb[1]);
+                    mma_bf16(s[2 * np + 1], qa[ks], kb[2], kb[3]);
+                }
+            }
+            // scale, mask, running maximum
+            const int kbase = t * FL_BN + (lane & 3) * 2;
+            float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < FL_BN / 8; ++i) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = kbase + i * 8 + e;
+                    const bool a = j <= pos_lo && j >= vis_lo_lo;
+                    const bool c = j <= pos_hi && j >= vis_lo_hi;
+                    s[i][e] = a ? s[i][e] * scale_log2 : -INFINITY;
+                    s[i][2 + e] = c ? s[i][2 + e] * scale_log2 : -INFINITY;
+                    mx_lo = fmaxf(mx_lo, s[i][e]);
+                    mx_hi = fmaxf(mx_hi, s[i][2 + e]);
+                }
+            }
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+            // a row that has seen no key yet keeps base 0 so that exp2(-inf - 0) = 0, not NaN
+            const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo;
+            const float base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+            const float corr_lo = exp2f(m_lo - base_lo), corr_hi = exp2f(m_hi - base_hi);
+            m_lo = mn_lo;
+            m_hi = mn_hi;
+            float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+            for (int i = 0; i < FL_BN / 8; ++i) {
+                s[i][0] = exp2f(s[i][0] - base_lo);
+                s[i][1] = exp2f(s[i][1] - base_lo);
+                s[i][2] = exp2f(s[i][2] - base_hi);
+                s[i][3] = exp2f(s[i][3] - base_hi);
+                sum_lo += s[i][0] + s[i][1];
+                sum_hi += s[i][2] + s[i][3];
+            }
+            l_lo = l_lo * corr_lo + sum_lo;        // per-lane partial sums; joined at the end
+            l_hi = l_hi * corr_hi + sum_hi;
+#pragma unroll
+            for (int i = 0; i < DH / 8; ++i) {
+                o[i][0] *= corr_lo; o[i][1] *= corr_lo;
+                o[i][2] *= corr_hi; o[i][3] *= corr_hi;
+            }
+            // O += P V
+#pragma unroll
+            for (int kk = 0; kk < FL_BN / 16; ++kk) {
+                uint32_t pa[4];
+                pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int dp = 0; dp < DH / 16; ++dp) {          // two n-tiles (16 dims) at a time
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD +
+                                              dp * 16 + (lane >> 4) * 8);
+                    mma_bf16(o[2 * dp], pa, vb[0], vb[1]);
+                    mma_bf16(o[2 * dp + 1], pa, vb[2], vb[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    if (!warp_active) return;
+
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+    const int col = (lane & 3) * 2;
+    if (n_splits == 1) {
+        const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+        if (r_lo < n_rows) {
+            bf16* dst = out + (size_t)(tok0 + r_lo / G) * out_stride + (size_t)(kvh * G + r_lo % G) * DH + col;
+#pragma unroll
+            for (int i = 0; i < DH / 8; ++i)
+                *(uint32_t*)(dst + i * 8) = pack_bf16(o[i][0] * inv_lo, o[i][1] * inv_lo);
+        }
+        if (r_hi < n_rows) {
+            bf16* dst = out + (size_t)(tok0 + r_hi / G) * out_stride + (size_t)(kvh * G + r_hi % G) * DH + col;
+#pragma unroll
+            for (int i = 0; i < DH / 8; ++i)
+                *(uint32_t*)(dst + i * 8) = pack_bf16(o[i][2] * inv_hi, o[i][3] * inv_hi);
+        }
+    } else {
+        if (r_lo < n_rows) {
+            const size_t at = ((size_t)(tok0 + r_lo / G) * H + kvh * G + r_lo % G) * n_splits + split;
+            float* dst = part_o + at * DH + col;
+#pragma unroll
+            for (int i = 0; i < DH / 8; ++i) *(float2*)(dst + i * 8) = make_float2(o[i][0], o[i][1]);
+            if ((lane & 3) == 0) { part_ml[at * 2] = m_lo; part_ml[at * 2 + 1] = l_lo; }
+        }
+        if (r_hi < n_rows) {
+            const size_t at = ((size_t)(tok0 + r_hi / G) * H + kvh * G + r_hi % G) * n_splits + split;
+            float* dst = part_o + at * DH + col;
+#pragma unroll
+            for (int i = 0; i < DH / 8; ++i) *(float2*)(dst + i * 8) = make_float2(o[i][2], o[i][3]);
+            if ((lane & 3) == 0) { part_ml[at * 2] = m_hi; part_ml[at * 2 + 1] = l_hi; }
+        }
+    }
+}
+
+// out[t, h, :] = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), m = max_s m_s.
+// A split that saw no key has m = -inf, l = 0 and its O is not read.
+__global__ void flash_combine_kernel(const float* __restrict__ part_o,
+                                     const float* __restrict__ part_ml, bf16* __restrict__ out,
+                                     long long out_stride, int H, int DH, int n_splits) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const size_t base = ((size_t)t * H + h) * n_splits;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+    float l = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = part_ml[(base + s) * 2];
+        if (ms != -INFINITY) l += part_ml[(base + s) * 2 + 1] * exp2f(ms - m);
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    for (int d = threadIdx.x; d < DH; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = part_ml[(base + s) * 2];
+            if (ms != -INFINITY) acc += part_o[(base + s) * DH + d] * exp2f(ms - m);
+        }
+        out[(size_t)t * out_stride + (size_t)h * DH + d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+template <int DH, int NW>
+static int flash_launch(const bf16* q, long long q_stride, bf16* out, long long out_stride,
+                        const bf16* k_cache, const bf16* v_cache, int page_size,
+                        const int* block_tables, int max_blocks, const int* positions,
+                        const int* seq_ids, const int* tile_tok0, const int* tile_ntok, int n_tiles,
+                        int H, int Hkv, float scale, int window, int n_splits, float* part_o,
+                        float* part_ml, cudaStream_t stream) {
+    constexpr int LD = DH + FL_PAD;
+    const size_t smem = (size_t)(16 * NW + 4 * FL_BN) * LD * sizeof(bf16);
+    auto kern = flash_paged_kernel<DH, NW>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const float scale_log2 = scale * 1.4426950408889634f;
+    kern<<<dim3(n_tiles, Hkv, n_splits), NW * 32, smem, stream>>>(
+        q, q_stride, out, out_stride, k_cache, v_cache, page_size, block_tables, max_blocks,
+        positions, seq_ids, tile_tok0, tile_ntok, H, Hkv, scale_log2, window, n_splits, part_o,
+        part_ml);
+    return launch_status();
+}
+
+// head sizes with a tensor-core instance; others are refused and the caller falls back
+TGO_API int tgo_attention_flash_supports(int dh, int group) {
+    return (dh == 16 || dh == 32 || dh == 64 || dh == 128) && group >= 1 && group <= 16;
+}
+
+TGO_API int tgo_attention_flash(const void* q, long long q_stride, void* out, long long out_stride,
+                                const void* k_cache, const void* v_cache, int page_size,
+                                const int* block_tables, int max_blocks, const int* positions,
+                                const int* seq_ids, const int* tile_tok0, const int* tile_ntok,
+                                int n_tiles, int H, int Hkv, int dh, float scale, int window,
+                                int wide, int n_splits, float* part_o, float* part_ml,
+                                cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (H <= 0 || Hkv <= 0 || H % Hkv || !tgo_attention_flash_supports(dh, H / Hkv) ||
+        page_size <= 0 || max_blocks <= 0 || window < 0 || n_splits < 1 || Hkv > 65535 ||
+        n_splits > 65535 || (n_splits > 1 && (!part_o || !part_ml)))
+        return TGO_E_BAD_ARG;
+#define FL_CASE(D)                                                                                  \
+    case D:                                                                                         \
+        rc = wide ? flash_launch<D, 4>((const bf16*)q, q_stride, (bf16*)out, out_stride,             \
+                                       (const bf16*)k_cache, (const bf16*)v_cache, page_size,       \
+                                       block_tables, max_blocks, positions, seq_ids, tile_tok0,     \
+                                       tile_ntok, n_tiles, H, Hkv, scale, window, n_splits, part_o, \
+                                       part_ml, stream)                                             \
+                  : flash_launch<D, 1>((const bf16*)q, q_stride, (bf16*)out, out_stride,             \
+                                       (const bf16*)k_cache, (const bf16*)v_cache, page_size,       \
+                                       block_tables, max_blocks, positions, seq_ids, tile_tok0,     \
+                                       tile_ntok, n_tiles, H, Hkv, scale, window, n_splits, part_o, \
+                                       part_ml, stream);                                            \
+        break;
+    int rc = TGO_E_BAD_ARG;
+    switch (dh) {
+        FL_CASE(16)
+        FL_CASE(32)
+        FL_CASE(64)
+        FL_CASE(128)
+    }
+#undef FL_CASE
+    return rc;
+}
+
+TGO_API int tgo_attention_flash_combine(const float* part_o, const float* part_ml, void* out,
+                                        long long out_stride, int T, int H, int dh, int n_splits,
+                                        cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H > 65535) return TGO_E_BAD_ARG;
+    flash_combine_kernel<<<dim3(T, H), dh < 128 ? 32 * ((dh + 31) / 32) : 128, 0, stream>>>(
+        part_o, part_ml, (bf16*)out, out_stride, H, dh, n_splits);
+    return launch_status();
+}

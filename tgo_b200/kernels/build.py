@@ -30,6 +30,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC
 LIBRARIES = {
     "elementwise": (["elementwise.cu"], []),
     "attention_generic": (["attention_generic.cu"], []),
+    "attention_flash": (["attention_flash.cu"], []),
     "sgemm": (["sgemm.cu"], []),
     "sampling": (["sampling.cu"], []),
 }

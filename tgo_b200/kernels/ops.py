@@ -206,10 +206,96 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     return torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
 
 
+NUM_SMS = 148
+
+
+def flash_supports(head_dim: int, group: int) -> bool:
+    """Whether the tensor-core attention kernel has an instance for this head size and
+    group (others go to the generic kernel)."""
+    return bool(load_library("attention_flash").tgo_attention_flash_supports(
+        c_int(head_dim), c_int(group)))
+
+
+def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
+                    head_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
+                    block_tables: torch.Tensor, positions: torch.Tensor, seq_ids: torch.Tensor,
+                    tile_tok0: Optional[torch.Tensor], tile_ntok: Optional[torch.Tensor],
+                    scale: float, window: int, wide: bool, n_splits: int = 1) -> None:
+    """Paged causal attention on the tensor cores (bfloat16). With tile arrays (int32,
+    first token and token count of each tile, tokens of one request, at most 64 // group
+    when `wide` else 16 // group) any step; without them every token is a tile of its own
+    (decode). n_splits > 1 cuts each request's keys over that many CTAs and joins them."""
+    _need_cuda(q, out, k_cache, v_cache, block_tables, positions, seq_ids, tile_tok0, tile_ntok)
+    T = q.shape[0]
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert k_cache.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    assert q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 2 == 0
+    assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
+    n_tiles = T if tile_tok0 is None else tile_tok0.numel()
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty((T, num_heads, n_splits, head_dim), dtype=torch.float32,
+                             device=q.device)
+        part_ml = torch.empty((T, num_heads, n_splits, 2), dtype=torch.float32, device=q.device)
+    lib = load_library("attention_flash")
+    _check(lib.tgo_attention_flash(
+        _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+        c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(positions),
+        _ptr(seq_ids), _ptr(tile_tok0), _ptr(tile_ntok), c_int(n_tiles), c_int(num_heads),
+        c_int(num_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(1 if wide else 0),
+        c_int(n_splits), _ptr(part_o), _ptr(part_ml), _stream()), "attention_flash",
+        f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads})")
+    if n_splits > 1:
+        _check(lib.tgo_attention_flash_combine(
+            _ptr(part_o), _ptr(part_ml), _ptr(out), c_ll(out.stride(0)), c_int(T),
+            c_int(num_heads), c_int(head_dim), c_int(n_splits), _stream()),
+            "attention_flash_combine")
+
+
+def _tiles(ctx, tokens_per_tile: int):
+    """Tile arrays of a step for the wide kernel, made once per step and group size."""
+    key = ("tiles", tokens_per_tile)
+    got = ctx.aux.get(key)
+    if got is None:
+        tok0, ntok, base = [], [], 0
+        for n in ctx.extents:
+            for o in range(0, n, tokens_per_tile):
+                tok0.append(base + o)
+                ntok.append(min(tokens_per_tile, n - o))
+            base += n
+        dev = torch.tensor([tok0, ntok], dtype=torch.int32).to(ctx.token_ids.device,
+                                                               non_blocking=True)
+        got = (dev[0], dev[1])
+        ctx.aux[key] = got
+    return got
+
+
+def decode_splits(ctx, num_kv_heads: int, window: int) -> int:
+    """How many CTAs share one request's keys in a decode step: enough to fill the GPU
+    about twice over, no more than there are 64-key tiles."""
+    reach = min(ctx.max_context, window) if window > 0 else ctx.max_context
+    tiles = max(1, (reach + 63) // 64 + (1 if window > 0 else 0))
+    want = max(1, (2 * NUM_SMS) // max(1, ctx.num_seqs * num_kv_heads))
+    return max(1, min(tiles, want, 64))
+
+
 def paged_attention(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
                     head_dim: int, cache, ctx, scale: float, window: int) -> None:
     """Attention of every token of the step over its request's cached keys and values.
     Picks the kernel by storage type, head size and what the step holds."""
+    group = num_heads // num_kv_heads
+    if q.dtype == torch.bfloat16 and flash_supports(head_dim, group):
+        if ctx.decode_only:
+            attention_flash(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
+                            cache.page_size, cache.block_tables, ctx.positions, ctx.seq_ids,
+                            None, None, scale, window, wide=False,
+                            n_splits=decode_splits(ctx, num_kv_heads, window))
+        else:
+            tok0, ntok = _tiles(ctx, 64 // group)
+            attention_flash(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
+                            cache.page_size, cache.block_tables, ctx.positions, ctx.seq_ids,
+                            tok0, ntok, scale, window, wide=True)
+        return
     attention_generic(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
                       cache.page_size, cache.block_tables, ctx.seq_ids, ctx.positions, scale,
                       window)
