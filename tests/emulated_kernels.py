@@ -35,24 +35,34 @@ def residual_add(h, delta):
     h += delta.float()
 
 
-def swiglu(gate_up, out):
-    f = out.shape[1]
-    g, u = gate_up[:, :f].float(), gate_up[:, f:].float()
+def _gate(gate_up, f, interleaved):
+    if interleaved:
+        v = gate_up.reshape(gate_up.shape[0], f // 8, 2, 8)
+        return v[:, :, 0].reshape(-1, f).float(), v[:, :, 1].reshape(-1, f).float()
+    return gate_up[:, :f].float(), gate_up[:, f:].float()
+
+
+def swiglu(gate_up, out, interleaved=False):
+    g, u = _gate(gate_up, out.shape[1], interleaved)
     out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
 
 
-def qk_norm_rope_cache(q, k, v, num_heads, num_kv_heads, head_dim, q_gain, k_gain, eps, positions,
-                       inv_freq, rotary_dim, slots, k_cache, v_cache, page_size):
+def rope_table(positions, inv_freq):
+    ang = positions.double()[:, None] * inv_freq[None, :]
+    return torch.cat([ang.cos(), ang.sin()], dim=1).float()
+
+
+def qk_norm_rope_cache(q, k, v, num_heads, num_kv_heads, head_dim, q_gain, k_gain, eps, rope,
+                       rotary_dim, slots, k_cache, v_cache, page_size):
     T = q.shape[0]
 
     def treat(x, heads, gain):
         y = x.reshape(T, heads, head_dim).float()
         if gain is not None:
             y = (y * torch.rsqrt((y * y).mean(-1, keepdim=True) + eps)) * gain
-        if inv_freq is not None:
+        if rope is not None:
             half = rotary_dim // 2
-            ang = positions.double()[:, None] * inv_freq[None, :]
-            cos, sin = ang.cos().float()[:, None, :], ang.sin().float()[:, None, :]
+            cos, sin = rope[:, None, :half], rope[:, None, half:]
             lo, hi = y[..., :half].clone(), y[..., half:rotary_dim].clone()
             y[..., :half] = lo * cos - hi * sin
             y[..., half:rotary_dim] = lo * sin + hi * cos
@@ -101,12 +111,23 @@ def paged_attention(q, out, num_heads, num_kv_heads, head_dim, cache, ctx, scale
                       window)
 
 
-def linear(x, w, out_dtype=None, out=None):
-    y = (x.float() @ w.float().t()).to(out_dtype or x.dtype)
-    if out is not None:
-        out.copy_(y)
-        return out
-    return y
+def linear(x, w, out_dtype=None, residual=None):
+    from tgo_b200.kernels import ops
+    x = ops.as_rows(x)
+    y = x.float() @ w.float().t()
+    if residual is not None:
+        residual += y
+        return None
+    return y.to(out_dtype or x.dtype)
+
+
+def gated_linear(x, w_gate_up, interleaved):
+    from tgo_b200.kernels import ops
+    x = ops.as_rows(x)
+    gu = (x.float() @ w_gate_up.float().t()).to(x.dtype)
+    out = torch.empty((x.shape[0], w_gate_up.shape[0] // 2), dtype=x.dtype)
+    swiglu(gu, out, interleaved)
+    return out
 
 
 def sgemm_tn(x, w, out):
@@ -141,8 +162,8 @@ def logits_adjust(row, bias_ids, bias, ids, counts, repetition, presence, freque
             row[i] = x
 
 
-NAMES = ["argmax", "sample", "logits_adjust", "embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",
-         "attention_generic", "paged_attention", "linear", "sgemm_tn"]
+NAMES = ["rope_table", "argmax", "sample", "logits_adjust", "embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",
+         "attention_generic", "paged_attention", "linear", "gated_linear", "sgemm_tn"]
 
 
 def install(monkeypatch):

@@ -75,6 +75,11 @@ def test_swiglu(f, T, dtype):
     g, u = gu[:, :f].float(), gu[:, f:].float()
     want = g / (1 + torch.exp(-g)) * u
     assert torch.allclose(out.float(), want, **tol(dtype))
+    if f % 8 == 0:
+        v = gu.reshape(T, f // 8, 2, 8)
+        g, u = v[:, :, 0].reshape(T, f).float(), v[:, :, 1].reshape(T, f).float()
+        ops().swiglu(gu, out, interleaved=True)
+        assert torch.allclose(out.float(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
 
 
 def rope_ref(x, pos, theta, rot):
@@ -110,7 +115,8 @@ def test_qk_norm_rope_cache(H, Hkv, dh, rot, dtype):
     want_q = rope_ref(norm(q.reshape(T, H, dh), qg), pos, theta, rot)
     want_k = rope_ref(norm(k.reshape(T, Hkv, dh), kg), pos, theta, rot)
     want_v = v.reshape(T, Hkv, dh).clone()
-    ops().qk_norm_rope_cache(q, k, v, H, Hkv, dh, qg, kg, eps, pos, inv, rot, slots, kc, vc, ps)
+    table = ops().rope_table(pos, inv)
+    ops().qk_norm_rope_cache(q, k, v, H, Hkv, dh, qg, kg, eps, table, rot, slots, kc, vc, ps)
     assert torch.allclose(q.reshape(T, H, dh).float(), want_q, **tol(dtype))
     for t in range(T):
         s = int(slots[t])
@@ -319,8 +325,8 @@ def test_kernels_refuse_what_they_cannot_take():
     o = ops()
     q = torch.zeros(1, 4 * 528, dtype=torch.float32, device=DEV)
     with pytest.raises(o.KernelError):
-        o.qk_norm_rope_cache(q, None, None, 4, 4, 528, None, None, 1e-6, None, None, 0, None,
-                             None, None, 0)
+        o.qk_norm_rope_cache(q, None, None, 4, 4, 528, None, None, 1e-6, None, 0, None, None,
+                             None, 0)
     with pytest.raises(o.KernelError):
         o.embed(torch.zeros(4, 4), torch.zeros(1, dtype=torch.int32), torch.zeros(1, 4))
 
@@ -389,3 +395,87 @@ def test_logits_adjust_matches_plain():
     want = plain.penalize(base, history, rep=1.3, presence=0.5, frequency=0.25)
     adjust_row(row, pol, history)
     assert np.allclose(row.cpu().numpy(), want, rtol=1e-6, atol=1e-6)
+
+
+# ------------------------------------------------------------- weight-streaming GEMM
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 16, 64), (3, 50, 96), (8, 257, 224), (9, 64, 4096),
+                                   (16, 100, 1000), (17, 33, 72), (40, 48, 512), (64, 130, 264)])
+def test_gemm_skinny(M, N, K):
+    x = rnd(M, K, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
+    want = x.float() @ w.float().t()
+    for dt in (torch.bfloat16, torch.float32):
+        out = torch.empty(M, N, dtype=dt, device=DEV)
+        ops().gemm_skinny(x, w, out)
+        assert torch.allclose(out.float(), want, rtol=1e-2 if dt == torch.bfloat16 else 1e-4,
+                              atol=2e-2 if dt == torch.bfloat16 else 1e-3), (M, N, K, dt)
+    h = rnd(M, N, seed=3)
+    h2 = h.clone()
+    ops().gemm_skinny(x, w, h2, accumulate=True)
+    assert torch.allclose(h2, h + want, rtol=1e-4, atol=1e-3)
+    # a row's result does not depend on the rows beside it
+    out_all = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops().gemm_skinny(x, w, out_all)
+    out_one = torch.empty(1, N, dtype=torch.float32, device=DEV)
+    ops().gemm_skinny(x[M - 1:M].contiguous(), w, out_one)
+    assert torch.equal(out_one[0], out_all[M - 1])
+
+
+def interleave8(gate, up):
+    f, d = gate.shape
+    return torch.stack([gate.view(f // 8, 8, d), up.view(f // 8, 8, d)], dim=1).reshape(2 * f, d)
+
+
+@pytest.mark.parametrize("M,f,K", [(2, 224, 64), (8, 128, 96), (16, 1000, 264)])
+def test_gemm_skinny_gated_output(M, f, K):
+    """A gate/up matrix with rows interleaved in eights: the kernel applies the gate itself."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=4)
+    wg = rnd(f, K, dtype=torch.bfloat16, scale=0.2, seed=5)
+    wu = rnd(f, K, dtype=torch.bfloat16, scale=0.2, seed=6)
+    g = (x.float() @ wg.float().t()).to(torch.bfloat16).float()
+    u = (x.float() @ wu.float().t()).to(torch.bfloat16).float()
+    want = g / (1 + torch.exp(-g)) * u
+    w = interleave8(wg, wu).contiguous()
+    out = torch.empty(M, f, dtype=torch.bfloat16, device=DEV)
+    ops().gemm_skinny(x, w, out, gated=True)
+    assert torch.allclose(out.float(), want, rtol=2e-2, atol=2e-2)
+    # the separate kernel on the interleaved product gives the same
+    gu = (x.float() @ w.float().t()).to(torch.bfloat16)
+    out2 = torch.empty(M, f, dtype=torch.bfloat16, device=DEV)
+    ops().swiglu(gu, out2, interleaved=True)
+    assert torch.allclose(out2.float(), want, rtol=2e-2, atol=2e-2)
+    # and gated_linear picks either
+    got = ops().gated_linear(x, w, True)
+    assert torch.allclose(got.float(), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 48, 64), (7, 100, 96), (16, 33, 4096)])
+def test_gemm_skinny_folds_the_norm(M, N, K):
+    h = rnd(M, K, seed=8, scale=3.0)
+    gain = 1 + 0.1 * rnd(K, seed=9)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=10)
+    eps = 1e-5
+    normed = (h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps)) * gain
+    want = normed @ w.float().t()
+    x = ops().NormedRows(h, gain, eps, torch.bfloat16)
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops().gemm_skinny(x, w, out)
+    # K products of two bfloat16-rounded factors (relative error 2^-9 each, random sign):
+    # three standard deviations of their sum
+    atol = 3 * 2.0 ** -8.5 * math.sqrt(K) * float(normed.pow(2).mean().sqrt()) * 0.1
+    assert torch.allclose(out, want, rtol=0, atol=atol)
+    # and the unfolded route agrees
+    y = ops().linear(x.materialize(), w, out_dtype=torch.float32)
+    assert torch.allclose(y, want, rtol=0, atol=atol)
+
+
+def test_linear_paths_agree():
+    """The same product through the weight-streaming kernel (few rows) and through the
+    library (many rows) differs by bfloat16 rounding only."""
+    w = rnd(300, 256, dtype=torch.bfloat16, scale=0.1, seed=6)
+    x = rnd(100, 256, dtype=torch.bfloat16, seed=7)
+    many = ops().linear(x, w)
+    few = ops().linear(x[:5].contiguous(), w)
+    assert torch.allclose(many[:5].float(), few.float(), rtol=2e-2, atol=2e-2)

@@ -283,11 +283,272 @@ flash_paged_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restr
     }
 }
 
+// Decode: one token per request. The G query heads that share a kv head are the (up to 16)
+// rows of one m16 tile, which all four warps hold; each 64-key tile is loaded by the whole
+// CTA and warp w takes its keys 16w .. 16w+15, keeping its own maximum, sum and O. At the
+// end the four partial states are joined through shared memory in warp order. With
+// n_splits > 1 the CTA covers one range of the request's key tiles and writes a partial
+// state for flash_combine_kernel.
+template <int DH>
+__global__ void __launch_bounds__(128)
+flash_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                    long long out_stride, const bf16* __restrict__ k_cache,
+                    const bf16* __restrict__ v_cache, int page_size, int page_shift,
+                    const int* __restrict__ block_tables, int max_blocks,
+                    const int* __restrict__ positions, const int* __restrict__ seq_ids, int H,
+                    int Hkv, float scale_log2, int window, int n_splits,
+                    float* __restrict__ part_o, float* __restrict__ part_ml,
+                    int* __restrict__ counters, int pages_cap) {
+    constexpr int LD = DH + FL_PAD;
+    constexpr int KS = DH / 16;
+    constexpr int CH = DH / 8;
+    constexpr int ROWS_PER_IT = 128 / CH;
+    __shared__ int s_last;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sq = (bf16*)smem_raw;                // [16][LD]
+    bf16* sk = sq + 16 * LD;                   // [2][64][LD]
+    bf16* sv = sk + 2 * FL_BN * LD;            // [2][64][LD]
+    __shared__ float s_ml[4][16][2];
+    pdl_wait();
+    pdl_launch();
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int G = H / Hkv;
+    const int p = positions[tok];
+    if (p < 0) {                               // a request that brings nothing: zeros out
+        if (split == 0)
+            for (int i = tid; i < G * DH; i += 128)
+                out[(size_t)tok * out_stride + (size_t)(kvh * G) * DH + i] = __float2bfloat16_rn(0.f);
+        if (n_splits > 1 && !counters)
+            for (int r = tid; r < G; r += 128) {
+                const size_t at = ((size_t)tok * H + kvh * G + r) * n_splits + split;
+                part_ml[at * 2] = -INFINITY;
+                part_ml[at * 2 + 1] = 0.f;
+            }
+        return;
+    }
+    const int* bt = block_tables + (size_t)seq_ids[tok] * max_blocks;
+    const int key_lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int key_hi = p + 1;
+    const int t_first = key_lo / FL_BN, t_end = (key_hi + FL_BN - 1) / FL_BN;
+    int t_lo = t_first, t_hi = t_end;
+    if (n_splits > 1) {
+        const int per = (t_end - t_first + n_splits - 1) / n_splits;
+        t_lo = t_first + split * per;
+        t_hi = t_lo + per < t_end ? t_lo + per : t_end;
+    }
+    // this CTA's slice of the block table -> shared memory, so that the address of a row is
+    // not a chain of two global loads
+    int* s_pages = (int*)(sv + 2 * FL_BN * LD);
+    const int pg_lo = (t_lo * FL_BN) / page_size;
+    {
+        int pg_hi = (t_hi * FL_BN + page_size - 1) / page_size;
+        if (pg_hi > max_blocks) pg_hi = max_blocks;
+        if (pg_hi - pg_lo > pages_cap) pg_hi = pg_lo + pages_cap;
+        for (int i = pg_lo + tid; i < pg_hi; i += 128) s_pages[i - pg_lo] = bt[i];
+    }
+    __syncthreads();
+    auto page_of = [&](int pi) { return pi - pg_lo < pages_cap ? s_pages[pi - pg_lo] : bt[pi]; };
+    for (int i = tid; i < 16 * CH; i += 128) {
+        const int r = i / CH, c = i % CH;
+        const bool ok = r < G;
+        cp_async16(sq + r * LD + c * 8,
+                   ok ? q + (size_t)tok * q_stride + (size_t)(kvh * G + r) * DH + c * 8 : q, ok);
+    }
+    const int c_mine = tid % CH, r_mine = tid / CH;
+    auto load_kv = [&](int t, int buf) {
+        bf16* dk = sk + buf * FL_BN * LD + c_mine * 8;
+        bf16* dv = sv + buf * FL_BN * LD + c_mine * 8;
+#pragma unroll
+        for (int r = r_mine; r < FL_BN; r += ROWS_PER_IT) {
+            const int j = t * FL_BN + r;
+            const bool ok = j >= key_lo && j < key_hi;
+            size_t off = 0;
+            if (ok) {
+                const int pi = page_shift >= 0 ? j >> page_shift : j / page_size;
+                const int po = j - pi * page_size;
+                off = (((size_t)page_of(pi) * Hkv + kvh) * page_size + po) * DH + c_mine * 8;
+            }
+            cp_async16(dk + r * LD, k_cache + off, ok);
+            cp_async16(dv + r * LD, v_cache + off, ok);
+        }
+    };
+    if (t_lo < t_hi) load_kv(t_lo, 0);
+    cp_async_commit();
+
+    float o[DH / 8][4];
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    const bool row_lo_ok = r_lo < G, row_hi_ok = r_hi < G;
+    uint32_t qa[KS][4];
+
+    for (int t = t_lo; t < t_hi; ++t) {
+        const int buf = (t - t_lo) & 1;
+        if (t + 1 < t_hi) load_kv(t + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (t == t_lo) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks)
+                ldmatrix_x4(qa[ks], sq + ((lane & 7) + ((lane >> 3) & 1) * 8) * LD + ks * 16 +
+                                        (lane >> 4) * 8);
+        }
+        const bf16* kt = sk + buf * FL_BN * LD + warp * 16 * LD;
+        const bf16* vt = sv + buf * FL_BN * LD + warp * 16 * LD;
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
+        s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            uint32_t kb[4];
+            ldmatrix_x4(kb, kt + ((lane & 7) + (lane >> 4) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16(s[0], qa[ks], kb[0], kb[1]);
+            mma_bf16(s[1], qa[ks], kb[2], kb[3]);
+        }
+        const int kbase = t * FL_BN + warp * 16 + (lane & 3) * 2;
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = kbase + i * 8 + e;
+                const bool vis = j >= key_lo && j < key_hi;
+                s[i][e] = (vis && row_lo_ok) ? s[i][e] * scale_log2 : -INFINITY;
+                s[i][2 + e] = (vis && row_hi_ok) ? s[i][2 + e] * scale_log2 : -INFINITY;
+                mx_lo = fmaxf(mx_lo, s[i][e]);
+                mx_hi = fmaxf(mx_hi, s[i][2 + e]);
+            }
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo;
+        const float base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+        const float corr_lo = exp2f(m_lo - base_lo), corr_hi = exp2f(m_hi - base_hi);
+        m_lo = mn_lo;
+        m_hi = mn_hi;
+        float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            s[i][0] = exp2f(s[i][0] - base_lo);
+            s[i][1] = exp2f(s[i][1] - base_lo);
+            s[i][2] = exp2f(s[i][2] - base_hi);
+            s[i][3] = exp2f(s[i][3] - base_hi);
+            sum_lo += s[i][0] + s[i][1];
+            sum_hi += s[i][2] + s[i][3];
+        }
+        l_lo = l_lo * corr_lo + sum_lo;
+        l_hi = l_hi * corr_hi + sum_hi;
+        uint32_t pa[4];
+        pa[0] = pack_bf16(s[0][0], s[0][1]);
+        pa[1] = pack_bf16(s[0][2], s[0][3]);
+        pa[2] = pack_bf16(s[1][0], s[1][1]);
+        pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int dp = 0; dp < DH / 16; ++dp) {
+            uint32_t vb[4];
+            ldmatrix_x4_trans(vb, vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * LD + dp * 16 +
+                                      (lane >> 4) * 8);
+            o[2 * dp][0] *= corr_lo; o[2 * dp][1] *= corr_lo;
+            o[2 * dp][2] *= corr_hi; o[2 * dp][3] *= corr_hi;
+            o[2 * dp + 1][0] *= corr_lo; o[2 * dp + 1][1] *= corr_lo;
+            o[2 * dp + 1][2] *= corr_hi; o[2 * dp + 1][3] *= corr_hi;
+            mma_bf16(o[2 * dp], pa, vb[0], vb[1]);
+            mma_bf16(o[2 * dp + 1], pa, vb[2], vb[3]);
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    pdl_launch_late();
+    // join the four warps' states: O through the (now free) key/value buffers
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    float* so = (float*)sk;                    // [4][16][DH]
+    const int col = (lane & 3) * 2;
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) {
+        *(float2*)(so + ((size_t)warp * 16 + r_lo) * DH + i * 8 + col) = make_float2(o[i][0], o[i][1]);
+        *(float2*)(so + ((size_t)warp * 16 + r_hi) * DH + i * 8 + col) = make_float2(o[i][2], o[i][3]);
+    }
+    if ((lane & 3) == 0) {
+        s_ml[warp][r_lo][0] = m_lo; s_ml[warp][r_lo][1] = l_lo;
+        s_ml[warp][r_hi][0] = m_hi; s_ml[warp][r_hi][1] = l_hi;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * DH; i += 128) {
+        const int r = i / DH, d = i % DH;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, s_ml[w][r][0]);
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = s_ml[w][r][0];
+            if (mw != -INFINITY) {
+                const float f = exp2f(mw - m);
+                l += s_ml[w][r][1] * f;
+                acc += so[((size_t)w * 16 + r) * DH + d] * f;
+            }
+        }
+        const int head = kvh * G + r;
+        if (n_splits == 1) {
+            out[(size_t)tok * out_stride + (size_t)head * DH + d] =
+                __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else {
+            const size_t at = ((size_t)tok * H + head) * n_splits + split;
+            part_o[at * DH + d] = acc;
+            if (d == 0) { part_ml[at * 2] = m; part_ml[at * 2 + 1] = l; }
+        }
+    }
+    if (n_splits == 1 || !counters) return;
+    // The CTA that finishes last for this (token, kv head) joins the splits: no CTA waits for
+    // another. The counter goes back to zero for the next launch.
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int prev = atomicAdd(&counters[tok * Hkv + kvh], 1);
+        s_last = prev == n_splits - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int i = tid; i < G * DH; i += 128) {
+        const int r = i / DH, d = i % DH;
+        const int head = kvh * G + r;
+        const size_t base = ((size_t)tok * H + head) * n_splits;
+        float m = -INFINITY;
+        for (int sp = 0; sp < n_splits; ++sp) m = fmaxf(m, __ldcg(part_ml + (base + sp) * 2));
+        float l = 0.f, acc = 0.f;
+        for (int sp = 0; sp < n_splits; ++sp) {
+            const float ms = __ldcg(part_ml + (base + sp) * 2);
+            if (ms != -INFINITY) {
+                const float f = exp2f(ms - m);
+                l += __ldcg(part_ml + (base + sp) * 2 + 1) * f;
+                acc += __ldcg(part_o + (base + sp) * DH + d) * f;
+            }
+        }
+        out[(size_t)tok * out_stride + (size_t)head * DH + d] =
+            __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    }
+    if (tid == 0) counters[tok * Hkv + kvh] = 0;
+}
+
 // out[t, h, :] = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), m = max_s m_s.
 // A split that saw no key has m = -inf, l = 0 and its O is not read.
 __global__ void flash_combine_kernel(const float* __restrict__ part_o,
                                      const float* __restrict__ part_ml, bf16* __restrict__ out,
                                      long long out_stride, int H, int DH, int n_splits) {
+    pdl_wait();
+    pdl_launch();
     const int t = blockIdx.x, h = blockIdx.y;
     const size_t base = ((size_t)t * H + h) * n_splits;
     float m = -INFINITY;
@@ -330,6 +591,32 @@ static int flash_launch(const bf16* q, long long q_stride, bf16* out, long long 
     return launch_status();
 }
 
+template <int DH>
+static int decode_launch(const bf16* q, long long q_stride, bf16* out, long long out_stride,
+                         const bf16* k_cache, const bf16* v_cache, int page_size,
+                         const int* block_tables, int max_blocks, const int* positions,
+                         const int* seq_ids, int T, int H, int Hkv, float scale, int window,
+                         int n_splits, float* part_o, float* part_ml, int* counters,
+                         cudaStream_t stream) {
+    constexpr int LD = DH + FL_PAD;
+    size_t smem = (size_t)(16 + 4 * FL_BN) * LD * sizeof(bf16);
+    const size_t merge = (size_t)4 * 16 * DH * sizeof(float) + (size_t)16 * LD * sizeof(bf16);
+    if (merge > smem) smem = merge;
+    int pages_cap = max_blocks < 2048 ? max_blocks : 2048;     // block-table entries kept on chip
+    smem += (size_t)pages_cap * sizeof(int);
+    auto kern = flash_decode_kernel<DH>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    int shift = -1;
+    for (int sft = 0; sft < 31; ++sft) if ((1 << sft) == page_size) shift = sft;
+    return tgo_launch_pdl(kern, dim3(T, Hkv, n_splits), dim3(128), smem, stream, q, q_stride, out,
+                          out_stride, k_cache, v_cache, page_size, shift, block_tables, max_blocks,
+                          positions, seq_ids, H, Hkv, scale * 1.4426950408889634f, window, n_splits,
+                          part_o, part_ml, counters, pages_cap);
+}
+
 // head sizes with a tensor-core instance; others are refused and the caller falls back
 TGO_API int tgo_attention_flash_supports(int dh, int group) {
     return (dh == 16 || dh == 32 || dh == 64 || dh == 128) && group >= 1 && group <= 16;
@@ -341,7 +628,7 @@ TGO_API int tgo_attention_flash(const void* q, long long q_stride, void* out, lo
                                 const int* seq_ids, const int* tile_tok0, const int* tile_ntok,
                                 int n_tiles, int H, int Hkv, int dh, float scale, int window,
                                 int wide, int n_splits, float* part_o, float* part_ml,
-                                cudaStream_t stream) {
+                                int* counters, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv || !tgo_attention_flash_supports(dh, H / Hkv) ||
         page_size <= 0 || max_blocks <= 0 || window < 0 || n_splits < 1 || Hkv > 65535 ||
@@ -361,6 +648,22 @@ TGO_API int tgo_attention_flash(const void* q, long long q_stride, void* out, lo
                                        part_ml, stream);                                            \
         break;
     int rc = TGO_E_BAD_ARG;
+    if (!tile_tok0 && !wide) {          // every token a tile of its own: the decode kernel
+#define FD_CASE(D)                                                                                 \
+    case D:                                                                                        \
+        return decode_launch<D>((const bf16*)q, q_stride, (bf16*)out, out_stride,                  \
+                                (const bf16*)k_cache, (const bf16*)v_cache, page_size, block_tables, \
+                                max_blocks, positions, seq_ids, n_tiles, H, Hkv, scale, window,    \
+                                n_splits, part_o, part_ml, counters, stream);
+        switch (dh) {
+            FD_CASE(16)
+            FD_CASE(32)
+            FD_CASE(64)
+            FD_CASE(128)
+        }
+#undef FD_CASE
+        return rc;
+    }
     switch (dh) {
         FL_CASE(16)
         FL_CASE(32)
@@ -376,7 +679,7 @@ TGO_API int tgo_attention_flash_combine(const float* part_o, const float* part_m
                                         cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H > 65535) return TGO_E_BAD_ARG;
-    flash_combine_kernel<<<dim3(T, H), dh < 128 ? 32 * ((dh + 31) / 32) : 128, 0, stream>>>(
-        part_o, part_ml, (bf16*)out, out_stride, H, dh, n_splits);
-    return launch_status();
+    return tgo_launch_pdl(flash_combine_kernel, dim3(T, H),
+                          dim3(dh < 128 ? 32 * ((dh + 31) / 32) : 128), 0, stream, part_o, part_ml,
+                          (bf16*)out, out_stride, H, dh, n_splits);
 }

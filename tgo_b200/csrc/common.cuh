@@ -54,3 +54,56 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch
+// Kernels of a decode step are short; launched this way the next kernel's blocks are
+// scheduled while the previous kernel drains, and wait at pdl_wait() until it has completed
+// and its writes are visible. Every kernel launched through tgo_launch_pdl calls pdl_wait()
+// first thing, in every thread, before it reads or writes global memory, so the chain of
+// dependencies stays what stream order would give. TGO_NO_PDL=1 turns the attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Measured on B200: letting dependents launch from the top of a kernel makes a decode step
+// slower (their blocks take the places of this kernel's later blocks); letting them launch
+// once a block has finished its streaming loop is what pdl_launch_late() does.
+#ifndef TGO_PDL_TRIGGER
+#define TGO_PDL_TRIGGER 0
+#endif
+#ifndef TGO_PDL_TRIGGER_LATE
+#define TGO_PDL_TRIGGER_LATE 1
+#endif
+__device__ __forceinline__ void pdl_launch() {
+#if TGO_PDL_TRIGGER
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void pdl_launch_late() {
+#if TGO_PDL_TRIGGER_LATE
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+
+#include <stdlib.h>
+static inline bool tgo_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("TGO_NO_PDL");
+        on = (e && e[0] == '1') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int tgo_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tgo_pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

@@ -10,6 +10,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int d, int V) {
+    pdl_wait();
+    pdl_launch();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < V;
@@ -23,9 +25,11 @@ TGO_API int tgo_embed(const void* table, int dtype, const int* ids, float* out, 
     if (T <= 0) return 0;
     const int threads = d >= 1024 ? 256 : 128;
     if (dtype == TGO_BF16)
-        embed_kernel<bf16><<<T, threads, 0, stream>>>((const bf16*)table, ids, out, d, V);
+        return tgo_launch_pdl(embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream,
+                              (const bf16*)table, ids, out, d, V);
     else if (dtype == TGO_F32)
-        embed_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, d, V);
+        return tgo_launch_pdl(embed_kernel<float>, dim3(T), dim3(threads), 0, stream,
+                              (const float*)table, ids, out, d, V);
     else
         return TGO_E_BAD_ARG;
     return launch_status();
@@ -41,6 +45,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
                                    const float* __restrict__ gain, float eps,
                                    TO* __restrict__ out, const int* __restrict__ rows, int d) {
     __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch();
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
     float* hr = h + (size_t)r * d;
@@ -96,14 +102,17 @@ static int add_rmsnorm_launch(float* h, const void* delta, const float* gain, fl
     if (d > 4096) threads = 1024;
     const int chunks = (d + threads - 1) / threads;
     if (chunks <= 4)
-        add_rmsnorm_kernel<TD, TO, 4><<<n, threads, 0, s>>>(h, dl, gain, eps, o, rows, d);
+        return tgo_launch_pdl(add_rmsnorm_kernel<TD, TO, 4>, dim3(n), dim3(threads), 0, s, h, dl,
+                              gain, eps, o, rows, d);
     else if (chunks <= 8)
-        add_rmsnorm_kernel<TD, TO, 8><<<n, threads, 0, s>>>(h, dl, gain, eps, o, rows, d);
+        return tgo_launch_pdl(add_rmsnorm_kernel<TD, TO, 8>, dim3(n), dim3(threads), 0, s, h, dl,
+                              gain, eps, o, rows, d);
     else if (chunks <= 16)
-        add_rmsnorm_kernel<TD, TO, 16><<<n, threads, 0, s>>>(h, dl, gain, eps, o, rows, d);
+        return tgo_launch_pdl(add_rmsnorm_kernel<TD, TO, 16>, dim3(n), dim3(threads), 0, s, h, dl,
+                              gain, eps, o, rows, d);
     else
-        add_rmsnorm_kernel<TD, TO, 0><<<n, threads, 0, s>>>(h, dl, gain, eps, o, rows, d);
-    return launch_status();
+        return tgo_launch_pdl(add_rmsnorm_kernel<TD, TO, 0>, dim3(n), dim3(threads), 0, s, h, dl,
+                              gain, eps, o, rows, d);
 }
 
 TGO_API int tgo_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* gain,
@@ -146,29 +155,38 @@ TGO_API int tgo_residual_add(float* h, const void* delta, int dtype, long long n
 }
 
 // ------------------------------------------------------------------- SiLU gate
-// out[t, j] = silu(gu[t, j]) * gu[t, f + j];  gu is [T, 2f] (gate columns, then up).
+// out[t, j] = silu(gate_j) * up_j over gu [T, 2f]. Two column layouts of gu:
+//   plain        gate_j = gu[t, j],                      up_j = gu[t, f + j]
+//   interleaved  gate_j = gu[t, 16 * (j / 8) + j % 8],   up_j = gu[t, 16 * (j / 8) + 8 + j % 8]
+// (eight gate columns, then the eight matching up columns: the row order in which a joined
+// gate/up matrix is kept so that one CTA of the weight-streaming product holds both).
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int f) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int f, int interleaved) {
+    pdl_wait();
+    pdl_launch();
     const size_t t = blockIdx.y;
-    const T* g = gu + t * 2 * (size_t)f;
-    const T* u = g + f;
+    const T* row = gu + t * 2 * (size_t)f;
     T* o = out + t * (size_t)f;
     for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < f; j += gridDim.x * blockDim.x) {
-        const float a = to_f32(g[j]);
+        const int gi = interleaved ? 16 * (j / 8) + j % 8 : j;
+        const int ui = interleaved ? gi + 8 : f + j;
+        const float a = to_f32(row[gi]);
         const float s = a / (1.f + expf(-a));
-        o[j] = from_f32<T>(s * to_f32(u[j]));
+        o[j] = from_f32<T>(s * to_f32(row[ui]));
     }
 }
 
 // bf16, 8 values per thread when f is a multiple of 8 (16-byte loads and stores).
-__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int f) {
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int f,
+                                     int interleaved) {
+    pdl_wait();
+    pdl_launch();
     const size_t t = blockIdx.y;
-    const uint4* g = (const uint4*)(gu + t * 2 * (size_t)f);
-    const uint4* u = (const uint4*)(gu + t * 2 * (size_t)f + f);
+    const uint4* row = (const uint4*)(gu + t * 2 * (size_t)f);
     uint4* o = (uint4*)(out + t * (size_t)f);
     const int n8 = f / 8;
     for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n8; j += gridDim.x * blockDim.x) {
-        uint4 gv = g[j], uv = u[j], ov;
+        uint4 gv = row[interleaved ? 2 * j : j], uv = row[interleaved ? 2 * j + 1 : n8 + j], ov;
         const __nv_bfloat162* gp = (const __nv_bfloat162*)&gv;
         const __nv_bfloat162* up = (const __nv_bfloat162*)&uv;
         __nv_bfloat162* op = (__nv_bfloat162*)&ov;
@@ -185,139 +203,161 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restri
     }
 }
 
-TGO_API int tgo_swiglu(const void* gate_up, void* out, int dtype, int T, int f,
+TGO_API int tgo_swiglu(const void* gate_up, void* out, int dtype, int T, int f, int interleaved,
                        cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (f <= 0 || T > 65535 * 32) return TGO_E_BAD_ARG;
+    if (f <= 0 || (interleaved && f % 8)) return TGO_E_BAD_ARG;
     // grid.y is limited to 65535 rows: larger batches go in slices.
     for (int t0 = 0; t0 < T; t0 += 65535) {
         const int rows = T - t0 < 65535 ? T - t0 : 65535;
+        int rc;
         if (dtype == TGO_BF16 && f % 8 == 0) {
-            const int bx = (f / 8 + 255) / 256;
-            swiglu_bf16x8_kernel<<<dim3(bx, rows), 256, 0, stream>>>(
-                (const bf16*)gate_up + (size_t)t0 * 2 * f, (bf16*)out + (size_t)t0 * f, f);
+            rc = tgo_launch_pdl(swiglu_bf16x8_kernel, dim3((f / 8 + 255) / 256, rows), dim3(256), 0,
+                                stream, (const bf16*)gate_up + (size_t)t0 * 2 * f,
+                                (bf16*)out + (size_t)t0 * f, f, interleaved);
         } else if (dtype == TGO_BF16) {
-            swiglu_kernel<bf16><<<dim3((f + 255) / 256, rows), 256, 0, stream>>>(
-                (const bf16*)gate_up + (size_t)t0 * 2 * f, (bf16*)out + (size_t)t0 * f, f);
+            rc = tgo_launch_pdl(swiglu_kernel<bf16>, dim3((f + 255) / 256, rows), dim3(256), 0,
+                                stream, (const bf16*)gate_up + (size_t)t0 * 2 * f,
+                                (bf16*)out + (size_t)t0 * f, f, interleaved);
         } else if (dtype == TGO_F32) {
-            swiglu_kernel<float><<<dim3((f + 255) / 256, rows), 256, 0, stream>>>(
-                (const float*)gate_up + (size_t)t0 * 2 * f, (float*)out + (size_t)t0 * f, f);
+            rc = tgo_launch_pdl(swiglu_kernel<float>, dim3((f + 255) / 256, rows), dim3(256), 0,
+                                stream, (const float*)gate_up + (size_t)t0 * 2 * f,
+                                (float*)out + (size_t)t0 * f, f, interleaved);
         } else {
             return TGO_E_BAD_ARG;
         }
+        if (rc) return rc;
     }
-    return launch_status();
+    return 0;
+}
+
+// ------------------------------------------------------------ rotation table
+// table[t, i] = cos(pos_t * inv_freq[i]), table[t, half + i] = sin(...), the angle and its
+// sine and cosine evaluated in float64 and rounded once to float32. Made once per step and
+// read by every layer that rotates with the same frequencies.
+__global__ void rope_table_kernel(const int* __restrict__ positions,
+                                  const double* __restrict__ inv_freq, float* __restrict__ table,
+                                  int half) {
+    pdl_wait();
+    pdl_launch();
+    const int t = blockIdx.x;
+    const double pos = (double)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        double s, c;
+        sincos(pos * inv_freq[i], &s, &c);
+        table[(size_t)t * 2 * half + i] = (float)c;
+        table[(size_t)t * 2 * half + half + i] = (float)s;
+    }
+}
+
+TGO_API int tgo_rope_table(const int* positions, const double* inv_freq, float* table, int T,
+                           int half, cudaStream_t stream) {
+    if (T <= 0 || half <= 0) return 0;
+    return tgo_launch_pdl(rope_table_kernel, dim3(T), dim3(half < 64 ? 32 : 64), 0, stream,
+                          positions, inv_freq, table, half);
 }
 
 // --------------------------------- per-head q/k RMSNorm + rotation + cache write
-// One block per token. Heads of q are normalised (if q_gain), rotated (if inv_freq) and
-// written back in place; heads of k likewise and then stored at the token's slot of the
-// paged cache; v is copied to its slot. The rotation pairs channel i with i + rot/2
-// (half-split), angle = position * inv_freq[i] evaluated in float64, the rotation itself
-// in float32. slot < 0 stores nothing. k or v may be null (a layer that reads another
-// layer's cache computes q only); with k given and k_cache null, k is written back in
-// place like q (used when another position encoding runs between the norm and the store).
+// One block per token. Heads of q are normalised (if q_gain), rotated (if a rotation table
+// is given) and written back in place; heads of k likewise and then stored at the token's
+// slot of the paged cache; v is copied to its slot. The rotation pairs channel i with
+// i + rot/2 (half-split) and is done in float32 with the table's cosines and sines.
+// slot < 0 stores nothing. k or v may be null (a layer that reads another layer's cache
+// computes q only); with k given and k_cache null, k is written back in place like q (used
+// when another position encoding runs between the norm and the store).
 //
 // Cache layout of one layer: [page][kv_head][offset in page][head_dim]; slot = page *
 // page_size + offset.
 #define QKR_MAX_DH 512
+#define QKR_WARPS 4
+// grid (tokens, ceil((H + 2 Hkv) / QKR_WARPS)): one warp per head vector; the warps past the
+// q and k heads copy the v heads.
 template <typename T>
 __global__ void qk_norm_rope_cache_kernel(
     T* __restrict__ q, long long q_stride, T* __restrict__ k, long long k_stride,
     const T* __restrict__ v, long long v_stride, int H, int Hkv, int dh,
     const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
-    const int* __restrict__ positions, const double* __restrict__ inv_freq, int rot,
+    const float* __restrict__ rope, int rot,
     const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
     int page_size) {
     extern __shared__ float smem[];
+    pdl_wait();
+    pdl_launch();
     const int t = blockIdx.x;
     const int half = rot / 2;
-    float* cs = smem;                 // [half] cos, [half] sin
-    const int nwarps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* buf = smem + 2 * half + warp * dh;
-    if (inv_freq) {
-        const double pos = (double)positions[t];
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            double s, c;
-            sincos(pos * inv_freq[i], &s, &c);
-            cs[i] = (float)c;
-            cs[half + i] = (float)s;
-        }
-    }
-    __syncthreads();
+    const int hh = blockIdx.y * QKR_WARPS + warp;
+    const int nk = k ? Hkv : 0, nv = v ? Hkv : 0;
+    if (hh >= H + nk + nv) return;
+    float* buf = smem + warp * dh;
+    const float* cs = rope ? rope + (size_t)t * rot : nullptr;   // [half] cos, [half] sin
     const int slot = slots ? slots[t] : -1;
     const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
-    const int n_heads = H + (k ? Hkv : 0);
-    for (int hh = warp; hh < n_heads; hh += nwarps) {
-        const bool is_q = hh < H;
-        const int head = is_q ? hh : hh - H;
-        T* vec = is_q ? q + (size_t)t * q_stride + (size_t)head * dh
-                      : k + (size_t)t * k_stride + (size_t)head * dh;
-        const float* gain = is_q ? q_gain : k_gain;
-        float ss = 0.f;
-        for (int i = lane; i < dh; i += 32) {
-            const float x = to_f32(vec[i]);
-            buf[i] = x;
-            ss += x * x;
-        }
-        if (gain) {
-            ss = warp_sum(ss);
-            const float scale = rsqrtf(ss / (float)dh + eps);
-            for (int i = lane; i < dh; i += 32) buf[i] = (buf[i] * scale) * gain[i];
-        }
-        __syncwarp();
-        T* dst = vec;
-        if (!is_q && k_cache) {
-            dst = slot >= 0 ? k_cache + (((size_t)page * Hkv + head) * page_size + off) * dh
-                            : nullptr;
-        }
-        if (dst) {
-            for (int i = lane; i < dh; i += 32) {
-                float y;
-                if (inv_freq && i < half)
-                    y = buf[i] * cs[i] - buf[i + half] * cs[half + i];
-                else if (inv_freq && i < rot)
-                    y = buf[i - half] * cs[half + i - half] + buf[i] * cs[i - half];
-                else
-                    y = buf[i];
-                dst[i] = from_f32<T>(y);
-            }
-        }
-        __syncwarp();
+    if (hh >= H + nk) {                                          // a v head: copy to its slot
+        const int head = hh - H - nk;
+        if (slot < 0) return;
+        const T* src = v + (size_t)t * v_stride + (size_t)head * dh;
+        T* dst = v_cache + (((size_t)page * Hkv + head) * page_size + off) * dh;
+        for (int i = lane; i < dh; i += 32) dst[i] = src[i];
+        return;
     }
-    if (v && slot >= 0) {
-        for (int i = threadIdx.x; i < Hkv * dh; i += blockDim.x) {
-            const int head = i / dh, c = i % dh;
-            v_cache[(((size_t)page * Hkv + head) * page_size + off) * dh + c] =
-                v[(size_t)t * v_stride + i];
-        }
+    const bool is_q = hh < H;
+    const int head = is_q ? hh : hh - H;
+    T* vec = is_q ? q + (size_t)t * q_stride + (size_t)head * dh
+                  : k + (size_t)t * k_stride + (size_t)head * dh;
+    const float* gain = is_q ? q_gain : k_gain;
+    float ss = 0.f;
+    for (int i = lane; i < dh; i += 32) {
+        const float x = to_f32(vec[i]);
+        buf[i] = x;
+        ss += x * x;
+    }
+    if (gain) {
+        ss = warp_sum(ss);
+        const float scale = rsqrtf(ss / (float)dh + eps);
+        for (int i = lane; i < dh; i += 32) buf[i] = (buf[i] * scale) * gain[i];
+    }
+    __syncwarp();
+    T* dst = vec;
+    if (!is_q && k_cache) {
+        dst = slot >= 0 ? k_cache + (((size_t)page * Hkv + head) * page_size + off) * dh : nullptr;
+    }
+    if (!dst) return;
+    for (int i = lane; i < dh; i += 32) {
+        float y;
+        if (cs && i < half)
+            y = buf[i] * cs[i] - buf[i + half] * cs[half + i];
+        else if (cs && i < rot)
+            y = buf[i - half] * cs[i] + buf[i] * cs[i - half];
+        else
+            y = buf[i];
+        dst[i] = from_f32<T>(y);
     }
 }
 
 TGO_API int tgo_qk_norm_rope_cache(void* q, long long q_stride, void* k, long long k_stride,
                                    const void* v, long long v_stride, int dtype, int T, int H,
                                    int Hkv, int dh, const float* q_gain, const float* k_gain,
-                                   float eps, const int* positions, const double* inv_freq,
-                                   int rot, const int* slots, void* k_cache, void* v_cache,
-                                   int page_size, cudaStream_t stream) {
+                                   float eps, const float* rope, int rot, const int* slots,
+                                   void* k_cache, void* v_cache, int page_size,
+                                   cudaStream_t stream) {
     if (T <= 0) return 0;
     if (dh <= 0 || dh > QKR_MAX_DH || rot < 0 || rot > dh || (rot & 1) || H <= 0) return TGO_E_BAD_ARG;
     if ((k || v) && Hkv <= 0) return TGO_E_BAD_ARG;
     if ((k_cache || v) && (page_size <= 0 || !slots)) return TGO_E_BAD_ARG;
     if ((v && !v_cache) || (k_cache && !k)) return TGO_E_BAD_ARG;
-    if (inv_freq && !positions) return TGO_E_BAD_ARG;
-    const int warps = 4;
-    const size_t smem = (size_t)(rot + warps * dh) * sizeof(float);
+    const int warps = QKR_WARPS;
+    const size_t smem = (size_t)(warps * dh) * sizeof(float);
+    const int vectors = H + (k ? Hkv : 0) + (v ? Hkv : 0);
+    const dim3 grid(T, (vectors + warps - 1) / warps);
     if (dtype == TGO_BF16)
-        qk_norm_rope_cache_kernel<bf16><<<T, warps * 32, smem, stream>>>(
+        return tgo_launch_pdl(qk_norm_rope_cache_kernel<bf16>, grid, dim3(warps * 32), smem, stream,
             (bf16*)q, q_stride, (bf16*)k, k_stride, (const bf16*)v, v_stride, H, Hkv, dh, q_gain,
-            k_gain, eps, positions, inv_freq, rot, slots, (bf16*)k_cache, (bf16*)v_cache, page_size);
+            k_gain, eps, rope, rot, slots, (bf16*)k_cache, (bf16*)v_cache, page_size);
     else if (dtype == TGO_F32)
-        qk_norm_rope_cache_kernel<float><<<T, warps * 32, smem, stream>>>(
+        return tgo_launch_pdl(qk_norm_rope_cache_kernel<float>, grid, dim3(warps * 32), smem, stream,
             (float*)q, q_stride, (float*)k, k_stride, (const float*)v, v_stride, H, Hkv, dh,
-            q_gain, k_gain, eps, positions, inv_freq, rot, slots, (float*)k_cache,
-            (float*)v_cache, page_size);
+            q_gain, k_gain, eps, rope, rot, slots, (float*)k_cache, (float*)v_cache, page_size);
     else
         return TGO_E_BAD_ARG;
     return launch_status();

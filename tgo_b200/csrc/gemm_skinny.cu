@@ -1,0 +1,215 @@
+// y[M,N] = act(x)[M,K] . W[N,K]^T for a handful of rows (M <= 64): the matrix products of a
+// decode step, which are bound by streaming W from HBM once.
+//
+// The weight rows sit on the M axis of mma.sync m16n8k16 and the batch on its N axis.
+// A CTA of 8 warps owns 16 rows of W (one m16 tile); each warp takes one eighth of K and the
+// eight partial tiles are added in shared memory in warp order, so the result does not
+// depend on timing. Both operands go from global memory straight into fragments with
+// 16-byte loads: the sum over k may run in any order as long as W and x agree on it, so a
+// thread's eight consecutive k values serve as the (2t, 2t+1) and (2t+8, 2t+9) pairs of two
+// k-steps. W is read with a no-allocate hint (each byte is used once); x stays cached.
+//
+// Input forms:  x bfloat16 [M,K];  or the float32 residual stream h [M,K] with a gain [K],
+// in which case the product is taken with bf16(h * gain) and each row of the result is
+// scaled by rsqrt(mean(h^2) + eps) at the end: RMSNorm without a kernel of its own (every
+// CTA forms the row sums itself, in a fixed order).
+// Output forms:  bfloat16 or float32 [M,N];  added into a float32 [M,N] (the residual);  or,
+// for a gate/up matrix whose rows are interleaved in eights (8 gate rows, the 8 matching up
+// rows, ...), silu(gate) * up as bfloat16 [M, N/2].
+#include "common.cuh"
+
+#define GS_WARPS 8
+#define GS_UNROLL 4
+
+#define GS_X_BF16 0
+#define GS_X_NORM 1
+#define GS_OUT_BF16 0
+#define GS_OUT_F32 1
+#define GS_OUT_ADD_F32 2
+#define GS_OUT_SWIGLU 3
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *(uint32_t*)&v;
+}
+
+template <int XMODE>
+__device__ __forceinline__ uint4 load_x(const void* __restrict__ x, const float* __restrict__ gain,
+                                        int m, int M, int K, int kk, bool valid_k, float& ss) {
+    uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    if (m >= M || !valid_k) return z;
+    if (XMODE == GS_X_BF16) return *(const uint4*)((const bf16*)x + (size_t)m * K + kk);
+    const float* row = (const float*)x + (size_t)m * K + kk;
+    const float4 h0 = *(const float4*)row, h1 = *(const float4*)(row + 4);
+    const float4 g0 = *(const float4*)(gain + kk), g1 = *(const float4*)(gain + kk + 4);
+    ss += h0.x * h0.x + h0.y * h0.y + h0.z * h0.z + h0.w * h0.w + h1.x * h1.x + h1.y * h1.y +
+          h1.z * h1.z + h1.w * h1.w;
+    z.x = pack2(h0.x * g0.x, h0.y * g0.y);
+    z.y = pack2(h0.z * g0.z, h0.w * g0.w);
+    z.z = pack2(h1.x * g1.x, h1.y * g1.y);
+    z.w = pack2(h1.z * g1.z, h1.w * g1.w);
+    return z;
+}
+
+template <int MT, int XMODE, int OMODE>
+__global__ void __launch_bounds__(GS_WARPS * 32)
+gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, float eps,
+                   const bf16* __restrict__ w, void* __restrict__ y, int M, int N, int K) {
+    __shared__ float red[GS_WARPS][16][MT * 8 + 1];
+    __shared__ float red_ss[GS_WARPS][MT * 8];
+    pdl_wait();
+    pdl_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * 16;
+    int slice = (K + GS_WARPS - 1) / GS_WARPS;
+    slice = (slice + 31) / 32 * 32;
+    const int k_begin = warp * slice;
+    const int k_end = k_begin + slice < K ? k_begin + slice : K;
+    const int row_lo = n0 + g, row_hi = n0 + g + 8;
+    const bf16* w_lo = w + (size_t)(row_lo < N ? row_lo : 0) * K;
+    const bf16* w_hi = w + (size_t)(row_hi < N ? row_hi : 0) * K;
+    const bool ok_lo = row_lo < N, ok_hi = row_hi < N;
+
+    float acc[MT][4];
+    float ss[MT];
+#pragma unroll
+    for (int j = 0; j < MT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; ss[j] = 0.f; }
+
+    for (int k = k_begin; k < k_end; k += 32 * GS_UNROLL) {
+        uint4 a_lo[GS_UNROLL], a_hi[GS_UNROLL];
+#pragma unroll
+        for (int u = 0; u < GS_UNROLL; ++u) {
+            const int kk = k + u * 32 + 8 * t;
+            const bool v = kk < k_end;
+            a_lo[u] = (v && ok_lo) ? ldg_stream(w_lo + kk) : make_uint4(0u, 0u, 0u, 0u);
+            a_hi[u] = (v && ok_hi) ? ldg_stream(w_hi + kk) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < GS_UNROLL; ++u) {
+            const int kk = k + u * 32 + 8 * t;
+            const bool v = kk < k_end;
+#pragma unroll
+            for (int j = 0; j < MT; ++j) {
+                const uint4 b = load_x<XMODE>(x, gain, j * 8 + g, M, K, kk, v, ss[j]);
+                mma_bf16_16816(acc[j], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b.x, b.y);
+                mma_bf16_16816(acc[j], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b.z, b.w);
+            }
+        }
+    }
+    pdl_launch_late();
+    // partial tiles -> shared memory: [warp][row of W][batch row]
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+        red[warp][g][j * 8 + 2 * t] = acc[j][0];
+        red[warp][g][j * 8 + 2 * t + 1] = acc[j][1];
+        red[warp][g + 8][j * 8 + 2 * t] = acc[j][2];
+        red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
+        if (XMODE == GS_X_NORM) {
+            float s = ss[j];
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            if (t == 0) red_ss[warp][j * 8 + g] = s;
+        }
+    }
+    __syncthreads();
+    if (OMODE == GS_OUT_SWIGLU) {
+        // rows 0..7 of the tile are gate columns n0/2 .. n0/2+7, rows 8..15 the matching up
+        for (int i = threadIdx.x; i < 8 * MT * 8; i += GS_WARPS * 32) {
+            const int r = i & 7, m = i >> 3;
+            const int col = n0 / 2 + r;
+            if (m >= M || col >= N / 2) continue;
+            float gt = 0.f, up = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < GS_WARPS; ++wv) { gt += red[wv][r][m]; up += red[wv][r + 8][m]; }
+            if (XMODE == GS_X_NORM) {
+                float tot = 0.f;
+#pragma unroll
+                for (int wv = 0; wv < GS_WARPS; ++wv) tot += red_ss[wv][m];
+                const float sc = rsqrtf(tot / (float)K + eps);
+                gt *= sc;
+                up *= sc;
+            }
+            // the gate and up values pass through bfloat16 as they do when the product is
+            // stored before the gate is applied
+            gt = __bfloat162float(__float2bfloat16_rn(gt));
+            up = __bfloat162float(__float2bfloat16_rn(up));
+            ((bf16*)y)[(size_t)m * (N / 2) + col] = __float2bfloat16_rn(gt / (1.f + expf(-gt)) * up);
+        }
+        return;
+    }
+    // 16 x (MT*8) outputs; consecutive threads take consecutive rows of W (contiguous in y)
+    for (int i = threadIdx.x; i < 16 * MT * 8; i += GS_WARPS * 32) {
+        const int r = i & 15, m = i >> 4;
+        const int n = n0 + r;
+        if (m >= M || n >= N) continue;
+        float s = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < GS_WARPS; ++wv) s += red[wv][r][m];
+        if (XMODE == GS_X_NORM) {
+            float tot = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < GS_WARPS; ++wv) tot += red_ss[wv][m];
+            s *= rsqrtf(tot / (float)K + eps);
+        }
+        const size_t at = (size_t)m * N + n;
+        if (OMODE == GS_OUT_BF16) ((bf16*)y)[at] = __float2bfloat16_rn(s);
+        else if (OMODE == GS_OUT_F32) ((float*)y)[at] = s;
+        else ((float*)y)[at] += s;
+    }
+}
+
+template <int MT, int XMODE>
+static int gs_launch_o(const void* x, const float* gain, float eps, const bf16* w, void* y, int M,
+                       int N, int K, int omode, cudaStream_t s) {
+    const dim3 grid((N + 15) / 16), block(GS_WARPS * 32);
+    switch (omode) {
+        case GS_OUT_BF16:
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_BF16>, grid, block, 0, s, x,
+                                  gain, eps, w, y, M, N, K);
+        case GS_OUT_F32:
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_F32>, grid, block, 0, s, x,
+                                  gain, eps, w, y, M, N, K);
+        case GS_OUT_ADD_F32:
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_ADD_F32>, grid, block, 0, s,
+                                  x, gain, eps, w, y, M, N, K);
+        default:
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_SWIGLU>, grid, block, 0, s,
+                                  x, gain, eps, w, y, M, N, K);
+    }
+}
+
+template <int MT>
+static int gs_launch(const void* x, const float* gain, float eps, const bf16* w, void* y, int M,
+                     int N, int K, int xmode, int omode, cudaStream_t s) {
+    if (xmode == GS_X_BF16) return gs_launch_o<MT, GS_X_BF16>(x, gain, eps, w, y, M, N, K, omode, s);
+    return gs_launch_o<MT, GS_X_NORM>(x, gain, eps, w, y, M, N, K, omode, s);
+}
+
+// Most rows this kernel takes; K must be a multiple of 8 (16-byte loads).
+TGO_API int tgo_gemm_skinny_max_rows() { return 64; }
+
+TGO_API int tgo_gemm_skinny(const void* x, const float* gain, float eps, const void* w, void* y,
+                            int M, int N, int K, int xmode, int omode, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || M > 64 || xmode < 0 || xmode > 1 || omode < 0 || omode > 3 ||
+        (xmode == GS_X_NORM && !gain) || (omode == GS_OUT_SWIGLU && N % 16))
+        return TGO_E_BAD_ARG;
+    const bf16* wp = (const bf16*)w;
+    if (M <= 8) return gs_launch<1>(x, gain, eps, wp, y, M, N, K, xmode, omode, stream);
+    if (M <= 16) return gs_launch<2>(x, gain, eps, wp, y, M, N, K, xmode, omode, stream);
+    if (M <= 32) return gs_launch<4>(x, gain, eps, wp, y, M, N, K, xmode, omode, stream);
+    return gs_launch<8>(x, gain, eps, wp, y, M, N, K, xmode, omode, stream);
+}

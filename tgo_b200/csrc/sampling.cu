@@ -88,20 +88,76 @@ __device__ Best block_argmax(const float* __restrict__ row, int V, float inv_t, 
     return scratch[32];
 }
 
-__global__ void __launch_bounds__(SM_THREADS)
-argmax_kernel(const float* __restrict__ logits, long long stride, int V, int* __restrict__ out) {
+// argmax in two passes so that a handful of rows still fills the GPU: AM_PARTS blocks per row
+// each reduce a contiguous slice to (value, id); one warp per row then reduces the parts.
+// Ties go to the lowest id at every level.
+#define AM_PARTS 32
+#define AM_THREADS 256
+
+__global__ void __launch_bounds__(AM_THREADS)
+argmax_part_kernel(const float* __restrict__ logits, long long stride, int V,
+                   float* __restrict__ part_v, int* __restrict__ part_i) {
     __shared__ Best scratch[33];
-    const float* row = logits + (size_t)blockIdx.x * stride;
-    const Best b = block_argmax(row, V, 1.f, scratch);
-    if (threadIdx.x == 0) out[blockIdx.x] = b.i;
+    pdl_wait();
+    pdl_launch();
+    const int r = blockIdx.y, part = blockIdx.x;
+    const int per = (V + AM_PARTS - 1) / AM_PARTS;
+    const int lo = part * per, hi = lo + per < V ? lo + per : V;
+    const float* row = logits + (size_t)r * stride;
+    Best b = {-INFINITY, 0x7fffffff};
+    for (int i = lo + threadIdx.x; i < hi; i += AM_THREADS) {
+        const float v = row[i];
+        if (v > b.v || (v == b.v && i < b.i)) { b.v = v; b.i = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other;
+        other.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+        other.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+        b = better(b, other);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) scratch[warp] = b;
+    __syncthreads();
+    if (warp == 0) {
+        Best t = lane < AM_THREADS / 32 ? scratch[lane] : Best{-INFINITY, 0x7fffffff};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            Best other;
+            other.v = __shfl_xor_sync(0xffffffffu, t.v, o);
+            other.i = __shfl_xor_sync(0xffffffffu, t.i, o);
+            t = better(t, other);
+        }
+        if (lane == 0) { part_v[r * AM_PARTS + part] = t.v; part_i[r * AM_PARTS + part] = t.i; }
+    }
 }
 
+__global__ void argmax_final_kernel(const float* __restrict__ part_v,
+                                    const int* __restrict__ part_i, int* __restrict__ out) {
+    pdl_wait();
+    pdl_launch();
+    const int r = blockIdx.x, lane = threadIdx.x;
+    Best b = {part_v[r * AM_PARTS + lane], part_i[r * AM_PARTS + lane]};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other;
+        other.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+        other.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+        b = better(b, other);
+    }
+    if (lane == 0) out[r] = b.i == 0x7fffffff ? 0 : b.i;
+}
+
+// scratch: n * 32 floats and n * 32 ints
 TGO_API int tgo_argmax(const float* logits, long long stride, int n, int V, int* out,
-                       cudaStream_t stream) {
+                       float* part_v, int* part_i, cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (V <= 0) return TGO_E_BAD_ARG;
-    argmax_kernel<<<n, SM_THREADS, 0, stream>>>(logits, stride, V, out);
-    return launch_status();
+    if (V <= 0 || n > 65535 || !part_v || !part_i) return TGO_E_BAD_ARG;
+    const int rc = tgo_launch_pdl(argmax_part_kernel, dim3(AM_PARTS, n), dim3(AM_THREADS), 0, stream,
+                                  logits, stride, V, part_v, part_i);
+    if (rc) return rc;
+    return tgo_launch_pdl(argmax_final_kernel, dim3(n), dim3(32), 0, stream,
+                          (const float*)part_v, (const int*)part_i, out);
 }
 
 // Exclusive prefix of per-thread values (float), in thread order; total in *total.

@@ -247,6 +247,9 @@ class Engine:
             self.model.forward(ctx, self.storage, tables, slots)
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
+        # what the eager run cached per step (tables made from its inputs) must be made
+        # again inside the capture, or the replays would keep reading the first step's
+        ctx.aux = {"graph": True}
         graph = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES[0]
         with torch.cuda.graph(graph):

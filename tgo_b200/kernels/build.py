@@ -24,7 +24,7 @@ import time
 CSRC = os.path.normpath(os.path.join(os.path.dirname(__file__), "..", "csrc"))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC",
-              "-Xcompiler", "-fvisibility=hidden"]
+              "-Xcompiler", "-fvisibility=hidden"] + os.environ.get("TGO_NVCC_DEFS", "").split()
 
 # library name -> (sources, extra link flags)
 LIBRARIES = {
@@ -32,6 +32,7 @@ LIBRARIES = {
     "attention_generic": (["attention_generic.cu"], []),
     "attention_flash": (["attention_flash.cu"], []),
     "sgemm": (["sgemm.cu"], []),
+    "gemm_skinny": (["gemm_skinny.cu"], []),
     "sampling": (["sampling.cu"], []),
 }
 

@@ -99,36 +99,49 @@ def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
                                 c_ll(h.numel()), _stream()), "residual_add")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, f + j]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    """out[t, j] = silu(gate_j) * up_j; gate_up holds the gate columns then the up columns,
+    or, `interleaved`, eight gate columns and the eight matching up columns in turn."""
     _need_cuda(gate_up, out)
     T, f = out.shape
     assert gate_up.shape == (T, 2 * f) and gate_up.is_contiguous() and out.is_contiguous()
     assert gate_up.dtype == out.dtype
     lib = load_library("elementwise")
     _check(lib.tgo_swiglu(_ptr(gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(T),
-                          c_int(f), _stream()), "swiglu", f"(T={T}, f={f})")
+                          c_int(f), c_int(1 if interleaved else 0), _stream()), "swiglu",
+           f"(T={T}, f={f})")
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """[T, 2 * half] float32: cos then sin of position * inv_freq, evaluated in float64."""
+    _need_cuda(positions, inv_freq)
+    assert positions.dtype == torch.int32 and inv_freq.dtype == torch.float64
+    T, half = positions.numel(), inv_freq.numel()
+    table = torch.empty((T, 2 * half), dtype=torch.float32, device=positions.device)
+    lib = load_library("elementwise")
+    _check(lib.tgo_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(table), c_int(T),
+                              c_int(half), _stream()), "rope_table")
+    return table
 
 
 def qk_norm_rope_cache(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor],
                        num_heads: int, num_kv_heads: int, head_dim: int,
                        q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
-                       positions: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor],
-                       rotary_dim: int, slots: Optional[torch.Tensor],
-                       k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
-                       page_size: int) -> None:
-    """Per-head RMSNorm of q and k (if gains are given), half-split rotation (if inv_freq
-    is given), q written back in place, k and v stored at `slots` of the paged cache
-    [page, kv_head, offset, head_dim]. q, k, v are 2-D views whose rows may be strided
-    (columns of one fused projection output)."""
-    _need_cuda(q, k, v, q_gain, k_gain, positions, inv_freq, slots, k_cache, v_cache)
+                       rope: Optional[torch.Tensor], rotary_dim: int,
+                       slots: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                       v_cache: Optional[torch.Tensor], page_size: int) -> None:
+    """Per-head RMSNorm of q and k (if gains are given), half-split rotation (if `rope`, a
+    table from rope_table, is given), q written back in place, k and v stored at `slots` of
+    the paged cache [page, kv_head, offset, head_dim]. q, k, v are 2-D views whose rows may
+    be strided (columns of one joined projection output)."""
+    _need_cuda(q, k, v, q_gain, k_gain, rope, slots, k_cache, v_cache)
     T = q.shape[0]
     for t in (q, k, v):
         if t is not None:
             assert t.stride(1) == 1 and t.dtype == q.dtype and t.shape[0] == T
-    if inv_freq is not None:
-        assert inv_freq.dtype == torch.float64 and inv_freq.numel() == rotary_dim // 2
-        assert positions is not None and positions.dtype == torch.int32
+    if rope is not None:
+        assert rope.dtype == torch.float32 and rope.shape == (T, rotary_dim)
+        assert rope.is_contiguous()
     if k_cache is not None:
         assert k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
         assert k_cache.is_contiguous() and v_cache.is_contiguous()
@@ -138,8 +151,7 @@ def qk_norm_rope_cache(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[t
         _ptr(q), c_ll(q.stride(0)), _ptr(k), c_ll(k.stride(0) if k is not None else 0),
         _ptr(v), c_ll(v.stride(0) if v is not None else 0), c_int(dtype_code(q.dtype)), c_int(T),
         c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), _ptr(q_gain), _ptr(k_gain),
-        c_float(eps), _ptr(positions), _ptr(inv_freq), c_int(rotary_dim if inv_freq is not None
-                                                              else 0),
+        c_float(eps), _ptr(rope), c_int(rotary_dim if rope is not None else 0),
         _ptr(slots), _ptr(k_cache), _ptr(v_cache), c_int(page_size), _stream()),
         "qk_norm_rope_cache", f"(head_dim={head_dim}, rotary_dim={rotary_dim})")
 
@@ -178,35 +190,138 @@ def sgemm_tn(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
            "sgemm_tn", f"(M={M}, N={N}, K={K})")
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y = x . w^T with w stored [out, in].
+SKINNY_MAX_ROWS = 8
+FOLD_NORM = False     # folding RMSNorm into the product re-reads h and the gain in every CTA;
+                      # measured slower than the separate norm kernel at every batch size
 
-    float32: this package's plain-FMA kernel. bfloat16: the library matrix product
-    (cuBLASLt through torch.mm) with float32 accumulation; out_dtype float32 keeps the
-    accumulator's width (used for the logits).
-    """
-    _need_cuda(x, w)
+
+class NormedRows:
+    """rmsnorm(h) * gain, not computed yet: a mixer or feed-forward whose first step is a
+    matrix product can hand this to `linear`, which folds the norm into the product when
+    the weight-streaming kernel runs it, and computes it with the norm kernel otherwise."""
+
+    def __init__(self, h: torch.Tensor, gain: torch.Tensor, eps: float, dtype: torch.dtype):
+        self.h, self.gain, self.eps, self.dtype = h, gain, float(eps), dtype
+        self._done = None
+
+    @property
+    def shape(self):
+        return self.h.shape
+
+    @property
+    def device(self):
+        return self.h.device
+
+    def materialize(self) -> torch.Tensor:
+        if self._done is None:
+            out = torch.empty(self.h.shape, dtype=self.dtype, device=self.h.device)
+            add_rmsnorm(self.h, None, self.gain, self.eps, out)
+            self._done = out
+        return self._done
+
+
+def as_rows(x) -> torch.Tensor:
+    """The tensor behind `x`, computing a pending norm if there is one."""
+    return x.materialize() if isinstance(x, NormedRows) else x
+
+
+def gemm_skinny(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+                gated: bool = False) -> None:
+    """out = x . w^T for at most 64 rows, bfloat16 weights, the weight-streaming kernel.
+    x: bfloat16 [M, K], or NormedRows over a float32 [M, K] (the norm is folded in).
+    out: bfloat16 or float32 [M, N]; with `accumulate` (float32) the product is added to it;
+    with `gated`, w is a gate/up matrix with rows interleaved in eights and out is
+    silu(gate) * up, bfloat16 [M, N / 2]."""
+    normed = isinstance(x, NormedRows)
+    xt = x.h if normed else x
+    _need_cuda(xt, w, out)
+    M, N, K = xt.shape[0], w.shape[0], w.shape[1]
+    assert w.dtype == torch.bfloat16 and xt.dtype == (torch.float32 if normed else torch.bfloat16)
+    assert xt.is_contiguous() and w.is_contiguous() and out.is_contiguous()
+    assert xt.shape[1] == K and xt.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+    if gated:
+        assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2) and N % 16 == 0
+        omode = 3
+    elif accumulate:
+        assert out.dtype == torch.float32 and out.shape == (M, N)
+        omode = 2
+    else:
+        assert out.dtype in (torch.bfloat16, torch.float32) and out.shape == (M, N)
+        omode = 0 if out.dtype == torch.bfloat16 else 1
+    lib = load_library("gemm_skinny")
+    _check(lib.tgo_gemm_skinny(_ptr(xt), _ptr(x.gain if normed else None),
+                               c_float(x.eps if normed else 0.0), _ptr(w), _ptr(out), c_int(M),
+                               c_int(N), c_int(K), c_int(1 if normed else 0), c_int(omode),
+                               _stream()), "gemm_skinny", f"(M={M}, N={N}, K={K})")
+
+
+def _skinny_ok(x, w) -> bool:
+    dt = x.dtype
+    return dt == torch.bfloat16 and w.dtype == torch.bfloat16 and \
+        x.shape[0] <= SKINNY_MAX_ROWS and w.shape[1] % 8 == 0
+
+
+def _dense(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     M, N = x.shape[0], w.shape[0]
-    out_dtype = out_dtype or x.dtype
     if x.dtype == torch.float32:
         assert out_dtype == torch.float32
-        if out is None:
-            out = torch.empty((M, N), dtype=torch.float32, device=x.device)
-        sgemm_tn(x, w, out)
+        y = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        sgemm_tn(x, w, y)
+        return y
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        return torch.mm(x, w.t()) if out_dtype == torch.bfloat16 else \
+            torch.mm(x, w.t(), out_dtype=torch.float32)
+    raise KernelError(f"linear: x is {x.dtype} and w is {w.dtype}")
+
+
+def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           residual: Optional[torch.Tensor] = None):
+    """y = x . w^T with w stored [out, in]. x is a tensor or NormedRows. residual: a float32
+    [M, N] tensor the product is added to, in which case nothing is returned.
+
+    float32: this package's plain-FMA kernel. bfloat16 with few rows (a decode step): this
+    package's weight-streaming kernel, which folds in a pending norm and the residual add.
+    bfloat16 with more rows: the library matrix product (cuBLASLt through torch.mm),
+    float32 accumulation; out_dtype float32 keeps the accumulator's width (the logits).
+    """
+    out_dtype = out_dtype or x.dtype
+    if isinstance(x, NormedRows) and not FOLD_NORM:
+        x = x.materialize()
+    if _skinny_ok(x, w):
+        M, N = x.shape[0], w.shape[0]
+        if residual is not None:
+            gemm_skinny(x, w, residual, accumulate=True)
+            return None
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        gemm_skinny(x, w, out)
         return out
-    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
-        raise KernelError(f"linear: x is {x.dtype} and w is {w.dtype}")
-    if out_dtype == torch.bfloat16:
-        if out is None:
-            return torch.mm(x, w.t())
-        return torch.mm(x, w.t(), out=out)
-    if out is None:
-        return torch.mm(x, w.t(), out_dtype=torch.float32)
-    return torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    y = _dense(as_rows(x), w, out_dtype)
+    if residual is not None:
+        residual_add(residual, y)
+        return None
+    return y
+
+
+def gated_linear(x, w_gate_up: torch.Tensor, interleaved: bool) -> torch.Tensor:
+    """silu(x . Wg^T) * (x . Wu^T) as [M, f] in x's dtype. w_gate_up is [2f, K]: the gate
+    rows then the up rows, or (`interleaved`) eight gate rows and the eight matching up rows
+    in turn, which lets the weight-streaming kernel apply the gate itself."""
+    M, f = x.shape[0], w_gate_up.shape[0] // 2
+    if isinstance(x, NormedRows) and not FOLD_NORM:
+        x = x.materialize()
+    if interleaved and _skinny_ok(x, w_gate_up):
+        out = torch.empty((M, f), dtype=torch.bfloat16, device=x.device)
+        gemm_skinny(x, w_gate_up, out, gated=True)
+        return out
+    xt = as_rows(x)
+    gu = _dense(xt, w_gate_up, xt.dtype)
+    out = torch.empty((M, f), dtype=xt.dtype, device=xt.device)
+    swiglu(gu, out, interleaved)
+    return out
 
 
 NUM_SMS = 148
+FUSED_JOIN = False
 
 
 def flash_supports(head_dim: int, group: int) -> bool:
@@ -232,20 +347,23 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
     assert q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 2 == 0
     assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
     n_tiles = T if tile_tok0 is None else tile_tok0.numel()
-    part_o = part_ml = None
+    part_o = part_ml = counters = None
+    decode = tile_tok0 is None and not wide
     if n_splits > 1:
         part_o = torch.empty((T, num_heads, n_splits, head_dim), dtype=torch.float32,
                              device=q.device)
         part_ml = torch.empty((T, num_heads, n_splits, 2), dtype=torch.float32, device=q.device)
+        if decode and FUSED_JOIN:   # the decode kernel joins the splits itself
+            counters = torch.zeros((T, num_kv_heads), dtype=torch.int32, device=q.device)
     lib = load_library("attention_flash")
     _check(lib.tgo_attention_flash(
         _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
         c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(positions),
         _ptr(seq_ids), _ptr(tile_tok0), _ptr(tile_ntok), c_int(n_tiles), c_int(num_heads),
         c_int(num_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(1 if wide else 0),
-        c_int(n_splits), _ptr(part_o), _ptr(part_ml), _stream()), "attention_flash",
-        f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads})")
-    if n_splits > 1:
+        c_int(n_splits), _ptr(part_o), _ptr(part_ml), _ptr(counters), _stream()),
+        "attention_flash", f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads})")
+    if n_splits > 1 and counters is None:
         _check(lib.tgo_attention_flash_combine(
             _ptr(part_o), _ptr(part_ml), _ptr(out), c_ll(out.stride(0)), c_int(T),
             c_int(num_heads), c_int(head_dim), c_int(n_splits), _stream()),
@@ -270,13 +388,17 @@ def _tiles(ctx, tokens_per_tile: int):
     return got
 
 
-def decode_splits(ctx, num_kv_heads: int, window: int) -> int:
-    """How many CTAs share one request's keys in a decode step: enough to fill the GPU
-    about twice over, no more than there are 64-key tiles."""
+def decode_splits(ctx, num_kv_heads: int, window: int, ctas_per_sm: int = 3) -> int:
+    """How many CTAs share one request's keys in a decode step: as many as fill the GPU once
+    (measured: one full wave beats more, shorter CTAs), each with at least two 64-key tiles;
+    a batch that nearly fills the GPU by itself is still cut in two, which evens out the
+    requests' lengths."""
     reach = min(ctx.max_context, window) if window > 0 else ctx.max_context
     tiles = max(1, (reach + 63) // 64 + (1 if window > 0 else 0))
-    want = max(1, (2 * NUM_SMS) // max(1, ctx.num_seqs * num_kv_heads))
-    return max(1, min(tiles, want, 64))
+    pairs = max(1, ctx.num_seqs * num_kv_heads)
+    wave = NUM_SMS * ctas_per_sm
+    s = max(1, -(-wave // pairs)) if pairs < wave else (2 if pairs < 2 * wave else 1)
+    return max(1, min(s, tiles // 2, 64))
 
 
 def paged_attention(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
@@ -308,8 +430,10 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     assert out.dtype == torch.int32 and out.numel() == n
     lib = load_library("sampling")
+    part_v = torch.empty((n, 32), dtype=torch.float32, device=logits.device)
+    part_i = torch.empty((n, 32), dtype=torch.int32, device=logits.device)
     _check(lib.tgo_argmax(_ptr(logits), c_ll(logits.stride(0)), c_int(n), c_int(V), _ptr(out),
-                          _stream()), "argmax")
+                          _ptr(part_v), _ptr(part_i), _stream()), "argmax")
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,

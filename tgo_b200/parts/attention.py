@@ -23,6 +23,8 @@ from .base import CacheNeed, LayerCache, Part
 
 
 class GQAAttention(Part):
+    takes_normed_rows = True      # its first step is a matrix product: the norm may fold in
+
     def __init__(self, spec: MixerSpec, hidden: int, prefix: str, device=None):
         self.hidden = hidden
         self.prefix = prefix
@@ -73,7 +75,9 @@ class GQAAttention(Part):
             self.k_gain = weights.pop(p + "k_norm.weight").contiguous()
 
     # ---- compute
-    def forward(self, x: torch.Tensor, ctx, cache: LayerCache) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx, cache: LayerCache, residual=None):
+        """With `residual` (the float32 stream) the result is added to it and None is
+        returned; else the result is returned."""
         H, Hkv, dh = self.H, self.Hkv, self.dh
         qw, kw = H * dh, Hkv * dh
         if cache.writable:
@@ -82,26 +86,26 @@ class GQAAttention(Part):
         else:
             q, k, v = ops.linear(x, self.w_q), None, None
         fused = self.position is None or getattr(self.position, "fusable", False)
-        inv_freq, rot = self.position.rotary() if (fused and self.position is not None) \
+        rope, rot = self.position.rotary(ctx) if (fused and self.position is not None) \
             else (None, 0)
         if fused:
             ops.qk_norm_rope_cache(q, k, v, H, Hkv, dh, self.q_gain, self.k_gain, self.eps,
-                                   ctx.positions, inv_freq, rot, cache.slots if k is not None
-                                   else None, cache.k if k is not None else None,
+                                   rope, rot, cache.slots if k is not None else None,
+                                   cache.k if k is not None else None,
                                    cache.v if k is not None else None, cache.page_size)
         else:
             # a position encoding this kernel does not know: norm, then the encoding's own
             # code, then the store
             if self.qk_norm:
                 ops.qk_norm_rope_cache(q, k, None, H, Hkv, dh, self.q_gain, self.k_gain,
-                                       self.eps, None, None, 0, None, None, None, 0)
-            self.position.apply(q, k, ctx.positions, H, Hkv, dh)
+                                       self.eps, None, 0, None, None, None, 0)
+            self.position.apply(q, k, ctx, H, Hkv, dh)
             if k is not None:
-                ops.qk_norm_rope_cache(q, k, v, H, Hkv, dh, None, None, 0.0, None, None, 0,
+                ops.qk_norm_rope_cache(q, k, v, H, Hkv, dh, None, None, 0.0, None, 0,
                                        cache.slots, cache.k, cache.v, cache.page_size)
-        a = torch.empty((x.shape[0], qw), dtype=x.dtype, device=x.device)
+        a = torch.empty((x.shape[0], qw), dtype=q.dtype, device=q.device)
         ops.paged_attention(q, a, H, Hkv, dh, cache, ctx, self.scale, self.window or 0)
-        return ops.linear(a, self.w_o)
+        return ops.linear(a, self.w_o, residual=residual)
 
 
 MIXERS.register("gqa_attention", GQAAttention)

@@ -10,13 +10,15 @@ Interfaces (duck-typed; `Part` only supplies the defaults):
   norm            forward(h, delta, out_dtype, rows=None) -> normed rows
                   h is the float32 residual stream [T, d]; delta, if given, is added
                   to it first (and stays added); rows selects rows instead of all.
-  position        `apply(q, k, positions, num_heads, num_kv_heads, head_dim)` in place; and,
-                  if the class sets `fusable = True`, `rotary()` -> (inv_freq float64
-                  tensor or None, rotary_dim), which lets the mixer do a half-split
-                  rotation inside its own kernel instead of calling `apply`.
+  position        `apply(q, k, ctx, num_heads, num_kv_heads, head_dim)` in place; and, if the
+                  class sets `fusable = True`, `rotary(ctx)` -> (table [T, rotary_dim] of
+                  cosines then sines, or None; rotary_dim), which lets the mixer do a
+                  half-split rotation inside its own kernel instead of calling `apply`.
   mixer           cache_need() -> CacheNeed or None; state_need() -> StateNeed or None;
-                  forward(x, ctx, cache) -> [T, d] in the activation dtype.
-  feed-forward    forward(x, ctx) -> [T, d].
+                  forward(x, ctx, cache) -> [T, d] in the activation dtype. A forward that
+                  also takes `residual=None` may add its result into that float32 tensor
+                  itself and return None.
+  feed-forward    forward(x, ctx) -> [T, d]; `residual` as for the mixer.
   block           forward(h, pending, ctx, cache) -> (h, pending): `pending` is a delta
                   not yet added to h, so the add can be fused into the next norm.
 """

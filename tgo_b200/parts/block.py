@@ -7,6 +7,8 @@ pending and handed to the next norm, which does it in its own kernel.
 """
 from __future__ import annotations
 
+import inspect
+
 from ..config.spec import LayerSpec
 from ..registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
 from .base import Part
@@ -29,6 +31,9 @@ class PreNormResidual(Part):
         self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, hidden, p + names["mixer"], device)
         self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(
             spec.feed_forward, hidden, p + names["feed_forward"], device)
+        # a part whose forward takes `residual` may add its result to the stream itself
+        self._mixer_adds = "residual" in inspect.signature(self.mixer.forward).parameters
+        self._ffn_adds = "residual" in inspect.signature(self.feed_forward.forward).parameters
 
     def parts(self):
         return [self.norm1, self.mixer, self.norm2, self.feed_forward]
@@ -43,10 +48,20 @@ class PreNormResidual(Part):
         for part in self.parts():
             part.bind(weights)
 
+    def _normed(self, norm, part, h, pending, ctx):
+        if getattr(part, "takes_normed_rows", False) and hasattr(norm, "lazy"):
+            return norm.lazy(h, pending, ctx.act_dtype)
+        return norm.forward(h, pending, ctx.act_dtype)
+
     def forward(self, h, pending, ctx, cache):
-        n = self.norm1.forward(h, pending, ctx.act_dtype)
-        a = self.mixer.forward(n, ctx, cache)
-        n = self.norm2.forward(h, a, ctx.act_dtype)
+        n = self._normed(self.norm1, self.mixer, h, pending, ctx)
+        if self._mixer_adds:
+            a = self.mixer.forward(n, ctx, cache, residual=h)
+        else:
+            a = self.mixer.forward(n, ctx, cache)
+        n = self._normed(self.norm2, self.feed_forward, h, a, ctx)
+        if self._ffn_adds:
+            return h, self.feed_forward.forward(n, ctx, residual=h)
         return h, self.feed_forward.forward(n, ctx)
 
 

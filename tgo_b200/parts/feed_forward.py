@@ -19,6 +19,7 @@ class SwiGLU(Part):
         self.prefix = prefix
         self.w_gate_up = None
         self.w_down = None
+        self.interleaved = False
 
     def weight_specs(self):
         p = self.prefix
@@ -26,17 +27,27 @@ class SwiGLU(Part):
                 WeightSpec(p + "up_proj.weight", (self.inter, self.hidden)),
                 WeightSpec(p + "down_proj.weight", (self.hidden, self.inter))]
 
+    takes_normed_rows = True      # its first step is a matrix product: the norm may fold in
+
     def bind(self, weights):
         p = self.prefix
-        self.w_gate_up = torch.cat([weights.pop(p + "gate_proj.weight"),
-                                    weights.pop(p + "up_proj.weight")], dim=0).contiguous()
+        gate, up = weights.pop(p + "gate_proj.weight"), weights.pop(p + "up_proj.weight")
+        f, d = self.inter, self.hidden
+        # eight gate rows, then the eight matching up rows, and so on: one 16-row tile of the
+        # weight-streaming product then holds a gate column and its up column together
+        self.interleaved = f % 8 == 0
+        if self.interleaved:
+            self.w_gate_up = torch.stack([gate.view(f // 8, 8, d), up.view(f // 8, 8, d)],
+                                         dim=1).reshape(2 * f, d).contiguous()
+        else:
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = weights.pop(p + "down_proj.weight").contiguous()
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        gu = ops.linear(x, self.w_gate_up)
-        act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        ops.swiglu(gu, act)
-        return ops.linear(act, self.w_down)
+    def forward(self, x: torch.Tensor, ctx, residual=None):
+        """With `residual` (the float32 stream) the result is added to it and None is
+        returned; else the result is returned."""
+        act = ops.gated_linear(x, self.w_gate_up, self.interleaved)
+        return ops.linear(act, self.w_down, residual=residual)
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)

@@ -36,3 +36,13 @@ class RMSNorm(Part):
 
 
 NORMS.register("rmsnorm", RMSNorm)
+
+
+def _lazy(self, h, delta, out_dtype):
+    """The norm of h (+ delta, added now), to be computed by whoever consumes it."""
+    if delta is not None:
+        ops.residual_add(h, delta)
+    return ops.NormedRows(h, self.gain, self.eps, out_dtype)
+
+
+RMSNorm.lazy = _lazy

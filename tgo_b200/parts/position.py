@@ -26,14 +26,25 @@ class RopeHalfSplit(Part):
         i = torch.arange(rot // 2, dtype=torch.float64)
         self.inv_freq = (self.theta ** (-2.0 * i / rot)).to(device)
 
-    def rotary(self):
-        """(inv_freq, rotary_dim): lets a mixer fuse the rotation into its own kernel."""
-        return self.inv_freq, self.rotary_dim
+        self._key = ("rope_table", rot, self.theta)
 
-    def apply(self, q, k, positions, num_heads, num_kv_heads, head_dim):
+    def table(self, ctx):
+        """Cosines and sines of this step's positions, made once per step and shared by
+        every layer with the same rotary_dim and theta."""
+        got = ctx.aux.get(self._key)
+        if got is None:
+            got = ops.rope_table(ctx.positions, self.inv_freq)
+            ctx.aux[self._key] = got
+        return got
+
+    def rotary(self, ctx):
+        """(table, rotary_dim): lets a mixer do the rotation inside its own kernel."""
+        return self.table(ctx), self.rotary_dim
+
+    def apply(self, q, k, ctx, num_heads, num_kv_heads, head_dim):
         """Rotate q [T, H*dh] and k [T, Hkv*dh] in place."""
         ops.qk_norm_rope_cache(q, k, None, num_heads, num_kv_heads, head_dim, None, None, 0.0,
-                               positions, self.inv_freq, self.rotary_dim, None, None, None, 0)
+                               self.table(ctx), self.rotary_dim, None, None, None, 0)
 
 
 class NoPosition(Part):
@@ -43,10 +54,10 @@ class NoPosition(Part):
     def __init__(self, spec: PositionSpec, head_dim: int, device):
         pass
 
-    def rotary(self):
+    def rotary(self, ctx):
         return None, 0
 
-    def apply(self, q, k, positions, num_heads, num_kv_heads, head_dim):
+    def apply(self, q, k, ctx, num_heads, num_kv_heads, head_dim):
         pass
 
 
