@@ -136,6 +136,7 @@ class RequestPages:
         self.slot = slot
         self.length = 0                      # tokens whose keys and values are in the cache
         self.tables: List[List[int]] = [[] for _ in range(n_groups)]
+        self.version = 0                     # bumped whenever a table changes
 
     def held(self, group: int) -> List[int]:
         return [p for p in self.tables[group] if p != NULL_PAGE]
@@ -169,9 +170,11 @@ class CacheManager:
 
     def _missing(self, req: RequestPages, g: int, upto: int) -> List[int]:
         """Logical pages of group g that positions [first live, upto) need and lack."""
-        first = self.groups[g].first_live_position(req.length) // self.page_size
         last = self.pages_for(upto)
         table = req.tables[g]
+        if self.groups[g].kind == "full":        # no holes: only the tail can be missing
+            return list(range(len(table), last))
+        first = self.groups[g].first_live_position(req.length) // self.page_size
         return [i for i in range(first, last) if i >= len(table) or table[i] == NULL_PAGE]
 
     def can_hold(self, n_tokens: int) -> bool:
@@ -215,12 +218,15 @@ class CacheManager:
                 raise PagesExhausted(g, len(missing), self.pools[g].free_count)
             plan.append((g, missing))
         for g, missing in plan:
+            if not missing:
+                continue
             pages = self.pools[g].take(len(missing))
             table = req.tables[g]
             for i, p in zip(missing, pages):
                 while len(table) <= i:
                     table.append(NULL_PAGE)
                 table[i] = p
+            req.version += 1
 
     def commit(self, request_id, new_length: int) -> List[tuple]:
         """The step landed: the request now holds `new_length` tokens. Pages that lie
@@ -244,6 +250,7 @@ class CacheManager:
             if gone:
                 self.pools[g].give(gone)
                 released += [(g, p) for p in gone]
+                req.version += 1
         return released
 
     def finish(self, request_id) -> List[tuple]:

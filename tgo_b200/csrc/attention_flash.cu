@@ -288,7 +288,8 @@ flash_paged_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restr
 // CTA and warp w takes its keys 16w .. 16w+15, keeping its own maximum, sum and O. At the
 // end the four partial states are joined through shared memory in warp order. With
 // n_splits > 1 the CTA covers one range of the request's key tiles and writes a partial
-// state for flash_combine_kernel.
+// state for flash_combine_kernel. (Joining the splits inside this kernel, by letting the
+// last CTA to finish do it, was measured slower than the separate small kernel.)
 template <int DH>
 __global__ void __launch_bounds__(128)
 flash_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
@@ -297,13 +298,11 @@ flash_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
                     const int* __restrict__ block_tables, int max_blocks,
                     const int* __restrict__ positions, const int* __restrict__ seq_ids, int H,
                     int Hkv, float scale_log2, int window, int n_splits,
-                    float* __restrict__ part_o, float* __restrict__ part_ml,
-                    int* __restrict__ counters, int pages_cap) {
+                    float* __restrict__ part_o, float* __restrict__ part_ml, int pages_cap) {
     constexpr int LD = DH + FL_PAD;
     constexpr int KS = DH / 16;
     constexpr int CH = DH / 8;
     constexpr int ROWS_PER_IT = 128 / CH;
-    __shared__ int s_last;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* sq = (bf16*)smem_raw;                // [16][LD]
     bf16* sk = sq + 16 * LD;                   // [2][64][LD]
@@ -320,7 +319,7 @@ flash_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
         if (split == 0)
             for (int i = tid; i < G * DH; i += 128)
                 out[(size_t)tok * out_stride + (size_t)(kvh * G) * DH + i] = __float2bfloat16_rn(0.f);
-        if (n_splits > 1 && !counters)
+        if (n_splits > 1)
             for (int r = tid; r < G; r += 128) {
                 const size_t at = ((size_t)tok * H + kvh * G + r) * n_splits + split;
                 part_ml[at * 2] = -INFINITY;
@@ -509,37 +508,6 @@ flash_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
             if (d == 0) { part_ml[at * 2] = m; part_ml[at * 2 + 1] = l; }
         }
     }
-    if (n_splits == 1 || !counters) return;
-    // The CTA that finishes last for this (token, kv head) joins the splits: no CTA waits for
-    // another. The counter goes back to zero for the next launch.
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const int prev = atomicAdd(&counters[tok * Hkv + kvh], 1);
-        s_last = prev == n_splits - 1;
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    for (int i = tid; i < G * DH; i += 128) {
-        const int r = i / DH, d = i % DH;
-        const int head = kvh * G + r;
-        const size_t base = ((size_t)tok * H + head) * n_splits;
-        float m = -INFINITY;
-        for (int sp = 0; sp < n_splits; ++sp) m = fmaxf(m, __ldcg(part_ml + (base + sp) * 2));
-        float l = 0.f, acc = 0.f;
-        for (int sp = 0; sp < n_splits; ++sp) {
-            const float ms = __ldcg(part_ml + (base + sp) * 2);
-            if (ms != -INFINITY) {
-                const float f = exp2f(ms - m);
-                l += __ldcg(part_ml + (base + sp) * 2 + 1) * f;
-                acc += __ldcg(part_o + (base + sp) * DH + d) * f;
-            }
-        }
-        out[(size_t)tok * out_stride + (size_t)head * DH + d] =
-            __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
-    }
-    if (tid == 0) counters[tok * Hkv + kvh] = 0;
 }
 
 // out[t, h, :] = sum_s O_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), m = max_s m_s.
@@ -596,8 +564,7 @@ static int decode_launch(const bf16* q, long long q_stride, bf16* out, long long
                          const bf16* k_cache, const bf16* v_cache, int page_size,
                          const int* block_tables, int max_blocks, const int* positions,
                          const int* seq_ids, int T, int H, int Hkv, float scale, int window,
-                         int n_splits, float* part_o, float* part_ml, int* counters,
-                         cudaStream_t stream) {
+                         int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
     constexpr int LD = DH + FL_PAD;
     size_t smem = (size_t)(16 + 4 * FL_BN) * LD * sizeof(bf16);
     const size_t merge = (size_t)4 * 16 * DH * sizeof(float) + (size_t)16 * LD * sizeof(bf16);
@@ -614,7 +581,7 @@ static int decode_launch(const bf16* q, long long q_stride, bf16* out, long long
     return tgo_launch_pdl(kern, dim3(T, Hkv, n_splits), dim3(128), smem, stream, q, q_stride, out,
                           out_stride, k_cache, v_cache, page_size, shift, block_tables, max_blocks,
                           positions, seq_ids, H, Hkv, scale * 1.4426950408889634f, window, n_splits,
-                          part_o, part_ml, counters, pages_cap);
+                          part_o, part_ml, pages_cap);
 }
 
 // head sizes with a tensor-core instance; others are refused and the caller falls back
@@ -628,7 +595,7 @@ TGO_API int tgo_attention_flash(const void* q, long long q_stride, void* out, lo
                                 const int* seq_ids, const int* tile_tok0, const int* tile_ntok,
                                 int n_tiles, int H, int Hkv, int dh, float scale, int window,
                                 int wide, int n_splits, float* part_o, float* part_ml,
-                                int* counters, cudaStream_t stream) {
+                                cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv || !tgo_attention_flash_supports(dh, H / Hkv) ||
         page_size <= 0 || max_blocks <= 0 || window < 0 || n_splits < 1 || Hkv > 65535 ||
@@ -654,7 +621,7 @@ TGO_API int tgo_attention_flash(const void* q, long long q_stride, void* out, lo
         return decode_launch<D>((const bf16*)q, q_stride, (bf16*)out, out_stride,                  \
                                 (const bf16*)k_cache, (const bf16*)v_cache, page_size, block_tables, \
                                 max_blocks, positions, seq_ids, n_tiles, H, Hkv, scale, window,    \
-                                n_splits, part_o, part_ml, counters, stream);
+                                n_splits, part_o, part_ml, stream);
         switch (dh) {
             FD_CASE(16)
             FD_CASE(32)

@@ -12,6 +12,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache.pages import NULL_PAGE, CacheManager
@@ -90,61 +91,106 @@ class Engine:
                     raise ValueError(f"step: request {e.request_id!r} wants the logits of "
                                      f"place {w} among {len(e.tokens)} tokens")
 
+    def _table_array(self, req, g):
+        """A request's block table of group g as an int32 array, rebuilt only when it changed."""
+        cache = req.__dict__.setdefault("_np_tables", {})
+        got = cache.get(g)
+        if got is None or got[0] != req.version:
+            got = (req.version, np.asarray(req.tables[g], dtype=np.int32))
+            cache[g] = got
+        return got[1]
+
     def _pack(self, entries: List[StepEntry], pad_to: int = 0, width_quantum: int = 1,
-              all_rows: bool = False):
-        """Host lists of one step, laid out as one flat int32 array:
+              all_rows: bool = False, out: Optional[np.ndarray] = None):
+        """Host data of one step, laid out as one flat int32 array:
         ids[T] pos[T] seq[T] q_start[B+1] ctx[B] state_slot[B] rows[n] then, per group,
         slots[T] table[B*width]. With pad_to > B, requests that bring nothing fill the batch:
-        one token each at position -1 (the kernels read and write nothing for it)."""
+        one token each at position -1 (the kernels read and write nothing for it).
+        Written into `out` if it is given and large enough."""
         cm = self.cache
+        ps = self.page_size
         reqs = [cm.requests[e.request_id] for e in entries]
-        ids, pos, seq, q_start, ctx_lens, slots_state, rows = [], [], [], [0], [], [], []
-        extents, firsts = [], []
-        for b, (e, r) in enumerate(zip(entries, reqs)):
-            n = len(e.tokens)
-            base = len(ids)
-            ids += [int(t) for t in e.tokens]
-            pos += list(range(r.length, r.length + n))
-            seq += [b] * n
-            q_start.append(base + n)
-            ctx_lens.append(r.length + n)
-            slots_state.append(r.slot)
-            rows += [base + int(w) for w in e.want]
-            extents.append(n)
-            firsts.append(r.length)
-        n_pad = max(0, pad_to - len(entries))
-        for k in range(n_pad):
-            ids.append(0)
-            pos.append(-1)
-            seq.append(len(entries) + k)
-            q_start.append(len(ids))
-            ctx_lens.append(0)
-            slots_state.append(-1)
-        T, B = len(ids), len(entries) + n_pad
+        n_real = len(entries)
+        extents = [len(e.tokens) for e in entries]
+        firsts = [r.length for r in reqs]
+        n_pad = max(0, pad_to - n_real)
+        B = n_real + n_pad
+        T = sum(extents) + n_pad
+        rows = []
         if all_rows:
-            rows = list(range(T))
-        group_slots, group_tables, widths = [], [], []
-        for g in range(len(cm.groups)):
-            sl = []
-            for e, r in zip(entries, reqs):
-                for p in range(r.length, r.length + len(e.tokens)):
-                    sl.append(cm.slot_of(r, g, p))
-            sl += [-1] * n_pad
-            group_slots.append(sl)
+            n_rows = T
+        else:
+            base = 0
+            for e, n in zip(entries, extents):
+                rows += [base + int(w) for w in e.want]
+                base += n
+            n_rows = len(rows)
+        n_groups = len(cm.groups)
+        widths = []
+        for g in range(n_groups):
             width = max(1, max(len(r.tables[g]) for r in reqs))
-            width = (width + width_quantum - 1) // width_quantum * width_quantum
-            widths.append(width)
-            tb = []
-            for r in reqs:
-                tb += r.tables[g] + [NULL_PAGE] * (width - len(r.tables[g]))
-            tb += [NULL_PAGE] * (width * n_pad)
-            group_tables.append(tb)
-        flat = ids + pos + seq + q_start + ctx_lens + slots_state + rows
-        for sl, tb in zip(group_slots, group_tables):
-            flat += sl + tb
-        meta = dict(T=T, B=B, n_rows=len(rows), widths=widths, extents=extents, firsts=firsts,
-                    max_context=max(ctx_lens))
-        return flat, meta
+            widths.append((width + width_quantum - 1) // width_quantum * width_quantum)
+        total = 3 * T + (B + 1) + 2 * B + n_rows + sum(T + B * w for w in widths)
+        buf = out if out is not None and out.size >= total else np.empty(total, dtype=np.int32)
+        ids, pos, seq = buf[0:T], buf[T:2 * T], buf[2 * T:3 * T]
+        o = 3 * T
+        q_start = buf[o:o + B + 1]
+        o += B + 1
+        ctx_lens = buf[o:o + B]
+        o += B
+        st_slots = buf[o:o + B]
+        o += B
+        rows_v = buf[o:o + n_rows]
+        o += n_rows
+        ext = np.asarray(extents, dtype=np.int64)
+        fst = np.asarray(firsts, dtype=np.int64)
+        starts = np.zeros(n_real + 1, dtype=np.int64)
+        np.cumsum(ext, out=starts[1:])
+        n_tok = int(starts[-1])
+        if n_tok == n_real:                      # every request brings one token
+            ids[:n_real] = [e.tokens[0] for e in entries]
+            pos[:n_real] = fst
+            seq[:n_real] = np.arange(n_real)
+        else:
+            for b, e in enumerate(entries):
+                a, z = int(starts[b]), int(starts[b + 1])
+                ids[a:z] = e.tokens
+                pos[a:z] = np.arange(firsts[b], firsts[b] + extents[b])
+                seq[a:z] = b
+        q_start[:n_real + 1] = starts
+        ctx_lens[:n_real] = fst + ext
+        st_slots[:n_real] = [r.slot for r in reqs]
+        if n_pad:
+            ids[n_tok:] = 0
+            pos[n_tok:] = -1
+            seq[n_tok:] = np.arange(n_real, B)
+            q_start[n_real + 1:] = n_tok + 1 + np.arange(n_pad)
+            ctx_lens[n_real:] = 0
+            st_slots[n_real:] = -1
+        rows_v[:] = np.arange(T) if all_rows else rows
+        token_pos = pos[:n_tok].astype(np.int64)
+        for g in range(n_groups):
+            width = widths[g]
+            slots = buf[o:o + T]
+            o += T
+            table = buf[o:o + B * width].reshape(B, width)
+            o += B * width
+            table[:] = NULL_PAGE
+            for b, r in enumerate(reqs):
+                arr = self._table_array(r, g)
+                table[b, :arr.size] = arr
+            tok_seq = seq[:n_tok].astype(np.int64)
+            pages = table[tok_seq, token_pos // ps]
+            if (pages == NULL_PAGE).any():
+                bad = int(np.argmax(pages == NULL_PAGE))
+                raise ValueError(f"cache: position {int(token_pos[bad])} of request "
+                                 f"{entries[int(tok_seq[bad])].request_id!r} has no page in "
+                                 f"group {g}")
+            slots[:n_tok] = pages.astype(np.int64) * ps + token_pos % ps
+            slots[n_tok:] = -1
+        meta = dict(T=T, B=B, n_rows=n_rows, widths=widths, extents=extents, firsts=firsts,
+                    max_context=int(ctx_lens[:n_real].max()), total=total)
+        return buf, meta
 
     def _views(self, dev: torch.Tensor, meta: dict):
         """Device views into a flat buffer laid out by `_pack`."""
@@ -172,11 +218,11 @@ class Engine:
     def build_context(self, entries: List[StepEntry]):
         """Host lists -> one pinned buffer -> one copy -> device views."""
         flat, meta = self._pack(entries)
-        host = torch.tensor(flat, dtype=torch.int32)
+        host = torch.from_numpy(flat[:meta["total"]])
         if self.device.type == "cuda":
             host = host.pin_memory()
         dev = host.to(self.device, non_blocking=True)
-        self.h2d_bytes_last = len(flat) * 4
+        self.h2d_bytes_last = meta["total"] * 4
         return self._views(dev, meta)
 
     def step(self, entries: List[StepEntry]) -> torch.Tensor:
@@ -211,17 +257,23 @@ class Engine:
         valid until the next step of the same bucket."""
         B = len(entries)
         bucket = next((b for b in self.BUCKETS if b >= B), B)
-        flat, meta = self._pack(entries, pad_to=bucket, width_quantum=self.WIDTH_QUANTUM,
-                                all_rows=True)
-        key = (bucket, tuple(meta["widths"]))
+        widths = tuple((max(1, max(len(self.cache.requests[e.request_id].tables[g])
+                                   for e in entries)) + self.WIDTH_QUANTUM - 1)
+                       // self.WIDTH_QUANTUM * self.WIDTH_QUANTUM
+                       for g in range(len(self.cache.groups)))
+        key = (bucket, widths)
         entry = self._graphs.get(key)
         if entry is None:
+            flat, meta = self._pack(entries, pad_to=bucket, width_quantum=self.WIDTH_QUANTUM,
+                                    all_rows=True)
             entry = self._capture(flat, meta)
             self._graphs[key] = entry
         graph, host, dev, logits, launches = entry
-        host.copy_(torch.tensor(flat, dtype=torch.int32))
+        # straight into the graph's pinned buffer, then one copy
+        _, meta = self._pack(entries, pad_to=bucket, width_quantum=self.WIDTH_QUANTUM,
+                             all_rows=True, out=host.numpy())
         dev.copy_(host, non_blocking=True)
-        self.h2d_bytes_last = len(flat) * 4
+        self.h2d_bytes_last = meta["total"] * 4
         graph.replay()
         ops.LAUNCHES[0] += launches
         want = [b for b, e in enumerate(entries) for _ in e.want]
@@ -232,8 +284,8 @@ class Engine:
         return logits[torch.tensor(want, device=self.device)]
 
     def _capture(self, flat, meta):
-        host = torch.tensor(flat, dtype=torch.int32).pin_memory()
-        dev = torch.empty(len(flat), dtype=torch.int32, device=self.device)
+        host = torch.from_numpy(flat[:meta["total"]].copy()).pin_memory()
+        dev = torch.empty(meta["total"], dtype=torch.int32, device=self.device)
         dev.copy_(host)
         meta = dict(meta)
         meta["max_context"] = max(meta["widths"]) * self.page_size if meta["widths"] else 0

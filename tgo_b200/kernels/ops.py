@@ -321,7 +321,6 @@ def gated_linear(x, w_gate_up: torch.Tensor, interleaved: bool) -> torch.Tensor:
 
 
 NUM_SMS = 148
-FUSED_JOIN = False
 
 
 def flash_supports(head_dim: int, group: int) -> bool:
@@ -347,23 +346,20 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
     assert q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 2 == 0
     assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
     n_tiles = T if tile_tok0 is None else tile_tok0.numel()
-    part_o = part_ml = counters = None
-    decode = tile_tok0 is None and not wide
+    part_o = part_ml = None
     if n_splits > 1:
         part_o = torch.empty((T, num_heads, n_splits, head_dim), dtype=torch.float32,
                              device=q.device)
         part_ml = torch.empty((T, num_heads, n_splits, 2), dtype=torch.float32, device=q.device)
-        if decode and FUSED_JOIN:   # the decode kernel joins the splits itself
-            counters = torch.zeros((T, num_kv_heads), dtype=torch.int32, device=q.device)
     lib = load_library("attention_flash")
     _check(lib.tgo_attention_flash(
         _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
         c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(positions),
         _ptr(seq_ids), _ptr(tile_tok0), _ptr(tile_ntok), c_int(n_tiles), c_int(num_heads),
         c_int(num_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(1 if wide else 0),
-        c_int(n_splits), _ptr(part_o), _ptr(part_ml), _ptr(counters), _stream()),
+        c_int(n_splits), _ptr(part_o), _ptr(part_ml), _stream()),
         "attention_flash", f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads})")
-    if n_splits > 1 and counters is None:
+    if n_splits > 1:
         _check(lib.tgo_attention_flash_combine(
             _ptr(part_o), _ptr(part_ml), _ptr(out), c_ll(out.stride(0)), c_int(T),
             c_int(num_heads), c_int(head_dim), c_int(n_splits), _stream()),
