@@ -1,0 +1,180 @@
+"""The engine's host side without a GPU: batch building, block tables, page reuse, windows,
+the scheduler's loop and sampling order, with torch stand-ins for the kernels
+(tests/emulated_kernels.py). Compared with the plain implementation, which shares no code
+with either."""
+import numpy as np
+import pytest
+import torch
+
+import emulated_kernels
+import plain_qwen3 as plain
+import tiny
+
+
+@pytest.fixture()
+def emulated(monkeypatch):
+    emulated_kernels.install(monkeypatch)
+
+
+def cpu_model(model_dir, cfg, dtype=torch.float32):
+    from tgo_b200.api import LoadedModel
+    from tgo_b200.engine.model import Model
+    from tgo_b200.registry import model_spec_from_config
+    from tgo_b200.weights.binder import load_weights
+    from tgo_b200.weights.safetensors import SafetensorsRepo
+    model = Model(model_spec_from_config(cfg), dtype, "cpu")
+    model.bind(load_weights(model.weight_specs(), SafetensorsRepo(model_dir), dtype, "cpu",
+                            model.tied_alias()))
+    return LoadedModel(model, cfg, model_dir)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_every_cutting_matches_plain(emulated, tmp_path, name):
+    cfg, run = tiny.TINIES[name]
+    d = tiny.make_model_dir(tmp_path / name, cfg, run["seed"], run["sigma"])
+    reqs = tiny.random_requests(cfg["vocab_size"], [5, 33, 70, 41], seed=2)
+    want = tiny.plain_logits(d, reqs)
+    loaded = cpu_model(d, cfg)
+    base = None
+    for fam in (tiny.trace_whole, tiny.trace_tail, tiny.trace_portions, tiny.trace_mixed):
+        trace = fam(reqs)
+        eng = loaded.new_engine(page_size=run["page_size"], max_tokens=tiny.max_tokens_of(trace),
+                                num_slots=4)
+        got = tiny.run_trace_engine(eng, trace)
+        worst, where, tol = tiny.compare(got, want, cfg, "float32")
+        assert worst <= tol, (fam.__name__, worst, where)
+        assert all(p.free_count == p.num_pages for p in eng.cache.pools)
+        base = base or got
+        assert set(got) == set(base)
+
+
+def test_step_refuses_bad_batches(emulated, tmp_path):
+    from tgo_b200.engine.step import StepEntry
+    cfg, run = tiny.TINIES["A"]
+    d = tiny.make_model_dir(tmp_path / "a", cfg, run["seed"], run["sigma"])
+    eng = cpu_model(d, cfg).new_engine(page_size=16, max_tokens=64, num_slots=2)
+    eng.admit("a")
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        eng.step([StepEntry("a", [256], [0])])
+    with pytest.raises(ValueError, match="twice"):
+        eng.step([StepEntry("a", [1], [0]), StepEntry("a", [2], [0])])
+    with pytest.raises(KeyError, match="not admitted"):
+        eng.step([StepEntry("b", [1], [0])])
+    with pytest.raises(ValueError, match="no tokens"):
+        eng.step([StepEntry("a", [], [])])
+    with pytest.raises(ValueError, match="place 3"):
+        eng.step([StepEntry("a", [1, 2], [3])])
+    with pytest.raises(ValueError, match="empty batch"):
+        eng.step([])
+    assert eng.length("a") == 0                       # nothing of the refused steps stuck
+    from tgo_b200.cache.pages import PagesExhausted
+    with pytest.raises(PagesExhausted):
+        eng.step([StepEntry("a", list(range(65)), [])])
+    assert eng.length("a") == 0 and eng.cache.pools[0].free_count == 4
+    logits = eng.step([StepEntry("a", [1, 2, 3], [])])
+    assert logits.shape == (0, 256) and eng.length("a") == 3
+
+
+def test_layer_run_twice_and_borrowed_cache(emulated, tmp_path):
+    """The run order is data: a layer named twice shares weights and owns two caches; a call
+    may read an earlier call's cache instead of writing its own."""
+    from tgo_b200.config.spec import LayerCall
+    from tgo_b200.engine.model import Model
+    from tgo_b200.engine.step import Engine, StepEntry
+    from tgo_b200.registry import model_spec_from_config
+    from tgo_b200.weights.binder import load_weights
+    from tgo_b200.weights.safetensors import SafetensorsRepo
+    cfg, run = tiny.TINIES["A"]
+    d = tiny.make_model_dir(tmp_path / "a", cfg, run["seed"], 0.2)
+    spec = model_spec_from_config(cfg)
+    spec.run_order = [LayerCall(0), LayerCall(1), LayerCall(0), LayerCall(1, cache_from=1)]
+    model = Model(spec, torch.float32, "cpu")
+    model.bind(load_weights(model.weight_specs(), SafetensorsRepo(d), torch.float32, "cpu",
+                            model.tied_alias()))
+    assert [len(g.calls) for g in model.groups] == [3]          # calls 0, 1, 2 own a cache
+    pc, pw = plain.load_model_dir(d)
+    toks = tiny.random_requests(256, [23], seed=5)["r0"]
+
+    def reference(tokens):
+        eps, T = pc["rms_norm_eps"], len(tokens)
+        pos = np.arange(T)
+        h = plain.embedding(pw["model.embed_tokens.weight"], tokens)
+        kv1 = None
+        for call, layer in enumerate([0, 1, 0, 1]):
+            p = f"model.layers.{layer}."
+            n = plain.rmsnorm(h, pw[p + "input_layernorm.weight"], eps)
+            H, hkv, dh = 4, 2, 16
+            q = plain.rmsnorm(plain.linear(n, pw[p + "self_attn.q_proj.weight"]).reshape(T, H, dh),
+                              pw[p + "self_attn.q_norm.weight"], eps)
+            q = plain.rope_half_split(q, pos, pc["rope_theta"])
+            if call == 3:
+                k, v = kv1
+            else:
+                k = plain.rmsnorm(plain.linear(n, pw[p + "self_attn.k_proj.weight"]).reshape(T, hkv, dh),
+                                  pw[p + "self_attn.k_norm.weight"], eps)
+                k = plain.rope_half_split(k, pos, pc["rope_theta"])
+                v = plain.linear(n, pw[p + "self_attn.v_proj.weight"]).reshape(T, hkv, dh)
+                if call == 1:
+                    kv1 = (k, v)
+            a = plain.causal_gqa_attention(q, k, v, 0.25).reshape(T, H * dh)
+            h = h + plain.linear(a, pw[p + "self_attn.o_proj.weight"])
+            n = plain.rmsnorm(h, pw[p + "post_attention_layernorm.weight"], eps)
+            h = h + plain.swiglu_mlp(n, pw[p + "mlp.gate_proj.weight"], pw[p + "mlp.up_proj.weight"],
+                                     pw[p + "mlp.down_proj.weight"])
+        return plain.linear(plain.rmsnorm(h, pw["model.norm.weight"], eps),
+                            pw["model.embed_tokens.weight"])
+    want = reference(toks)
+    eng = Engine(model, page_size=8, max_tokens=64, num_slots=1)
+    eng.admit("x")
+    got = torch.cat([eng.step([StepEntry("x", toks[:9], list(range(9)))]),
+                     eng.step([StepEntry("x", toks[9:], list(range(14)))])]).numpy()
+    assert np.abs(got - want).max() < 1e-4 * max(1, np.abs(want).max())
+
+
+def test_generate_greedy_and_seeded_sampling(emulated, tmp_path):
+    from tgo_b200.sampling.policy import DrawStream, Policy
+    cfg, run = tiny.TINIES["B"]
+    d = tiny.make_model_dir(tmp_path / "b", cfg, seed=7, sigma=0.25)
+    loaded = cpu_model(d, cfg)
+    pc, pw = plain.load_model_dir(d)
+    prompts = list(tiny.random_requests(384, [1, 9, 40], seed=4).values())
+    out = loaded.generate(prompts, Policy(max_tokens=6), slots=2, chunk=16, page_size=8)
+    for p, o in zip(prompts, out):
+        assert o == plain.greedy_generate(pc, pw, p, 6)
+    assert len({tuple(o) for o in out}) > 1 and len(set(out[2])) > 1     # not a degenerate model
+    # temperature 0.8, seeded: the same draws walk the plain distribution to the same tokens
+    pol = Policy(temperature=0.8, seed=11, max_tokens=5)
+    got = loaded.generate(prompts[:2], pol, slots=2, chunk=16, page_size=8)
+    again = loaded.generate(prompts[:2], pol, slots=1, chunk=5, page_size=8)
+    assert got == again                                   # batching does not change the stream
+    for p, o in zip(prompts[:2], got):
+        draws, seq = DrawStream(11), list(p)
+        for tok in o:
+            logits = plain.forward(pc, pw, seq)[-1].astype(np.float32)
+            ids, w, total = plain.policy_distribution(logits, temperature=0.8)
+            assert tok == plain.walk(ids, w, total, draws.next())
+            seq.append(tok)
+
+
+def test_session_and_context_limits(emulated, tmp_path):
+    from tgo_b200.engine.session import ContextExhausted
+    from tgo_b200.sampling.policy import Policy
+    cfg, run = tiny.TINIES["A"]
+    d = tiny.make_model_dir(tmp_path / "a", cfg, run["seed"], 0.2)
+    loaded = cpu_model(d, cfg)
+    pc, pw = plain.load_model_dir(d)
+    s = loaded.new_session(context=48, page_size=16, chunk=7)
+    prompt = tiny.random_requests(256, [20], seed=1)["r0"]
+    assert list(s.complete(prompt, Policy(max_tokens=5))) == plain.greedy_generate(pc, pw, prompt, 5)
+    assert s.usage == {"prompt_tokens": 20, "completion_tokens": 5}
+    assert list(s.complete(prompt[:3], Policy(max_tokens=2))) == plain.greedy_generate(pc, pw, prompt[:3], 2)
+    with pytest.raises(ContextExhausted):
+        list(s.complete(list(range(48))))
+    with pytest.raises(ContextExhausted):
+        list(s.complete(prompt, Policy(max_tokens=40)))
+    with pytest.raises(ValueError, match="empty"):
+        list(s.complete([]))
+    assert s.engine.cache.pools[0].free_count == 3
+    stop = plain.greedy_generate(pc, pw, prompt, 3)[2]
+    s2 = loaded.new_session(context=48, stop_ids=[stop])
+    assert len(list(s2.complete(prompt, Policy(max_tokens=5)))) <= 2

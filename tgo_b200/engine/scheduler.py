@@ -61,14 +61,18 @@ def next_step(slots: Sequence[SlotState], chunk: int, budget: int) -> List[Work]
 
     Pass 1: every live slot still in its prompt brings min(chunk, what is left of the
     prompt, what is left of the budget), in slot order. Pass 2: every slot past its
-    prompt brings its one fed token while the budget lasts. A slot left out just waits.
-    The result is in slot order.
+    prompt brings its one fed token. A slot left out just waits. The result is in slot
+    order. Unlike the reference, whose budget is the whole pool and never binds, the
+    budget here is a real limit on a step's tokens, so one token is set aside for every
+    decoding slot before the prompts share the rest: a long prompt cannot stall the
+    requests that are already producing.
     """
     if chunk <= 0:
         raise ValueError(f"scheduler: the prefill chunk is {chunk}; a chunk is at least one token")
     if budget <= 0:
         raise ValueError(f"scheduler: a step of {budget} tokens carries nothing")
-    work, left = [], budget
+    decoders = sum(1 for s in slots if s.live and not s.in_prompt() and s.feed is not None)
+    work, left = [], max(budget - decoders, 0)
     for i, s in enumerate(slots):
         if not s.live or not s.in_prompt():
             continue
@@ -77,6 +81,7 @@ def next_step(slots: Sequence[SlotState], chunk: int, budget: int) -> List[Work]
             continue
         work.append(Work(i, s.prompt[s.prefilled:s.prefilled + n], True))
         left -= n
+    left += min(decoders, budget)
     for i, s in enumerate(slots):
         if not s.live or s.in_prompt() or s.feed is None or left <= 0:
             continue
@@ -136,7 +141,7 @@ class Scheduler:
         self.engine = engine
         self.chunk = chunk or DEFAULT_CHUNK
         self.reserve = reserve
-        self.budget = max_batched_tokens or max(self.chunk, slots)
+        self.budget = max_batched_tokens or (self.chunk + slots)
         self.slots = [SlotState() for _ in range(slots)]
         self._arrivals = 0
         self._ids = 0
