@@ -1,0 +1,340 @@
+"""Each part alone on the GPU against the plain implementation, and parts defined here, in
+the test, registered, built and stepped without a change to the package: a mixer with state
+of its own, and a position encoding the attention kernel does not know."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import tiny
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return (3e-2 if dtype == torch.bfloat16 else 2e-5) * max(1.0, scale)
+
+
+def rnd(*shape, scale=1.0, seed=0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def bf16_exact(t):
+    return t.to(torch.bfloat16).float()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_part(dtype):
+    from tgo_b200.config.spec import NormSpec
+    from tgo_b200.parts.norm import RMSNorm
+    d, eps = 200, 1e-5
+    part = RMSNorm(NormSpec("rmsnorm", eps), d, "n.weight")
+    assert [(w.name, w.shape, w.role) for w in part.weight_specs()] == [("n.weight", (d,), "gain")]
+    gain = 1 + 0.1 * rnd(d, seed=1)
+    part.bind({"n.weight": gain.to(DEV)})
+    h, delta = rnd(7, d, seed=2), bf16_exact(rnd(7, d, seed=3))
+    hd = h.to(DEV)
+    out = part.forward(hd, delta.to(dtype).to(DEV), dtype)
+    want = plain.rmsnorm((h + delta).double().numpy(), gain.double().numpy(), eps)
+    assert np.abs(out.float().cpu().numpy() - want).max() < tol(dtype, np.abs(want).max())
+    assert torch.allclose(hd.cpu(), h + delta, atol=1e-6)          # the add stays in the stream
+    lazy = part.lazy(hd, None, dtype)
+    assert torch.equal(lazy.materialize(), part.forward(hd, None, dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dh,rot", [(16, 16), (64, 32), (96, 96)])
+def test_rope_part(dtype, dh, rot):
+    from tgo_b200.config.spec import PositionSpec
+    from tgo_b200.parts.base import StepContext
+    from tgo_b200.parts.position import RopeHalfSplit
+    H, Hkv, T, theta = 3, 1, 6, 12345.0
+    part = RopeHalfSplit(PositionSpec("rope_half_split", rot, theta), dh, DEV)
+    pos = torch.tensor([0, 1, 5, 77, 300, 4095], dtype=torch.int32, device=DEV)
+    q, k = bf16_exact(rnd(T, H * dh, seed=1)), bf16_exact(rnd(T, Hkv * dh, seed=2))
+    qd, kd = q.to(dtype).to(DEV), k.to(dtype).to(DEV)
+    ctx = StepContext(T, 1, pos, pos, pos, pos, pos, pos, pos, dtype)
+    part.apply(qd, kd, ctx, H, Hkv, dh)
+    wq = plain.rope_half_split(q.double().numpy().reshape(T, H, dh), pos.cpu().numpy(), theta, rot)
+    wk = plain.rope_half_split(k.double().numpy().reshape(T, Hkv, dh), pos.cpu().numpy(), theta, rot)
+    assert np.abs(qd.float().cpu().numpy().reshape(T, H, dh) - wq).max() < tol(dtype, 3)
+    assert np.abs(kd.float().cpu().numpy().reshape(T, Hkv, dh) - wk).max() < tol(dtype, 3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T", [3, 150])
+@pytest.mark.parametrize("d,f", [(96, 224), (72, 100)])
+def test_swiglu_part(dtype, T, d, f):
+    from tgo_b200.config.spec import FeedForwardSpec
+    from tgo_b200.parts.feed_forward import SwiGLU
+    part = SwiGLU(FeedForwardSpec("swiglu", f), d, "mlp.")
+    assert {w.name: w.shape for w in part.weight_specs()} == {
+        "mlp.gate_proj.weight": (f, d), "mlp.up_proj.weight": (f, d), "mlp.down_proj.weight": (d, f)}
+    w = {n: bf16_exact(rnd(*s.shape, scale=0.2, seed=i)) for i, (n, s) in
+         enumerate((s.name, s) for s in part.weight_specs())}
+    part.bind({n: t.to(dtype).to(DEV) for n, t in w.items()})
+    assert part.interleaved == (f % 8 == 0)
+    x = bf16_exact(rnd(T, d, seed=9))
+    want = plain.swiglu_mlp(x.double().numpy(), *(w[f"mlp.{n}_proj.weight"].double().numpy()
+                                                  for n in ("gate", "up", "down")))
+    out = part.forward(x.to(dtype).to(DEV), None)
+    assert np.abs(out.float().cpu().numpy() - want).max() < tol(dtype, np.abs(want).max())
+    h = rnd(T, d, seed=4).to(DEV)
+    h0 = h.clone()
+    assert part.forward(x.to(dtype).to(DEV), None, residual=h) is None
+    assert np.abs((h - h0).cpu().numpy() - want).max() < tol(dtype, np.abs(want).max())
+
+
+def attention_setup(dtype, window, H=6, Hkv=2, dh=32, d=96, theta=1e4, eps=1e-5):
+    from tgo_b200.config.spec import MixerSpec, PositionSpec
+    from tgo_b200.parts.attention import GQAAttention
+    spec = MixerSpec("gqa_attention", H, Hkv, dh, qk_norm=True, window=window,
+                     position=PositionSpec("rope_half_split", dh, theta), norm_eps=eps)
+    part = GQAAttention(spec, d, "a.", DEV)
+    w = {}
+    for i, s in enumerate(part.weight_specs()):
+        t = rnd(*s.shape, scale=0.15, seed=20 + i)
+        w[s.name] = bf16_exact(1 + t if s.role == "gain" else t)
+    part.bind({n: (t if n.endswith("norm.weight") else t.to(dtype)).to(DEV) for n, t in w.items()})
+    cfg = dict(num_attention_heads=H, num_key_value_heads=Hkv, head_dim=dh, hidden_size=d,
+               rms_norm_eps=eps, rope_theta=theta)
+    return part, w, cfg
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [None, 20])
+def test_attention_part_whole_and_in_portions(dtype, window):
+    """The mixer alone over its own little cache: one request whole, then the same request in
+    portions beside another request's single tokens."""
+    from tgo_b200.parts.base import CacheNeed, LayerCache, StepContext
+    part, w, cfg = attention_setup(dtype, window)
+    assert part.cache_need() == CacheNeed("window" if window else "full", window, 2, 32)
+    assert part.state_need() is None
+    T, ps, d = 45, 8, 96
+    x = bf16_exact(rnd(T, d, seed=3))
+    want = plain.attention_block(x.double().numpy(), np.arange(T),
+                                 {k: v.double().numpy() for k, v in w.items()}, "a.", cfg, window)
+    pages = 16
+    kc = torch.zeros(pages, 2, ps, 32, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    table = torch.tensor([[9, 3, 12, 1, 7, 5], [2, 4, 6, 8, 10, 11]], dtype=torch.int32, device=DEV)
+
+    def step(chunks):
+        """chunks: list of (request, first position, rows of x)."""
+        ids, pos, seq, slots, rows = [], [], [], [], []
+        for b, (req, first, xs) in enumerate(chunks):
+            n = xs.shape[0]
+            pos += list(range(first, first + n))
+            seq += [b] * n
+            slots += [int(table[req, p // ps]) * ps + p % ps for p in range(first, first + n)]
+            rows.append(xs)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)     # noqa: E731
+        n_tok = len(pos)
+        ctx = StepContext(n_tok, len(chunks), i32([0] * n_tok), i32(pos), i32(seq), i32([0]),
+                          i32([0]), i32([0]), i32([0]), dtype, extents=[c[2].shape[0] for c in chunks],
+                          max_context=max(c[1] + c[2].shape[0] for c in chunks),
+                          decode_only=all(c[2].shape[0] == 1 for c in chunks))
+        tb = torch.stack([table[c[0]] for c in chunks]).contiguous()
+        cache = LayerCache(kc, vc, ps, tb, i32(slots), True)
+        out = part.forward(torch.cat(rows).to(dtype).to(DEV), ctx, cache)
+        return out.float().cpu().numpy()
+    got = step([(0, 0, x)])
+    assert np.abs(got - want).max() < tol(dtype, np.abs(want).max())
+    # again in portions of request 1's pages, with request 0 decoding beside it
+    outs, o = [], 0
+    for n in (7, 2, 16, 1, 1, 18):
+        chunk = [(1, o, x[o:o + n])]
+        if o:
+            chunk.append((0, 44, x[44:45]))                   # rewrites its last position
+        outs.append(step(chunk)[:n])
+        o += n
+    assert np.abs(np.concatenate(outs) - want).max() < tol(dtype, np.abs(want).max())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_block_part(dtype, tmp_path):
+    """A whole layer (both norms, mixer, feed-forward, both adds) against the plain layer."""
+    cfg, run = tiny.TINIES["B"]
+    d = tiny.make_model_dir(tmp_path / "b", cfg, 3, 0.1)
+    import tgo_b200
+    from tgo_b200.engine.step import StepEntry
+    model = tgo_b200.open(d, dtype=dtype)
+    pc, pw = plain.load_model_dir(d)
+    toks = tiny.random_requests(384, [30], 1)["r0"]
+    eng = model.new_engine(page_size=8, max_tokens=64, num_slots=1, graphs=False)
+    eng.admit("x")
+    eng.cache.grow("x", 30)
+    ctx, tables, slots = eng.build_context([StepEntry("x", toks, [])])
+    h = torch.tensor(plain.embedding(pw["model.embed_tokens.weight"], toks), dtype=torch.float32,
+                     device=DEV)
+    block = model.model.blocks[1]                              # the layer with the window
+    cache = model.model.layer_cache(1, ctx, eng.storage, tables, slots)
+    h2, pending = block.forward(h.clone(), None, ctx, cache)
+    got = (h2 if pending is None else h2 + pending.float()).cpu().numpy()
+    x = h.double().cpu().numpy()
+    p = "model.layers.1."
+    n = plain.rmsnorm(x, pw[p + "input_layernorm.weight"], pc["rms_norm_eps"])
+    x = x + plain.attention_block(n, np.arange(30), pw, p + "self_attn.", pc, 24)
+    n = plain.rmsnorm(x, pw[p + "post_attention_layernorm.weight"], pc["rms_norm_eps"])
+    x = x + plain.swiglu_mlp(n, pw[p + "mlp.gate_proj.weight"], pw[p + "mlp.up_proj.weight"],
+                             pw[p + "mlp.down_proj.weight"])
+    assert np.abs(got - x).max() < tol(dtype, np.abs(x).max())
+
+
+# ------------------------------------------------------------- parts defined in the test
+
+
+class DecayMixer:
+    """A mixer with fixed-size state of its own and no keys or values: per request
+    s <- decay * s + x_t, y_t = s . W^T, tokens in order. Written with torch on the device
+    (a test part; the package's own mixers use its kernels)."""
+
+    def __init__(self, spec, hidden, prefix, device=None):
+        self.hidden, self.prefix = hidden, prefix
+        self.decay = dict(spec.extra)["decay"]
+        self.w = None
+
+    def weight_specs(self):
+        from tgo_b200.weights.binder import WeightSpec
+        return [WeightSpec(self.prefix + "mix.weight", (self.hidden, self.hidden))]
+
+    def bind(self, weights):
+        self.w = weights.pop(self.prefix + "mix.weight")
+
+    def cache_need(self):
+        return None
+
+    def state_need(self):
+        from tgo_b200.parts.base import StateNeed
+        return StateNeed((self.hidden,))
+
+    def read_state(self, state, slots, b):
+        return state.index_select(0, slots[b:b + 1])[0]        # no trip to the host
+
+    def forward(self, x, ctx, cache):
+        out = torch.empty_like(x)
+        slots = ctx.state_slots.long()
+        base = 0
+        for b, n in enumerate(ctx.extents):
+            s = self.read_state(cache.state, slots, b)
+            for t in range(base, base + n):
+                s = self.decay * s + x[t].float()
+                out[t] = (s @ self.w.float().t()).to(x.dtype)
+            cache.state.index_copy_(0, slots[b:b + 1], s[None])
+            base += n
+        return out
+
+
+class ChattyDecayMixer(DecayMixer):
+    """The same, but it asks the host for the slot number: such a forward cannot be captured
+    as a CUDA graph, and the engine then runs decode steps one launch at a time."""
+
+    def read_state(self, state, slots, b):
+        return state[int(slots[b].item())]
+
+
+class ShiftPosition:
+    """A position encoding the attention kernel does not know: channel 0 of every head of q
+    and k gets + position / 64. Not fusable, so the mixer calls `apply` between its norm
+    and its store."""
+    fusable = False
+
+    def __init__(self, spec, head_dim, device):
+        self.head_dim = head_dim
+
+    def apply(self, q, k, ctx, num_heads, num_kv_heads, head_dim):
+        add = (ctx.positions.float() / 64)[:, None]
+        for t, heads in ((q, num_heads), (k, num_kv_heads)):
+            if t is not None:
+                v = t.view(t.shape[0], heads, head_dim)
+                v[:, :, 0] = (v[:, :, 0].float() + add).to(t.dtype)
+
+
+def toy_spec(raw):
+    """config.json -> ModelSpec of a two-layer toy: a decay mixer, then attention with the
+    shift encoding. Nothing of it is a model of anyone's."""
+    from tgo_b200.config.spec import (FeedForwardSpec, LayerCall, LayerSpec, MixerSpec, ModelSpec,
+                                      NormSpec, PositionSpec)
+    d, V = raw["width"], raw["vocab"]
+    norm = NormSpec("rmsnorm", raw["eps"])
+    ffn = FeedForwardSpec("swiglu", raw["inner"])
+    layers = [LayerSpec("prenorm_residual", "layers.0.",
+                        MixerSpec(raw.get("mixer", "test_decay"), extra=(("decay", raw["decay"]),)),
+                        ffn, norm, names=(("mixer", "decay."),)),
+              LayerSpec("prenorm_residual", "layers.1.",
+                        MixerSpec("gqa_attention", 4, 2, 16, qk_norm=True,
+                                  position=PositionSpec("test_shift"), norm_eps=raw["eps"]), ffn, norm)]
+    return ModelSpec("ToyForTests", d, V, layers, [LayerCall(0), LayerCall(1)], norm, "embed.weight",
+                     "norm.weight", None, source=dict(raw))
+
+
+@pytest.fixture()
+def toy_registered():
+    from tgo_b200.registry import ARCHITECTURES, MIXERS, POSITIONS
+    ARCHITECTURES.register("ToyForTests", toy_spec, replace=True)
+    MIXERS.register("test_decay", DecayMixer, replace=True)
+    MIXERS.register("test_chatty_decay", ChattyDecayMixer, replace=True)
+    POSITIONS.register("test_shift", ShiftPosition, replace=True)
+    yield
+    ARCHITECTURES.unregister("ToyForTests")
+    MIXERS.unregister("test_decay")
+    MIXERS.unregister("test_chatty_decay")
+    POSITIONS.unregister("test_shift")
+
+
+def toy_plain(w, raw, toks):
+    eps, T = raw["eps"], len(toks)
+    h = w["embed.weight"][np.asarray(toks)]
+    # layer 0: the decay mixer
+    n = plain.rmsnorm(h, w["layers.0.input_layernorm.weight"], eps)
+    s, ys = np.zeros(raw["width"]), []
+    for t in range(T):
+        s = raw["decay"] * s + n[t]
+        ys.append(s @ w["layers.0.decay.mix.weight"].T)
+    h = h + np.stack(ys)
+    n = plain.rmsnorm(h, w["layers.0.post_attention_layernorm.weight"], eps)
+    h = h + plain.swiglu_mlp(n, w["layers.0.mlp.gate_proj.weight"], w["layers.0.mlp.up_proj.weight"],
+                             w["layers.0.mlp.down_proj.weight"])
+    # layer 1: attention with the shift encoding
+    p = "layers.1.self_attn."
+    n = plain.rmsnorm(h, w["layers.1.input_layernorm.weight"], eps)
+    q = plain.rmsnorm(plain.linear(n, w[p + "q_proj.weight"]).reshape(T, 4, 16), w[p + "q_norm.weight"], eps)
+    k = plain.rmsnorm(plain.linear(n, w[p + "k_proj.weight"]).reshape(T, 2, 16), w[p + "k_norm.weight"], eps)
+    v = plain.linear(n, w[p + "v_proj.weight"]).reshape(T, 2, 16)
+    q[:, :, 0] += np.arange(T)[:, None] / 64
+    k[:, :, 0] += np.arange(T)[:, None] / 64
+    a = plain.causal_gqa_attention(q, k, v, 0.25).reshape(T, 64)
+    h = h + plain.linear(a, w[p + "o_proj.weight"])
+    n = plain.rmsnorm(h, w["layers.1.post_attention_layernorm.weight"], eps)
+    h = h + plain.swiglu_mlp(n, w["layers.1.mlp.gate_proj.weight"], w["layers.1.mlp.up_proj.weight"],
+                             w["layers.1.mlp.down_proj.weight"])
+    return plain.linear(plain.rmsnorm(h, w["norm.weight"], eps), w["embed.weight"])
+
+
+@pytest.mark.parametrize("dtype,mixer", [("float32", "test_decay"), ("bfloat16", "test_decay"),
+                                         ("float32", "test_chatty_decay")])
+def test_toy_parts_are_registered_built_and_stepped(toy_registered, tmp_path, dtype, mixer):
+    import tgo_b200
+    raw = dict(architectures=["ToyForTests"], width=48, vocab=90, inner=80, eps=1e-5, decay=0.75,
+               mixer=mixer)
+    d = tiny.make_model_dir(tmp_path / "toy", raw, seed=2, sigma=0.15)
+    model = tgo_b200.open(d, dtype=dtype)
+    assert model.model.state_shapes == {0: (48,)} and [g.calls for g in model.model.groups] == [[1]]
+    w = plain.read_safetensors(str(tmp_path / "toy" / "model.safetensors"))
+    reqs = tiny.random_requests(90, [40, 3, 21], seed=6)
+    want = {rid: toy_plain(w, raw, toks) for rid, toks in reqs.items()}
+    for fam in (tiny.trace_whole, tiny.trace_tail, tiny.trace_portions, tiny.trace_mixed):
+        trace = fam(reqs)
+        eng = model.new_engine(page_size=8, max_tokens=tiny.max_tokens_of(trace), num_slots=4)
+        got = tiny.run_trace_engine(eng, trace)
+        scale = max(np.abs(v).max() for v in want.values())
+        worst = max(np.abs(row - want[rid][pos]).max() for (rid, pos), row in got.items())
+        assert worst < tol(torch.bfloat16 if dtype == "bfloat16" else torch.float32, scale) * 2, \
+            (fam.__name__, worst)
+        if fam is tiny.trace_tail:             # single-token steps: captured, unless chatty
+            assert eng.use_graphs == (mixer == "test_decay")

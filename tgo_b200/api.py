@@ -73,9 +73,9 @@ class LoadedModel:
                 "source": self.source}
 
     def new_engine(self, page_size: int = 16, max_tokens: Optional[int] = None,
-                   num_pages: Optional[int] = None, num_slots: int = 4):
+                   num_pages: Optional[int] = None, num_slots: int = 4, graphs: bool = True):
         from .engine.step import Engine
-        return Engine(self.model, page_size, max_tokens, num_pages, num_slots)
+        return Engine(self.model, page_size, max_tokens, num_pages, num_slots, graphs)
 
     def new_scheduler(self, slots: int, chunk: int = 0, reserve: int = 512,
                       pool_tokens: Optional[int] = None, page_size: int = 16,

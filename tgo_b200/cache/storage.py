@@ -34,7 +34,8 @@ class CacheStorage:
                 self.where[call] = (g, i)
         self.state: Dict[int, torch.Tensor] = {}
         for call, shape in (state_shapes or {}).items():
-            self.state[call] = torch.zeros((num_slots,) + tuple(shape), dtype=torch.float32,
+            # one row more than there are slots: padded batch rows read and write that one
+            self.state[call] = torch.zeros((num_slots + 1,) + tuple(shape), dtype=torch.float32,
                                            device=device)
 
     def layer(self, call: int):

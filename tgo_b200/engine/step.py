@@ -9,6 +9,7 @@ model/batch.go:66-152 are the reference's descriptor and commit rule).
 """
 from __future__ import annotations
 
+import sys
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -166,7 +167,7 @@ class Engine:
             seq[n_tok:] = np.arange(n_real, B)
             q_start[n_real + 1:] = n_tok + 1 + np.arange(n_pad)
             ctx_lens[n_real:] = 0
-            st_slots[n_real:] = -1
+            st_slots[n_real:] = cm.slots.num_slots      # the spare slot nobody owns
         rows_v[:] = np.arange(T) if all_rows else rows
         token_pos = pos[:n_tok].astype(np.int64)
         for g in range(n_groups):
@@ -266,7 +267,17 @@ class Engine:
         if entry is None:
             flat, meta = self._pack(entries, pad_to=bucket, width_quantum=self.WIDTH_QUANTUM,
                                     all_rows=True)
-            entry = self._capture(flat, meta)
+            try:
+                entry = self._capture(flat, meta)
+            except RuntimeError as e:
+                # a part that talks to the host in its forward (a part from outside the
+                # package may) cannot be captured: run such a model step by step instead
+                print(f"[tgo_b200] decode steps are not captured as graphs: {str(e)[:120]}",
+                      file=sys.stderr)
+                self.use_graphs = False
+                torch.cuda.synchronize(self.device)
+                ctx, tables, slots = self.build_context(entries)
+                return self.model.forward(ctx, self.storage, tables, slots)
             self._graphs[key] = entry
         graph, host, dev, logits, launches = entry
         # straight into the graph's pinned buffer, then one copy
@@ -292,12 +303,16 @@ class Engine:
         ctx, tables, slots = self._views(dev, meta)
         ctx.aux["graph"] = True
         # one eager run first: libraries initialise and kernels compile outside the capture.
-        # The cache rows it writes are the ones the replay writes again.
+        # The cache rows it writes are the ones the replay writes again; fixed-size state is
+        # not idempotent (a mixer advances it), so it is put back afterwards.
+        saved = {call: t.clone() for call, t in self.storage.state.items()}
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
             self.model.forward(ctx, self.storage, tables, slots)
         torch.cuda.current_stream(self.device).wait_stream(side)
+        for call, t in saved.items():
+            self.storage.state[call].copy_(t)
         torch.cuda.synchronize(self.device)
         # what the eager run cached per step (tables made from its inputs) must be made
         # again inside the capture, or the replays would keep reading the first step's
