@@ -650,3 +650,74 @@ TGO_API int tgo_attention_flash_combine(const float* part_o, const float* part_m
                           dim3(dh < 128 ? 32 * ((dh + 31) / 32) : 128), 0, stream, part_o, part_ml,
                           (bf16*)out, out_stride, H, dh, n_splits);
 }
+
+// ------------------------------------------------------------ no-allocation entry point
+// See attention_decode_static.h: the same decode kernels, with the partial outputs of the
+// key splits in an array that is part of the library image instead of caller memory.
+#include "attention_decode_static.h"
+
+#include <mutex>
+
+static __device__ __align__(256) float tgo_decode_static_scratch[TGO_DECODE_STATIC_SCRATCH_FLOATS];
+
+#define TGO_STATIC_MAX_DEVICES 64
+
+// Device address of the array on the current device. In host code the array's name is only
+// a handle for the runtime, not an address a kernel could use; the address comes from
+// cudaGetSymbolAddress, once per device, with that device current.
+static int decode_static_scratch(float** ptr) {
+    static std::mutex lock;
+    static float* known[TGO_STATIC_MAX_DEVICES] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= TGO_STATIC_MAX_DEVICES) return TGO_E_BAD_ARG;
+    std::lock_guard<std::mutex> guard(lock);
+    if (!known[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, tgo_decode_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        known[dev] = (float*)p;
+    }
+    *ptr = known[dev];
+    return 0;
+}
+
+int tgo_attention_decode_static(const void* q, long long q_stride, void* out, long long out_stride,
+                                const void* k_cache, const void* v_cache, int page_size,
+                                const int* block_tables, int max_blocks, const int* positions,
+                                const int* seq_ids, int T, int H, int Hkv, int dh, float scale,
+                                int window, int n_splits, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || Hkv <= 0 || H % Hkv || !tgo_attention_flash_supports(dh, H / Hkv) ||
+        page_size <= 0 || max_blocks <= 0 || window < 0 || n_splits < 1 || n_splits > 65535 ||
+        Hkv > 65535)
+        return TGO_E_BAD_ARG;
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
+    if (n_splits > 1) {
+        const size_t n_o = (size_t)T * H * n_splits * dh, n_ml = (size_t)T * H * n_splits * 2;
+        if (n_o + n_ml > (size_t)TGO_DECODE_STATIC_SCRATCH_FLOATS) return TGO_E_SCRATCH_TOO_SMALL;
+        float* base = nullptr;
+        const int rc = decode_static_scratch(&base);
+        if (rc) return rc;
+        part_o = base;
+        part_ml = base + n_o;
+    }
+    int rc = TGO_E_BAD_ARG;
+#define FS_CASE(D)                                                                                   \
+    case D:                                                                                          \
+        rc = decode_launch<D>((const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_cache, \
+                              (const bf16*)v_cache, page_size, block_tables, max_blocks, positions,  \
+                              seq_ids, T, H, Hkv, scale, window, n_splits, part_o, part_ml, stream); \
+        break;
+    switch (dh) {
+        FS_CASE(16)
+        FS_CASE(32)
+        FS_CASE(64)
+        FS_CASE(128)
+    }
+#undef FS_CASE
+    if (rc || n_splits == 1) return rc;
+    return tgo_attention_flash_combine(part_o, part_ml, out, out_stride, T, H, dh, n_splits, stream);
+}
