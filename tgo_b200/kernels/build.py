@@ -125,6 +125,15 @@ def compile_library(name: str, verbose: bool = True, ptxas_info: bool = False) -
             os.unlink(tmp)
         raise KernelBuildError(f"nvcc failed on {name}:\n{' '.join(cmd)}\n{text}")
     os.replace(tmp, out)
+    # older builds of the same library (other source hashes) are of no use any more
+    prefix = f"libtgo_{name}_"
+    for other in os.listdir(os.path.dirname(out)):
+        if other.startswith(prefix) and other.endswith(".so") and \
+                os.path.join(os.path.dirname(out), other) != out:
+            try:
+                os.unlink(os.path.join(os.path.dirname(out), other))
+            except OSError:
+                pass
     if verbose:
         print(f"[tgo_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s",
               file=sys.stderr, flush=True)
