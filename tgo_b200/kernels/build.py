@@ -33,6 +33,7 @@ LIBRARIES = {
     "attention_flash": (["attention_flash.cu"], []),
     "sgemm": (["sgemm.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
+    "gemm_tc": (["gemm_tc.cu"], []),
     "sampling": (["sampling.cu"], []),
 }
 

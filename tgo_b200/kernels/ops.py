@@ -464,3 +464,43 @@ def logits_adjust(row: torch.Tensor, bias_ids: Optional[torch.Tensor],
                                  _ptr(counts), c_int(ni), c_float(repetition), c_float(presence),
                                  c_float(frequency), c_int(row.numel()), _stream()),
            "logits_adjust")
+
+
+_tc_err = {}
+
+
+def gemm_tc_error_flag(device) -> torch.Tensor:
+    """The int32 flag a tensor-core product sets if one of its waits ran out (0: none;
+    1 producer, 2 issuer, 3 epilogue). One per device, made at first use."""
+    key = torch.device(device).index or 0
+    if key not in _tc_err:
+        _tc_err[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_err[key]
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+            transpose: Optional[bool] = None, splits: int = 1) -> None:
+    """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, float32
+    accumulation in tensor memory, TMA-fed). out: bfloat16 or float32, or float32 that the
+    product is added to. transpose: the weight rows take the 128-wide axis and x (at most
+    256 rows) the other (decode); default: when x has at most 64 rows. splits > 1 cuts K
+    over that many CTAs per tile and adds the float32 partials in order."""
+    _need_cuda(x, w, out)
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+    assert x.is_contiguous() and w.is_contiguous() and out.is_contiguous() and out.shape == (M, N)
+    if accumulate:
+        assert out.dtype == torch.float32
+        omode = 2
+    else:
+        omode = 0 if out.dtype == torch.bfloat16 else 1
+        assert out.dtype in (torch.bfloat16, torch.float32)
+    if transpose is None:
+        transpose = M <= 64
+    ws = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
+    lib = load_library("gemm_tc")
+    _check(lib.tgo_gemm_tc(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_int(omode),
+                           c_int(1 if transpose else 0), c_int(splits), _ptr(ws),
+                           _ptr(gemm_tc_error_flag(x.device)), _stream()), "gemm_tc",
+           f"(M={M}, N={N}, K={K})")
