@@ -471,11 +471,62 @@ def test_gemm_skinny_folds_the_norm(M, N, K):
     assert torch.allclose(y, want, rtol=0, atol=atol)
 
 
-def test_linear_paths_agree():
-    """The same product through the weight-streaming kernel (few rows) and through the
-    library (many rows) differs by bfloat16 rounding only."""
-    w = rnd(300, 256, dtype=torch.bfloat16, scale=0.1, seed=6)
-    x = rnd(100, 256, dtype=torch.bfloat16, seed=7)
+# ------------------------------------------------------------------ tcgen05 product
+
+
+def tc_flag():
+    return int(ops().gemm_tc_error_flag(DEV).item())
+
+
+@pytest.mark.parametrize("M,N,K,transpose,splits", [
+    (128, 128, 64, False, 1), (200, 300, 264, False, 1), (700, 520, 1000, False, 1),
+    (1024, 2048, 4096, False, 1), (300, 512, 2048, False, 3), (8, 128, 64, True, 1),
+    (33, 200, 264, True, 1), (64, 512, 4096, True, 4), (200, 256, 512, True, 1)])
+def test_gemm_tc(M, N, K, transpose, splits):
+    """The tcgen05 kernel in both orientations, with tails in every dimension and K splits."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=M + K)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=N + K)
+    want = x.float() @ w.float().t()
+    atol = 3 * 2.0 ** -8.5 * math.sqrt(K) * 0.1 + 1e-3         # float32 accumulation of exact bf16 products
+    for dt in (torch.float32, torch.bfloat16):
+        out = torch.zeros(M, N, dtype=dt, device=DEV)
+        ops().gemm_tc(x, w, out, transpose=transpose, splits=splits)
+        torch.cuda.synchronize()
+        assert tc_flag() == 0
+        if dt == torch.float32:
+            assert torch.allclose(out, want, rtol=1e-4, atol=1e-3), (M, N, K)
+        else:
+            assert torch.allclose(out.float(), want, rtol=1e-2, atol=atol + 2e-2)
+    h = rnd(M, N, seed=3)
+    h2 = h.clone()
+    ops().gemm_tc(x, w, h2, accumulate=True, transpose=transpose, splits=splits)
+    assert torch.allclose(h2, h + want, rtol=1e-4, atol=1e-3) and tc_flag() == 0
+
+
+@pytest.mark.parametrize("M,f,K,transpose", [(300, 512, 264, False), (1000, 1000, 512, False),
+                                             (24, 256, 512, True), (64, 1008, 264, True)])
+def test_gemm_tc_gated_output(M, f, K, transpose):
+    x = rnd(M, K, dtype=torch.bfloat16, seed=4)
+    wg = rnd(f, K, dtype=torch.bfloat16, scale=0.2, seed=5)
+    wu = rnd(f, K, dtype=torch.bfloat16, scale=0.2, seed=6)
+    g = (x.float() @ wg.float().t()).to(torch.bfloat16).float()
+    u = (x.float() @ wu.float().t()).to(torch.bfloat16).float()
+    want = g / (1 + torch.exp(-g)) * u
+    out = torch.zeros(M, f, dtype=torch.bfloat16, device=DEV)
+    ops().gemm_tc(x, interleave8(wg, wu).contiguous(), out, transpose=transpose, gated=True)
+    torch.cuda.synchronize()
+    assert tc_flag() == 0
+    assert torch.allclose(out.float(), want, rtol=2e-2, atol=2e-2 * float(want.abs().max()))
+
+
+def test_linear_picks_by_rows_and_agrees():
+    """1..8 rows: the weight-streaming kernel; 9..64: the library; more: tcgen05. The same
+    product through each differs by bfloat16 rounding only."""
+    w = rnd(384, 512, dtype=torch.bfloat16, scale=0.1, seed=6)
+    x = rnd(200, 512, dtype=torch.bfloat16, seed=7)
     many = ops().linear(x, w)
+    mid = ops().linear(x[:40].contiguous(), w)
     few = ops().linear(x[:5].contiguous(), w)
+    assert torch.allclose(many[:40].float(), mid.float(), rtol=2e-2, atol=2e-2)
     assert torch.allclose(many[:5].float(), few.float(), rtol=2e-2, atol=2e-2)
+    assert tc_flag() == 0

@@ -309,7 +309,6 @@ flash_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
     bf16* sv = sk + 2 * FL_BN * LD;            // [2][64][LD]
     __shared__ float s_ml[4][16][2];
     pdl_wait();
-    pdl_launch();
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;

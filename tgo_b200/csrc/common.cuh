@@ -62,9 +62,11 @@ static inline int launch_status() { return (int)cudaGetLastError(); }
 // first thing, in every thread, before it reads or writes global memory, so the chain of
 // dependencies stays what stream order would give. TGO_NO_PDL=1 turns the attribute off.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-// Measured on B200: letting dependents launch from the top of a kernel makes a decode step
-// slower (their blocks take the places of this kernel's later blocks); letting them launch
-// once a block has finished its streaming loop is what pdl_launch_late() does.
+// Letting dependents launch from the top of a kernel (pdl_launch) was measured slower on
+// B200 in every variant tried (all kernels; only the small ones): it is compiled out unless
+// TGO_PDL_TRIGGER=1. Kernels that fill the GPU call pdl_launch_late() once a block has
+// finished its streaming loop. What does help: a matrix product issues its first weight
+// loads, which depend on nothing, before its pdl_wait().
 #ifndef TGO_PDL_TRIGGER
 #define TGO_PDL_TRIGGER 0
 #endif

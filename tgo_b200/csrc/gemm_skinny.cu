@@ -69,8 +69,6 @@ gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, f
                    const bf16* __restrict__ w, void* __restrict__ y, int M, int N, int K) {
     __shared__ float red[GS_WARPS][16][MT * 8 + 1];
     __shared__ float red_ss[GS_WARPS][MT * 8];
-    pdl_wait();
-    pdl_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * 16;
@@ -88,14 +86,27 @@ gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, f
 #pragma unroll
     for (int j = 0; j < MT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; ss[j] = 0.f; }
 
-    for (int k = k_begin; k < k_end; k += 32 * GS_UNROLL) {
-        uint4 a_lo[GS_UNROLL], a_hi[GS_UNROLL];
+    // The weights depend on no earlier kernel: the first loads go out before this kernel
+    // waits for the one that makes x, so the stream from HBM is already running when it ends.
+    uint4 a_lo[GS_UNROLL], a_hi[GS_UNROLL];
 #pragma unroll
-        for (int u = 0; u < GS_UNROLL; ++u) {
-            const int kk = k + u * 32 + 8 * t;
-            const bool v = kk < k_end;
-            a_lo[u] = (v && ok_lo) ? ldg_stream(w_lo + kk) : make_uint4(0u, 0u, 0u, 0u);
-            a_hi[u] = (v && ok_hi) ? ldg_stream(w_hi + kk) : make_uint4(0u, 0u, 0u, 0u);
+    for (int u = 0; u < GS_UNROLL; ++u) {
+        const int kk = k_begin + u * 32 + 8 * t;
+        const bool v = kk < k_end;
+        a_lo[u] = (v && ok_lo) ? ldg_stream(w_lo + kk) : make_uint4(0u, 0u, 0u, 0u);
+        a_hi[u] = (v && ok_hi) ? ldg_stream(w_hi + kk) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    pdl_wait();
+
+    for (int k = k_begin; k < k_end; k += 32 * GS_UNROLL) {
+        if (k > k_begin) {
+#pragma unroll
+            for (int u = 0; u < GS_UNROLL; ++u) {
+                const int kk = k + u * 32 + 8 * t;
+                const bool v = kk < k_end;
+                a_lo[u] = (v && ok_lo) ? ldg_stream(w_lo + kk) : make_uint4(0u, 0u, 0u, 0u);
+                a_hi[u] = (v && ok_hi) ? ldg_stream(w_hi + kk) : make_uint4(0u, 0u, 0u, 0u);
+            }
         }
 #pragma unroll
         for (int u = 0; u < GS_UNROLL; ++u) {

@@ -28,12 +28,14 @@
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 192
+#define TC_GROUP_M 16
 #define TC_WAIT_CYCLES 4000000000ll
 
 #define TC_OUT_BF16 0
 #define TC_OUT_F32 1
 #define TC_OUT_ADD_F32 2
 #define TC_OUT_PARTIAL 3      // float32 partial tile of a K split
+#define TC_OUT_SWIGLU 4       // silu(gate) * up of a gate/up matrix interleaved in eights, bfloat16
 
 __device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -98,12 +100,115 @@ struct TcSmem {
     static constexpr int STAGE = A_BYTES + B_BYTES;
     static constexpr int STAGES = (200 * 1024) / STAGE < 8 ? (200 * 1024) / STAGE : 8;
     static constexpr size_t TOTAL = (size_t)STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static_assert(2 * BN <= 512, "two accumulators must fit the 512 columns of tensor memory");
 };
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(bar)) : "memory");
+}
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    g = bf16_round(g);      // as when the product is stored before the gate is applied
+    u = bf16_round(u);
+    return g / (1.f + expf(-g)) * u;
+}
+
+// One thread's 32 consecutive accumulator columns (row `gm` of A, rows gn0.. of B) -> memory.
+template <int OMODE, bool TRANSPOSE>
+__device__ __forceinline__ void tc_store(const uint32_t (&r)[32], void* __restrict__ out, int gm, int gn0,
+                                         int rows_a, int rows_b, long long ld_out, int split) {
+    if (OMODE == TC_OUT_SWIGLU) {
+        if (!TRANSPOSE) {
+            // columns come as 8 gate, 8 up, 8 gate, 8 up: 16 outputs at column gn0 / 2
+            if (gm >= rows_a) return;
+            bf16* dst = (bf16*)out + (size_t)gm * ld_out + gn0 / 2;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (gn0 + 16 * h + 16 > rows_b) break;
+                uint32_t pk[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float a = silu_mul(__uint_as_float(r[16 * h + 2 * j]), __uint_as_float(r[16 * h + 8 + 2 * j]));
+                    const float b = silu_mul(__uint_as_float(r[16 * h + 2 * j + 1]), __uint_as_float(r[16 * h + 9 + 2 * j]));
+                    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+                    pk[j] = *(uint32_t*)&v;
+                }
+                if ((ld_out & 7) == 0) *(uint4*)(dst + 8 * h) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                else
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) *(uint32_t*)(dst + 8 * h + 2 * j) = pk[j];
+            }
+        } else {
+            // rows of A come as 8 gate, 8 up: the up value sits eight lanes further on
+            const int within = gm & 15;
+            const int feature = (gm >> 4) * 8 + (within & 7);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float mine = __uint_as_float(r[j]);
+                const float up = __shfl_down_sync(0xffffffffu, mine, 8);
+                const int gn = gn0 + j;
+                if (within < 8 && gm + 8 < rows_a + 8 && gm < rows_a && gn < rows_b)
+                    ((bf16*)out)[(size_t)gn * ld_out + feature] = __float2bfloat16_rn(silu_mul(mine, up));
+            }
+        }
+        return;
+    }
+    if (gm >= rows_a) return;
+    if (!TRANSPOSE && OMODE != TC_OUT_PARTIAL && gn0 + 32 <= rows_b && (ld_out & 7) == 0) {
+        if (OMODE == TC_OUT_BF16) {
+            uint4* dst = (uint4*)((bf16*)out + (size_t)gm * ld_out + gn0);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                uint4 pk;
+                __nv_bfloat162 h;
+                h = __floats2bfloat162_rn(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1]));
+                pk.x = *(uint32_t*)&h;
+                h = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                pk.y = *(uint32_t*)&h;
+                h = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                pk.z = *(uint32_t*)&h;
+                h = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                pk.w = *(uint32_t*)&h;
+                dst[v] = pk;
+            }
+        } else {
+            float4* dst = (float4*)((float*)out + (size_t)gm * ld_out + gn0);
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+                float4 x = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                       __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                if (OMODE == TC_OUT_ADD_F32) {
+                    const float4 y = dst[v];
+                    x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+                }
+                dst[v] = x;
+            }
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const int gn = gn0 + j;
+        if (gn >= rows_b) break;
+        const float v = __uint_as_float(r[j]);
+        size_t at;
+        if (OMODE == TC_OUT_PARTIAL)
+            at = ((size_t)split * (TRANSPOSE ? rows_b : rows_a) + (TRANSPOSE ? gn : gm)) * ld_out + (TRANSPOSE ? gm : gn);
+        else
+            at = TRANSPOSE ? (size_t)gn * ld_out + gm : (size_t)gm * ld_out + gn;
+        if (OMODE == TC_OUT_BF16) ((bf16*)out)[at] = __float2bfloat16_rn(v);
+        else if (OMODE == TC_OUT_ADD_F32) ((float*)out)[at] += v;
+        else ((float*)out)[at] = v;
+    }
+}
+
+// Persistent: the grid is at most one CTA per SM and each CTA walks tiles blockIdx.x,
+// blockIdx.x + gridDim.x, ... The accumulator is double-buffered in TMEM (2 x BN columns), so
+// the epilogue of one tile runs while the next tile's products are issued.
 template <int BN, int OMODE, bool TRANSPOSE>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               void* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out,
+               void* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out, int splits,
                int kb_per_split, int* __restrict__ err) {
     using L = TcSmem<BN>;
     constexpr int STAGES = L::STAGES;
@@ -111,25 +216,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(base + (size_t)STAGES * L::STAGE);
     uint64_t* empty = full + STAGES;
-    uint64_t* acc_full = empty + STAGES;
-    uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+    uint64_t* acc_full = empty + STAGES;       // [2]
+    uint64_t* acc_empty = acc_full + 2;        // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    // Tile order: the A-row tiles of one group of TC_GROUP_M run first over a B tile, so the
+    // CTAs that are resident together share B tiles (and a small set of A tiles) in L2 instead
+    // of streaming all of B once per row of tiles.
+    const int tiles_m = (rows_a + TC_BM - 1) / TC_BM;
+    const int tiles_n = (rows_b + BN - 1) / BN;
+    const int n_tiles = tiles_m * tiles_n;
+    const int total = n_tiles * splits;
+    const int per_group = TC_GROUP_M * tiles_n;
     const int kb_total = (K + TC_BK - 1) / TC_BK;
-    const int kb_lo = blockIdx.z * kb_per_split;
-    const int kb_hi = kb_lo + kb_per_split < kb_total ? kb_lo + kb_per_split : kb_total;
-    const int n_kb = kb_hi > kb_lo ? kb_hi - kb_lo : 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_full, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(tc_smem(tmem_slot)), "r"((uint32_t)BN) : "memory");
+                     ::"r"(tc_smem(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -137,16 +247,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // work item w -> (split, m0, n0, k-block range)
+    auto locate = [&](int w, int& split, int& m0, int& n0, int& kb_lo, int& n_kb) {
+        split = w / n_tiles;
+        const int tile = w % n_tiles;
+        const int group = tile / per_group, within = tile % per_group;
+        const int group_m = tiles_m - group * TC_GROUP_M < TC_GROUP_M ? tiles_m - group * TC_GROUP_M : TC_GROUP_M;
+        m0 = (group * TC_GROUP_M + within % group_m) * TC_BM;
+        n0 = (within / group_m) * BN;
+        kb_lo = split * kb_per_split;
+        const int kb_hi = kb_lo + kb_per_split < kb_total ? kb_lo + kb_per_split : kb_total;
+        n_kb = kb_hi > kb_lo ? kb_hi - kb_lo : 0;
+    };
+
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < n_kb; ++i) {
-                const int s = i % STAGES;
-                const uint32_t round = (uint32_t)(i / STAGES);
-                if (!mbar_wait(&empty[s], (round & 1) ^ 1, err, 1)) break;
-                mbar_expect_tx(&full[s], L::STAGE);
-                unsigned char* st = base + (size_t)s * L::STAGE;
-                tma_load_2d(st, &map_a, (kb_lo + i) * TC_BK, m0, &full[s]);
-                tma_load_2d(st + L::A_BYTES, &map_b, (kb_lo + i) * TC_BK, n0, &full[s]);
+            uint32_t it = 0;                                    // stage uses so far, over all tiles
+            bool ok = true;
+            for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+                int split, m0, n0, kb_lo, n_kb;
+                locate(w, split, m0, n0, kb_lo, n_kb);
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, err, 1);
+                    if (!ok) break;
+                    mbar_expect_tx(&full[s], L::STAGE);
+                    unsigned char* st = base + (size_t)s * L::STAGE;
+                    tma_load_2d(st, &map_a, (kb_lo + i) * TC_BK, m0, &full[s]);
+                    tma_load_2d(st + L::A_BYTES, &map_b, (kb_lo + i) * TC_BK, n0, &full[s]);
+                }
             }
         }
     } else if (warp == 1) {
@@ -154,68 +283,72 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // instruction descriptor: float32 accumulate, bf16 x bf16, both K-major, N, M = 128
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                    ((uint32_t)(TC_BM >> 4) << 24);
+            uint32_t it = 0, local = 0;
             bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % STAGES;
-                const uint32_t round = (uint32_t)(i / STAGES);
-                ok = mbar_wait(&full[s], round & 1, err, 2);
+            for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++local) {
+                int split, m0, n0, kb_lo, n_kb;
+                locate(w, split, m0, n0, kb_lo, n_kb);
+                const uint32_t buf = local & 1;
+                ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, err, 4);   // epilogue let go of it
                 if (!ok) break;
                 tc_fence_after();
-                unsigned char* st = base + (size_t)s * L::STAGE;
-                const uint64_t da = umma_desc(st), db = umma_desc(st + L::A_BYTES);
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&full[s], (it / STAGES) & 1, err, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    unsigned char* st = base + (size_t)s * L::STAGE;
+                    const uint64_t da = umma_desc(st), db = umma_desc(st + L::A_BYTES);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)        // 16 bf16 = 32 bytes = 2 descriptor units
-                    umma_bf16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
-                              (i > 0 || k > 0) ? 1u : 0u);
-                umma_commit(&empty[s]);
+                    for (int k = 0; k < TC_BK / 16; ++k)    // 16 bf16 = 32 bytes = 2 descriptor units
+                        umma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                                  (i > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);
+                }
+                umma_commit(&acc_full[buf]);    // arrives once every MMA issued above has finished
             }
-            umma_commit(acc_full);          // arrives once every MMA issued above has finished
         }
     } else {
-        const int quarter = warp & 3;                       // TMEM lanes this warp may read
-        const bool ok = mbar_wait(acc_full, 0, err, 3);
-        tc_fence_after();
-        const int row = quarter * 32 + lane;                // row of the tile = TMEM lane
+        const int quarter = warp & 3;                           // TMEM lanes this warp may read
+        const int row = quarter * 32 + lane;                    // row of the tile = TMEM lane
+        uint32_t local = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < total; w += gridDim.x, ++local) {
+            int split, m0, n0, kb_lo, n_kb;
+            locate(w, split, m0, n0, kb_lo, n_kb);
+            const uint32_t buf = local & 1;
+            if (ok) ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, err, 3);
+            tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-            uint32_t r[32];
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32);
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                  "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-                  "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-                  "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-                  "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                : "r"(taddr));
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (!ok || n_kb == 0) continue;
-            const int gm = m0 + row;                        // row of A
-            if (gm >= rows_a) continue;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int gn = n0 + c * 32 + j;             // row of B
-                if (gn >= rows_b) break;
-                const float v = __uint_as_float(r[j]);
-                size_t at;
-                if (OMODE == TC_OUT_PARTIAL)
-                    at = ((size_t)blockIdx.z * (TRANSPOSE ? rows_b : rows_a) + (TRANSPOSE ? gn : gm)) * ld_out +
-                         (TRANSPOSE ? gm : gn);
-                else
-                    at = TRANSPOSE ? (size_t)gn * ld_out + gm : (size_t)gm * ld_out + gn;
-                if (OMODE == TC_OUT_BF16) ((bf16*)out)[at] = __float2bfloat16_rn(v);
-                else if (OMODE == TC_OUT_ADD_F32) ((float*)out)[at] += v;
-                else ((float*)out)[at] = v;
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + (uint32_t)(c * 32);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                      "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+                      "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+                      "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+                      "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                    : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (ok && n_kb > 0)
+                    tc_store<OMODE, TRANSPOSE>(r, out, m0 + row, n0 + c * 32, rows_a, rows_b, ld_out, split);
             }
+            // the accumulator may be overwritten: one arrival per epilogue warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
     }
 }
 
@@ -273,8 +406,18 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, in
     const size_t smem = TcSmem<BN>::TOTAL;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    const dim3 grid((rows_b + BN - 1) / BN, (rows_a + TC_BM - 1) / TC_BM, splits);
-    kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, out, rows_a, rows_b, K, ld_out, kb_per_split, err);
+    const int total = ((rows_b + BN - 1) / BN) * ((rows_a + TC_BM - 1) / TC_BM) * splits;
+    int sms = 148;
+    {
+        int dev = 0;
+        static int cached[64] = {};
+        if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+            if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+            if (cached[dev] > 0) sms = cached[dev];
+        }
+    }
+    const dim3 grid(total < sms ? total : sms);
+    kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err);
     return launch_status();
 }
 
@@ -285,6 +428,7 @@ static int tc_dispatch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, 
         case TC_OUT_BF16: return tc_launch<BN, TC_OUT_BF16, TRANSPOSE>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
         case TC_OUT_F32: return tc_launch<BN, TC_OUT_F32, TRANSPOSE>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
         case TC_OUT_ADD_F32: return tc_launch<BN, TC_OUT_ADD_F32, TRANSPOSE>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
+        case TC_OUT_SWIGLU: return tc_launch<BN, TC_OUT_SWIGLU, TRANSPOSE>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
         default: return tc_launch<BN, TC_OUT_PARTIAL, TRANSPOSE>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
     }
 }
@@ -293,14 +437,18 @@ static int tc_dispatch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, 
 //   transpose == 0: x is the A operand (rows on the 128-wide axis): prefill, many rows.
 //   transpose == 1: w is the A operand and x the B operand (M <= 256 rows padded to a
 //                   multiple of 16): decode, few rows; the tile is stored transposed.
-// omode: 0 bfloat16, 1 float32, 2 add into float32. splits > 1: K is cut; `workspace` must
-// hold splits * M * N floats. err: one int on the device that a timed-out wait sets.
+// omode: 0 bfloat16, 1 float32, 2 add into float32, 4 w is a gate/up matrix with rows
+// interleaved in eights and out is silu(gate) * up, bfloat16 [M, N / 2] (no splits).
+// splits > 1: K is cut; `workspace` must hold splits * M * N floats.
+// err: one int on the device that a timed-out wait sets.
 TGO_API int tgo_gemm_tc(const void* x, const void* w, void* out, int M, int N, int K, int omode,
                         int transpose, int splits, float* workspace, int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 || omode < 0 || omode > 2 || splits < 1 || (splits > 1 && !workspace) ||
+    if (K <= 0 || K % 8 || omode < 0 || omode == TC_OUT_PARTIAL || omode > TC_OUT_SWIGLU || splits < 1 ||
+        (splits > 1 && (!workspace || omode == TC_OUT_SWIGLU)) || (omode == TC_OUT_SWIGLU && N % 16) ||
         ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
         return TGO_E_BAD_ARG;
+    const long long ld = omode == TC_OUT_SWIGLU ? N / 2 : N;
     const int kb_total = (K + TC_BK - 1) / TC_BK;
     if (splits > kb_total) splits = kb_total;
     const int kb_per_split = (kb_total + splits - 1) / splits;
@@ -313,8 +461,8 @@ TGO_API int tgo_gemm_tc(const void* x, const void* w, void* out, int M, int N, i
         const int bn = N >= 256 ? 256 : 128;
         if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
         if ((rc = make_map(&mb, w, N, K, bn))) return rc;
-        rc = bn == 256 ? tc_dispatch<256, false>(ma, mb, dst, M, N, K, N, om, splits, kb_per_split, err, stream)
-                       : tc_dispatch<128, false>(ma, mb, dst, M, N, K, N, om, splits, kb_per_split, err, stream);
+        rc = bn == 256 ? tc_dispatch<256, false>(ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream)
+                       : tc_dispatch<128, false>(ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream);
     } else {
         if (M > 256) return TGO_E_BAD_ARG;
         const int bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
@@ -322,10 +470,10 @@ TGO_API int tgo_gemm_tc(const void* x, const void* w, void* out, int M, int N, i
         if ((rc = make_map(&mb, x, M, K, bn))) return rc;
         // A = w (N rows), B = x (M rows); D^T is stored: out[m, n], leading dimension N
         switch (bn) {
-            case 32: rc = tc_dispatch<32, true>(ma, mb, dst, N, M, K, N, om, splits, kb_per_split, err, stream); break;
-            case 64: rc = tc_dispatch<64, true>(ma, mb, dst, N, M, K, N, om, splits, kb_per_split, err, stream); break;
-            case 128: rc = tc_dispatch<128, true>(ma, mb, dst, N, M, K, N, om, splits, kb_per_split, err, stream); break;
-            default: rc = tc_dispatch<256, true>(ma, mb, dst, N, M, K, N, om, splits, kb_per_split, err, stream); break;
+            case 32: rc = tc_dispatch<32, true>(ma, mb, dst, N, M, K, ld, om, splits, kb_per_split, err, stream); break;
+            case 64: rc = tc_dispatch<64, true>(ma, mb, dst, N, M, K, ld, om, splits, kb_per_split, err, stream); break;
+            case 128: rc = tc_dispatch<128, true>(ma, mb, dst, N, M, K, ld, om, splits, kb_per_split, err, stream); break;
+            default: rc = tc_dispatch<256, true>(ma, mb, dst, N, M, K, ld, om, splits, kb_per_split, err, stream); break;
         }
     }
     if (rc || splits == 1) return rc;

@@ -261,12 +261,41 @@ def _skinny_ok(x, w) -> bool:
         x.shape[0] <= SKINNY_MAX_ROWS and w.shape[1] % 8 == 0
 
 
+# Which kernel multiplies, by the number of rows (measured in the running model on B200):
+#   1..8     gemm_skinny (weight streaming, mma.sync)        faster than the library
+#   9..64    the library product (cuBLASLt through torch.mm)  the tcgen05 kernel in its decode
+#            orientation is 3-8 % behind it per product: too few 128-row tiles for 148 SMs
+#   65..     gemm_tc (tcgen05 + TMEM + TMA)                   within 3 % of the library, and it
+#            applies the gate in its epilogue
+TC_MIN_ROWS = 65
+USE_TC = True            # False: the library product for every size above 8 rows
+
+
+def _tc_ok(x, w) -> bool:
+    return USE_TC and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and \
+        x.shape[0] >= TC_MIN_ROWS and w.shape[1] % 8 == 0 and x.is_contiguous() and \
+        w.is_contiguous() and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
+def _tc_splits(M: int, N: int, K: int) -> int:
+    """K splits for the decode orientation: enough work items to give every SM one, while a
+    split keeps at least eight 64-wide k-blocks."""
+    if M > 64:
+        return 1
+    tiles = (N + 127) // 128
+    return max(1, min(NUM_SMS // tiles, (K // 64) // 8))
+
+
 def _dense(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     M, N = x.shape[0], w.shape[0]
     if x.dtype == torch.float32:
         assert out_dtype == torch.float32
         y = torch.empty((M, N), dtype=torch.float32, device=x.device)
         sgemm_tn(x, w, y)
+        return y
+    if _tc_ok(x, w):
+        y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        gemm_tc(x, w, y, splits=_tc_splits(M, N, w.shape[1]))
         return y
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         return torch.mm(x, w.t()) if out_dtype == torch.bfloat16 else \
@@ -277,12 +306,14 @@ def _dense(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Te
 def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
            residual: Optional[torch.Tensor] = None):
     """y = x . w^T with w stored [out, in]. x is a tensor or NormedRows. residual: a float32
-    [M, N] tensor the product is added to, in which case nothing is returned.
+    [M, N] tensor the product belongs to: either it is added there and None is returned, or
+    the product is returned for the caller to add (the block hands it to the next norm).
 
     float32: this package's plain-FMA kernel. bfloat16 with few rows (a decode step): this
-    package's weight-streaming kernel, which folds in a pending norm and the residual add.
-    bfloat16 with more rows: the library matrix product (cuBLASLt through torch.mm),
-    float32 accumulation; out_dtype float32 keeps the accumulator's width (the logits).
+    package's weight-streaming kernel. bfloat16 with more rows: this package's tcgen05
+    kernel (TMA-fed, accumulators in tensor memory), in the decode orientation up to 64
+    rows. Both bfloat16 kernels do the residual add in their epilogue; out_dtype float32
+    keeps the accumulator's width (the logits).
     """
     out_dtype = out_dtype or x.dtype
     if isinstance(x, NormedRows) and not FOLD_NORM:
@@ -295,7 +326,16 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         gemm_skinny(x, w, out)
         return out
-    y = _dense(as_rows(x), w, out_dtype)
+    x = as_rows(x)
+    if residual is not None and _tc_ok(x, w):
+        if x.shape[0] > 64:
+            # many rows: a read-modify-write of the float32 stream from the product's epilogue
+            # is slow (each thread owns a row); hand the product back and let the next norm,
+            # which reads the stream anyway, add it
+            return _dense(x, w, out_dtype)
+        gemm_tc(x, w, residual, accumulate=True, splits=_tc_splits(x.shape[0], w.shape[0], w.shape[1]))
+        return None
+    y = _dense(x, w, out_dtype)
     if residual is not None:
         residual_add(residual, y)
         return None
@@ -305,7 +345,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
 def gated_linear(x, w_gate_up: torch.Tensor, interleaved: bool) -> torch.Tensor:
     """silu(x . Wg^T) * (x . Wu^T) as [M, f] in x's dtype. w_gate_up is [2f, K]: the gate
     rows then the up rows, or (`interleaved`) eight gate rows and the eight matching up rows
-    in turn, which lets the weight-streaming kernel apply the gate itself."""
+    in turn, which lets the bfloat16 kernels apply the gate in their epilogue."""
     M, f = x.shape[0], w_gate_up.shape[0] // 2
     if isinstance(x, NormedRows) and not FOLD_NORM:
         x = x.materialize()
@@ -314,6 +354,10 @@ def gated_linear(x, w_gate_up: torch.Tensor, interleaved: bool) -> torch.Tensor:
         gemm_skinny(x, w_gate_up, out, gated=True)
         return out
     xt = as_rows(x)
+    if interleaved and _tc_ok(xt, w_gate_up) and f % 8 == 0:
+        out = torch.empty((M, f), dtype=torch.bfloat16, device=xt.device)
+        gemm_tc(xt, w_gate_up, out, gated=True)
+        return out
     gu = _dense(xt, w_gate_up, xt.dtype)
     out = torch.empty((M, f), dtype=xt.dtype, device=xt.device)
     swiglu(gu, out, interleaved)
@@ -479,18 +523,24 @@ def gemm_tc_error_flag(device) -> torch.Tensor:
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
-            transpose: Optional[bool] = None, splits: int = 1) -> None:
+            transpose: Optional[bool] = None, splits: int = 1, gated: bool = False) -> None:
     """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, float32
     accumulation in tensor memory, TMA-fed). out: bfloat16 or float32, or float32 that the
     product is added to. transpose: the weight rows take the 128-wide axis and x (at most
     256 rows) the other (decode); default: when x has at most 64 rows. splits > 1 cuts K
-    over that many CTAs per tile and adds the float32 partials in order."""
+    over that many CTAs per tile and adds the float32 partials in order. gated: w is a
+    gate/up matrix with rows interleaved in eights and out is silu(gate) * up, bfloat16
+    [M, N / 2]."""
     _need_cuda(x, w, out)
     M, K = x.shape
     N = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
-    assert x.is_contiguous() and w.is_contiguous() and out.is_contiguous() and out.shape == (M, N)
-    if accumulate:
+    assert x.is_contiguous() and w.is_contiguous() and out.is_contiguous()
+    assert out.shape == ((M, N // 2) if gated else (M, N))
+    if gated:
+        assert out.dtype == torch.bfloat16 and N % 16 == 0 and splits == 1
+        omode = 4
+    elif accumulate:
         assert out.dtype == torch.float32
         omode = 2
     else:

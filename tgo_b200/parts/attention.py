@@ -76,8 +76,8 @@ class GQAAttention(Part):
 
     # ---- compute
     def forward(self, x: torch.Tensor, ctx, cache: LayerCache, residual=None):
-        """With `residual` (the float32 stream) the result is added to it and None is
-        returned; else the result is returned."""
+        """With `residual` (the float32 stream) the result may be added to it, and None is
+        then returned; otherwise the result is returned for the caller to add."""
         H, Hkv, dh = self.H, self.Hkv, self.dh
         qw, kw = H * dh, Hkv * dh
         if cache.writable:

@@ -17,7 +17,7 @@ Interfaces (duck-typed; `Part` only supplies the defaults):
   mixer           cache_need() -> CacheNeed or None; state_need() -> StateNeed or None;
                   forward(x, ctx, cache) -> [T, d] in the activation dtype. A forward that
                   also takes `residual=None` may add its result into that float32 tensor
-                  itself and return None.
+                  itself and return None (or return the result as usual).
   feed-forward    forward(x, ctx) -> [T, d]; `residual` as for the mixer.
   block           forward(h, pending, ctx, cache) -> (h, pending): `pending` is a delta
                   not yet added to h, so the add can be fused into the next norm.

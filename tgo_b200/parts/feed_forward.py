@@ -44,8 +44,8 @@ class SwiGLU(Part):
         self.w_down = weights.pop(p + "down_proj.weight").contiguous()
 
     def forward(self, x: torch.Tensor, ctx, residual=None):
-        """With `residual` (the float32 stream) the result is added to it and None is
-        returned; else the result is returned."""
+        """With `residual` (the float32 stream) the result may be added to it, and None is
+        then returned; otherwise the result is returned for the caller to add."""
         act = ops.gated_linear(x, self.w_gate_up, self.interleaved)
         return ops.linear(act, self.w_down, residual=residual)
 
