@@ -132,6 +132,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the 36 (0: all)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64, and prefill")
+    ap.add_argument("--only", default="", choices=["", "prefill", "decode"],
+                    help="profiling aid: run just the 2,048-token prefill, or just the decode "
+                         "steps, and print a short line instead of the contract line")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -150,6 +153,19 @@ def main():
         config["num_hidden_layers"] = args.layers
     model = tgo_b200.open_random(config, seed=SEED, dtype="bfloat16", sigma=0.02, gain_sigma=0.05)
     peaks = load_peaks()
+    if args.only == "prefill":
+        pre = measure_prefill(model, PREFILL_TOKENS, warmup=2, steps=max(1, min(args.steps, 3)),
+                              seed=SEED, page_size=PAGE)
+        print(json.dumps({"only": "prefill", "layers": config["num_hidden_layers"],
+                          "ms": round(pre["ms"], 3), "tflops": round(pre["tflops"], 1)}))
+        return 0
+    if args.only == "decode":
+        r = measure_decode(model, args.batch, PROMPT, args.steps, warmup=warmup, seed=SEED,
+                           page_size=PAGE)
+        print(json.dumps({"only": "decode", "layers": config["num_hidden_layers"],
+                          "batch": args.batch, "ms_per_step": round(r["ms_per_step"], 4),
+                          "gbs": round(r["gbs"], 1)}))
+        return 0
 
     clocks = ClockSampler()
     main_run = measure_decode(model, args.batch, PROMPT, args.steps, warmup=warmup, seed=SEED,

@@ -1,7 +1,7 @@
 // Paged causal attention on the tensor cores for bfloat16 storage, prefill and decode.
 //
 // One CTA takes a tile of query rows of one request and one kv head: the rows are the
-// (token, query head of the group) pairs of up to 16*NW/G consecutive tokens, G = H/Hkv,
+// (token, query head of the group) pairs of up to 128/G consecutive tokens, G = H/Hkv,
 // so every row of the tile reads the same keys and values. Keys and values come from the
 // paged cache [page][kv_head][offset][DH] through the request's block table, 64 at a time,
 // by cp.async into shared memory (two buffers: the next tile loads while this one is
@@ -50,103 +50,110 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *(uint32_t*)&v;
 }
 
-template <int DH, int NW>
-__global__ void __launch_bounds__(NW * 32)
-flash_paged_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
-                   long long out_stride, const bf16* __restrict__ k_cache,
-                   const bf16* __restrict__ v_cache, int page_size,
-                   const int* __restrict__ block_tables, int max_blocks,
-                   const int* __restrict__ positions, const int* __restrict__ seq_ids,
-                   const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok, int H,
-                   int Hkv, float scale_log2, int window, int n_splits,
-                   float* __restrict__ part_o, float* __restrict__ part_ml) {
-    constexpr int BM = 16 * NW;
+#define FP_WARPS 4
+#define FP_RW 2                  // m16 row tiles per warp
+#define FP_BM (16 * FP_WARPS * FP_RW)
+
+// Prefill: a tile of up to FP_BM query rows (consecutive tokens of one request x the G heads
+// of one kv head). Each warp owns FP_RW m16 tiles, so every key and value fragment it loads
+// from shared memory feeds FP_RW products.
+template <int DH>
+__global__ void __launch_bounds__(FP_WARPS * 32)
+flash_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                     long long out_stride, const bf16* __restrict__ k_cache,
+                     const bf16* __restrict__ v_cache, int page_size, int page_shift,
+                     const int* __restrict__ block_tables, int max_blocks,
+                     const int* __restrict__ positions, const int* __restrict__ seq_ids,
+                     const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok, int H,
+                     int Hkv, float scale_log2, int window, int pages_cap) {
     constexpr int LD = DH + FL_PAD;            // shared-memory row stride in bf16
     constexpr int KS = DH / 16;                // k-steps of Q K^T
     constexpr int CH = DH / 8;                 // 16-byte chunks per row
+    constexpr int THREADS = FP_WARPS * 32;
+    constexpr int ROWS_PER_IT = THREADS / CH;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* sq = (bf16*)smem_raw;                // [BM][LD]
-    bf16* sk = sq + BM * LD;                   // [2][FL_BN][LD]
+    bf16* sq = (bf16*)smem_raw;                // [FP_BM][LD]
+    bf16* sk = sq + FP_BM * LD;                // [2][FL_BN][LD]
     bf16* sv = sk + 2 * FL_BN * LD;            // [2][FL_BN][LD]
+    int* s_pages = (int*)(sv + 2 * FL_BN * LD);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    // later tiles of a request read more keys: they are started first, so that the kernel
+    // does not end on a few long CTAs
+    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
     const int G = H / Hkv;
-    const int tok0 = tile_tok0 ? tile_tok0[tile] : tile;
-    const int ntok = tile_ntok ? tile_ntok[tile] : 1;
+    const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
     const int n_rows = ntok * G;
     const int p0 = positions[tok0];            // position of the tile's first token
-    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
-
     if (p0 < 0) {                              // a request that brings nothing: zeros out
-        if (n_splits == 1) {
-            for (int i = tid; i < n_rows * DH; i += NW * 32) {
-                const int r = i / DH, d = i % DH;
-                out[(size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * DH + d] =
-                    __float2bfloat16_rn(0.f);
-            }
-        } else {
-            for (int r = tid; r < n_rows; r += NW * 32) {
-                const size_t at = ((size_t)(tok0 + r / G) * H + kvh * G + r % G) * n_splits + split;
-                part_ml[at * 2] = -INFINITY;
-                part_ml[at * 2 + 1] = 0.f;
-            }
+        for (int i = tid; i < n_rows * DH; i += THREADS) {
+            const int r = i / DH, d = i % DH;
+            out[(size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * DH + d] =
+                __float2bfloat16_rn(0.f);
         }
         return;
     }
-    const int b = seq_ids[tok0];
-    const int* bt = block_tables + (size_t)b * max_blocks;
+    const int* bt = block_tables + (size_t)seq_ids[tok0] * max_blocks;
     const int p_last = p0 + ntok - 1;
     // keys any row of the tile may read: [key_lo, key_hi)
     const int key_lo = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
     const int key_hi = p_last + 1;
-    const int t_first = key_lo / FL_BN, t_end = (key_hi + FL_BN - 1) / FL_BN;
-    int t_lo = t_first, t_hi = t_end;
-    if (n_splits > 1) {
-        const int per = (t_end - t_first + n_splits - 1) / n_splits;
-        t_lo = t_first + split * per;
-        t_hi = t_lo + per < t_end ? t_lo + per : t_end;
-    }
+    const int t_lo = key_lo / FL_BN, t_hi = (key_hi + FL_BN - 1) / FL_BN;
 
-    // ---- Q tile -> shared memory (rows beyond n_rows are zeros)
-    for (int i = tid; i < BM * CH; i += NW * 32) {
+    // the tile's slice of the block table -> shared memory
+    const int pg_lo = (t_lo * FL_BN) / page_size;
+    {
+        int pg_hi = (t_hi * FL_BN + page_size - 1) / page_size;
+        if (pg_hi > max_blocks) pg_hi = max_blocks;
+        if (pg_hi - pg_lo > pages_cap) pg_hi = pg_lo + pages_cap;
+        for (int i = pg_lo + tid; i < pg_hi; i += THREADS) s_pages[i - pg_lo] = bt[i];
+    }
+    for (int i = tid; i < FP_BM * CH; i += THREADS) {
         const int r = i / CH, c = i % CH;
         const bool ok = r < n_rows;
         const bf16* src = ok ? q + (size_t)(tok0 + r / G) * q_stride + (size_t)(kvh * G + r % G) * DH + c * 8 : q;
         cp_async16(sq + r * LD + c * 8, src, ok);
     }
+    __syncthreads();
+    auto page_of = [&](int pi) { return pi - pg_lo < pages_cap ? s_pages[pi - pg_lo] : bt[pi]; };
+    const int c_mine = tid % CH, r_mine = tid / CH;
     auto load_kv = [&](int t, int buf) {
-        bf16* dk = sk + buf * FL_BN * LD;
-        bf16* dv = sv + buf * FL_BN * LD;
-        for (int i = tid; i < FL_BN * CH; i += NW * 32) {
-            const int r = i / CH, c = i % CH;
+        bf16* dk = sk + buf * FL_BN * LD + c_mine * 8;
+        bf16* dv = sv + buf * FL_BN * LD + c_mine * 8;
+#pragma unroll
+        for (int r = r_mine; r < FL_BN; r += ROWS_PER_IT) {
             const int j = t * FL_BN + r;
             const bool ok = j >= key_lo && j < key_hi;
             size_t off = 0;
             if (ok) {
-                const int page = bt[j / page_size];
-                off = (((size_t)page * Hkv + kvh) * page_size + (j % page_size)) * DH + c * 8;
+                const int pi = page_shift >= 0 ? j >> page_shift : j / page_size;
+                const int po = j - pi * page_size;
+                off = (((size_t)page_of(pi) * Hkv + kvh) * page_size + po) * DH + c_mine * 8;
             }
-            cp_async16(dk + r * LD + c * 8, k_cache + off, ok);
-            cp_async16(dv + r * LD + c * 8, v_cache + off, ok);
+            cp_async16(dk + r * LD, k_cache + off, ok);
+            cp_async16(dv + r * LD, v_cache + off, ok);
         }
     };
-    if (t_lo < t_hi) load_kv(t_lo, 0);
+    load_kv(t_lo, 0);
     cp_async_commit();
 
-    float o[DH / 8][4];
+    float o[FP_RW][DH / 8][4];
+    float m_run[FP_RW][2], l_run[FP_RW][2];
+    int pos_row[FP_RW][2], vis_row[FP_RW][2];
 #pragma unroll
-    for (int i = 0; i < DH / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
-    // positions of this lane's two rows (rows beyond the tile read nothing)
-    const int pos_lo = r_lo < n_rows ? p0 + r_lo / G : -1;
-    const int pos_hi = r_hi < n_rows ? p0 + r_hi / G : -1;
-    const int vis_lo_lo = (window > 0 && pos_lo - window + 1 > 0) ? pos_lo - window + 1 : 0;
-    const int vis_lo_hi = (window > 0 && pos_hi - window + 1 > 0) ? pos_hi - window + 1 : 0;
-    const bool warp_active = warp * 16 < n_rows;
-
-    uint32_t qa[KS][4];
-    bool q_loaded = false;
+    for (int rw = 0; rw < FP_RW; ++rw) {
+#pragma unroll
+        for (int i = 0; i < DH / 8; ++i) { o[rw][i][0] = o[rw][i][1] = o[rw][i][2] = o[rw][i][3] = 0.f; }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = (warp * FP_RW + rw) * 16 + (lane >> 2) + 8 * h;
+            m_run[rw][h] = -INFINITY;
+            l_run[rw][h] = 0.f;
+            pos_row[rw][h] = r < n_rows ? p0 + r / G : -1;      // rows beyond the tile read nothing
+            vis_row[rw][h] = (window > 0 && pos_row[rw][h] - window + 1 > 0) ? pos_row[rw][h] - window + 1 : 0;
+        }
+    }
+    const bool warp_active = warp * FP_RW * 16 < n_rows;
 
     for (int t = t_lo; t < t_hi; ++t) {
         const int buf = (t - t_lo) & 1;
@@ -155,88 +162,103 @@ flash_paged_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restr
         cp_async_wait<1>();
         __syncthreads();
         if (warp_active) {
-            if (!q_loaded) {
-#pragma unroll
-                for (int ks = 0; ks < KS; ++ks)
-                    ldmatrix_x4(qa[ks], sq + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD +
-                                            ks * 16 + (lane >> 4) * 8);
-                q_loaded = true;
-            }
             const bf16* kt = sk + buf * FL_BN * LD;
             const bf16* vt = sv + buf * FL_BN * LD;
-            float s[FL_BN / 8][4];
+            float s[FP_RW][FL_BN / 8][4];
 #pragma unroll
-            for (int i = 0; i < FL_BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+            for (int rw = 0; rw < FP_RW; ++rw)
+#pragma unroll
+                for (int i = 0; i < FL_BN / 8; ++i) { s[rw][i][0] = s[rw][i][1] = s[rw][i][2] = s[rw][i][3] = 0.f; }
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
+                uint32_t qa[FP_RW][4];
+#pragma unroll
+                for (int rw = 0; rw < FP_RW; ++rw)
+                    ldmatrix_x4(qa[rw], sq + ((warp * FP_RW + rw) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD +
+                                            ks * 16 + (lane >> 4) * 8);
 #pragma unroll
                 for (int np = 0; np < FL_BN / 16; ++np) {       // two n-tiles (16 keys) at a time
                     uint32_t kb[4];
                     ldmatrix_x4(kb, kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * LD + ks * 16 +
                                         ((lane >> 3) & 1) * 8);
-                    mma_bf16(s[2 * np], qa[ks], kb[0], kb[1]);
-                    mma_bf16(s[2 * np + 1], qa[ks], kb[2], kb[3]);
+#pragma unroll
+                    for (int rw = 0; rw < FP_RW; ++rw) {
+                        mma_bf16(s[rw][2 * np], qa[rw], kb[0], kb[1]);
+                        mma_bf16(s[rw][2 * np + 1], qa[rw], kb[2], kb[3]);
+                    }
                 }
             }
-            // scale, mask, running maximum
+            // a tile that lies wholly inside every row's range needs no mask
+            const int first_row_pos = p0 + (warp * FP_RW * 16) / G;
+            const bool full = (t + 1) * FL_BN - 1 <= first_row_pos && t * FL_BN >= key_lo &&
+                              (window == 0 || t * FL_BN >= p_last - window + 1) &&
+                              (warp * FP_RW + FP_RW) * 16 <= n_rows;
             const int kbase = t * FL_BN + (lane & 3) * 2;
-            float mx_lo = -INFINITY, mx_hi = -INFINITY;
+            uint32_t pa[FP_RW][FL_BN / 16][4];
 #pragma unroll
-            for (int i = 0; i < FL_BN / 8; ++i) {
+            for (int rw = 0; rw < FP_RW; ++rw) {
+                float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int j = kbase + i * 8 + e;
-                    const bool a = j <= pos_lo && j >= vis_lo_lo;
-                    const bool c = j <= pos_hi && j >= vis_lo_hi;
-                    s[i][e] = a ? s[i][e] * scale_log2 : -INFINITY;
-                    s[i][2 + e] = c ? s[i][2 + e] * scale_log2 : -INFINITY;
-                    mx_lo = fmaxf(mx_lo, s[i][e]);
-                    mx_hi = fmaxf(mx_hi, s[i][2 + e]);
+                for (int i = 0; i < FL_BN / 8; ++i) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int j = kbase + i * 8 + e;
+                        const bool a = full || (j <= pos_row[rw][0] && j >= vis_row[rw][0]);
+                        const bool c = full || (j <= pos_row[rw][1] && j >= vis_row[rw][1]);
+                        s[rw][i][e] = a ? s[rw][i][e] * scale_log2 : -INFINITY;
+                        s[rw][i][2 + e] = c ? s[rw][i][2 + e] * scale_log2 : -INFINITY;
+                        mx[0] = fmaxf(mx[0], s[rw][i][e]);
+                        mx[1] = fmaxf(mx[1], s[rw][i][2 + e]);
+                    }
                 }
-            }
-            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-            const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-            // a row that has seen no key yet keeps base 0 so that exp2(-inf - 0) = 0, not NaN
-            const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo;
-            const float base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
-            const float corr_lo = exp2f(m_lo - base_lo), corr_hi = exp2f(m_hi - base_hi);
-            m_lo = mn_lo;
-            m_hi = mn_hi;
-            float sum_lo = 0.f, sum_hi = 0.f;
+                float corr[2], base[2], sum[2] = {0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < FL_BN / 8; ++i) {
-                s[i][0] = exp2f(s[i][0] - base_lo);
-                s[i][1] = exp2f(s[i][1] - base_lo);
-                s[i][2] = exp2f(s[i][2] - base_hi);
-                s[i][3] = exp2f(s[i][3] - base_hi);
-                sum_lo += s[i][0] + s[i][1];
-                sum_hi += s[i][2] + s[i][3];
-            }
-            l_lo = l_lo * corr_lo + sum_lo;        // per-lane partial sums; joined at the end
-            l_hi = l_hi * corr_hi + sum_hi;
+                for (int h = 0; h < 2; ++h) {
+                    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                    const float mn = fmaxf(m_run[rw][h], mx[h]);
+                    // a row that has seen no key yet keeps base 0 so that exp2(-inf - 0) = 0
+                    base[h] = mn == -INFINITY ? 0.f : mn;
+                    corr[h] = exp2f(m_run[rw][h] - base[h]);
+                    m_run[rw][h] = mn;
+                }
 #pragma unroll
-            for (int i = 0; i < DH / 8; ++i) {
-                o[i][0] *= corr_lo; o[i][1] *= corr_lo;
-                o[i][2] *= corr_hi; o[i][3] *= corr_hi;
+                for (int i = 0; i < FL_BN / 8; ++i) {
+                    s[rw][i][0] = exp2f(s[rw][i][0] - base[0]);
+                    s[rw][i][1] = exp2f(s[rw][i][1] - base[0]);
+                    s[rw][i][2] = exp2f(s[rw][i][2] - base[1]);
+                    s[rw][i][3] = exp2f(s[rw][i][3] - base[1]);
+                    sum[0] += s[rw][i][0] + s[rw][i][1];
+                    sum[1] += s[rw][i][2] + s[rw][i][3];
+                }
+                l_run[rw][0] = l_run[rw][0] * corr[0] + sum[0];     // per-lane partial sums
+                l_run[rw][1] = l_run[rw][1] * corr[1] + sum[1];
+#pragma unroll
+                for (int i = 0; i < DH / 8; ++i) {
+                    o[rw][i][0] *= corr[0]; o[rw][i][1] *= corr[0];
+                    o[rw][i][2] *= corr[1]; o[rw][i][3] *= corr[1];
+                }
+#pragma unroll
+                for (int kk = 0; kk < FL_BN / 16; ++kk) {
+                    pa[rw][kk][0] = pack_bf16(s[rw][2 * kk][0], s[rw][2 * kk][1]);
+                    pa[rw][kk][1] = pack_bf16(s[rw][2 * kk][2], s[rw][2 * kk][3]);
+                    pa[rw][kk][2] = pack_bf16(s[rw][2 * kk + 1][0], s[rw][2 * kk + 1][1]);
+                    pa[rw][kk][3] = pack_bf16(s[rw][2 * kk + 1][2], s[rw][2 * kk + 1][3]);
+                }
             }
             // O += P V
 #pragma unroll
             for (int kk = 0; kk < FL_BN / 16; ++kk) {
-                uint32_t pa[4];
-                pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-                pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-                pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-                pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
                 for (int dp = 0; dp < DH / 16; ++dp) {          // two n-tiles (16 dims) at a time
                     uint32_t vb[4];
                     ldmatrix_x4_trans(vb, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD +
                                               dp * 16 + (lane >> 4) * 8);
-                    mma_bf16(o[2 * dp], pa, vb[0], vb[1]);
-                    mma_bf16(o[2 * dp + 1], pa, vb[2], vb[3]);
+#pragma unroll
+                    for (int rw = 0; rw < FP_RW; ++rw) {
+                        mma_bf16(o[rw][2 * dp], pa[rw][kk], vb[0], vb[1]);
+                        mma_bf16(o[rw][2 * dp + 1], pa[rw][kk], vb[2], vb[3]);
+                    }
                 }
             }
         }
@@ -244,41 +266,21 @@ flash_paged_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restr
     }
     cp_async_wait<0>();
     if (!warp_active) return;
-
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
-    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-
     const int col = (lane & 3) * 2;
-    if (n_splits == 1) {
-        const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
-        if (r_lo < n_rows) {
-            bf16* dst = out + (size_t)(tok0 + r_lo / G) * out_stride + (size_t)(kvh * G + r_lo % G) * DH + col;
+#pragma unroll
+    for (int rw = 0; rw < FP_RW; ++rw) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float l = l_run[rw][h];
+            l += __shfl_xor_sync(0xffffffffu, l, 1);
+            l += __shfl_xor_sync(0xffffffffu, l, 2);
+            const int r = (warp * FP_RW + rw) * 16 + (lane >> 2) + 8 * h;
+            if (r >= n_rows) continue;
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* dst = out + (size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * DH + col;
 #pragma unroll
             for (int i = 0; i < DH / 8; ++i)
-                *(uint32_t*)(dst + i * 8) = pack_bf16(o[i][0] * inv_lo, o[i][1] * inv_lo);
-        }
-        if (r_hi < n_rows) {
-            bf16* dst = out + (size_t)(tok0 + r_hi / G) * out_stride + (size_t)(kvh * G + r_hi % G) * DH + col;
-#pragma unroll
-            for (int i = 0; i < DH / 8; ++i)
-                *(uint32_t*)(dst + i * 8) = pack_bf16(o[i][2] * inv_hi, o[i][3] * inv_hi);
-        }
-    } else {
-        if (r_lo < n_rows) {
-            const size_t at = ((size_t)(tok0 + r_lo / G) * H + kvh * G + r_lo % G) * n_splits + split;
-            float* dst = part_o + at * DH + col;
-#pragma unroll
-            for (int i = 0; i < DH / 8; ++i) *(float2*)(dst + i * 8) = make_float2(o[i][0], o[i][1]);
-            if ((lane & 3) == 0) { part_ml[at * 2] = m_lo; part_ml[at * 2 + 1] = l_lo; }
-        }
-        if (r_hi < n_rows) {
-            const size_t at = ((size_t)(tok0 + r_hi / G) * H + kvh * G + r_hi % G) * n_splits + split;
-            float* dst = part_o + at * DH + col;
-#pragma unroll
-            for (int i = 0; i < DH / 8; ++i) *(float2*)(dst + i * 8) = make_float2(o[i][2], o[i][3]);
-            if ((lane & 3) == 0) { part_ml[at * 2] = m_hi; part_ml[at * 2 + 1] = l_hi; }
+                *(uint32_t*)(dst + i * 8) = pack_bf16(o[rw][i][2 * h] * inv, o[rw][i][2 * h + 1] * inv);
         }
     }
 }
@@ -536,25 +538,25 @@ __global__ void flash_combine_kernel(const float* __restrict__ part_o,
     }
 }
 
-template <int DH, int NW>
-static int flash_launch(const bf16* q, long long q_stride, bf16* out, long long out_stride,
-                        const bf16* k_cache, const bf16* v_cache, int page_size,
-                        const int* block_tables, int max_blocks, const int* positions,
-                        const int* seq_ids, const int* tile_tok0, const int* tile_ntok, int n_tiles,
-                        int H, int Hkv, float scale, int window, int n_splits, float* part_o,
-                        float* part_ml, cudaStream_t stream) {
+template <int DH>
+static int prefill_launch(const bf16* q, long long q_stride, bf16* out, long long out_stride,
+                          const bf16* k_cache, const bf16* v_cache, int page_size,
+                          const int* block_tables, int max_blocks, const int* positions,
+                          const int* seq_ids, const int* tile_tok0, const int* tile_ntok, int n_tiles,
+                          int H, int Hkv, float scale, int window, cudaStream_t stream) {
     constexpr int LD = DH + FL_PAD;
-    const size_t smem = (size_t)(16 * NW + 4 * FL_BN) * LD * sizeof(bf16);
-    auto kern = flash_paged_kernel<DH, NW>;
+    const int pages_cap = max_blocks < 4096 ? max_blocks : 4096;
+    const size_t smem = (size_t)(FP_BM + 4 * FL_BN) * LD * sizeof(bf16) + (size_t)pages_cap * sizeof(int);
+    auto kern = flash_prefill_kernel<DH>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    const float scale_log2 = scale * 1.4426950408889634f;
-    kern<<<dim3(n_tiles, Hkv, n_splits), NW * 32, smem, stream>>>(
-        q, q_stride, out, out_stride, k_cache, v_cache, page_size, block_tables, max_blocks,
-        positions, seq_ids, tile_tok0, tile_ntok, H, Hkv, scale_log2, window, n_splits, part_o,
-        part_ml);
+    int shift = -1;
+    for (int sft = 0; sft < 31; ++sft) if ((1 << sft) == page_size) shift = sft;
+    kern<<<dim3(n_tiles, Hkv), FP_WARPS * 32, smem, stream>>>(
+        q, q_stride, out, out_stride, k_cache, v_cache, page_size, shift, block_tables, max_blocks,
+        positions, seq_ids, tile_tok0, tile_ntok, H, Hkv, scale * 1.4426950408889634f, window, pages_cap);
     return launch_status();
 }
 
@@ -588,56 +590,45 @@ TGO_API int tgo_attention_flash_supports(int dh, int group) {
     return (dh == 16 || dh == 32 || dh == 64 || dh == 128) && group >= 1 && group <= 16;
 }
 
+// Query rows (token x head of the group) one prefill tile holds: a tile takes
+// tgo_attention_flash_tile_rows() / group consecutive tokens of one request.
+TGO_API int tgo_attention_flash_tile_rows() { return FP_BM; }
+
+// With tile arrays: the prefill kernel (n_splits must be 1). Without: every token is a tile
+// of its own and the decode kernel runs, with n_splits CTAs per (token, kv head).
 TGO_API int tgo_attention_flash(const void* q, long long q_stride, void* out, long long out_stride,
                                 const void* k_cache, const void* v_cache, int page_size,
                                 const int* block_tables, int max_blocks, const int* positions,
                                 const int* seq_ids, const int* tile_tok0, const int* tile_ntok,
                                 int n_tiles, int H, int Hkv, int dh, float scale, int window,
-                                int wide, int n_splits, float* part_o, float* part_ml,
+                                int n_splits, float* part_o, float* part_ml,
                                 cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv || !tgo_attention_flash_supports(dh, H / Hkv) ||
         page_size <= 0 || max_blocks <= 0 || window < 0 || n_splits < 1 || Hkv > 65535 ||
-        n_splits > 65535 || (n_splits > 1 && (!part_o || !part_ml)))
+        n_splits > 65535 || (n_splits > 1 && (!part_o || !part_ml || tile_tok0)) ||
+        (tile_tok0 && !tile_ntok))
         return TGO_E_BAD_ARG;
-#define FL_CASE(D)                                                                                  \
+    const bf16* qp = (const bf16*)q;
+    const bf16* kp = (const bf16*)k_cache;
+    const bf16* vp = (const bf16*)v_cache;
+    bf16* op = (bf16*)out;
+#define FA_CASE(D)                                                                                  \
     case D:                                                                                         \
-        rc = wide ? flash_launch<D, 4>((const bf16*)q, q_stride, (bf16*)out, out_stride,             \
-                                       (const bf16*)k_cache, (const bf16*)v_cache, page_size,       \
-                                       block_tables, max_blocks, positions, seq_ids, tile_tok0,     \
-                                       tile_ntok, n_tiles, H, Hkv, scale, window, n_splits, part_o, \
-                                       part_ml, stream)                                             \
-                  : flash_launch<D, 1>((const bf16*)q, q_stride, (bf16*)out, out_stride,             \
-                                       (const bf16*)k_cache, (const bf16*)v_cache, page_size,       \
-                                       block_tables, max_blocks, positions, seq_ids, tile_tok0,     \
-                                       tile_ntok, n_tiles, H, Hkv, scale, window, n_splits, part_o, \
-                                       part_ml, stream);                                            \
-        break;
-    int rc = TGO_E_BAD_ARG;
-    if (!tile_tok0 && !wide) {          // every token a tile of its own: the decode kernel
-#define FD_CASE(D)                                                                                 \
-    case D:                                                                                        \
-        return decode_launch<D>((const bf16*)q, q_stride, (bf16*)out, out_stride,                  \
-                                (const bf16*)k_cache, (const bf16*)v_cache, page_size, block_tables, \
-                                max_blocks, positions, seq_ids, n_tiles, H, Hkv, scale, window,    \
-                                n_splits, part_o, part_ml, stream);
-        switch (dh) {
-            FD_CASE(16)
-            FD_CASE(32)
-            FD_CASE(64)
-            FD_CASE(128)
-        }
-#undef FD_CASE
-        return rc;
-    }
+        return tile_tok0 ? prefill_launch<D>(qp, q_stride, op, out_stride, kp, vp, page_size,        \
+                                             block_tables, max_blocks, positions, seq_ids, tile_tok0, \
+                                             tile_ntok, n_tiles, H, Hkv, scale, window, stream)      \
+                         : decode_launch<D>(qp, q_stride, op, out_stride, kp, vp, page_size,         \
+                                            block_tables, max_blocks, positions, seq_ids, n_tiles, H, \
+                                            Hkv, scale, window, n_splits, part_o, part_ml, stream);
     switch (dh) {
-        FL_CASE(16)
-        FL_CASE(32)
-        FL_CASE(64)
-        FL_CASE(128)
+        FA_CASE(16)
+        FA_CASE(32)
+        FA_CASE(64)
+        FA_CASE(128)
     }
-#undef FL_CASE
-    return rc;
+#undef FA_CASE
+    return TGO_E_BAD_ARG;
 }
 
 TGO_API int tgo_attention_flash_combine(const float* part_o, const float* part_ml, void* out,

@@ -92,11 +92,91 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     }
 }
 
+// The same with four consecutive elements per thread and 16-byte accesses, for d % 4 == 0
+// and rows that fit 4 * CH4 * blockDim registers.
+template <typename TD> struct Delta4;
+template <> struct Delta4<bf16> {
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 v = *(const uint2*)p;
+        const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&v.x);
+        const float2 b = __bfloat1622float2(*(const __nv_bfloat162*)&v.y);
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
+template <> struct Delta4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *(const float4*)p; }
+};
+template <typename TO> struct Out4;
+template <> struct Out4<bf16> {
+    static __device__ __forceinline__ void store(bf16* p, float4 x) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(x.x, x.y), b = __floats2bfloat162_rn(x.z, x.w);
+        uint2 v;
+        v.x = *(uint32_t*)&a;
+        v.y = *(uint32_t*)&b;
+        *(uint2*)p = v;
+    }
+};
+template <> struct Out4<float> {
+    static __device__ __forceinline__ void store(float* p, float4 x) { *(float4*)p = x; }
+};
+
+template <typename TD, typename TO, int CH4>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                       const float* __restrict__ gain, float eps,
+                                       TO* __restrict__ out, const int* __restrict__ rows, int d) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch();
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    float* hr = h + (size_t)r * d;
+    const TD* dr = delta ? delta + (size_t)r * d : nullptr;
+    TO* o = out + (size_t)i * d;
+    float4 x[CH4];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH4; ++c) {
+        const int j = 4 * (threadIdx.x + c * blockDim.x);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j < d) {
+            v = *(const float4*)(hr + j);
+            if (dr) {
+                const float4 dl = Delta4<TD>::load(dr + j);
+                v.x += dl.x; v.y += dl.y; v.z += dl.z; v.w += dl.w;
+                if (!rows) *(float4*)(hr + j) = v;
+            }
+        }
+        x[c] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    const float total = block_sum(ss, scratch);
+    const float scale = rsqrtf(total / (float)d + eps);
+#pragma unroll
+    for (int c = 0; c < CH4; ++c) {
+        const int j = 4 * (threadIdx.x + c * blockDim.x);
+        if (j < d) {
+            const float4 g = *(const float4*)(gain + j);
+            Out4<TO>::store(o + j, make_float4((x[c].x * scale) * g.x, (x[c].y * scale) * g.y,
+                                               (x[c].z * scale) * g.z, (x[c].w * scale) * g.w));
+        }
+    }
+}
+
 template <typename TD, typename TO>
 static int add_rmsnorm_launch(float* h, const void* delta, const float* gain, float eps, void* out,
                               const int* rows, int n, int d, cudaStream_t s) {
     const TD* dl = (const TD*)delta;
     TO* o = (TO*)out;
+    if (d % 4 == 0 && d <= 16384 && ((uintptr_t)h % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
+        ((uintptr_t)gain % 16 == 0) && (!delta || (uintptr_t)delta % 16 == 0)) {
+        const int quads = d / 4;
+        const int vt = quads <= 256 ? 128 : quads <= 1024 ? 256 : 512;
+        const int ch = (quads + vt - 1) / vt;
+        if (ch <= 1) return tgo_launch_pdl(add_rmsnorm_vec_kernel<TD, TO, 1>, dim3(n), dim3(vt), 0, s, h, dl, gain, eps, o, rows, d);
+        if (ch <= 2) return tgo_launch_pdl(add_rmsnorm_vec_kernel<TD, TO, 2>, dim3(n), dim3(vt), 0, s, h, dl, gain, eps, o, rows, d);
+        if (ch <= 4) return tgo_launch_pdl(add_rmsnorm_vec_kernel<TD, TO, 4>, dim3(n), dim3(vt), 0, s, h, dl, gain, eps, o, rows, d);
+        return tgo_launch_pdl(add_rmsnorm_vec_kernel<TD, TO, 8>, dim3(n), dim3(vt), 0, s, h, dl, gain, eps, o, rows, d);
+    }
     int threads = 256;
     if (d > 2048) threads = 512;
     if (d > 4096) threads = 1024;
@@ -335,6 +415,91 @@ __global__ void qk_norm_rope_cache_kernel(
     }
 }
 
+// The same for head_dim 128 with the whole head rotated (or none of it): each lane holds four
+// consecutive channels (one 8- or 16-byte access), the partner channel i +- 64 sits in lane
+// +- 16, and nothing goes through shared memory.
+template <typename T> struct Vec4;
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&x)[4]) {
+        const uint2 v = *(const uint2*)p;
+        const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&v.x);
+        const float2 b = __bfloat1622float2(*(const __nv_bfloat162*)&v.y);
+        x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&x)[4]) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(x[0], x[1]), b = __floats2bfloat162_rn(x[2], x[3]);
+        uint2 v;
+        v.x = *(uint32_t*)&a;
+        v.y = *(uint32_t*)&b;
+        *(uint2*)p = v;
+    }
+};
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&x)[4]) {
+        const float4 v = *(const float4*)p;
+        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&x)[4]) {
+        *(float4*)p = make_float4(x[0], x[1], x[2], x[3]);
+    }
+};
+
+template <typename T>
+__global__ void qk_norm_rope_cache_dh128_kernel(
+    T* __restrict__ q, long long q_stride, T* __restrict__ k, long long k_stride,
+    const T* __restrict__ v, long long v_stride, int H, int Hkv,
+    const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+    const float* __restrict__ rope, const int* __restrict__ slots, T* __restrict__ k_cache,
+    T* __restrict__ v_cache, int page_size) {
+    constexpr int dh = 128;
+    pdl_wait();
+    pdl_launch();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hh = blockIdx.y * QKR_WARPS + warp;
+    const int nk = k ? Hkv : 0, nv = v ? Hkv : 0;
+    if (hh >= H + nk + nv) return;
+    const int slot = slots ? slots[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+    float x[4];
+    if (hh >= H + nk) {
+        const int head = hh - H - nk;
+        if (slot < 0) return;
+        Vec4<T>::load(v + (size_t)t * v_stride + (size_t)head * dh + 4 * lane, x);
+        Vec4<T>::store(v_cache + (((size_t)page * Hkv + head) * page_size + off) * dh + 4 * lane, x);
+        return;
+    }
+    const bool is_q = hh < H;
+    const int head = is_q ? hh : hh - H;
+    T* vec = is_q ? q + (size_t)t * q_stride + (size_t)head * dh : k + (size_t)t * k_stride + (size_t)head * dh;
+    const float* gain = is_q ? q_gain : k_gain;
+    Vec4<T>::load(vec + 4 * lane, x);
+    if (gain) {
+        float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+        ss = warp_sum(ss);
+        const float scale = rsqrtf(ss / (float)dh + eps);
+        const float4 g = *(const float4*)(gain + 4 * lane);
+        x[0] = (x[0] * scale) * g.x; x[1] = (x[1] * scale) * g.y;
+        x[2] = (x[2] * scale) * g.z; x[3] = (x[3] * scale) * g.w;
+    }
+    if (rope) {
+        // channels 4*lane .. +3; lanes 0..15 hold the low half, their partners are 16 lanes on
+        const float* cs = rope + (size_t)t * dh;              // [64] cos, [64] sin
+        const int i0 = 4 * (lane & 15);
+        const float4 c = *(const float4*)(cs + i0), sn = *(const float4*)(cs + 64 + i0);
+        const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
+            x[e] = lane < 16 ? x[e] * cc[e] - other * sv[e] : other * sv[e] + x[e] * cc[e];
+        }
+    }
+    T* dst = vec;
+    if (!is_q && k_cache)
+        dst = slot >= 0 ? k_cache + (((size_t)page * Hkv + head) * page_size + off) * dh : nullptr;
+    if (dst) Vec4<T>::store(dst + 4 * lane, x);
+}
+
 TGO_API int tgo_qk_norm_rope_cache(void* q, long long q_stride, void* k, long long k_stride,
                                    const void* v, long long v_stride, int dtype, int T, int H,
                                    int Hkv, int dh, const float* q_gain, const float* k_gain,
@@ -350,6 +515,19 @@ TGO_API int tgo_qk_norm_rope_cache(void* q, long long q_stride, void* k, long lo
     const size_t smem = (size_t)(warps * dh) * sizeof(float);
     const int vectors = H + (k ? Hkv : 0) + (v ? Hkv : 0);
     const dim3 grid(T, (vectors + warps - 1) / warps);
+    const int esz = dtype == TGO_BF16 ? 2 : 4;
+    const bool aligned = ((uintptr_t)q * 1 % 16 == 0) && (q_stride * esz) % 16 == 0 &&
+                         (!k || (((uintptr_t)k % 16 == 0) && (k_stride * esz) % 16 == 0)) &&
+                         (!v || (((uintptr_t)v % 16 == 0) && (v_stride * esz) % 16 == 0));
+    if (dh == 128 && (rot == 128 || !rope) && aligned && (dtype == TGO_BF16 || dtype == TGO_F32)) {
+        if (dtype == TGO_BF16)
+            return tgo_launch_pdl(qk_norm_rope_cache_dh128_kernel<bf16>, grid, dim3(warps * 32), 0, stream,
+                                  (bf16*)q, q_stride, (bf16*)k, k_stride, (const bf16*)v, v_stride, H, Hkv,
+                                  q_gain, k_gain, eps, rope, slots, (bf16*)k_cache, (bf16*)v_cache, page_size);
+        return tgo_launch_pdl(qk_norm_rope_cache_dh128_kernel<float>, grid, dim3(warps * 32), 0, stream,
+                              (float*)q, q_stride, (float*)k, k_stride, (const float*)v, v_stride, H, Hkv,
+                              q_gain, k_gain, eps, rope, slots, (float*)k_cache, (float*)v_cache, page_size);
+    }
     if (dtype == TGO_BF16)
         return tgo_launch_pdl(qk_norm_rope_cache_kernel<bf16>, grid, dim3(warps * 32), smem, stream,
             (bf16*)q, q_stride, (bf16*)k, k_stride, (const bf16*)v, v_stride, H, Hkv, dh, q_gain,

@@ -200,8 +200,12 @@ class NormedRows:
     matrix product can hand this to `linear`, which folds the norm into the product when
     the weight-streaming kernel runs it, and computes it with the norm kernel otherwise."""
 
-    def __init__(self, h: torch.Tensor, gain: torch.Tensor, eps: float, dtype: torch.dtype):
+    def __init__(self, h: torch.Tensor, gain: torch.Tensor, eps: float, dtype: torch.dtype,
+                 delta: Optional[torch.Tensor] = None):
+        """`delta`, if given, is still to be added to h (and stays added): the norm kernel
+        does that add on its way."""
         self.h, self.gain, self.eps, self.dtype = h, gain, float(eps), dtype
+        self.delta = delta
         self._done = None
 
     @property
@@ -215,7 +219,8 @@ class NormedRows:
     def materialize(self) -> torch.Tensor:
         if self._done is None:
             out = torch.empty(self.h.shape, dtype=self.dtype, device=self.h.device)
-            add_rmsnorm(self.h, None, self.gain, self.eps, out)
+            add_rmsnorm(self.h, self.delta, self.gain, self.eps, out)
+            self.delta = None
             self._done = out
         return self._done
 
@@ -233,6 +238,9 @@ def gemm_skinny(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
     with `gated`, w is a gate/up matrix with rows interleaved in eights and out is
     silu(gate) * up, bfloat16 [M, N / 2]."""
     normed = isinstance(x, NormedRows)
+    if normed and x.delta is not None:
+        residual_add(x.h, x.delta)
+        x.delta = None
     xt = x.h if normed else x
     _need_cuda(xt, w, out)
     M, N, K = xt.shape[0], w.shape[0], w.shape[1]
@@ -378,11 +386,12 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
                     head_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
                     block_tables: torch.Tensor, positions: torch.Tensor, seq_ids: torch.Tensor,
                     tile_tok0: Optional[torch.Tensor], tile_ntok: Optional[torch.Tensor],
-                    scale: float, window: int, wide: bool, n_splits: int = 1) -> None:
+                    scale: float, window: int, wide: bool = True, n_splits: int = 1) -> None:
     """Paged causal attention on the tensor cores (bfloat16). With tile arrays (int32,
-    first token and token count of each tile, tokens of one request, at most 64 // group
-    when `wide` else 16 // group) any step; without them every token is a tile of its own
-    (decode). n_splits > 1 cuts each request's keys over that many CTAs and joins them."""
+    first token and token count of each tile, tokens of one request, at most
+    flash_tile_rows() // group of them) any step; without them every token is a tile of its
+    own (decode), and n_splits > 1 cuts each request's keys over that many CTAs and joins
+    them. (`wide` is accepted and ignored.)"""
     _need_cuda(q, out, k_cache, v_cache, block_tables, positions, seq_ids, tile_tok0, tile_ntok)
     T = q.shape[0]
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
@@ -400,7 +409,7 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
         _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
         c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(positions),
         _ptr(seq_ids), _ptr(tile_tok0), _ptr(tile_ntok), c_int(n_tiles), c_int(num_heads),
-        c_int(num_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(1 if wide else 0),
+        c_int(num_kv_heads), c_int(head_dim), c_float(scale), c_int(window),
         c_int(n_splits), _ptr(part_o), _ptr(part_ml), _stream()),
         "attention_flash", f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads})")
     if n_splits > 1:
@@ -408,6 +417,11 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
             _ptr(part_o), _ptr(part_ml), _ptr(out), c_ll(out.stride(0)), c_int(T),
             c_int(num_heads), c_int(head_dim), c_int(n_splits), _stream()),
             "attention_flash_combine")
+
+
+def flash_tile_rows() -> int:
+    """Query rows (token x head of the group) one prefill tile of the attention kernel holds."""
+    return int(load_library("attention_flash").tgo_attention_flash_tile_rows())
 
 
 def _tiles(ctx, tokens_per_tile: int):
@@ -453,7 +467,7 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
                             None, None, scale, window, wide=False,
                             n_splits=decode_splits(ctx, num_kv_heads, window))
         else:
-            tok0, ntok = _tiles(ctx, 64 // group)
+            tok0, ntok = _tiles(ctx, flash_tile_rows() // group)
             attention_flash(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
                             cache.page_size, cache.block_tables, ctx.positions, ctx.seq_ids,
                             tok0, ntok, scale, window, wide=True)

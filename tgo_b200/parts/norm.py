@@ -39,10 +39,9 @@ NORMS.register("rmsnorm", RMSNorm)
 
 
 def _lazy(self, h, delta, out_dtype):
-    """The norm of h (+ delta, added now), to be computed by whoever consumes it."""
-    if delta is not None:
-        ops.residual_add(h, delta)
-    return ops.NormedRows(h, self.gain, self.eps, out_dtype)
+    """The norm of h (+ delta, which the norm kernel adds to h on its way), to be computed
+    by whoever consumes it."""
+    return ops.NormedRows(h, self.gain, self.eps, out_dtype, delta)
 
 
 RMSNorm.lazy = _lazy
