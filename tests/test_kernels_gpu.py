@@ -530,3 +530,48 @@ def test_linear_picks_by_rows_and_agrees():
     assert torch.allclose(many[:40].float(), mid.float(), rtol=2e-2, atol=2e-2)
     assert torch.allclose(many[:5].float(), few.float(), rtol=2e-2, atol=2e-2)
     assert tc_flag() == 0
+
+
+# --------------------------------------------------------------------- chain of products
+
+
+@pytest.mark.parametrize("M,d,a_w,f,qkv_n", [(1, 64, 64, 128, 128), (3, 96, 192, 224, 320),
+                                              (5, 1000, 520, 1008, 776), (8, 2048, 1024, 3072, 1536)])
+def test_gemm_chain(M, d, a_w, f, qkv_n):
+    """o-projection into the stream, norm + gate/up + gate, down into the stream, norm + the
+    next q/k/v, as one kernel, against float32 matrix products with the same roundings.
+    Run twice: the barrier's state carries over from launch to launch."""
+    o = ops()
+
+    def bf(*s, seed):
+        return rnd(*s, scale=0.05, seed=seed).to(torch.bfloat16)
+
+    eps = 1e-6
+    h = rnd(M, d, scale=2.0, seed=1)
+    g1, g2 = 1 + 0.1 * rnd(d, seed=2), 1 + 0.1 * rnd(d, seed=3)
+    wqkv, wo = bf(qkv_n, d, seed=4), bf(d, a_w, seed=5)
+    wg, wu, wd = bf(f, d, seed=6), bf(f, d, seed=7), bf(d, f, seed=8)
+    wgu = torch.stack([wg.view(f // 8, 8, d), wu.view(f // 8, 8, d)], dim=1).reshape(2 * f, d).contiguous()
+    a = rnd(M, a_w, seed=9).to(torch.bfloat16)
+
+    def norm(x, g):
+        return ((x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)) * g).to(torch.bfloat16).float()
+
+    h_want = h + a.float() @ wo.float().t()
+    n2 = norm(h_want, g2)
+    gt = (n2 @ wg.float().t()).to(torch.bfloat16).float()
+    up = (n2 @ wu.float().t()).to(torch.bfloat16).float()
+    act_want = (gt / (1 + torch.exp(-gt)) * up).to(torch.bfloat16).float()
+    h_want = h_want + act_want @ wd.float().t()
+    qkv_want = norm(h_want, g1) @ wqkv.float().t()
+    for _ in range(2):
+        hh = h.clone()
+        act = torch.zeros(M, f, dtype=torch.bfloat16, device=DEV)
+        qkv = torch.zeros(M, qkv_n, dtype=torch.bfloat16, device=DEV)
+        o.gemm_chain([(a, wo, hh, "add"), (o.NormedRows(hh, g2, eps, torch.bfloat16), wgu, act, "gated"),
+                      (act, wd, hh, "add"), (o.NormedRows(hh, g1, eps, torch.bfloat16), wqkv, qkv, "bf16")], M)
+        torch.cuda.synchronize()
+        assert int(o.gemm_chain_error_flag(DEV).item()) == 0
+        assert torch.allclose(act.float(), act_want, rtol=3e-2, atol=3e-2 * act_want.abs().max().item())
+        assert torch.allclose(hh, h_want, rtol=1e-2, atol=1e-2 * h_want.abs().max().item())
+        assert torch.allclose(qkv.float(), qkv_want, rtol=3e-2, atol=3e-2 * qkv_want.abs().max().item())

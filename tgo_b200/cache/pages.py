@@ -163,6 +163,7 @@ class CacheManager:
         self.pools = [PagePool(n) for n in pages_per_group]
         self.slots = SlotPool(num_slots)
         self.requests: Dict[object, RequestPages] = {}
+        self._has_window = any(g.kind == "window" for g in groups)
 
     # ------------------------------------------------------------------ arithmetic
     def pages_for(self, n_tokens: int) -> int:
@@ -206,7 +207,12 @@ class CacheManager:
     def grow(self, request_id, upto: int) -> None:
         """Hold pages for every position below `upto` that a step may read or write.
         All groups together or nothing at all."""
-        self._grow(self.requests[request_id], upto, full_only=False)
+        req = self.requests[request_id]
+        # tail pages are never given back before the request ends, so a request whose tables
+        # already reach `upto` in every group needs nothing (the common decode step)
+        if upto <= min(len(t) for t in req.tables) * self.page_size:
+            return
+        self._grow(req, upto, full_only=False)
 
     def _grow(self, req: RequestPages, upto: int, full_only: bool) -> None:
         plan = []
@@ -236,6 +242,8 @@ class CacheManager:
         if new_length < req.length:
             raise ValueError("cache: a request's length cannot shrink")
         req.length = new_length
+        if not self._has_window:
+            return []
         released = []
         for g, grp in enumerate(self.groups):
             if grp.kind != "window":

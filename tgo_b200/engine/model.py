@@ -130,9 +130,19 @@ class Model:
         h = torch.empty((ctx.num_tokens, s.hidden_size), dtype=torch.float32, device=self.device)
         ops.embed(self.embedding, ctx.token_ids, h)
         pending = None
-        for ci, call in enumerate(s.run_order):
-            cache = self.layer_cache(ci, ctx, storage, group_tables, group_slots)
-            h, pending = self.blocks[call.layer].forward(h, pending, ctx, cache)
+        # a decode step of a few rows: the products of consecutive parts (and layers) are
+        # collected and run as chains in one persistent kernel each, if every block keeps to
+        # the kernels of this package
+        chained = ctx.decode_only and self.dtype == torch.bfloat16 and \
+            all(getattr(b, "chain_safe", False) for b in self.blocks) and \
+            ops.begin_chain(ctx.num_tokens)
+        try:
+            for ci, call in enumerate(s.run_order):
+                cache = self.layer_cache(ci, ctx, storage, group_tables, group_slots)
+                h, pending = self.blocks[call.layer].forward(h, pending, ctx, cache)
+        finally:
+            if chained:
+                ops.end_chain()
         n_want = ctx.logit_rows.numel()
         if n_want == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=self.device)

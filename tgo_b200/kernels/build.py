@@ -34,6 +34,7 @@ LIBRARIES = {
     "sgemm": (["sgemm.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
+    "gemm_chain": (["gemm_chain.cu"], []),
     "sampling": (["sampling.cu"], []),
 }
 

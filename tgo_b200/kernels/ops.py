@@ -24,6 +24,84 @@ class KernelError(RuntimeError):
     pass
 
 
+class _Chain:
+    """Products of a decode step that have been asked for and not launched yet."""
+
+    def __init__(self, rows: int):
+        self.rows = rows
+        self.phases = []
+
+
+_CHAIN = None
+CHAIN_MAX_ROWS = 8
+CHAIN_MAX_PHASES = 4
+USE_CHAINS = False     # measured slower than separate launches (see gemm_chain.cu); kept tested, off
+
+
+def begin_chain(rows: int) -> bool:
+    """From now until end_chain, small-batch products asked of `linear` / `gated_linear` are
+    collected and run, up to four at a time, as one persistent kernel (gemm_chain). Every
+    other kernel wrapper of this module launches what has been collected first, so the
+    order of effects stays the order of the calls. Code between begin and end must touch
+    device data through this module only (or call flush_chain first)."""
+    global _CHAIN
+    if not USE_CHAINS or rows > CHAIN_MAX_ROWS or rows <= 0:
+        return False
+    _CHAIN = _Chain(rows)
+    return True
+
+
+def flush_chain() -> None:
+    if _CHAIN is not None and _CHAIN.phases:
+        phases, _CHAIN.phases = _CHAIN.phases, []
+        gemm_chain(phases, _CHAIN.rows)
+
+
+def end_chain() -> None:
+    global _CHAIN
+    try:
+        flush_chain()
+    finally:
+        _CHAIN = None
+
+
+def _chain_take(x, w: torch.Tensor, mode: str, out_dtype, residual) -> Optional[tuple]:
+    """Collect the product if a chain is open and the kernel takes it. Returns (result,) or
+    None when the caller has to run it the ordinary way."""
+    if _CHAIN is None:
+        return None
+    normed = isinstance(x, NormedRows)
+    xt = x.h if normed else x
+    N, K = w.shape
+    M = xt.shape[0]
+    ok = (M == _CHAIN.rows and w.dtype == torch.bfloat16 and w.is_contiguous() and K % 8 == 0
+          and xt.is_contiguous() and xt.shape[1] == K and K <= 12288 and xt.data_ptr() % 16 == 0
+          and w.data_ptr() % 16 == 0)
+    if normed:
+        ok = ok and x.delta is None and x._done is None and x.dtype == torch.bfloat16
+    else:
+        ok = ok and xt.dtype == torch.bfloat16
+    if mode == "gated":
+        ok = ok and N % 16 == 0
+    elif mode == "add":
+        ok = ok and residual is not None and residual.dtype == torch.float32 and \
+            residual.is_contiguous() and residual.shape == (M, N)
+    else:
+        ok = ok and out_dtype == torch.bfloat16
+    if not ok:
+        return None
+    if len(_CHAIN.phases) >= CHAIN_MAX_PHASES:
+        flush_chain()
+    if mode == "add":
+        out = residual
+    elif mode == "gated":
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=xt.device)
+    else:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=xt.device)
+    _CHAIN.phases.append((x, w, out, mode))
+    return (None if mode == "add" else out,)
+
+
 def dtype_code(dt: torch.dtype) -> int:
     try:
         return _CODES[dt]
@@ -40,6 +118,8 @@ def _stream():
 
 
 def _need_cuda(*tensors) -> None:
+    if _CHAIN is not None and _CHAIN.phases:
+        flush_chain()          # every kernel wrapper comes through here first
     for t in tensors:
         if t is not None and not t.is_cuda:
             raise KernelError("the kernels run on a CUDA device only; got a tensor on "
@@ -219,7 +299,7 @@ class NormedRows:
     def materialize(self) -> torch.Tensor:
         if self._done is None:
             out = torch.empty(self.h.shape, dtype=self.dtype, device=self.h.device)
-            add_rmsnorm(self.h, self.delta, self.gain, self.eps, out)
+            add_rmsnorm(self.h, self.delta, self.gain, self.eps, out)      # launches a pending chain first
             self.delta = None
             self._done = out
         return self._done
@@ -324,6 +404,9 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
     keeps the accumulator's width (the logits).
     """
     out_dtype = out_dtype or x.dtype
+    taken = _chain_take(x, w, "add" if residual is not None else "bf16", out_dtype, residual)
+    if taken is not None:
+        return taken[0]
     if isinstance(x, NormedRows) and not FOLD_NORM:
         x = x.materialize()
     if _skinny_ok(x, w):
@@ -355,6 +438,10 @@ def gated_linear(x, w_gate_up: torch.Tensor, interleaved: bool) -> torch.Tensor:
     rows then the up rows, or (`interleaved`) eight gate rows and the eight matching up rows
     in turn, which lets the bfloat16 kernels apply the gate in their epilogue."""
     M, f = x.shape[0], w_gate_up.shape[0] // 2
+    if interleaved:
+        taken = _chain_take(x, w_gate_up, "gated", torch.bfloat16, None)
+        if taken is not None:
+            return taken[0]
     if isinstance(x, NormedRows) and not FOLD_NORM:
         x = x.materialize()
     if interleaved and _skinny_ok(x, w_gate_up):
@@ -568,3 +655,63 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
                            c_int(1 if transpose else 0), c_int(splits), _ptr(ws),
                            _ptr(gemm_tc_error_flag(x.device)), _stream()), "gemm_tc",
            f"(M={M}, N={N}, K={K})")
+
+
+# ------------------------------------------------------------------ chains of products
+_chain_state = {}
+
+
+def _chain_buffers(device):
+    """Per device: the grid barrier's two counters (they reset themselves) and an error flag."""
+    key = torch.device(device).index or 0
+    if key not in _chain_state:
+        _chain_state[key] = (torch.zeros(2, dtype=torch.int32, device=device),
+                             torch.zeros(1, dtype=torch.int32, device=device))
+    return _chain_state[key]
+
+
+def gemm_chain_error_flag(device) -> torch.Tensor:
+    """Set to 7 if a grid barrier of a product chain ever gave up waiting."""
+    return _chain_buffers(device)[1]
+
+
+def gemm_chain(phases, M: int) -> None:
+    """Run up to four small-batch products back to back in one persistent kernel.
+
+    phases: list of (x, w, out, mode) with
+      x     bfloat16 [M, K], or NormedRows over the float32 [M, K] stream (norm folded in);
+      w     bfloat16 [N, K];
+      out   per mode: "bf16" -> bfloat16 [M, N]; "add" -> float32 [M, N] the product is added
+            to; "gated" -> bfloat16 [M, N / 2] = silu(gate) * up, w interleaved in eights.
+    A phase may read what an earlier phase of the same chain wrote (a grid barrier stands
+    between phases). M <= 8."""
+    import struct
+    rows = []
+    dev = None
+    for x, w, out, mode in phases:
+        normed = isinstance(x, NormedRows)
+        xt = x.h if normed else x
+        _need_cuda(xt, w, out)
+        dev = xt.device
+        N, K = w.shape
+        assert xt.shape == (M, K) and xt.is_contiguous() and w.is_contiguous() and out.is_contiguous()
+        assert w.dtype == torch.bfloat16 and xt.dtype == (torch.float32 if normed else torch.bfloat16)
+        if mode == "bf16":
+            assert out.dtype == torch.bfloat16 and out.shape == (M, N)
+            ok = 0
+        elif mode == "add":
+            assert out.dtype == torch.float32 and out.shape == (M, N)
+            ok = 2
+        elif mode == "gated":
+            assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2) and N % 16 == 0
+            ok = 3
+        else:
+            raise KernelError(f"gemm_chain: unknown output mode {mode!r}")
+        eps_bits = struct.unpack("<I", struct.pack("<f", x.eps if normed else 0.0))[0]
+        rows += [xt.data_ptr(), x.gain.data_ptr() if normed else 0, w.data_ptr(), out.data_ptr(),
+                 eps_bits, 0 if normed else 1, ok, N, K]
+    arr = (ctypes.c_longlong * len(rows))(*rows)
+    barrier, err = _chain_buffers(dev)
+    lib = load_library("gemm_chain")
+    _check(lib.tgo_gemm_chain(arr, c_int(len(phases)), c_int(M), _ptr(barrier), _ptr(err), _stream()),
+           "gemm_chain", f"({len(phases)} phases, M={M})")

@@ -24,6 +24,7 @@ from .base import CacheNeed, LayerCache, Part
 
 class GQAAttention(Part):
     takes_normed_rows = True      # its first step is a matrix product: the norm may fold in
+    chain_safe = True             # touches device data through kernels/ops.py only
 
     def __init__(self, spec: MixerSpec, hidden: int, prefix: str, device=None):
         self.hidden = hidden
@@ -95,7 +96,8 @@ class GQAAttention(Part):
                                    cache.v if k is not None else None, cache.page_size)
         else:
             # a position encoding this kernel does not know: norm, then the encoding's own
-            # code, then the store
+            # code (which may use anything: products still pending must have run), then the store
+            ops.flush_chain()
             if self.qk_norm:
                 ops.qk_norm_rope_cache(q, k, None, H, Hkv, dh, self.q_gain, self.k_gain,
                                        self.eps, None, 0, None, None, None, 0)

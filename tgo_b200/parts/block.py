@@ -32,6 +32,11 @@ class PreNormResidual(Part):
         self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(
             spec.feed_forward, hidden, p + names["feed_forward"], device)
         # a part whose forward takes `residual` may add its result to the stream itself
+        # every part reaches the device through the package's kernels only: its products may
+        # be collected into chains (see kernels/ops.py begin_chain)
+        self.chain_safe = all(getattr(part, "chain_safe", False)
+                              for part in (self.mixer, self.feed_forward)) and \
+            hasattr(self.norm1, "lazy") and hasattr(self.norm2, "lazy")
         self._mixer_adds = "residual" in inspect.signature(self.mixer.forward).parameters
         self._ffn_adds = "residual" in inspect.signature(self.feed_forward.forward).parameters
 

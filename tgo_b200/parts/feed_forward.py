@@ -28,6 +28,7 @@ class SwiGLU(Part):
                 WeightSpec(p + "down_proj.weight", (self.hidden, self.inter))]
 
     takes_normed_rows = True      # its first step is a matrix product: the norm may fold in
+    chain_safe = True             # touches device data through kernels/ops.py only
 
     def bind(self, weights):
         p = self.prefix
