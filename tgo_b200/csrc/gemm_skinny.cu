@@ -2,9 +2,15 @@
 // decode step, which are bound by streaming W from HBM once.
 //
 // The weight rows sit on the M axis of mma.sync m16n8k16 and the batch on its N axis.
-// A CTA of 8 warps owns 16 rows of W (one m16 tile); each warp takes one eighth of K and the
-// eight partial tiles are added in shared memory in warp order, so the result does not
-// depend on timing. Both operands go from global memory straight into fragments with
+// A CTA of 8 warps owns 16 rows of W (one m16 tile); each warp takes an equal share of K and
+// the partial tiles are added in shared memory in warp order, so the result does not depend
+// on timing. What bounds the kernel is how many bytes of W are on their way from HBM at any
+// moment, so a thread keeps two small sets of weight registers and loads one while it
+// multiplies the other; the sets are small enough (80 registers a thread) for three CTAs on
+// an SM. MEASURED on B200, Qwen3-8B layer shapes at 8 rows, the four products of a layer:
+// one set of 8 loads, 92 us; two sets of 8 (110 registers, two CTAs), 100 us; two sets of 4,
+// 83 us; 16 warps a CTA for the narrow matrices, 89 us; W through TMA boxes of 16 rows x 128
+// bytes into per-warp rings, 92-121 us (the vocabulary product fell from 5.8 to 3.2 TB/s). Both operands go from global memory straight into fragments with
 // 16-byte loads: the sum over k may run in any order as long as W and x agree on it, so a
 // thread's eight consecutive k values serve as the (2t, 2t+1) and (2t+8, 2t+9) pairs of two
 // k-steps. W is read with a no-allocate hint (each byte is used once); x stays cached.
@@ -18,8 +24,9 @@
 // rows, ...), silu(gate) * up as bfloat16 [M, N/2].
 #include "common.cuh"
 
-#define GS_WARPS 8
-#define GS_UNROLL 4
+#ifndef GS_UNROLL
+#define GS_UNROLL 2
+#endif
 
 #define GS_X_BF16 0
 #define GS_X_NORM 1
@@ -63,7 +70,7 @@ __device__ __forceinline__ uint4 load_x(const void* __restrict__ x, const float*
     return z;
 }
 
-template <int MT, int XMODE, int OMODE>
+template <int MT, int XMODE, int OMODE, int GS_WARPS>
 __global__ void __launch_bounds__(GS_WARPS * 32)
 gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, float eps,
                    const bf16* __restrict__ w, void* __restrict__ y, int M, int N, int K) {
@@ -80,34 +87,24 @@ gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, f
     const bf16* w_lo = w + (size_t)(row_lo < N ? row_lo : 0) * K;
     const bf16* w_hi = w + (size_t)(row_hi < N ? row_hi : 0) * K;
     const bool ok_lo = row_lo < N, ok_hi = row_hi < N;
+    constexpr int STEP = 32 * GS_UNROLL;
 
     float acc[MT][4];
     float ss[MT];
 #pragma unroll
     for (int j = 0; j < MT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; ss[j] = 0.f; }
 
-    // The weights depend on no earlier kernel: the first loads go out before this kernel
-    // waits for the one that makes x, so the stream from HBM is already running when it ends.
-    uint4 a_lo[GS_UNROLL], a_hi[GS_UNROLL];
+    uint4 a_lo[GS_UNROLL], a_hi[GS_UNROLL], b_lo[GS_UNROLL], b_hi[GS_UNROLL];
+    auto load_w = [&](uint4 (&lo)[GS_UNROLL], uint4 (&hi)[GS_UNROLL], int k) {
 #pragma unroll
-    for (int u = 0; u < GS_UNROLL; ++u) {
-        const int kk = k_begin + u * 32 + 8 * t;
-        const bool v = kk < k_end;
-        a_lo[u] = (v && ok_lo) ? ldg_stream(w_lo + kk) : make_uint4(0u, 0u, 0u, 0u);
-        a_hi[u] = (v && ok_hi) ? ldg_stream(w_hi + kk) : make_uint4(0u, 0u, 0u, 0u);
-    }
-    pdl_wait();
-
-    for (int k = k_begin; k < k_end; k += 32 * GS_UNROLL) {
-        if (k > k_begin) {
-#pragma unroll
-            for (int u = 0; u < GS_UNROLL; ++u) {
-                const int kk = k + u * 32 + 8 * t;
-                const bool v = kk < k_end;
-                a_lo[u] = (v && ok_lo) ? ldg_stream(w_lo + kk) : make_uint4(0u, 0u, 0u, 0u);
-                a_hi[u] = (v && ok_hi) ? ldg_stream(w_hi + kk) : make_uint4(0u, 0u, 0u, 0u);
-            }
+        for (int u = 0; u < GS_UNROLL; ++u) {
+            const int kk = k + u * 32 + 8 * t;
+            const bool v = kk < k_end;
+            lo[u] = (v && ok_lo) ? ldg_stream(w_lo + kk) : make_uint4(0u, 0u, 0u, 0u);
+            hi[u] = (v && ok_hi) ? ldg_stream(w_hi + kk) : make_uint4(0u, 0u, 0u, 0u);
         }
+    };
+    auto multiply = [&](const uint4 (&lo)[GS_UNROLL], const uint4 (&hi)[GS_UNROLL], int k) {
 #pragma unroll
         for (int u = 0; u < GS_UNROLL; ++u) {
             const int kk = k + u * 32 + 8 * t;
@@ -115,10 +112,21 @@ gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, f
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
                 const uint4 b = load_x<XMODE>(x, gain, j * 8 + g, M, K, kk, v, ss[j]);
-                mma_bf16_16816(acc[j], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b.x, b.y);
-                mma_bf16_16816(acc[j], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b.z, b.w);
+                mma_bf16_16816(acc[j], lo[u].x, hi[u].x, lo[u].y, hi[u].y, b.x, b.y);
+                mma_bf16_16816(acc[j], lo[u].z, hi[u].z, lo[u].w, hi[u].w, b.z, b.w);
             }
         }
+    };
+    // The weights depend on no earlier kernel: the first loads go out before this kernel
+    // waits for the one that makes x, so the stream from HBM is already running when it ends.
+    load_w(a_lo, a_hi, k_begin);
+    load_w(b_lo, b_hi, k_begin + STEP);
+    pdl_wait();
+    for (int k = k_begin; k < k_end; k += 2 * STEP) {
+        multiply(a_lo, a_hi, k);
+        load_w(a_lo, a_hi, k + 2 * STEP);
+        if (k + STEP < k_end) multiply(b_lo, b_hi, k + STEP);
+        load_w(b_lo, b_hi, k + 3 * STEP);
     }
     pdl_launch_late();
     // partial tiles -> shared memory: [warp][row of W][batch row]
@@ -182,31 +190,31 @@ gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, f
     }
 }
 
-template <int MT, int XMODE>
+template <int MT, int XMODE, int WARPS>
 static int gs_launch_o(const void* x, const float* gain, float eps, const bf16* w, void* y, int M,
                        int N, int K, int omode, cudaStream_t s) {
-    const dim3 grid((N + 15) / 16), block(GS_WARPS * 32);
+    const dim3 grid((N + 15) / 16), block(WARPS * 32);
     switch (omode) {
         case GS_OUT_BF16:
-            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_BF16>, grid, block, 0, s, x,
-                                  gain, eps, w, y, M, N, K);
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_BF16, WARPS>, grid, block, 0,
+                                  s, x, gain, eps, w, y, M, N, K);
         case GS_OUT_F32:
-            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_F32>, grid, block, 0, s, x,
-                                  gain, eps, w, y, M, N, K);
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_F32, WARPS>, grid, block, 0,
+                                  s, x, gain, eps, w, y, M, N, K);
         case GS_OUT_ADD_F32:
-            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_ADD_F32>, grid, block, 0, s,
-                                  x, gain, eps, w, y, M, N, K);
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_ADD_F32, WARPS>, grid, block,
+                                  0, s, x, gain, eps, w, y, M, N, K);
         default:
-            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_SWIGLU>, grid, block, 0, s,
-                                  x, gain, eps, w, y, M, N, K);
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_SWIGLU, WARPS>, grid, block,
+                                  0, s, x, gain, eps, w, y, M, N, K);
     }
 }
 
 template <int MT>
 static int gs_launch(const void* x, const float* gain, float eps, const bf16* w, void* y, int M,
                      int N, int K, int xmode, int omode, cudaStream_t s) {
-    if (xmode == GS_X_BF16) return gs_launch_o<MT, GS_X_BF16>(x, gain, eps, w, y, M, N, K, omode, s);
-    return gs_launch_o<MT, GS_X_NORM>(x, gain, eps, w, y, M, N, K, omode, s);
+    if (xmode == GS_X_BF16) return gs_launch_o<MT, GS_X_BF16, 8>(x, gain, eps, w, y, M, N, K, omode, s);
+    return gs_launch_o<MT, GS_X_NORM, 8>(x, gain, eps, w, y, M, N, K, omode, s);
 }
 
 // Most rows this kernel takes; K must be a multiple of 8 (16-byte loads).
