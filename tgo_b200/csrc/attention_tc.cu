@@ -1,0 +1,536 @@
+// Paged causal attention for prompt portions on the tcgen05 tensor cores (head size 128,
+// bfloat16): S = Q K^T and O += P V are tcgen05.mma with the accumulators in tensor memory,
+// K and V pages come in by TMA, and the softmax runs in registers between the two.
+//
+// A CTA owns one tile of 128 query rows: the G query heads that share a kv head, for 128 / G
+// consecutive tokens of one request (row r = token r / G, head r % G), so K and V are read
+// once for the whole group. It walks the request's keys in tiles of 128.
+//
+//   warp 0      producer: asks TMA for the pages of the next K and V tiles, one page per lane
+//               (a page is two boxes of page_size rows x 64 columns, 128-byte swizzle; the
+//               pages of a tile lie one after the other in shared memory, which is the
+//               K-major layout for K and the MN-major layout for V that the tensor core wants);
+//   warp 1      issuer: one lane issues S_j = Q K_j^T (8 k-steps) into one of two S buffers in
+//               tensor memory, one tile ahead of the softmax, and O += P_j V_j with P read
+//               from tensor memory (two products of 64 output columns, 8 k-steps each);
+//   warps 2-9   softmax: two threads per row, one for keys 0..63 of the tile and one for keys
+//               64..127 (warps 2-5 and 6-9). Each reads its half row of S (64 float32), masks,
+//               takes the maximum, swaps it with its partner through shared memory, writes
+//               P = exp2(S * scale - m) as bfloat16 over the first half of the S buffer, and
+//               keeps its part of the row sum. The running maximum is only moved when
+//               some row of the warp has grown by more than 2^8 since it was set; then the
+//               rows of O in tensor memory are rescaled. (The result is the same: the factor
+//               cancels in O / l; only the range of P changes, and 2^8 is far from overflow.)
+//
+// Tensor memory (512 columns): S0 0..127, S1 128..255, O 256..383; P_j lies over S_j.
+// Rows of V that no query may read (past the request's end in its last page, before the
+// window) are zeroed in shared memory before P V: P is zero there, but the cache may hold
+// anything, NaN included. Keys of K in such rows give S values that the mask replaces.
+//
+// Every wait has a time limit (about two seconds): it records a code, the CTA stops issuing,
+// frees its tensor memory and returns. No cluster, no multicast.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+#define AT_BM 128
+#define AT_BN 128
+#define AT_DH 128
+#define AT_THREADS 320
+#define AT_SOFTMAX_THREADS 256
+#define AT_WAIT_CYCLES 4000000000ll
+#define AT_BLOCK_BYTES (128 * 64 * 2)          // 128 rows x 64 columns of bf16
+#define AT_TILE_BYTES (2 * AT_BLOCK_BYTES)     // a Q, K or V tile: two column halves
+#define AT_PAGES_CAP 4096
+
+__device__ int at_error_flag = 0;
+
+__device__ __forceinline__ uint32_t at_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void at_mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(at_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void at_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(at_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void at_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(at_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool at_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(at_smem(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity, int code) {
+    if (at_try(bar, parity)) return true;
+    const long long start = clock64();
+    while (!at_try(bar, parity)) {
+        if (clock64() - start > AT_WAIT_CYCLES) {
+            atomicExch(&at_error_flag, code);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void at_tma_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(at_smem(dst)), "l"(map), "r"(at_smem(bar)), "r"(x), "r"(y) : "memory");
+}
+// operands in shared memory -> accumulator in tensor memory
+__device__ __forceinline__ void at_mma_ss(uint32_t d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// A in tensor memory, B in shared memory
+__device__ __forceinline__ void at_mma_ts(uint32_t d, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void at_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void at_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void at_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory operand descriptor, rows of 128 bytes with the 128-byte swizzle, groups of 8
+// rows 1024 bytes apart. For a K-major operand the rows are the M or N index; for an MN-major
+// one (V) the rows are the k index and the 64 columns one block of N. Both offsets hold the
+// distance between 8-row groups: whichever the unit takes for that direction, it is right,
+// and the other direction has extent one.
+__device__ __forceinline__ uint64_t at_desc(const void* tile) {
+    uint64_t d = (uint64_t)((at_smem(tile) & 0x3ffff) >> 4);
+    d |= (uint64_t)(1024 >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ void at_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void at_tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+          "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+          "r"(r[30]), "r"(r[31]), "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *(uint32_t*)&v;
+}
+
+// error codes: 1 producer, 2 issuer, 3 softmax
+__global__ void __launch_bounds__(AT_THREADS)
+attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                            long long out_stride, int page_size, int page_shift,
+                            const int* __restrict__ block_tables, int max_blocks,
+                            const int* __restrict__ positions, const int* __restrict__ seq_ids,
+                            const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok, int H,
+                            int Hkv, float scale_log2, int window) {
+    extern __shared__ unsigned char at_raw[];
+    unsigned char* base = (unsigned char*)(((uintptr_t)at_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = base;                                   // [2 halves][128 rows][128 B]
+    unsigned char* sK = sQ + AT_TILE_BYTES;                     // [2 stages][2 halves][128][128 B]
+    unsigned char* sV = sK + 2 * AT_TILE_BYTES;                 // [2 stages][2 halves][128][128 B]
+    uint64_t* bars = (uint64_t*)(sV + 2 * AT_TILE_BYTES);
+    uint64_t* k_full = bars;            // [2]
+    uint64_t* k_empty = bars + 2;       // [2]
+    uint64_t* v_full = bars + 4;        // [2]
+    uint64_t* v_empty = bars + 6;       // [2]
+    uint64_t* s_full = bars + 8;        // [2]
+    uint64_t* p_full = bars + 10;       // [2]
+    uint64_t* o_done = bars + 12;       // [1]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 13);
+    float* s_xm = (float*)(bars + 14);  // [2 tile parities][2 halves][128 rows] row maxima
+    float* s_xl = s_xm + 512;           // [2 halves][128 rows] row sums at the end
+    int* s_pages = (int*)(s_xl + 256);  // [AT_PAGES_CAP]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // later tiles of a request read more keys: they start first
+    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
+    const int G = H / Hkv;
+    const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
+    const int n_rows = ntok * G;
+    const int p0 = positions[tok0];
+    if (p0 < 0) {                              // a request that brings nothing: zeros out
+        for (int i = tid; i < n_rows * AT_DH; i += AT_THREADS) {
+            const int r = i / AT_DH, d = i % AT_DH;
+            out[(size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * AT_DH + d] = __float2bfloat16_rn(0.f);
+        }
+        return;
+    }
+    const int* bt = block_tables + (size_t)seq_ids[tok0] * max_blocks;
+    const int p_last = p0 + ntok - 1;
+    const int key_lo = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+    const int key_hi = p_last + 1;
+    const int t_lo = key_lo / AT_BN, t_hi = (key_hi + AT_BN - 1) / AT_BN;
+    const int n_it = t_hi - t_lo;
+    const int pages_per_tile = AT_BN >> page_shift;
+    const int pg_lo = t_lo * pages_per_tile;
+
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) {
+            at_mbar_init(&k_full[i], 1); at_mbar_init(&k_empty[i], 1);
+            at_mbar_init(&v_full[i], 1); at_mbar_init(&v_empty[i], 1);
+            at_mbar_init(&s_full[i], 1); at_mbar_init(&p_full[i], 8);
+        }
+        at_mbar_init(o_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(at_smem(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // this tile's slice of the block table
+    {
+        int pg_hi = t_hi * pages_per_tile;
+        if (pg_hi > max_blocks) pg_hi = max_blocks;
+        if (pg_hi - pg_lo > AT_PAGES_CAP) pg_hi = pg_lo + AT_PAGES_CAP;
+        for (int i = pg_lo + tid; i < pg_hi; i += AT_THREADS) s_pages[i - pg_lo] = bt[i];
+    }
+    // Q rows -> shared memory in the swizzled K-major layout; rows past the tile are zeros
+    for (int i = tid; i < AT_BM * 16; i += AT_THREADS) {
+        const int r = i >> 4, c = i & 15;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < n_rows)
+            v = *(const uint4*)(q + (size_t)(tok0 + r / G) * q_stride + (size_t)(kvh * G + r % G) * AT_DH + c * 8);
+        *(uint4*)(sQ + (c >> 3) * AT_BLOCK_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    at_fence_before();
+    __syncthreads();
+    at_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tm_s[2] = {tmem, tmem + 128u};
+    const uint32_t tm_o = tmem + 256u;
+
+    if (warp == 0) {
+        auto page_of = [&](int pi) { return pi - pg_lo < AT_PAGES_CAP ? s_pages[pi - pg_lo] : bt[pi]; };
+        bool ok = true;
+        for (int it = 0; it < n_it; ++it) {
+            const int s = it & 1;
+            const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+            const int j = t_lo + it;
+            // pages of this tile that hold a key some row may read
+            int first = j * pages_per_tile, last = first + pages_per_tile;      // [first, last)
+            while (first < last && (first + 1) * page_size <= key_lo) ++first;
+            while (last > first && (last - 1) * page_size >= key_hi) --last;
+            const uint32_t bytes = (uint32_t)(last - first) * (uint32_t)page_size * 256u;
+            ok = __all_sync(0xffffffffu, ok && at_wait(&k_empty[s], ph ^ 1u, 1));
+            if (!ok) break;
+            if (lane == 0) at_expect_tx(&k_full[s], bytes);
+            __syncwarp();
+            for (int pi = first + lane; pi < last; pi += 32) {
+                const int row = (page_of(pi) * Hkv + kvh) * page_size;
+                unsigned char* dst = sK + s * AT_TILE_BYTES + (pi - j * pages_per_tile) * page_size * 128;
+                at_tma_2d(dst, &map_k, 0, row, &k_full[s]);
+                at_tma_2d(dst + AT_BLOCK_BYTES, &map_k, 64, row, &k_full[s]);
+            }
+            ok = __all_sync(0xffffffffu, at_wait(&v_empty[s], ph ^ 1u, 1));
+            if (!ok) break;
+            if (lane == 0) at_expect_tx(&v_full[s], bytes);
+            __syncwarp();
+            for (int pi = first + lane; pi < last; pi += 32) {
+                const int row = (page_of(pi) * Hkv + kvh) * page_size;
+                unsigned char* dst = sV + s * AT_TILE_BYTES + (pi - j * pages_per_tile) * page_size * 128;
+                at_tma_2d(dst, &map_v, 0, row, &v_full[s]);
+                at_tma_2d(dst + AT_BLOCK_BYTES, &map_v, 64, row, &v_full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // float32 accumulate, bf16 x bf16, M = 128; S: N = 128, both K-major;
+            // O: N = 64 per product, B (V) MN-major
+            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) |
+                                      ((uint32_t)(128 >> 4) << 24);
+            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                                      ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            const uint64_t dq0 = at_desc(sQ), dq1 = at_desc(sQ + AT_BLOCK_BYTES);
+            bool ok = true;
+            auto issue_qk = [&](int it) {
+                const int s = it & 1;
+                if (!at_wait(&k_full[s], (uint32_t)(it >> 1) & 1u, 2)) return false;
+                at_fence_after();
+                const uint64_t dk0 = at_desc(sK + s * AT_TILE_BYTES), dk1 = at_desc(sK + s * AT_TILE_BYTES + AT_BLOCK_BYTES);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) at_mma_ss(tm_s[s], dq0 + 2 * k, dk0 + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) at_mma_ss(tm_s[s], dq1 + 2 * k, dk1 + 2 * k, idesc_qk, 1u);
+                at_commit(&k_empty[s]);
+                at_commit(&s_full[s]);
+                return true;
+            };
+            if (n_it > 0) ok = issue_qk(0);
+            for (int it = 0; it < n_it && ok; ++it) {
+                const int s = it & 1;
+                const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+                if (it + 1 < n_it) ok = issue_qk(it + 1);
+                if (!ok) break;
+                ok = at_wait(&p_full[s], ph, 2) && at_wait(&v_full[s], ph, 2);
+                if (!ok) break;
+                at_fence_after();
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint64_t dv = at_desc(sV + s * AT_TILE_BYTES + h * AT_BLOCK_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)           // 16 keys = 2 groups of 8 rows = 2048 bytes
+                        at_mma_ts(tm_o + 64u * h, tm_s[s] + 8u * k, dv + (uint64_t)(128 * k), idesc_pv,
+                                  (it > 0 || k > 0) ? 1u : 0u);
+                }
+                at_commit(&v_empty[s]);
+                at_commit(o_done);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;              // the 32 lanes of tensor memory this warp may touch
+        const int half = (warp - 2) >> 2;          // keys 0..63 or 64..127 of every tile
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const bool row_ok = row < n_rows;
+        const int pos = row_ok ? p0 + row / G : -1;
+        const int vis_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        // the warp's rows: lowest position and highest window start, for the "no mask" test
+        const int warp_first = quarter * 32, warp_last = quarter * 32 + 31;
+        const bool warp_rows_ok = warp_last < n_rows;
+        const int warp_pos_min = p0 + warp_first / G;
+        const int warp_pos_max = p0 + (warp_last < n_rows ? warp_last : n_rows - 1) / G;
+        const int warp_vis_max = (window > 0 && warp_pos_max - window + 1 > 0) ? warp_pos_max - window + 1 : 0;
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int it = 0; it < n_it; ++it) {
+            const int s = it & 1;
+            const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+            const int kbase = (t_lo + it) * AT_BN + 64 * half;
+            if (ok) ok = at_wait(&s_full[s], ph, 3);
+            at_fence_after();
+            float sc[64];
+            {
+                uint32_t r0[32], r1[32];
+                at_tmem_ld32(tm_s[s] + lane_base + 64u * half, r0);
+                at_tmem_ld32(tm_s[s] + lane_base + 64u * half + 32u, r1);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 32; ++i) { sc[i] = __uint_as_float(r0[i]); sc[32 + i] = __uint_as_float(r1[i]); }
+            }
+            const bool full = warp_rows_ok && kbase + 63 <= warp_pos_min && kbase >= warp_vis_max;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (full) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) { sc[i] *= scale_log2; mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]); }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    const int key = kbase + i;
+                    sc[i] = (key <= pos && key >= vis_lo) ? sc[i] * scale_log2 : -INFINITY;
+                    mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
+                }
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // the other half of the row: both threads of a row end up with the same maximum
+            float* xm = s_xm + (it & 1) * 256;
+            xm[half * 128 + row] = mx;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            mx = fmaxf(mx, xm[(half ^ 1) * 128 + row]);
+            const float m_new = fmaxf(m_used, mx);
+            const bool grow = m_new > m_used + 8.f || (m_used == -INFINITY && m_new != -INFINITY);
+            const bool rescale = __any_sync(0xffffffffu, grow);
+            float corr = 1.f;
+            if (rescale) {
+                corr = m_new == -INFINITY ? 1.f : exp2f(m_used - m_new);       // exp2(-inf) = 0 for a first value
+                m_used = m_new;
+            }
+            const float base_m = m_used == -INFINITY ? 0.f : m_used;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            {
+                uint32_t r[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float a = exp2f(sc[2 * i] - base_m), b = exp2f(sc[2 * i + 1] - base_m);
+                    sum4[i & 3] += a + b;
+                    r[i] = at_pack(a, b);
+                }
+                at_tmem_st32(tm_s[s] + lane_base + 32u * half, r);
+            }
+            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            // rows of V that nobody may read: zeros (this thread's half of its row of the tile)
+            const int tile_lo = (t_lo + it) * AT_BN;
+            if (tile_lo + AT_BN > key_hi || tile_lo < key_lo) {
+                if (ok) ok = at_wait(&v_full[s], ph, 3);
+                const int key = tile_lo + row;
+                if (key >= key_hi || key < key_lo) {
+                    unsigned char* vrow = sV + s * AT_TILE_BYTES + half * AT_BLOCK_BYTES + row * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) *(uint4*)(vrow + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            if (it > 0) {
+                if (ok) ok = at_wait(o_done, (uint32_t)(it - 1) & 1u, 3);       // P_{it-1} V_{it-1} is in O
+                at_fence_after();
+                if (rescale) {
+                    uint32_t r[32];
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        at_tmem_ld32(tm_o + lane_base + 64u * half + 32u * c, r);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+                        at_tmem_st32(tm_o + lane_base + 64u * half + 32u * c, r);
+                    }
+                }
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            at_fence_before();
+            // a wait that ran out: nothing is signalled any more (the issuer's own wait runs
+            // out in turn), but every thread keeps walking the loop, so that the barriers and
+            // the warp-wide loads and stores above stay matched
+            ok = __all_sync(0xffffffffu, ok);
+            if (lane == 0 && ok) at_arrive(&p_full[s]);
+        }
+        if (ok && n_it > 0) ok = at_wait(o_done, (uint32_t)(n_it - 1) & 1u, 3);
+        at_fence_after();
+        s_xl[half * 128 + row] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        l += s_xl[(half ^ 1) * 128 + row];
+        // every lane takes part in the loads from tensor memory (they are warp-wide); only
+        // the rows of the tile are written
+        const bool warp_ok = __all_sync(0xffffffffu, ok);
+        if (warp_ok) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* dst = out + (size_t)(tok0 + (row_ok ? row : 0) / G) * out_stride +
+                        (size_t)(kvh * G + (row_ok ? row : 0) % G) * AT_DH + 64 * half;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t r[32];
+                at_tmem_ld32(tm_o + lane_base + 64u * half + 32u * c, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 v;
+                        v.x = at_pack(__uint_as_float(r[8 * i]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
+                        v.y = at_pack(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
+                        v.z = at_pack(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
+                        v.w = at_pack(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
+                        *(uint4*)(dst + c * 32 + i * 8) = v;
+                    }
+                }
+            }
+        }
+    }
+    at_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        at_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------ host
+typedef CUresult (*AtEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                               CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                               CUtensorMapFloatOOBfill);
+
+// The tensor map of one layer's K or V pages, [rows, 128] bf16 in boxes of page_size x 64;
+// made once per (address, rows, page size) and kept.
+static const CUtensorMap* at_map_of(const void* pages, long long rows, int page_size) {
+    static std::mutex lock;
+    static std::unordered_map<uint64_t, CUtensorMap> maps;
+    static AtEncodeFn encode = nullptr;
+    std::lock_guard<std::mutex> hold(lock);
+    if (!encode) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess ||
+            qr != cudaDriverEntryPointSuccess)
+            return nullptr;
+        encode = (AtEncodeFn)p;
+    }
+    const uint64_t key = (uint64_t)(uintptr_t)pages ^ ((uint64_t)rows * 0x9e3779b97f4a7c15ull) ^ ((uint64_t)page_size << 56);
+    auto it = maps.find(key);
+    if (it != maps.end()) return &it->second;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {AT_DH, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {AT_DH * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    const cuuint32_t elem[2] = {1, 1};
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return nullptr;
+    return &maps.emplace(key, map).first->second;
+}
+
+// 1 if this kernel takes the shape: head size 128, a group that divides 128, pages of 8, 16,
+// 32, 64 or 128 tokens.
+TGO_API int tgo_attention_tc_supports(int dh, int group, int page_size) {
+    const bool g_ok = group == 1 || group == 2 || group == 4 || group == 8 || group == 16;
+    const bool p_ok = page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
+    return dh == AT_DH && g_ok && p_ok;
+}
+
+// Reads (and waits for the device to reach) the code a wait that ran out left; 0: none did.
+TGO_API int tgo_attention_tc_error(int* value) {
+    return (int)cudaMemcpyFromSymbol(value, at_error_flag, sizeof(int));
+}
+
+// Prompt portions: tiles of up to 128 / group consecutive tokens of one request each
+// (tile_tok0, tile_ntok). k_cache and v_cache: [n_pages, Hkv, page_size, 128] bf16.
+TGO_API int tgo_attention_tc_prefill(const void* q, long long q_stride, void* out, long long out_stride,
+                                     const void* k_cache, const void* v_cache, int n_pages, int page_size,
+                                     const int* block_tables, int max_blocks, const int* positions,
+                                     const int* seq_ids, const int* tile_tok0, const int* tile_ntok,
+                                     int n_tiles, int H, int Hkv, int dh, float scale, int window,
+                                     cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (H <= 0 || Hkv <= 0 || H % Hkv || !tgo_attention_tc_supports(dh, H / Hkv, page_size) || n_pages <= 0 ||
+        max_blocks <= 0 || window < 0 || Hkv > 65535 || !tile_tok0 || !tile_ntok || q_stride % 8 ||
+        out_stride % 8 || ((uintptr_t)q % 16) || ((uintptr_t)out % 16) || ((uintptr_t)k_cache % 128) ||
+        ((uintptr_t)v_cache % 128))
+        return TGO_E_BAD_ARG;
+    const long long rows = (long long)n_pages * Hkv * page_size;
+    if (rows > 0x7fffffffll) return TGO_E_BAD_ARG;
+    const CUtensorMap* mk = at_map_of(k_cache, rows, page_size);
+    const CUtensorMap* mv = at_map_of(v_cache, rows, page_size);
+    if (!mk || !mv) return TGO_E_BAD_ARG;
+    constexpr size_t smem = 1024 + 5 * (size_t)AT_TILE_BYTES + 14 * 8 + 768 * sizeof(float) + AT_PAGES_CAP * sizeof(int);
+    static bool once = false;
+    if (!once) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_prefill_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        once = true;
+    }
+    int shift = 0;
+    while ((1 << shift) < page_size) ++shift;
+    attention_tc_prefill_kernel<<<dim3(n_tiles, Hkv), AT_THREADS, smem, stream>>>(
+        *mk, *mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_size, shift, block_tables, max_blocks,
+        positions, seq_ids, tile_tok0, tile_ntok, H, Hkv, scale * 1.4426950408889634f, window);
+    return launch_status();
+}

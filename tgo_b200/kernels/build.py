@@ -31,6 +31,7 @@ LIBRARIES = {
     "elementwise": (["elementwise.cu"], []),
     "attention_generic": (["attention_generic.cu"], []),
     "attention_flash": (["attention_flash.cu"], []),
+    "attention_tc": (["attention_tc.cu"], []),
     "sgemm": (["sgemm.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),

@@ -506,6 +506,46 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
             "attention_flash_combine")
 
 
+USE_TC_ATTENTION = True     # prompt portions with head size 128 on the tcgen05 kernel
+TC_ATTENTION_MIN_TOKENS = 1  # steps with fewer tokens than this keep the mma.sync kernel
+
+
+def attention_tc_supports(head_dim: int, group: int, page_size: int) -> bool:
+    return bool(load_library("attention_tc").tgo_attention_tc_supports(c_int(head_dim), c_int(group),
+                                                                       c_int(page_size)))
+
+
+def attention_tc_error() -> int:
+    """The code a wait of the tcgen05 attention kernel left when it ran out (1 producer,
+    2 issuer, 3 softmax), or 0. Synchronises with the device."""
+    value = ctypes.c_int(0)
+    _check(load_library("attention_tc").tgo_attention_tc_error(ctypes.byref(value)), "attention_tc_error")
+    return int(value.value)
+
+
+def attention_tc_prefill(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
+                         head_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
+                         block_tables: torch.Tensor, positions: torch.Tensor, seq_ids: torch.Tensor,
+                         tile_tok0: torch.Tensor, tile_ntok: torch.Tensor, scale: float,
+                         window: int) -> None:
+    """Paged causal attention of prompt portions on the tcgen05 tensor cores (bfloat16, head
+    size 128): tiles of 128 // group consecutive tokens of one request (tile_tok0, tile_ntok,
+    int32); K and V pages [n_pages, kv_heads, page_size, 128] come in by TMA."""
+    _need_cuda(q, out, k_cache, v_cache, block_tables, positions, seq_ids, tile_tok0, tile_ntok)
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.shape == v_cache.shape and k_cache.shape[1:] == (num_kv_heads, page_size, head_dim)
+    assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
+    lib = load_library("attention_tc")
+    _check(lib.tgo_attention_tc_prefill(
+        _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+        c_int(k_cache.shape[0]), c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]),
+        _ptr(positions), _ptr(seq_ids), _ptr(tile_tok0), _ptr(tile_ntok), c_int(tile_tok0.numel()),
+        c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_float(scale), c_int(window),
+        _stream()), "attention_tc_prefill",
+        f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads}, page_size={page_size})")
+
+
 def flash_tile_rows() -> int:
     """Query rows (token x head of the group) one prefill tile of the attention kernel holds."""
     return int(load_library("attention_flash").tgo_attention_flash_tile_rows())
@@ -553,6 +593,13 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
                             cache.page_size, cache.block_tables, ctx.positions, ctx.seq_ids,
                             None, None, scale, window, wide=False,
                             n_splits=decode_splits(ctx, num_kv_heads, window))
+        elif USE_TC_ATTENTION and q.shape[0] >= TC_ATTENTION_MIN_TOKENS and \
+                attention_tc_supports(head_dim, group, cache.page_size) and \
+                cache.k.is_contiguous() and cache.v.is_contiguous():
+            tok0, ntok = _tiles(ctx, 128 // group)
+            attention_tc_prefill(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
+                                 cache.page_size, cache.block_tables, ctx.positions, ctx.seq_ids,
+                                 tok0, ntok, scale, window)
         else:
             tok0, ntok = _tiles(ctx, flash_tile_rows() // group)
             attention_flash(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
