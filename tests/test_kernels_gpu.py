@@ -575,3 +575,72 @@ def test_gemm_chain(M, d, a_w, f, qkv_n):
         assert torch.allclose(act.float(), act_want, rtol=3e-2, atol=3e-2 * act_want.abs().max().item())
         assert torch.allclose(hh, h_want, rtol=1e-2, atol=1e-2 * h_want.abs().max().item())
         assert torch.allclose(qkv.float(), qkv_want, rtol=3e-2, atol=3e-2 * qkv_want.abs().max().item())
+
+
+# --------------------------------------------------------------------- attention on tcgen05
+
+
+TC_CASES = [
+    # extents, firsts, H, Hkv, page size, window
+    ([32], [0], 4, 1, 16, 0),                               # one query tile, one key tile
+    ([200], [0], 8, 2, 16, 0),                              # ragged last tile, two key tiles
+    ([70, 1, 5, 1, 130], [0, 199, 61, 0, 100], 32, 8, 16, 0),      # portions beside single tokens
+    ([70, 1, 5, 1, 130], [0, 199, 61, 0, 100], 32, 8, 16, 37),     # with a window
+    ([300, 17], [50, 400], 3, 3, 32, 0),                    # no grouping, odd head count
+    ([300], [0], 16, 1, 64, 100),                           # 16 heads a group, window over tiles
+    ([513], [0], 8, 4, 128, 0),                             # a page as large as a key tile
+    ([40], [1000], 8, 2, 8, 0),                             # small pages, a long context behind
+]
+
+
+@pytest.mark.parametrize("extents,firsts,H,Hkv,ps,window", TC_CASES)
+def test_attention_tc_prefill(extents, firsts, H, Hkv, ps, window):
+    """The tcgen05 attention kernel alone (head size 128) over a scattered paged cache whose
+    unwritten rows hold NaN, against the plain float32 attention."""
+    o, dh = ops(), 128
+    assert o.attention_tc_supports(dh, H // Hkv, ps)
+    case = paged_case(extents, firsts, H, Hkv, dh, ps, torch.bfloat16, seed=len(extents) + ps)
+    scale = 1 / math.sqrt(dh)
+    want = attention_ref(case, H, Hkv, dh, scale, window)
+    out = torch.full_like(case["q"], float("nan"))
+    tok0, ntok = o._tiles(Ctx(case, False), 128 // (H // Hkv))
+    o.attention_tc_prefill(case["q"], out, H, Hkv, dh, case["kc"], case["vc"], ps, case["bt"],
+                           case["pos"], case["seq"], tok0, ntok, scale, window)
+    torch.cuda.synchronize()
+    assert o.attention_tc_error() == 0
+    assert torch.allclose(out.float().cpu(), want, **tol(torch.bfloat16))
+
+
+def test_attention_tc_far_key_and_growing_scores():
+    """Head size 128 through the dispatch: one key among 700 carries nearly all the weight
+    (a tile's or a page's edge would lose it), and scores that grow along the keys force the
+    kernel to move its running maximum and rescale what it has summed."""
+    H, Hkv, dh, ps = 8, 2, 128, 16
+    for far in (0, 127, 128, 255, 256, 640, 699):
+        def crafted(b, K, V, far=far):
+            K *= 0.05
+            K[far] = 0
+            K[far, :, 0] = 30.0
+            V[far] = 7.0
+        case = paged_case([40], [660], H, Hkv, dh, ps, torch.bfloat16, seed=far, crafted=crafted)
+        q = torch.zeros_like(case["q"])
+        q[:, 0::dh] = 8.0
+        case["q"] = q
+        out = torch.zeros_like(q)
+        ops().paged_attention(q, out, H, Hkv, dh, Cache(case, ps), Ctx(case, False), 1 / math.sqrt(dh), 0)
+        sees = case["pos"] >= far
+        assert torch.allclose(out[sees].float(), torch.full_like(out[sees], 7.0).float(), atol=0.05), far
+
+    def ramp(b, K, V):
+        n = K.shape[0]
+        K[:] = 0
+        K[:, :, 0] = torch.arange(n, dtype=torch.float32)[:, None] * 0.25     # later keys score higher
+    case = paged_case([64], [600], H, Hkv, dh, ps, torch.bfloat16, seed=5, crafted=ramp)
+    q = torch.zeros_like(case["q"])
+    q[:, 0::dh] = 4.0
+    case["q"] = q
+    want = attention_ref(case, H, Hkv, dh, 1.0, 0)
+    out = torch.zeros_like(q)
+    ops().paged_attention(q, out, H, Hkv, dh, Cache(case, ps), Ctx(case, False), 1.0, 0)
+    assert ops().attention_tc_error() == 0
+    assert torch.allclose(out.float().cpu(), want, **tol(torch.bfloat16))

@@ -10,9 +10,9 @@
 //               (a page is two boxes of page_size rows x 64 columns, 128-byte swizzle; the
 //               pages of a tile lie one after the other in shared memory, which is the
 //               K-major layout for K and the MN-major layout for V that the tensor core wants);
-//   warp 1      issuer: one lane issues S_j = Q K_j^T (8 k-steps) into one of two S buffers in
-//               tensor memory, one tile ahead of the softmax, and O += P_j V_j with P read
-//               from tensor memory (two products of 64 output columns, 8 k-steps each);
+//   warp 1      issuer: one lane issues S_j = Q K_j^T (8 k-steps) into tensor memory and, once
+//               the softmax has written P_j, O += P_j V_j with P read from tensor memory (two
+//               products of 64 output columns, 8 k-steps each);
 //   warps 2-9   softmax: two threads per row, one for keys 0..63 of the tile and one for keys
 //               64..127 (warps 2-5 and 6-9). Each reads its half row of S (64 float32), masks,
 //               takes the maximum, swaps it with its partner through shared memory, writes
@@ -22,7 +22,14 @@
 //               rows of O in tensor memory are rescaled. (The result is the same: the factor
 //               cancels in O / l; only the range of P changes, and 2^8 is far from overflow.)
 //
-// Tensor memory (512 columns): S0 0..127, S1 128..255, O 256..383; P_j lies over S_j.
+// Tensor memory: 256 columns a CTA, S 0..127 and O 128..255; P_j lies over S_j. Shared memory:
+// one tile each of Q, K and V (96 KB). Two CTAs share an SM: inside a CTA the product, the
+// softmax and the second product of a key tile follow one another, and the other CTA's work
+// (and its start and its end) fills the gaps. MEASURED on B200, 2048-token prompt of 32/8
+// heads: 262 us for the mma.sync kernel; 136 us for one CTA per SM with two S buffers and one
+// softmax thread per row; 100 us with two threads per row; 95 us in this form. Per key tile
+// the softmax needs about 2000 cycles of an SM (the special-function unit alone 1024: 128 x 128
+// exponentials at 16 a cycle) against 1024 for the two products.
 // Rows of V that no query may read (past the request's end in its last page, before the
 // window) are zeroed in shared memory before P V: P is zero there, but the cache may hold
 // anything, NaN included. Keys of K in such rows give S values that the mask replaces.
@@ -44,7 +51,7 @@
 #define AT_WAIT_CYCLES 4000000000ll
 #define AT_BLOCK_BYTES (128 * 64 * 2)          // 128 rows x 64 columns of bf16
 #define AT_TILE_BYTES (2 * AT_BLOCK_BYTES)     // a Q, K or V tile: two column halves
-#define AT_PAGES_CAP 4096
+#define AT_PAGES_CAP 1024
 
 __device__ int at_error_flag = 0;
 
@@ -137,13 +144,19 @@ __device__ __forceinline__ void at_tmem_st32(uint32_t taddr, const uint32_t (&r)
           "r"(r[30]), "r"(r[31]), "r"(taddr)
         : "memory");
 }
+// 2^x on the special-function unit; -inf gives 0
+__device__ __forceinline__ float at_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *(uint32_t*)&v;
 }
 
 // error codes: 1 producer, 2 issuer, 3 softmax
-__global__ void __launch_bounds__(AT_THREADS)
+__global__ void __launch_bounds__(AT_THREADS, 2)
 attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
                             long long out_stride, int page_size, int page_shift,
@@ -154,16 +167,16 @@ attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     extern __shared__ unsigned char at_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)at_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = base;                                   // [2 halves][128 rows][128 B]
-    unsigned char* sK = sQ + AT_TILE_BYTES;                     // [2 stages][2 halves][128][128 B]
-    unsigned char* sV = sK + 2 * AT_TILE_BYTES;                 // [2 stages][2 halves][128][128 B]
-    uint64_t* bars = (uint64_t*)(sV + 2 * AT_TILE_BYTES);
-    uint64_t* k_full = bars;            // [2]
-    uint64_t* k_empty = bars + 2;       // [2]
-    uint64_t* v_full = bars + 4;        // [2]
-    uint64_t* v_empty = bars + 6;       // [2]
-    uint64_t* s_full = bars + 8;        // [2]
-    uint64_t* p_full = bars + 10;       // [2]
-    uint64_t* o_done = bars + 12;       // [1]
+    unsigned char* sK = sQ + AT_TILE_BYTES;                     // [2 halves][128][128 B]
+    unsigned char* sV = sK + AT_TILE_BYTES;                     // [2 halves][128][128 B]
+    uint64_t* bars = (uint64_t*)(sV + AT_TILE_BYTES);
+    uint64_t* k_full = bars;            // one phase per key tile each
+    uint64_t* k_empty = bars + 1;
+    uint64_t* v_full = bars + 2;
+    uint64_t* v_empty = bars + 3;
+    uint64_t* s_full = bars + 4;
+    uint64_t* p_full = bars + 5;
+    uint64_t* o_done = bars + 6;
     uint32_t* tmem_slot = (uint32_t*)(bars + 13);
     float* s_xm = (float*)(bars + 14);  // [2 tile parities][2 halves][128 rows] row maxima
     float* s_xl = s_xm + 512;           // [2 halves][128 rows] row sums at the end
@@ -193,17 +206,15 @@ attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int pg_lo = t_lo * pages_per_tile;
 
     if (tid == 0) {
-        for (int i = 0; i < 2; ++i) {
-            at_mbar_init(&k_full[i], 1); at_mbar_init(&k_empty[i], 1);
-            at_mbar_init(&v_full[i], 1); at_mbar_init(&v_empty[i], 1);
-            at_mbar_init(&s_full[i], 1); at_mbar_init(&p_full[i], 8);
-        }
+        at_mbar_init(k_full, 1); at_mbar_init(k_empty, 1);
+        at_mbar_init(v_full, 1); at_mbar_init(v_empty, 1);
+        at_mbar_init(s_full, 1); at_mbar_init(p_full, 8);
         at_mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(at_smem(tmem_slot)), "r"(512u) : "memory");
+                     ::"r"(at_smem(tmem_slot)), "r"(256u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // this tile's slice of the block table
@@ -226,40 +237,38 @@ attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     __syncthreads();
     at_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tm_s[2] = {tmem, tmem + 128u};
-    const uint32_t tm_o = tmem + 256u;
+    const uint32_t tm_s = tmem, tm_o = tmem + 128u;
 
     if (warp == 0) {
         auto page_of = [&](int pi) { return pi - pg_lo < AT_PAGES_CAP ? s_pages[pi - pg_lo] : bt[pi]; };
         bool ok = true;
         for (int it = 0; it < n_it; ++it) {
-            const int s = it & 1;
-            const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+            const uint32_t ph = (uint32_t)it & 1u;
             const int j = t_lo + it;
             // pages of this tile that hold a key some row may read
             int first = j * pages_per_tile, last = first + pages_per_tile;      // [first, last)
             while (first < last && (first + 1) * page_size <= key_lo) ++first;
             while (last > first && (last - 1) * page_size >= key_hi) --last;
             const uint32_t bytes = (uint32_t)(last - first) * (uint32_t)page_size * 256u;
-            ok = __all_sync(0xffffffffu, ok && at_wait(&k_empty[s], ph ^ 1u, 1));
+            ok = __all_sync(0xffffffffu, ok && at_wait(k_empty, ph ^ 1u, 1));
             if (!ok) break;
-            if (lane == 0) at_expect_tx(&k_full[s], bytes);
+            if (lane == 0) at_expect_tx(k_full, bytes);
             __syncwarp();
             for (int pi = first + lane; pi < last; pi += 32) {
                 const int row = (page_of(pi) * Hkv + kvh) * page_size;
-                unsigned char* dst = sK + s * AT_TILE_BYTES + (pi - j * pages_per_tile) * page_size * 128;
-                at_tma_2d(dst, &map_k, 0, row, &k_full[s]);
-                at_tma_2d(dst + AT_BLOCK_BYTES, &map_k, 64, row, &k_full[s]);
+                unsigned char* dst = sK + (pi - j * pages_per_tile) * page_size * 128;
+                at_tma_2d(dst, &map_k, 0, row, k_full);
+                at_tma_2d(dst + AT_BLOCK_BYTES, &map_k, 64, row, k_full);
             }
-            ok = __all_sync(0xffffffffu, at_wait(&v_empty[s], ph ^ 1u, 1));
+            ok = __all_sync(0xffffffffu, at_wait(v_empty, ph ^ 1u, 1));
             if (!ok) break;
-            if (lane == 0) at_expect_tx(&v_full[s], bytes);
+            if (lane == 0) at_expect_tx(v_full, bytes);
             __syncwarp();
             for (int pi = first + lane; pi < last; pi += 32) {
                 const int row = (page_of(pi) * Hkv + kvh) * page_size;
-                unsigned char* dst = sV + s * AT_TILE_BYTES + (pi - j * pages_per_tile) * page_size * 128;
-                at_tma_2d(dst, &map_v, 0, row, &v_full[s]);
-                at_tma_2d(dst + AT_BLOCK_BYTES, &map_v, 64, row, &v_full[s]);
+                unsigned char* dst = sV + (pi - j * pages_per_tile) * page_size * 128;
+                at_tma_2d(dst, &map_v, 0, row, v_full);
+                at_tma_2d(dst + AT_BLOCK_BYTES, &map_v, 64, row, v_full);
             }
         }
     } else if (warp == 1) {
@@ -271,38 +280,33 @@ attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                       ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
             const uint64_t dq0 = at_desc(sQ), dq1 = at_desc(sQ + AT_BLOCK_BYTES);
+            const uint64_t dk0 = at_desc(sK), dk1 = at_desc(sK + AT_BLOCK_BYTES);
             bool ok = true;
-            auto issue_qk = [&](int it) {
-                const int s = it & 1;
-                if (!at_wait(&k_full[s], (uint32_t)(it >> 1) & 1u, 2)) return false;
-                at_fence_after();
-                const uint64_t dk0 = at_desc(sK + s * AT_TILE_BYTES), dk1 = at_desc(sK + s * AT_TILE_BYTES + AT_BLOCK_BYTES);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) at_mma_ss(tm_s[s], dq0 + 2 * k, dk0 + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) at_mma_ss(tm_s[s], dq1 + 2 * k, dk1 + 2 * k, idesc_qk, 1u);
-                at_commit(&k_empty[s]);
-                at_commit(&s_full[s]);
-                return true;
-            };
-            if (n_it > 0) ok = issue_qk(0);
             for (int it = 0; it < n_it && ok; ++it) {
-                const int s = it & 1;
-                const uint32_t ph = (uint32_t)(it >> 1) & 1u;
-                if (it + 1 < n_it) ok = issue_qk(it + 1);
+                const uint32_t ph = (uint32_t)it & 1u;
+                ok = at_wait(k_full, ph, 2);
                 if (!ok) break;
-                ok = at_wait(&p_full[s], ph, 2) && at_wait(&v_full[s], ph, 2);
+                at_fence_after();
+                // S (and the P that lay over it) is free: the product that read P was issued
+                // before this one, and products run in the order they were issued
+#pragma unroll
+                for (int k = 0; k < 4; ++k) at_mma_ss(tm_s, dq0 + 2 * k, dk0 + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) at_mma_ss(tm_s, dq1 + 2 * k, dk1 + 2 * k, idesc_qk, 1u);
+                at_commit(k_empty);
+                at_commit(s_full);
+                ok = at_wait(p_full, ph, 2) && at_wait(v_full, ph, 2);
                 if (!ok) break;
                 at_fence_after();
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const uint64_t dv = at_desc(sV + s * AT_TILE_BYTES + h * AT_BLOCK_BYTES);
+                    const uint64_t dv = at_desc(sV + h * AT_BLOCK_BYTES);
 #pragma unroll
                     for (int k = 0; k < 8; ++k)           // 16 keys = 2 groups of 8 rows = 2048 bytes
-                        at_mma_ts(tm_o + 64u * h, tm_s[s] + 8u * k, dv + (uint64_t)(128 * k), idesc_pv,
+                        at_mma_ts(tm_o + 64u * h, tm_s + 8u * k, dv + (uint64_t)(128 * k), idesc_pv,
                                   (it > 0 || k > 0) ? 1u : 0u);
                 }
-                at_commit(&v_empty[s]);
+                at_commit(v_empty);
                 at_commit(o_done);
             }
         }
@@ -323,16 +327,15 @@ attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
         for (int it = 0; it < n_it; ++it) {
-            const int s = it & 1;
-            const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+            const uint32_t ph = (uint32_t)it & 1u;
             const int kbase = (t_lo + it) * AT_BN + 64 * half;
-            if (ok) ok = at_wait(&s_full[s], ph, 3);
+            if (ok) ok = at_wait(s_full, ph, 3);
             at_fence_after();
             float sc[64];
             {
                 uint32_t r0[32], r1[32];
-                at_tmem_ld32(tm_s[s] + lane_base + 64u * half, r0);
-                at_tmem_ld32(tm_s[s] + lane_base + 64u * half + 32u, r1);
+                at_tmem_ld32(tm_s + lane_base + 64u * half, r0);
+                at_tmem_ld32(tm_s + lane_base + 64u * half + 32u, r1);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                 for (int i = 0; i < 32; ++i) { sc[i] = __uint_as_float(r0[i]); sc[32 + i] = __uint_as_float(r1[i]); }
@@ -341,16 +344,17 @@ attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (full) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) { sc[i] *= scale_log2; mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]); }
+                for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
             } else {
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
                     const int key = kbase + i;
-                    sc[i] = (key <= pos && key >= vis_lo) ? sc[i] * scale_log2 : -INFINITY;
+                    sc[i] = (key <= pos && key >= vis_lo) ? sc[i] : -INFINITY;
                     mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
                 }
             }
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // the scale is positive: the maximum of the scaled values is the scaled maximum
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
             // the other half of the row: both threads of a row end up with the same maximum
             float* xm = s_xm + (it & 1) * 256;
             xm[half * 128 + row] = mx;
@@ -370,20 +374,21 @@ attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 uint32_t r[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const float a = exp2f(sc[2 * i] - base_m), b = exp2f(sc[2 * i + 1] - base_m);
+                    const float a = at_ex2(fmaf(sc[2 * i], scale_log2, -base_m));
+                    const float b = at_ex2(fmaf(sc[2 * i + 1], scale_log2, -base_m));
                     sum4[i & 3] += a + b;
                     r[i] = at_pack(a, b);
                 }
-                at_tmem_st32(tm_s[s] + lane_base + 32u * half, r);
+                at_tmem_st32(tm_s + lane_base + 32u * half, r);
             }
             l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             // rows of V that nobody may read: zeros (this thread's half of its row of the tile)
             const int tile_lo = (t_lo + it) * AT_BN;
             if (tile_lo + AT_BN > key_hi || tile_lo < key_lo) {
-                if (ok) ok = at_wait(&v_full[s], ph, 3);
+                if (ok) ok = at_wait(v_full, ph, 3);
                 const int key = tile_lo + row;
                 if (key >= key_hi || key < key_lo) {
-                    unsigned char* vrow = sV + s * AT_TILE_BYTES + half * AT_BLOCK_BYTES + row * 128;
+                    unsigned char* vrow = sV + half * AT_BLOCK_BYTES + row * 128;
 #pragma unroll
                     for (int c = 0; c < 8; ++c) *(uint4*)(vrow + c * 16) = make_uint4(0u, 0u, 0u, 0u);
                 }
@@ -410,7 +415,7 @@ attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             // out in turn), but every thread keeps walking the loop, so that the barriers and
             // the warp-wide loads and stores above stay matched
             ok = __all_sync(0xffffffffu, ok);
-            if (lane == 0 && ok) at_arrive(&p_full[s]);
+            if (lane == 0 && ok) at_arrive(p_full);
         }
         if (ok && n_it > 0) ok = at_wait(o_done, (uint32_t)(n_it - 1) & 1u, 3);
         at_fence_after();
@@ -447,7 +452,7 @@ attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     __syncthreads();
     if (warp == 1) {
         at_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
     }
 }
 
@@ -495,6 +500,7 @@ TGO_API int tgo_attention_tc_supports(int dh, int group, int page_size) {
     return dh == AT_DH && g_ok && p_ok;
 }
 
+
 // Reads (and waits for the device to reach) the code a wait that ran out left; 0: none did.
 TGO_API int tgo_attention_tc_error(int* value) {
     return (int)cudaMemcpyFromSymbol(value, at_error_flag, sizeof(int));
@@ -519,7 +525,7 @@ TGO_API int tgo_attention_tc_prefill(const void* q, long long q_stride, void* ou
     const CUtensorMap* mk = at_map_of(k_cache, rows, page_size);
     const CUtensorMap* mv = at_map_of(v_cache, rows, page_size);
     if (!mk || !mv) return TGO_E_BAD_ARG;
-    constexpr size_t smem = 1024 + 5 * (size_t)AT_TILE_BYTES + 14 * 8 + 768 * sizeof(float) + AT_PAGES_CAP * sizeof(int);
+    constexpr size_t smem = 1024 + 3 * (size_t)AT_TILE_BYTES + 14 * 8 + 768 * sizeof(float) + AT_PAGES_CAP * sizeof(int);
     static bool once = false;
     if (!once) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_prefill_kernel,
