@@ -593,11 +593,14 @@ TC_CASES = [
 ]
 
 
+@pytest.mark.parametrize("persistent", [True, False])
 @pytest.mark.parametrize("extents,firsts,H,Hkv,ps,window", TC_CASES)
-def test_attention_tc_prefill(extents, firsts, H, Hkv, ps, window):
-    """The tcgen05 attention kernel alone (head size 128) over a scattered paged cache whose
-    unwritten rows hold NaN, against the plain float32 attention."""
+def test_attention_tc_prefill(extents, firsts, H, Hkv, ps, window, persistent, monkeypatch):
+    """The tcgen05 attention kernels alone (head size 128; one CTA per SM drawing items, and
+    one CTA per item) over a scattered paged cache whose unwritten rows hold NaN, against
+    the plain float32 attention."""
     o, dh = ops(), 128
+    monkeypatch.setattr(o, "TC_ATTENTION_PERSISTENT", persistent)
     assert o.attention_tc_supports(dh, H // Hkv, ps)
     case = paged_case(extents, firsts, H, Hkv, dh, ps, torch.bfloat16, seed=len(extents) + ps)
     scale = 1 / math.sqrt(dh)

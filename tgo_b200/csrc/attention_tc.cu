@@ -27,7 +27,8 @@
 // softmax and the second product of a key tile follow one another, and the other CTA's work
 // (and its start and its end) fills the gaps. MEASURED on B200, 2048-token prompt of 32/8
 // heads: 262 us for the mma.sync kernel; 136 us for one CTA per SM with two S buffers and one
-// softmax thread per row; 100 us with two threads per row; 95 us in this form. Per key tile
+// softmax thread per row; 100 us with two threads per row; 91 us in this form; 78 us for
+// the persistent form further down. Per key tile
 // the softmax needs about 2000 cycles of an SM (the special-function unit alone 1024: 128 x 128
 // exponentials at 16 a cycle) against 1024 for the two products.
 // Rows of V that no query may read (past the request's end in its last page, before the
@@ -52,6 +53,12 @@
 #define AT_BLOCK_BYTES (128 * 64 * 2)          // 128 rows x 64 columns of bf16
 #define AT_TILE_BYTES (2 * AT_BLOCK_BYTES)     // a Q, K or V tile: two column halves
 #define AT_PAGES_CAP 1024
+#ifndef AP_PV_N
+#define AP_PV_N 128      // output columns of one P V product: 128, or 64 (two products a k-step)
+#endif
+#ifndef AP_LBO_BYTES
+#define AP_LBO_BYTES AT_BLOCK_BYTES
+#endif
 
 __device__ int at_error_flag = 0;
 
@@ -120,6 +127,17 @@ __device__ __forceinline__ uint64_t at_desc(const void* tile) {
     return d;
 }
 
+// The same for V when one product spans both 64-column blocks: the second block of columns
+// lies AP_LBO_BYTES after the first.
+__device__ __forceinline__ uint64_t at_desc_mn(const void* tile) {
+    uint64_t d = (uint64_t)((at_smem(tile) & 0x3ffff) >> 4);
+    d |= (uint64_t)((AP_PV_N == 128 ? AP_LBO_BYTES : 1024) >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
 __device__ __forceinline__ void at_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -143,6 +161,14 @@ __device__ __forceinline__ void at_tmem_st32(uint32_t taddr, const uint32_t (&r)
           "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
           "r"(r[30]), "r"(r[31]), "r"(taddr)
         : "memory");
+}
+// Barrier 1 of the 256 softmax threads; every thread gets the OR of the predicates.
+__device__ __forceinline__ bool at_bar_or(bool pred) {
+    uint32_t r;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\t"
+                 "bar.red.or.pred q, 1, 256, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(r) : "r"((uint32_t)pred) : "memory");
+    return r != 0;
 }
 // 2^x on the special-function unit; -inf gives 0
 __device__ __forceinline__ float at_ex2(float x) {
@@ -456,6 +482,447 @@ attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
 }
 
+// ------------------------------------------------------------------ persistent form
+// One CTA per SM walks work items (query tile, kv head) that it draws from a counter, longest
+// first. Inside the CTA everything is double-buffered, so the parts of neighbouring key tiles
+// and of neighbouring items overlap:
+//   tensor memory (512 columns)  S0, S1 (128 each; P lies over S) and O0, O1 (128 each): the
+//                 issuer runs Q K^T one key tile ahead of the softmax, and starts the next
+//                 item while the softmax threads still write the last one's O out;
+//   shared memory  two Q tiles, two K tiles, two V tiles (192 KB);
+//   warp 0   draws the items (the next one while it loads this one), reads their sizes,
+//            copies the item's Q rows into shared memory and publishes a record of the item
+//            in a ring of four;
+//   warps 12 and 10  follow the records and ask TMA for the K and for the V pages, a warp
+//            each, so that K runs ahead of V and neither waits for the next item's Q;
+//   warps 1 and 11  issue S = Q K^T and O += P V, a thread each (a thread starts a product
+//            about every 80 cycles); warps 2-9 softmax, two threads a row, as above.
+// The counter is a global of this library, set to zero on the stream before each launch:
+// launches of this kernel must not overlap (the engine issues them on one stream).
+// A record (and its Q buffer) is only replaced when every reader has seen it: the products
+// with the item's Q have run, and the second issuer, the K and V warps and the eight softmax
+// warps have each read the record; so no waiter ever falls two phases behind a barrier.
+#define AP_THREADS 416
+
+struct ApItem {          // what warp 0 tells the others about an item
+    int valid;           // 0: no more items
+    int tok0, n_rows, p0, n_it, t_lo, key_lo, key_hi, seq, kvh;
+    int pad[6];
+};
+
+__device__ unsigned int ap_ticket = 0;      // set to zero on the stream before every launch
+
+__global__ void __launch_bounds__(AP_THREADS, 1)
+attention_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                               const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                               long long out_stride, int page_size, int page_shift,
+                               const int* __restrict__ block_tables, int max_blocks,
+                               const int* __restrict__ positions, const int* __restrict__ seq_ids,
+                               const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok,
+                               int n_tiles, int H, int Hkv, float scale_log2, int window) {
+    extern __shared__ unsigned char at_raw[];
+    unsigned char* base = (unsigned char*)(((uintptr_t)at_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = base;                                   // [2][2 halves][128 rows][128 B]
+    unsigned char* sK = sQ + 2 * AT_TILE_BYTES;                 // [2 stages]
+    unsigned char* sV = sK + 2 * AT_TILE_BYTES;                 // [2 stages]
+    uint64_t* bars = (uint64_t*)(sV + 2 * AT_TILE_BYTES);
+    uint64_t* q_full = bars;            // [2]
+    uint64_t* q_empty = bars + 2;       // [2]
+    uint64_t* k_full = bars + 4;        // [2]
+    uint64_t* k_empty = bars + 6;       // [2]
+    uint64_t* v_full = bars + 8;        // [2]
+    uint64_t* v_empty = bars + 10;      // [2]
+    uint64_t* s_full = bars + 12;       // [2]
+    uint64_t* p_full = bars + 14;       // [2]
+    uint64_t* o_free = bars + 16;       // [2]
+    uint64_t* o_done = bars + 18;       // [1]
+    uint64_t* p_free = bars + 19;       // [2]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 21);
+    ApItem* ring = (ApItem*)(bars + 22);                        // [4]
+    float* s_xm = (float*)(ring + 4);   // [2][2 halves][128 rows]
+    float* s_xl = s_xm + 512;           // [2 halves][128 rows]
+    int* s_pages_k = (int*)(s_xl + 256);          // [AT_PAGES_CAP]
+    int* s_pages_v = s_pages_k + AT_PAGES_CAP;    // [AT_PAGES_CAP]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = H / Hkv;
+    const int n_items = n_tiles * Hkv;
+    const int pages_per_tile = AT_BN >> page_shift;
+
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) {
+            at_mbar_init(&q_full[i], 1); at_mbar_init(&q_empty[i], 12);
+            at_mbar_init(&k_full[i], 1); at_mbar_init(&k_empty[i], 1);
+            at_mbar_init(&v_full[i], 1); at_mbar_init(&v_empty[i], 1);
+            at_mbar_init(&s_full[i], 1); at_mbar_init(&p_full[i], 8);
+            at_mbar_init(&o_free[i], 8); at_mbar_init(&p_free[i], 1);
+        }
+        at_mbar_init(o_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(at_smem(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    at_fence_before();
+    __syncthreads();
+    at_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    // pages of key tile j that hold a key some row of the item may read: [first, last)
+    auto page_range = [&](int j, int key_lo, int key_hi, int& first, int& last) {
+        first = j * pages_per_tile;
+        last = first + pages_per_tile;
+        while (first < last && (first + 1) * page_size <= key_lo) ++first;
+        while (last > first && (last - 1) * page_size >= key_hi) --last;
+    };
+
+    if (warp == 0) {
+        // ---------------------------------------------------------- items and Q
+        bool ok = true;
+        // The next item is drawn, and its tile looked up, while this one is being loaded.
+        auto draw = [&](int& item, int& tok0, int& ntok) {
+            item = 0;
+            if (lane == 0) item = (int)atomicAdd(&ap_ticket, 1u);
+            item = __shfl_sync(0xffffffffu, item, 0);
+            tok0 = ntok = 0;
+            if (item < n_items) {
+                const int tile = n_tiles - 1 - item / Hkv;      // longest first: later tiles read more keys
+                tok0 = tile_tok0[tile];
+                ntok = tile_ntok[tile];
+            }
+        };
+        int item, tok0, ntok;
+        draw(item, tok0, ntok);
+        for (uint32_t n = 0; ok; ++n) {
+            ApItem* rec = &ring[n & 3];
+            const uint32_t qb = n & 1u, qph = (n >> 1) & 1u;
+            // the Q buffer (and with it the turn to publish) is free once the products of the
+            // item two back have run and everybody has read its record
+            ok = __all_sync(0xffffffffu, at_wait(&q_empty[qb], qph ^ 1u, 1));
+            if (!ok) break;
+            if (item >= n_items) {
+                if (lane == 0) {
+                    rec->valid = 0;
+                    at_arrive(&q_full[qb]);
+                }
+                break;
+            }
+            const int kvh = item % Hkv;
+            const int n_rows = ntok * G;
+            const int p0 = positions[tok0], seq = seq_ids[tok0];
+            const int q_tok0 = tok0;
+            int item_next, tok0_next, ntok_next;
+            draw(item_next, tok0_next, ntok_next);
+            const int p_last = p0 + ntok - 1;
+            const int key_lo = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+            const int key_hi = p_last + 1;
+            const int t_lo = key_lo / AT_BN, t_hi = (key_hi + AT_BN - 1) / AT_BN;
+            const int n_it = p0 < 0 ? 0 : t_hi - t_lo;
+            if (n_it > 0) {
+                // Q rows -> shared memory in the swizzled K-major layout, all copies in flight at
+                // once; rows past the tile are zeros
+                unsigned char* dq = sQ + qb * AT_TILE_BYTES;
+#pragma unroll 8
+                for (int i = lane; i < AT_BM * 16; i += 32) {
+                    const int r = i >> 4, c = i & 15;
+                    const bool in = r < n_rows;
+                    const bf16* src = in ? q + (size_t)(q_tok0 + r / G) * q_stride + (size_t)(kvh * G + r % G) * AT_DH + c * 8 : q;
+                    const uint32_t to = at_smem(dq + (c >> 3) * AT_BLOCK_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(to), "l"(src), "r"(in ? 16 : 0) : "memory");
+                }
+                asm volatile("cp.async.wait_all;" ::: "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            __syncwarp();
+            if (lane == 0) {
+                rec->valid = 1; rec->tok0 = q_tok0; rec->n_rows = n_rows; rec->p0 = p0; rec->n_it = n_it;
+                rec->t_lo = t_lo; rec->key_lo = key_lo; rec->key_hi = key_hi; rec->seq = seq; rec->kvh = kvh;
+                at_arrive(&q_full[qb]);
+            }
+            item = item_next; tok0 = tok0_next; ntok = ntok_next;
+        }
+    } else if (warp == 10 || warp == 12) {
+        // ---------------------------------------------------------- V (warp 10), K (warp 12)
+        const bool is_k = warp == 12;
+        int* s_pages = is_k ? s_pages_k : s_pages_v;
+        unsigned char* tiles = is_k ? sK : sV;
+        uint64_t* full = is_k ? k_full : v_full;
+        uint64_t* empty = is_k ? k_empty : v_empty;
+        const CUtensorMap* map = is_k ? &map_k : &map_v;
+        bool ok = true;
+        uint32_t g = 0;
+        for (uint32_t n = 0; ok; ++n) {
+            const uint32_t qb = n & 1u, qph = (n >> 1) & 1u;
+            ok = __all_sync(0xffffffffu, at_wait(&q_full[qb], qph, 1));
+            if (!ok) break;
+            const ApItem rec = ring[n & 3];
+            if (!rec.valid) break;
+            __syncwarp();
+            if (lane == 0) at_arrive(&q_empty[qb]);
+            const int* bt = block_tables + (size_t)rec.seq * max_blocks;
+            const int pg_lo = rec.t_lo * pages_per_tile;
+            if (rec.n_it > 0) {
+                int pg_hi = (rec.t_lo + rec.n_it) * pages_per_tile;
+                if (pg_hi > max_blocks) pg_hi = max_blocks;
+                if (pg_hi - pg_lo > AT_PAGES_CAP) pg_hi = pg_lo + AT_PAGES_CAP;
+                for (int i = pg_lo + lane; i < pg_hi; i += 32) s_pages[i - pg_lo] = bt[i];
+            }
+            __syncwarp();
+            auto page_of = [&](int pi) { return pi - pg_lo < AT_PAGES_CAP ? s_pages[pi - pg_lo] : bt[pi]; };
+            for (int it = 0; it < rec.n_it; ++it, ++g) {
+                const uint32_t s = g & 1u, ph = (g >> 1) & 1u;
+                const int j = rec.t_lo + it;
+                int first, last;
+                page_range(j, rec.key_lo, rec.key_hi, first, last);
+                ok = __all_sync(0xffffffffu, at_wait(&empty[s], ph ^ 1u, 1));
+                if (!ok) break;
+                if (lane == 0) at_expect_tx(&full[s], (uint32_t)(last - first) * (uint32_t)page_size * 256u);
+                __syncwarp();
+                for (int pi = first + lane; pi < last; pi += 32) {
+                    const int row = (page_of(pi) * Hkv + rec.kvh) * page_size;
+                    unsigned char* dst = tiles + s * AT_TILE_BYTES + (pi - j * pages_per_tile) * page_size * 128;
+                    at_tma_2d(dst, map, 0, row, &full[s]);
+                    at_tma_2d(dst + AT_BLOCK_BYTES, map, 64, row, &full[s]);
+                }
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------- issuer of S = Q K^T
+        // (a thread can start a product about every 80 cycles, so the two kinds of product
+        // have a thread each)
+        if (lane == 0) {
+            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) |
+                                      ((uint32_t)(128 >> 4) << 24);
+            uint32_t g = 0;
+            bool ok = true;
+            for (uint32_t n = 0; ok; ++n) {
+                const uint32_t qb = n & 1u;
+                if (!at_wait(&q_full[qb], (n >> 1) & 1u, 2)) break;
+                const ApItem* rec = &ring[n & 3];
+                if (!rec->valid) break;
+                const int n_it = rec->n_it;
+                const unsigned char* qt = sQ + qb * AT_TILE_BYTES;
+                const uint64_t dq0 = at_desc(qt), dq1 = at_desc(qt + AT_BLOCK_BYTES);
+                for (int it = 0; it < n_it; ++it, ++g) {
+                    const uint32_t s = g & 1u, ph = (g >> 1) & 1u;
+                    // K has landed, and the P that lay in this S buffer has been multiplied
+                    ok = at_wait(&k_full[s], ph, 2) && at_wait(&p_free[s], ph ^ 1u, 2);
+                    if (!ok) break;
+                    at_fence_after();
+                    const uint64_t dk0 = at_desc(sK + s * AT_TILE_BYTES), dk1 = at_desc(sK + s * AT_TILE_BYTES + AT_BLOCK_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) at_mma_ss(tmem + 128u * s, dq0 + 2 * k, dk0 + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) at_mma_ss(tmem + 128u * s, dq1 + 2 * k, dk1 + 2 * k, idesc_qk, 1u);
+                    at_commit(&k_empty[s]);
+                    at_commit(&s_full[s]);
+                }
+                at_commit(&q_empty[qb]);               // the item's products with Q have run
+            }
+        }
+    } else if (warp == 11) {
+        // ---------------------------------------------------------- issuer of O += P V
+        if (lane == 0) {
+            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                                      ((uint32_t)(AP_PV_N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            uint32_t g = 0;
+            bool ok = true;
+            for (uint32_t n = 0; ok; ++n) {
+                if (!at_wait(&q_full[n & 1u], (n >> 1) & 1u, 2)) break;
+                const ApItem* rec = &ring[n & 3];
+                if (!rec->valid) break;
+                const int n_it = rec->n_it;
+                at_arrive(&q_empty[n & 1u]);
+                const uint32_t ob = n & 1u;
+                const uint32_t tm_o = tmem + 256u + 128u * ob;
+                for (int it = 0; it < n_it && ok; ++it, ++g) {
+                    const uint32_t s = g & 1u, ph = (g >> 1) & 1u;
+                    if (it == 0) ok = at_wait(&o_free[ob], ((n >> 1) & 1u) ^ 1u, 2);    // item n-2's O is out
+                    ok = ok && at_wait(&p_full[s], ph, 2) && at_wait(&v_full[s], ph, 2);
+                    if (!ok) break;
+                    at_fence_after();
+#pragma unroll
+                    for (int h = 0; h < 128 / AP_PV_N; ++h) {
+                        const uint64_t dv = at_desc_mn(sV + s * AT_TILE_BYTES + h * AT_BLOCK_BYTES);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k)           // 16 keys = 2 groups of 8 rows = 2048 bytes
+                            at_mma_ts(tm_o + 64u * h, tmem + 128u * s + 8u * k, dv + (uint64_t)(128 * k), idesc_pv,
+                                      (it > 0 || k > 0) ? 1u : 0u);
+                    }
+                    at_commit(&v_empty[s]);
+                    at_commit(&p_free[s]);
+                    at_commit(o_done);
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------- softmax
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        bool ok = true;
+        uint32_t g = 0;
+        for (uint32_t n = 0;; ++n) {
+            if (ok) ok = at_wait(&q_full[n & 1u], (n >> 1) & 1u, 3);
+            if (at_bar_or(!ok)) break;             // a wait ran out somewhere: all 256 leave together
+            const ApItem rec = ring[n & 3];
+            if (!rec.valid) break;
+            __syncwarp();
+            if (lane == 0) at_arrive(&q_empty[n & 1u]);
+            const uint32_t ob = n & 1u;
+            const uint32_t tm_o = tmem + 256u + 128u * ob;
+            const int n_rows = rec.n_rows, p0 = rec.p0, n_it = rec.n_it, key_lo = rec.key_lo, key_hi = rec.key_hi;
+            const bool row_ok = row < n_rows;
+            bf16* dst = out + (size_t)(rec.tok0 + (row_ok ? row : 0) / G) * out_stride +
+                        (size_t)(rec.kvh * G + (row_ok ? row : 0) % G) * AT_DH + 64 * half;
+            if (n_it == 0) {                       // a request that brings nothing: zeros out
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) *(uint4*)(dst + i * 8) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                __syncwarp();
+                if (lane == 0) at_arrive(&o_free[ob]);
+                continue;
+            }
+            const int pos = row_ok ? p0 + row / G : -1;
+            const int vis_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+            const int warp_first = quarter * 32, warp_last = quarter * 32 + 31;
+            const bool warp_rows_ok = warp_last < n_rows;
+            const int warp_pos_min = p0 + warp_first / G;
+            const int warp_pos_max = p0 + (warp_last < n_rows ? warp_last : n_rows - 1) / G;
+            const int warp_vis_max = (window > 0 && warp_pos_max - window + 1 > 0) ? warp_pos_max - window + 1 : 0;
+            float m_used = -INFINITY, l = 0.f;
+            for (int it = 0; it < n_it; ++it, ++g) {
+                const uint32_t s = g & 1u, ph = (g >> 1) & 1u;
+                const uint32_t tm_s = tmem + 128u * s;
+                const int tile_lo = (rec.t_lo + it) * AT_BN;
+                const int kbase = tile_lo + 64 * half;
+                if (ok) ok = at_wait(&s_full[s], ph, 3);
+                at_fence_after();
+                float sc[64];
+                {
+                    uint32_t r0[32], r1[32];
+                    at_tmem_ld32(tm_s + lane_base + 64u * half, r0);
+                    at_tmem_ld32(tm_s + lane_base + 64u * half + 32u, r1);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) { sc[i] = __uint_as_float(r0[i]); sc[32 + i] = __uint_as_float(r1[i]); }
+                }
+                const bool full = warp_rows_ok && kbase + 63 <= warp_pos_min && kbase >= warp_vis_max;
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                if (full) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        const int key = kbase + i;
+                        sc[i] = (key <= pos && key >= vis_lo) ? sc[i] : -INFINITY;
+                        mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
+                    }
+                }
+                float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+                float* xm = s_xm + (g & 1u) * 256;
+                xm[half * 128 + row] = mx;
+                // the barrier: both halves have read their S (P is written over it below), and
+                // whether any thread's wait ran out, so that all leave together
+                if (at_bar_or(!ok)) { ok = false; break; }
+                mx = fmaxf(mx, xm[(half ^ 1) * 128 + row]);
+                const float m_new = fmaxf(m_used, mx);
+                const bool grow = m_new > m_used + 8.f || (m_used == -INFINITY && m_new != -INFINITY);
+                const bool rescale = __any_sync(0xffffffffu, grow);
+                float corr = 1.f;
+                if (rescale) {
+                    corr = m_new == -INFINITY ? 1.f : exp2f(m_used - m_new);
+                    m_used = m_new;
+                }
+                const float base_m = m_used == -INFINITY ? 0.f : m_used;
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+                {
+                    uint32_t r[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float a = at_ex2(fmaf(sc[2 * i], scale_log2, -base_m));
+                        const float b = at_ex2(fmaf(sc[2 * i + 1], scale_log2, -base_m));
+                        sum4[i & 3] += a + b;
+                        r[i] = at_pack(a, b);
+                    }
+                    at_tmem_st32(tm_s + lane_base + 32u * half, r);
+                }
+                l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+                if (tile_lo + AT_BN > key_hi || tile_lo < key_lo) {     // rows of V that nobody may read
+                    if (ok) ok = at_wait(&v_full[s], ph, 3);
+                    const int key = tile_lo + row;
+                    if (key >= key_hi || key < key_lo) {
+                        unsigned char* vrow = sV + s * AT_TILE_BYTES + half * AT_BLOCK_BYTES + row * 128;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) *(uint4*)(vrow + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                if (it > 0) {
+                    if (ok) ok = at_wait(o_done, (g - 1u) & 1u, 3);         // the previous P V is in O
+                    at_fence_after();
+                    if (rescale) {
+                        uint32_t r[32];
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            at_tmem_ld32(tm_o + lane_base + 64u * half + 32u * c, r);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+                            at_tmem_st32(tm_o + lane_base + 64u * half + 32u * c, r);
+                        }
+                    }
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                at_fence_before();
+                const bool warp_ok = __all_sync(0xffffffffu, ok);
+                if (lane == 0 && warp_ok) at_arrive(&p_full[s]);
+            }
+            if (!ok) break;                        // decided at a barrier: the same for all 256
+            ok = at_wait(o_done, (g - 1u) & 1u, 3);                         // the item's last P V
+            at_fence_after();
+            s_xl[half * 128 + row] = l;
+            if (at_bar_or(!ok)) break;
+            l += s_xl[(half ^ 1) * 128 + row];
+            {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t r[32];
+                    at_tmem_ld32(tm_o + lane_base + 64u * half + 32u * c, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (row_ok) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint4 v;
+                            v.x = at_pack(__uint_as_float(r[8 * i]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
+                            v.y = at_pack(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
+                            v.z = at_pack(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
+                            v.w = at_pack(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
+                            *(uint4*)(dst + c * 32 + i * 8) = v;
+                        }
+                    }
+                }
+                at_fence_before();
+                __syncwarp();
+                if (lane == 0) at_arrive(&o_free[ob]);
+            }
+        }
+    }
+    at_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        at_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
 // ------------------------------------------------------------------------------ host
 typedef CUresult (*AtEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -508,12 +975,14 @@ TGO_API int tgo_attention_tc_error(int* value) {
 
 // Prompt portions: tiles of up to 128 / group consecutive tokens of one request each
 // (tile_tok0, tile_ntok). k_cache and v_cache: [n_pages, Hkv, page_size, 128] bf16.
+// persistent = 1: one CTA per SM that draws (tile, kv head) items from a counter;
+// 0: one CTA per item, two per SM.
 TGO_API int tgo_attention_tc_prefill(const void* q, long long q_stride, void* out, long long out_stride,
                                      const void* k_cache, const void* v_cache, int n_pages, int page_size,
                                      const int* block_tables, int max_blocks, const int* positions,
                                      const int* seq_ids, const int* tile_tok0, const int* tile_ntok,
                                      int n_tiles, int H, int Hkv, int dh, float scale, int window,
-                                     cudaStream_t stream) {
+                                     int persistent, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv || !tgo_attention_tc_supports(dh, H / Hkv, page_size) || n_pages <= 0 ||
         max_blocks <= 0 || window < 0 || Hkv > 65535 || !tile_tok0 || !tile_ntok || q_stride % 8 ||
@@ -521,10 +990,35 @@ TGO_API int tgo_attention_tc_prefill(const void* q, long long q_stride, void* ou
         ((uintptr_t)v_cache % 128))
         return TGO_E_BAD_ARG;
     const long long rows = (long long)n_pages * Hkv * page_size;
-    if (rows > 0x7fffffffll) return TGO_E_BAD_ARG;
+    if (rows > 0x7fffffffll || (long long)n_tiles * Hkv > 0x7fffffffll) return TGO_E_BAD_ARG;
     const CUtensorMap* mk = at_map_of(k_cache, rows, page_size);
     const CUtensorMap* mv = at_map_of(v_cache, rows, page_size);
     if (!mk || !mv) return TGO_E_BAD_ARG;
+    int shift = 0;
+    while ((1 << shift) < page_size) ++shift;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    if (persistent) {
+        constexpr size_t smem = 1024 + 6 * (size_t)AT_TILE_BYTES + 22 * 8 + 4 * sizeof(ApItem) +
+                                768 * sizeof(float) + 2 * AT_PAGES_CAP * sizeof(int);
+        static int sms = 0;
+        static unsigned int* ticket = nullptr;
+        if (!sms) {
+            cudaError_t e = cudaFuncSetAttribute(attention_tc_persistent_kernel,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            int dev = 0;
+            if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+            if ((e = cudaGetSymbolAddress((void**)&ticket, ap_ticket)) != cudaSuccess) return (int)e;
+            if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        }
+        cudaError_t e = cudaMemsetAsync(ticket, 0, sizeof(unsigned int), stream);
+        if (e != cudaSuccess) return (int)e;
+        const int items = n_tiles * Hkv;
+        attention_tc_persistent_kernel<<<dim3(items < sms ? items : sms), AP_THREADS, smem, stream>>>(
+            *mk, *mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_size, shift, block_tables, max_blocks,
+            positions, seq_ids, tile_tok0, tile_ntok, n_tiles, H, Hkv, scale_log2, window);
+        return launch_status();
+    }
     constexpr size_t smem = 1024 + 3 * (size_t)AT_TILE_BYTES + 14 * 8 + 768 * sizeof(float) + AT_PAGES_CAP * sizeof(int);
     static bool once = false;
     if (!once) {
@@ -533,10 +1027,8 @@ TGO_API int tgo_attention_tc_prefill(const void* q, long long q_stride, void* ou
         if (e != cudaSuccess) return (int)e;
         once = true;
     }
-    int shift = 0;
-    while ((1 << shift) < page_size) ++shift;
     attention_tc_prefill_kernel<<<dim3(n_tiles, Hkv), AT_THREADS, smem, stream>>>(
         *mk, *mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_size, shift, block_tables, max_blocks,
-        positions, seq_ids, tile_tok0, tile_ntok, H, Hkv, scale * 1.4426950408889634f, window);
+        positions, seq_ids, tile_tok0, tile_ntok, H, Hkv, scale_log2, window);
     return launch_status();
 }

@@ -508,6 +508,7 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
 
 USE_TC_ATTENTION = True     # prompt portions with head size 128 on the tcgen05 kernel
 TC_ATTENTION_MIN_TOKENS = 1  # steps with fewer tokens than this keep the mma.sync kernel
+TC_ATTENTION_PERSISTENT = True   # one CTA per SM drawing items, or one CTA per item
 
 
 def attention_tc_supports(head_dim: int, group: int, page_size: int) -> bool:
@@ -542,7 +543,7 @@ def attention_tc_prefill(q: torch.Tensor, out: torch.Tensor, num_heads: int, num
         c_int(k_cache.shape[0]), c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]),
         _ptr(positions), _ptr(seq_ids), _ptr(tile_tok0), _ptr(tile_ntok), c_int(tile_tok0.numel()),
         c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_float(scale), c_int(window),
-        _stream()), "attention_tc_prefill",
+        c_int(1 if TC_ATTENTION_PERSISTENT else 0), _stream()), "attention_tc_prefill",
         f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads}, page_size={page_size})")
 
 
