@@ -8,7 +8,7 @@ import tiny
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 17, 33, 70, 100, 64], "B": [1, 9, 40, 70, 129, 48]}
+LENGTHS = {"A": [5, 17, 33, 70, 100, 64], "B": [1, 9, 40, 70, 129, 48], "C": [3, 150, 66, 200, 31, 290]}
 FAMILIES = {"whole": tiny.trace_whole, "tail": tiny.trace_tail, "portions": tiny.trace_portions,
             "mixed": tiny.trace_mixed}
 
@@ -26,7 +26,7 @@ def models(tmp_path_factory):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("family", list(FAMILIES))
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_replay_matches_plain(models, tmp_path, name, family, dtype):
     d, cfg, run, reqs, want = models[name]
     trace = FAMILIES[family](reqs)
@@ -37,7 +37,7 @@ def test_replay_matches_plain(models, tmp_path, name, family, dtype):
     assert worst <= tol, f"{name}/{family}/{dtype}: error {worst:.3e} at {where}, allowed {tol:.3e}"
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_float32_cuts_agree_bit_for_bit(models, name):
     """In float32 every sum's order depends on the position alone, so the four ways of
     cutting give the same bits, not just close values."""

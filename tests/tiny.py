@@ -8,6 +8,12 @@ Two configurations of the one architecture that differ in every size and option:
 
 In A the q width equals the hidden size and layers equal kv heads, so a confusion of
 those two pairs passes there; B is the configuration that tells them apart.
+
+A third, TINY_C, has the head size (128) that the tcgen05 attention kernel takes, a window
+layer, and prompts long enough for the tcgen05 product, so that replay in bfloat16 goes
+through those kernels too:
+
+  TINY_C      2    160     4    2   128       512      272   320   5e5    1e-5   no    40 (layer 0)  16
 """
 from __future__ import annotations
 
@@ -35,7 +41,14 @@ TINY_B = dict(architectures=["Qwen3ForCausalLM"], hidden_size=96, num_hidden_lay
               layer_types=["full_attention", "sliding_attention", "full_attention"])
 TINY_B_RUN = dict(seed=1, sigma=0.03, page_size=8)
 
-TINIES = {"A": (TINY_A, TINY_A_RUN), "B": (TINY_B, TINY_B_RUN)}
+TINY_C = dict(architectures=["Qwen3ForCausalLM"], hidden_size=160, num_hidden_layers=2,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=272,
+              vocab_size=320, rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=False,
+              max_position_embeddings=512, attention_bias=False, sliding_window=40,
+              layer_types=["sliding_attention", "full_attention"])
+TINY_C_RUN = dict(seed=2, sigma=0.03, page_size=16)
+
+TINIES = {"A": (TINY_A, TINY_A_RUN), "B": (TINY_B, TINY_B_RUN), "C": (TINY_C, TINY_C_RUN)}
 
 
 def make_model_dir(path, config, seed, sigma, gain_sigma=0.1):
