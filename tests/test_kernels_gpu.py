@@ -94,6 +94,44 @@ def rope_ref(x, pos, theta, rot):
     return y
 
 
+@pytest.mark.parametrize("H,Hkv", [(8, 2), (5, 1), (32, 8), (3, 3)])
+def test_qk_norm_rope_cache_many_tokens(H, Hkv):
+    """Head size 128, bfloat16, a prompt portion's worth of tokens: the kernel with half a
+    warp per head vector (head counts that leave half-warps idle or mix q, k and v in a warp)."""
+    T, ps, pages, eps, theta, dh = 70, 16, 9, 1e-6, 1e6, 128
+    dtype = torch.bfloat16
+    qkv = rnd(T, (H + 2 * Hkv) * dh, dtype=dtype, seed=H)
+    q, k, v = qkv[:, :H * dh], qkv[:, H * dh:(H + Hkv) * dh], qkv[:, (H + Hkv) * dh:]
+    qg, kg = 1 + 0.1 * rnd(dh, seed=5), 1 + 0.1 * rnd(dh, seed=6)
+    pos = torch.arange(300, 300 + T, dtype=torch.int32, device=DEV)
+    slot_list = [(5 * t + 3) % (pages * ps) if t != 11 else -1 for t in range(T)]     # scattered, one padded
+    assert len({s for s in slot_list if s >= 0}) == T - 1
+    slots = torch.tensor(slot_list, dtype=torch.int32, device=DEV)
+    inv = (theta ** (-2.0 * torch.arange(dh // 2, dtype=torch.float64) / dh)).to(DEV)
+    kc = torch.zeros(pages, Hkv, ps, dh, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+
+    def norm(x, g):
+        x = x.float()
+        return (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)) * g
+    want_q = rope_ref(norm(q.reshape(T, H, dh), qg), pos, theta, dh)
+    want_k = rope_ref(norm(k.reshape(T, Hkv, dh), kg), pos, theta, dh)
+    want_v = v.reshape(T, Hkv, dh).clone()
+    table = ops().rope_table(pos, inv)
+    ops().qk_norm_rope_cache(q, k, v, H, Hkv, dh, qg, kg, eps, table, dh, slots, kc, vc, ps)
+    assert torch.allclose(q.reshape(T, H, dh).float(), want_q, **tol(dtype))
+    for t in range(T):
+        s = slot_list[t]
+        if s < 0:
+            continue
+        assert torch.allclose(kc[s // ps, :, s % ps].float(), want_k[t], **tol(dtype))
+        assert torch.equal(vc[s // ps, :, s % ps], want_v[t])
+    written = {s for s in slot_list if s >= 0}
+    for s in range(pages * ps):
+        if s not in written:
+            assert not kc[s // ps, :, s % ps].any() and not vc[s // ps, :, s % ps].any()
+
+
 @pytest.mark.parametrize("H,Hkv,dh,rot", [(5, 5, 16, 16), (6, 2, 48, 32), (8, 1, 128, 128),
                                           (3, 3, 80, 80)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -71,3 +71,43 @@ def test_decode_with_chained_products_matches_plain(models, name, monkeypatch):
     worst, where, tol = tiny.compare(got, want, cfg, "bfloat16")
     assert worst <= tol, f"{name}: error {worst:.3e} at {where}, allowed {tol:.3e}"
     assert int(ops.gemm_chain_error_flag("cuda:0").item()) == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_prompt_portions_through_graphs_give_the_same_bits(models, name, dtype):
+    """Equal-sized portions of a long prompt: the second is captured as a CUDA graph and the
+    later ones replay it. Same kernels, same order, so the logits equal those of an engine
+    that never captures, bit for bit; and a portion of another request between the replays
+    goes through the same graph with its own positions and pages."""
+    import torch
+    import tgo_b200
+    from tgo_b200.engine.step import StepEntry
+    d, cfg, run, reqs, _ = models[name]
+    model = tgo_b200.open(d, dtype=dtype)
+    rng = np.random.default_rng(5)
+    long_a = rng.integers(0, cfg["vocab_size"], 200).tolist()
+    long_b = rng.integers(0, cfg["vocab_size"], 120).tolist()
+    size = 40
+    steps = []
+    for i in range(0, 200, size):
+        steps.append(("a", long_a[i:i + size]))
+        if i // size in (1, 2, 3):
+            j = (i // size - 1) * size
+            steps.append(("b", long_b[j:j + size]))
+    got = {}
+    for graphs in (False, True):
+        eng = model.new_engine(page_size=run["page_size"], max_tokens=512, num_slots=2, graphs=graphs)
+        eng.PORTION_GRAPH_MIN_TOKENS = 32
+        eng.admit("a")
+        eng.admit("b")
+        outs = []
+        for rid, toks in steps:
+            outs.append(eng.step([StepEntry(rid, toks, [0, size - 1])]).clone())
+        torch.cuda.synchronize()
+        got[graphs] = outs
+        if graphs:
+            assert len(eng._portion_graphs) == 1 or len({k[2] for k in eng._portion_graphs}) > 1
+            assert eng._portion_graphs, "no portion was captured"
+    for a, b in zip(got[False], got[True]):
+        assert torch.equal(a, b)

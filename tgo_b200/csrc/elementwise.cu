@@ -500,6 +500,95 @@ __global__ void qk_norm_rope_cache_dh128_kernel(
     if (dst) Vec4<T>::store(dst + 4 * lane, x);
 }
 
+// The same for many tokens of bfloat16 with head size 128 (a prompt portion): one CTA per
+// token, half a warp per head vector with 16-byte accesses (lane l of the half holds channels
+// 8l .. 8l+7, its rotation partner is 8 lanes on), the CTA's 16 half-warps walk the token's
+// q, k and v heads.
+#define QKW_WARPS 8
+__global__ void __launch_bounds__(QKW_WARPS * 32)
+qk_norm_rope_cache_dh128_wide_kernel(
+    bf16* __restrict__ q, long long q_stride, bf16* __restrict__ k, long long k_stride,
+    const bf16* __restrict__ v, long long v_stride, int H, int Hkv,
+    const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+    const float* __restrict__ rope, const int* __restrict__ slots, bf16* __restrict__ k_cache,
+    bf16* __restrict__ v_cache, int page_size) {
+    constexpr int dh = 128;
+    pdl_wait();
+    pdl_launch();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, hl = lane & 15;
+    const int half_id = threadIdx.x >> 4;                    // 0 .. 15
+    const int nk = k ? Hkv : 0, nv = v ? Hkv : 0;
+    const int total = H + nk + nv;
+    const int slot = slots ? slots[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+    // the token's cos and sin for this lane's channels (the low and the high half share them)
+    float cc[8], sv[8];
+    if (rope) {
+        const float* cs = rope + (size_t)t * dh;              // [64] cos, [64] sin
+        const int i0 = 8 * (hl & 7);
+        const float4 c0 = *(const float4*)(cs + i0), c1 = *(const float4*)(cs + i0 + 4);
+        const float4 s0 = *(const float4*)(cs + 64 + i0), s1 = *(const float4*)(cs + 64 + i0 + 4);
+        cc[0] = c0.x; cc[1] = c0.y; cc[2] = c0.z; cc[3] = c0.w; cc[4] = c1.x; cc[5] = c1.y; cc[6] = c1.z; cc[7] = c1.w;
+        sv[0] = s0.x; sv[1] = s0.y; sv[2] = s0.z; sv[3] = s0.w; sv[4] = s1.x; sv[5] = s1.y; sv[6] = s1.z; sv[7] = s1.w;
+    }
+    // every half-warp runs the same number of rounds, so that the shuffles below are complete
+    const int rounds = (total + 15) / 16;
+    for (int r = 0; r < rounds; ++r) {
+        const int hh = r * 16 + half_id;
+        const bool live = hh < total;
+        const bool is_v = live && hh >= H + nk;
+        const bool is_q = live && hh < H;
+        const int head = !live ? 0 : is_q ? hh : is_v ? hh - H - nk : hh - H;
+        const bf16* src = !live ? q : is_q ? q + (size_t)t * q_stride + (size_t)head * dh
+                          : is_v ? v + (size_t)t * v_stride + (size_t)head * dh
+                                 : k + (size_t)t * k_stride + (size_t)head * dh;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (live) raw = *(const uint4*)(src + 8 * hl);
+        if (is_v) {
+            if (slot >= 0) *(uint4*)(v_cache + (((size_t)page * Hkv + head) * page_size + off) * dh + 8 * hl) = raw;
+            continue;                                        // no shuffles on this path ...
+        }
+        // ... but a half-warp of v and a half-warp of q or k may share a warp: the shuffles
+        // below stay inside the half-warp and name only its lanes
+        const unsigned mask = 0xffffu << (lane & 16);
+        float x[8];
+        {
+            const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x), b = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
+            const float2 c = __bfloat1622float2(*(const __nv_bfloat162*)&raw.z), d = __bfloat1622float2(*(const __nv_bfloat162*)&raw.w);
+            x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y; x[4] = c.x; x[5] = c.y; x[6] = d.x; x[7] = d.y;
+        }
+        const float* gain = is_q ? q_gain : k_gain;
+        if (gain) {
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(mask, ss, o);      // within the half-warp
+            const float scale = rsqrtf(ss / (float)dh + eps);
+            const float4 g0 = *(const float4*)(gain + 8 * hl), g1 = *(const float4*)(gain + 8 * hl + 4);
+            x[0] = (x[0] * scale) * g0.x; x[1] = (x[1] * scale) * g0.y; x[2] = (x[2] * scale) * g0.z; x[3] = (x[3] * scale) * g0.w;
+            x[4] = (x[4] * scale) * g1.x; x[5] = (x[5] * scale) * g1.y; x[6] = (x[6] * scale) * g1.z; x[7] = (x[7] * scale) * g1.w;
+        }
+        if (rope) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float other = __shfl_xor_sync(mask, x[e], 8);
+                x[e] = hl < 8 ? x[e] * cc[e] - other * sv[e] : other * sv[e] + x[e] * cc[e];
+            }
+        }
+        if (!live) continue;
+        uint4 o4;
+        { __nv_bfloat162 p0 = __floats2bfloat162_rn(x[0], x[1]), p1 = __floats2bfloat162_rn(x[2], x[3]);
+          __nv_bfloat162 p2 = __floats2bfloat162_rn(x[4], x[5]), p3 = __floats2bfloat162_rn(x[6], x[7]);
+          o4.x = *(uint32_t*)&p0; o4.y = *(uint32_t*)&p1; o4.z = *(uint32_t*)&p2; o4.w = *(uint32_t*)&p3; }
+        bf16* dst = is_q ? q + (size_t)t * q_stride + (size_t)head * dh : k + (size_t)t * k_stride + (size_t)head * dh;
+        if (!is_q && k_cache)
+            dst = slot >= 0 ? k_cache + (((size_t)page * Hkv + head) * page_size + off) * dh : nullptr;
+        if (dst) *(uint4*)(dst + 8 * hl) = o4;
+    }
+}
+
 TGO_API int tgo_qk_norm_rope_cache(void* q, long long q_stride, void* k, long long k_stride,
                                    const void* v, long long v_stride, int dtype, int T, int H,
                                    int Hkv, int dh, const float* q_gain, const float* k_gain,
@@ -519,6 +608,10 @@ TGO_API int tgo_qk_norm_rope_cache(void* q, long long q_stride, void* k, long lo
     const bool aligned = ((uintptr_t)q * 1 % 16 == 0) && (q_stride * esz) % 16 == 0 &&
                          (!k || (((uintptr_t)k % 16 == 0) && (k_stride * esz) % 16 == 0)) &&
                          (!v || (((uintptr_t)v % 16 == 0) && (v_stride * esz) % 16 == 0));
+    if (dh == 128 && (rot == 128 || !rope) && aligned && dtype == TGO_BF16 && T >= 64)
+        return tgo_launch_pdl(qk_norm_rope_cache_dh128_wide_kernel, dim3(T), dim3(QKW_WARPS * 32), 0, stream,
+                              (bf16*)q, q_stride, (bf16*)k, k_stride, (const bf16*)v, v_stride, H, Hkv,
+                              q_gain, k_gain, eps, rope, slots, (bf16*)k_cache, (bf16*)v_cache, page_size);
     if (dh == 128 && (rot == 128 || !rope) && aligned && (dtype == TGO_BF16 || dtype == TGO_F32)) {
         if (dtype == TGO_BF16)
             return tgo_launch_pdl(qk_norm_rope_cache_dh128_kernel<bf16>, grid, dim3(warps * 32), 0, stream,

@@ -106,8 +106,7 @@ def measure_prefill(loaded, tokens: int, warmup: int = 3, steps: int = 3, seed: 
                     page_size: int = 16) -> dict:
     """One request of `tokens` prompt tokens in one step, logits of its last token."""
     model = loaded.model
-    eng = Engine(model, page_size=page_size, max_tokens=round_up(tokens, 64), num_slots=1,
-                 graphs=False)
+    eng = Engine(model, page_size=page_size, max_tokens=round_up(tokens, 64), num_slots=1)
     prompt = random_prompts(model.spec.vocab_size, 1, tokens, seed)[0]
     flush = L2Flusher(model.device)
     times = []

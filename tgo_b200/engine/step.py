@@ -40,7 +40,8 @@ class Engine:
         """The pool of every group holds `num_pages` pages, or enough for `max_tokens`
         tokens (each live request's count rounded up to whole pages). With `graphs`, steps
         in which every request brings one token are captured once per batch-size bucket
-        as a CUDA graph and replayed."""
+        as a CUDA graph and replayed; so is a step that is one request's prompt portion of
+        a size that has come before (the fixed-size portions of a long prompt)."""
         if page_size <= 0:
             raise ValueError(f"engine: page size {page_size}")
         if num_pages is None:
@@ -58,6 +59,8 @@ class Engine:
         self.use_graphs = graphs and self.device.type == "cuda"
         self.h2d_bytes_last = 0       # bytes of the last step's inputs copied to the device
         self._graphs = {}
+        self._portion_graphs = {}     # key -> captured graph of a one-request prompt portion
+        self._portion_seen = {}       # key -> times the shape came without a graph
 
     # ------------------------------------------------------------------ requests
     def admit(self, request_id, reserve_tokens: int = 0):
@@ -247,6 +250,10 @@ class Engine:
             self.cache.grow(e.request_id, r.length + len(e.tokens))
         if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
             logits = self._graph_step(entries)
+        elif self.use_graphs and len(entries) == 1 and \
+                len(entries[0].tokens) >= self.PORTION_GRAPH_MIN_TOKENS and \
+                (logits := self._portion_graph_step(entries)) is not None:
+            pass
         else:
             ctx, tables, slots = self.build_context(entries)
             logits = self.model.forward(ctx, self.storage, tables, slots)
@@ -288,11 +295,15 @@ class Engine:
                 ctx, tables, slots = self.build_context(entries)
                 return self.model.forward(ctx, self.storage, tables, slots)
             self._graphs[key] = entry
-        graph, host, dev, logits, launches = entry
-        # straight into the graph's pinned buffer, then one copy
+        graph, host, dev, logits, launches, copied = entry
+        # straight into the graph's pinned buffer, then one copy; the buffer is the host's to
+        # write again only when the last copy out of it has run (a caller that does not read
+        # a step's result before the next step would otherwise overwrite it in flight)
+        copied.synchronize()
         _, meta = self._pack(entries, pad_to=bucket, width_quantum=self.WIDTH_QUANTUM,
                              all_rows=True, out=host.numpy())
         dev.copy_(host, non_blocking=True)
+        copied.record()
         self.h2d_bytes_last = meta["total"] * 4
         graph.replay()
         ops.LAUNCHES[0] += launches
@@ -302,6 +313,51 @@ class Engine:
         if not want:
             return logits[:0]
         return logits[torch.tensor(want, device=self.device)]
+
+    # ------------------------------------------------- graphs of prompt portions
+    PORTION_GRAPH_MIN_TOKENS = 256      # shorter portions gain nothing from a graph
+    PORTION_GRAPHS_KEPT = 4
+
+    def _portion_graph_step(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
+        """One request's prompt portion through a captured graph, if its shape (token count,
+        wanted places, block-table width in quanta) has come before: the second time a shape
+        comes it is captured, from then on replayed. Everything the kernels need that is not
+        in the shape (positions, slots, block table, token ids) is data in the step's buffer.
+        Returns None when the step has to run the ordinary way."""
+        e = entries[0]
+        widths = tuple((max(1, len(self.cache.requests[e.request_id].tables[g])) +
+                        self.WIDTH_QUANTUM - 1) // self.WIDTH_QUANTUM * self.WIDTH_QUANTUM
+                       for g in range(len(self.cache.groups)))
+        key = (len(e.tokens), tuple(int(w) for w in e.want), widths)
+        entry = self._portion_graphs.get(key)
+        if entry is None:
+            seen = self._portion_seen.get(key, 0) + 1
+            self._portion_seen[key] = seen
+            if seen < 2:
+                return None
+            if len(self._portion_seen) > 64:
+                self._portion_seen.clear()
+            flat, meta = self._pack(entries, width_quantum=self.WIDTH_QUANTUM)
+            try:
+                entry = self._capture(flat, meta)
+            except RuntimeError as err:
+                print(f"[tgo_b200] prompt portions are not captured as graphs: {str(err)[:120]}",
+                      file=sys.stderr)
+                self.PORTION_GRAPH_MIN_TOKENS = 1 << 62        # this engine stops trying
+                torch.cuda.synchronize(self.device)
+                return None
+            while len(self._portion_graphs) >= self.PORTION_GRAPHS_KEPT:
+                self._portion_graphs.pop(next(iter(self._portion_graphs)))     # the oldest
+            self._portion_graphs[key] = entry
+        graph, host, dev, logits, launches, copied = entry
+        copied.synchronize()              # see _graph_step
+        _, meta = self._pack(entries, width_quantum=self.WIDTH_QUANTUM, out=host.numpy())
+        dev.copy_(host, non_blocking=True)
+        copied.record()
+        self.h2d_bytes_last = meta["total"] * 4
+        graph.replay()
+        ops.LAUNCHES[0] += launches
+        return logits
 
     def _capture(self, flat, meta):
         host = torch.from_numpy(flat[:meta["total"]].copy()).pin_memory()
@@ -325,9 +381,14 @@ class Engine:
         torch.cuda.synchronize(self.device)
         # what the eager run cached per step (tables made from its inputs) must be made
         # again inside the capture, or the replays would keep reading the first step's
-        ctx.aux = {"graph": True}
+        # (the attention tile lists depend on the step's shape alone and are kept: they are
+        # made on the host, which a capture cannot do)
+        ctx.aux = {"graph": True, **{k: v for k, v in ctx.aux.items()
+                                     if isinstance(k, tuple) and k and k[0] == "tiles"}}
         graph = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES[0]
         with torch.cuda.graph(graph):
             logits = self.model.forward(ctx, self.storage, tables, slots)
-        return graph, host, dev, logits, ops.LAUNCHES[0] - before
+        copied = torch.cuda.Event()
+        copied.record()
+        return graph, host, dev, logits, ops.LAUNCHES[0] - before, copied
