@@ -519,6 +519,7 @@ def tc_flag():
 @pytest.mark.parametrize("M,N,K,transpose,splits", [
     (128, 128, 64, False, 1), (200, 300, 264, False, 1), (700, 520, 1000, False, 1),
     (1024, 2048, 4096, False, 1), (300, 512, 2048, False, 3), (8, 128, 64, True, 1),
+    (2048, 4096, 192, False, 1), (2048, 6144, 128, False, 1), (130, 1001, 72, False, 1),   # tiles 232 / 240 wide
     (33, 200, 264, True, 1), (64, 512, 4096, True, 4), (200, 256, 512, True, 1)])
 def test_gemm_tc(M, N, K, transpose, splits):
     """The tcgen05 kernel in both orientations, with tails in every dimension and K splits."""

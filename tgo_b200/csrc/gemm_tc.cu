@@ -100,7 +100,10 @@ struct TcSmem {
     static constexpr int STAGE = A_BYTES + B_BYTES;
     static constexpr int STAGES = (200 * 1024) / STAGE < 8 ? (200 * 1024) / STAGE : 8;
     static constexpr size_t TOTAL = (size_t)STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
-    static_assert(2 * BN <= 512, "two accumulators must fit the 512 columns of tensor memory");
+    // columns of tensor memory per accumulator and in all: powers of two (an allocation has to be)
+    static constexpr int ACC_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;
+    static_assert(BN % 8 == 0 && BN <= 256, "a tile is at most 256 wide, in steps of 8");
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -239,7 +242,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(tc_smem(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
+                     ::"r"(tc_smem(tmem_slot)), "r"((uint32_t)L::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -292,7 +295,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, err, 4);   // epilogue let go of it
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BN;
+                const uint32_t d_tmem = tmem_base + buf * L::ACC_COLS;
                 for (int i = 0; i < n_kb; ++i, ++it) {
                     const int s = it % STAGES;
                     ok = mbar_wait(&full[s], (it / STAGES) & 1, err, 2);
@@ -321,9 +324,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (ok) ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, err, 3);
             tc_fence_after();
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            // a tile that is not a multiple of 32 wide: its last group of columns is cut at the
+            // tile's edge (what lies beyond belongs to the next tile)
+            const int n_edge = n0 + BN < rows_b ? n0 + BN : rows_b;
+            for (int c = 0; c < (BN + 31) / 32; ++c) {
                 uint32_t r[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + (uint32_t)(c * 32);
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * L::ACC_COLS + (uint32_t)(c * 32);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -336,7 +342,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     : "r"(taddr));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (ok && n_kb > 0)
-                    tc_store<OMODE, TRANSPOSE>(r, out, m0 + row, n0 + c * 32, rows_a, rows_b, ld_out, split);
+                    tc_store<OMODE, TRANSPOSE>(r, out, m0 + row, n0 + c * 32, rows_a, n_edge, ld_out, split);
             }
             // the accumulator may be overwritten: one arrival per epilogue warp
             tc_fence_before();
@@ -348,7 +354,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)L::TMEM_COLS) : "memory");
     }
 }
 
@@ -458,11 +464,27 @@ TGO_API int tgo_gemm_tc(const void* x, const void* w, void* out, int M, int N, i
     CUtensorMap ma, mb;
     int rc;
     if (!transpose) {
-        const int bn = N >= 256 ? 256 : 128;
+        // Tile width: the CTAs walk the tiles in rounds, and the last round is as long as the
+        // others however few tiles it has; among the widths built, the one with the least
+        // rounds x width wins (4096 columns under 2048 rows: 288 tiles of 232 in two rounds
+        // instead of 256 tiles of 256 in two rounds, of which the second is 3/4 empty).
+        int bn = N >= 256 ? 256 : 128;
+        if (N >= 256 && om != TC_OUT_SWIGLU && om != TC_OUT_PARTIAL) {
+            const int tiles_m = (M + TC_BM - 1) / TC_BM;
+            long long best = -1;
+            const int widths[3] = {256, 240, 232};
+            for (int i = 0; i < 3; ++i) {
+                const long long tiles = (long long)tiles_m * ((N + widths[i] - 1) / widths[i]);
+                const long long cost = ((tiles + 147) / 148) * widths[i];
+                if (best < 0 || cost < best) { best = cost; bn = widths[i]; }
+            }
+        }
         if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
         if ((rc = make_map(&mb, w, N, K, bn))) return rc;
-        rc = bn == 256 ? tc_dispatch<256, false>(ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream)
-                       : tc_dispatch<128, false>(ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream);
+        if (bn == 256) rc = tc_dispatch<256, false>(ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream);
+        else if (bn == 240) rc = tc_dispatch<240, false>(ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream);
+        else if (bn == 232) rc = tc_dispatch<232, false>(ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream);
+        else rc = tc_dispatch<128, false>(ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream);
     } else {
         if (M > 256) return TGO_E_BAD_ARG;
         const int bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;

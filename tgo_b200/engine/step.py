@@ -295,7 +295,7 @@ class Engine:
                 ctx, tables, slots = self.build_context(entries)
                 return self.model.forward(ctx, self.storage, tables, slots)
             self._graphs[key] = entry
-        graph, host, dev, logits, launches, copied = entry
+        graph, host, dev, logits, launches, copied, _ = entry
         # straight into the graph's pinned buffer, then one copy; the buffer is the host's to
         # write again only when the last copy out of it has run (a caller that does not read
         # a step's result before the next step would otherwise overwrite it in flight)
@@ -339,7 +339,8 @@ class Engine:
                 self._portion_seen.clear()
             flat, meta = self._pack(entries, width_quantum=self.WIDTH_QUANTUM)
             try:
-                entry = self._capture(flat, meta)
+                # the shape has run before, so everything it needs is loaded: no warm-up run
+                entry = self._capture(flat, meta, warm=False)
             except RuntimeError as err:
                 print(f"[tgo_b200] prompt portions are not captured as graphs: {str(err)[:120]}",
                       file=sys.stderr)
@@ -349,7 +350,7 @@ class Engine:
             while len(self._portion_graphs) >= self.PORTION_GRAPHS_KEPT:
                 self._portion_graphs.pop(next(iter(self._portion_graphs)))     # the oldest
             self._portion_graphs[key] = entry
-        graph, host, dev, logits, launches, copied = entry
+        graph, host, dev, logits, launches, copied, _ = entry
         copied.synchronize()              # see _graph_step
         _, meta = self._pack(entries, width_quantum=self.WIDTH_QUANTUM, out=host.numpy())
         dev.copy_(host, non_blocking=True)
@@ -359,7 +360,7 @@ class Engine:
         ops.LAUNCHES[0] += launches
         return logits
 
-    def _capture(self, flat, meta):
+    def _capture(self, flat, meta, warm: bool = True):
         host = torch.from_numpy(flat[:meta["total"]].copy()).pin_memory()
         dev = torch.empty(meta["total"], dtype=torch.int32, device=self.device)
         dev.copy_(host)
@@ -367,22 +368,34 @@ class Engine:
         meta["max_context"] = max(meta["widths"]) * self.page_size if meta["widths"] else 0
         ctx, tables, slots = self._views(dev, meta)
         ctx.aux["graph"] = True
-        # one eager run first: libraries initialise and kernels compile outside the capture.
-        # The cache rows it writes are the ones the replay writes again; fixed-size state is
-        # not idempotent (a mixer advances it), so it is put back afterwards.
-        saved = {call: t.clone() for call, t in self.storage.state.items()}
-        side = torch.cuda.Stream(device=self.device)
-        side.wait_stream(torch.cuda.current_stream(self.device))
-        with torch.cuda.stream(side):
-            self.model.forward(ctx, self.storage, tables, slots)
-        torch.cuda.current_stream(self.device).wait_stream(side)
-        for call, t in saved.items():
-            self.storage.state[call].copy_(t)
-        torch.cuda.synchronize(self.device)
-        # what the eager run cached per step (tables made from its inputs) must be made
-        # again inside the capture, or the replays would keep reading the first step's
-        # (the attention tile lists depend on the step's shape alone and are kept: they are
-        # made on the host, which a capture cannot do)
+        if warm:
+            # one eager run first: libraries initialise and kernels compile outside the
+            # capture. The cache rows it writes are the ones the replay writes again;
+            # fixed-size state is not idempotent (a mixer advances it), so it is put back.
+            saved = {call: t.clone() for call, t in self.storage.state.items()}
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                self.model.forward(ctx, self.storage, tables, slots)
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            for call, t in saved.items():
+                self.storage.state[call].copy_(t)
+            torch.cuda.synchronize(self.device)
+        elif not ctx.decode_only:
+            # the attention tile lists are made on the host, which a capture cannot do: make
+            # them now, for every number of tokens a tile may hold
+            groups = set()
+            for ls in self.model.spec.layers:
+                heads = getattr(ls.mixer, "num_heads", None)
+                kv_heads = getattr(ls.mixer, "num_kv_heads", None)
+                if heads and kv_heads:
+                    groups.add(max(1, heads // kv_heads))
+            for g in groups:
+                ops._tiles(ctx, max(1, 128 // g))
+            torch.cuda.synchronize(self.device)
+        # what an eager run cached per step (tables made from its inputs) must be made again
+        # inside the capture, or the replays would keep reading the first step's; the tile
+        # lists depend on the step's shape alone and are kept
         ctx.aux = {"graph": True, **{k: v for k, v in ctx.aux.items()
                                      if isinstance(k, tuple) and k and k[0] == "tiles"}}
         graph = torch.cuda.CUDAGraph()
@@ -391,4 +404,6 @@ class Engine:
             logits = self.model.forward(ctx, self.storage, tables, slots)
         copied = torch.cuda.Event()
         copied.record()
-        return graph, host, dev, logits, ops.LAUNCHES[0] - before, copied
+        # the context goes along: tensors made outside the capture that the graph's kernels
+        # read (the tile lists) must live as long as the graph
+        return graph, host, dev, logits, ops.LAUNCHES[0] - before, copied, ctx
