@@ -629,6 +629,8 @@ TC_CASES = [
     ([300], [0], 16, 1, 64, 100),                           # 16 heads a group, window over tiles
     ([513], [0], 8, 4, 128, 0),                             # a page as large as a key tile
     ([40], [1000], 8, 2, 8, 0),                             # small pages, a long context behind
+    ([40], [17000], 4, 1, 16, 0),                           # more pages than the on-chip table slice holds
+    ([40], [17000], 4, 1, 16, 300),                         # the same behind a window
 ]
 
 
