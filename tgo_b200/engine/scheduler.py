@@ -338,6 +338,8 @@ class Runner:
                     done_now.append(req)
                 else:
                     self.sched.feed(p.slot, tok)
+        if done_now and hasattr(self.sched.engine, "check_kernels"):
+            self.sched.engine.check_kernels()     # before a result is handed out
         return done_now
 
     def run(self) -> None:

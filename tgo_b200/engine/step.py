@@ -71,6 +71,13 @@ class Engine:
     def finish(self, request_id):
         return self.cache.finish(request_id)
 
+    def check_kernels(self) -> None:
+        """Raise if a kernel gave up one of its bounded waits (its output is then garbage).
+        Synchronises with the device: called where the host waits for results anyway."""
+        bad = ops.kernel_wait_errors()
+        if bad:
+            raise RuntimeError(f"engine: a kernel's wait ran out, results are not valid: {bad}")
+
     def length(self, request_id) -> int:
         return self.cache.requests[request_id].length
 

@@ -723,6 +723,27 @@ def gemm_chain_error_flag(device) -> torch.Tensor:
     return _chain_buffers(device)[1]
 
 
+def kernel_wait_errors() -> dict:
+    """Which kernels of this package gave up a wait (on an mbarrier or a grid barrier) since
+    the process began: {kernel: code}, empty when none did. Their results are then not to be
+    trusted. Looks only at libraries that are loaded; synchronises with the device."""
+    from .build import _loaded
+    out = {}
+    if "attention_tc" in _loaded:
+        code = attention_tc_error()
+        if code:
+            out["attention_tc"] = code
+    for key, flag in _tc_err.items():
+        code = int(flag.item())
+        if code:
+            out[f"gemm_tc (device {key})"] = code
+    for key, state in _chain_state.items():
+        code = int(state[1].item())
+        if code:
+            out[f"gemm_chain ({key})"] = code
+    return out
+
+
 def gemm_chain(phases, M: int) -> None:
     """Run up to four small-batch products back to back in one persistent kernel.
 
