@@ -1,0 +1,403 @@
+// Decode attention (one token per request) with the cache pages brought in by TMA: the same
+// arithmetic as flash_decode_kernel (attention_flash.cu: mma.sync m16n8k16, the G query heads
+// of a kv head as the rows of one m16 tile, 64 keys a tile, four warps with 16 keys each,
+// float32 softmax state, partial results per key split for flash_combine_kernel), for head
+// size 128 and pages of 8, 16, 32 or 64 tokens. What changes is who moves the data: a fifth
+// warp asks the tensor memory accelerator for the pages of the next tiles (two boxes of
+// page_size rows x 64 columns per page and per K / V, 128-byte swizzle) into a ring of two
+// stages with an mbarrier each, so the four computing warps issue no copies and no addresses
+// for them: that kernel is bound by instruction issue, not by the bandwidth it asks for.
+//
+// Rows of a tile that no query may read (past the request's last key, before its window) are
+// not masked in V by the copy as cp.async's zero fill did: the warp that owns such keys
+// writes zeros over its V rows before it multiplies (P is zero there, the cache may hold NaN).
+//
+// Every mbarrier wait has a time limit (about two seconds), after which a flag is set and the
+// CTA runs to its end without waiting again.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "mma_sync.cuh"
+
+#define DT_BN 64
+#define DT_DH 128
+#ifndef DT_STAGES
+#define DT_STAGES 2
+#endif
+#ifndef DT_MIN_BLOCKS
+#define DT_MIN_BLOCKS 3
+#endif
+#define DT_HALF_BYTES (DT_BN * 128)            // 64 keys x 64 columns of bf16
+#define DT_TILE_BYTES (2 * DT_HALF_BYTES)      // K or V of one tile
+#define DT_STAGE_BYTES (2 * DT_TILE_BYTES)     // K and V
+#define DT_THREADS 160
+#define DT_PAGES_CAP 1024
+#define DT_WAIT_CYCLES 4000000000ll
+
+__device__ int dt_error_flag = 0;
+
+__device__ __forceinline__ bool dt_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool dt_wait(uint32_t bar, uint32_t parity) {
+    if (dt_try(bar, parity)) return true;
+    const long long start = clock64();
+    while (!dt_try(bar, parity)) {
+        if (clock64() - start > DT_WAIT_CYCLES) {
+            atomicExch(&dt_error_flag, 1);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void dt_tma(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// byte offset of 16-byte piece `c` (0..15) of row `r` in a tile of two swizzled halves
+__device__ __forceinline__ uint32_t dt_at(int r, int c) {
+    return (uint32_t)((c >> 3) * DT_HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+
+__global__ void __launch_bounds__(DT_THREADS, DT_MIN_BLOCKS)
+flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                        const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                        long long out_stride, int page_size, int page_shift,
+                        const int* __restrict__ block_tables, int max_blocks,
+                        const int* __restrict__ positions, const int* __restrict__ seq_ids, int H,
+                        int Hkv, float scale_log2, int window, int n_splits,
+                        float* __restrict__ part_o, float* __restrict__ part_ml) {
+    constexpr int DH = DT_DH, KS = DH / 16, CH = DH / 8, LDQ = DH + 8;
+    extern __shared__ unsigned char dt_raw[];
+    unsigned char* base = (unsigned char*)(((uintptr_t)dt_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* ring = base;                                      // [stage][K | V][2 halves][64][128 B]
+    uint64_t* bars = (uint64_t*)(ring + DT_STAGES * DT_STAGE_BYTES); // full[S], empty[S]
+    bf16* sq = (bf16*)(bars + 2 * DT_STAGES);                        // [16][LDQ]
+    float* s_ml = (float*)(sq + 16 * LDQ);                           // [4][16][2]
+    int* s_pages = (int*)(s_ml + 4 * 16 * 2);                        // [DT_PAGES_CAP]
+    pdl_wait();
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int G = H / Hkv;
+    const int p = positions[tok];
+    if (p < 0) {                               // a request that brings nothing: zeros out
+        if (split == 0)
+            for (int i = tid; i < G * DH; i += DT_THREADS)
+                out[(size_t)tok * out_stride + (size_t)(kvh * G) * DH + i] = __float2bfloat16_rn(0.f);
+        if (n_splits > 1)
+            for (int r = tid; r < G; r += DT_THREADS) {
+                const size_t at = ((size_t)tok * H + kvh * G + r) * n_splits + split;
+                part_ml[at * 2] = -INFINITY;
+                part_ml[at * 2 + 1] = 0.f;
+            }
+        return;
+    }
+    const int* bt = block_tables + (size_t)seq_ids[tok] * max_blocks;
+    const int key_lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int key_hi = p + 1;
+    const int t_first = key_lo / DT_BN, t_end = (key_hi + DT_BN - 1) / DT_BN;
+    int t_lo = t_first, t_hi = t_end;
+    if (n_splits > 1) {
+        const int per = (t_end - t_first + n_splits - 1) / n_splits;
+        t_lo = t_first + split * per;
+        t_hi = t_lo + per < t_end ? t_lo + per : t_end;
+    }
+    const int n_it = t_hi > t_lo ? t_hi - t_lo : 0;
+    const int pages_per_tile = DT_BN >> page_shift;
+    const int pg_lo = t_lo * pages_per_tile;
+    {
+        int pg_hi = t_hi * pages_per_tile;
+        if (pg_hi > max_blocks) pg_hi = max_blocks;
+        if (pg_hi - pg_lo > DT_PAGES_CAP) pg_hi = pg_lo + DT_PAGES_CAP;
+        for (int i = pg_lo + tid; i < pg_hi; i += DT_THREADS) s_pages[i - pg_lo] = bt[i];
+    }
+    if (tid == 0) {
+        for (int s = 0; s < DT_STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bars[s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(smem_u32(&bars[DT_STAGES + s])));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = tid; i < 16 * CH; i += DT_THREADS) {
+        const int r = i / CH, c = i % CH;
+        const bool ok = r < G;
+        cp_async16(sq + r * LDQ + c * 8,
+                   ok ? q + (size_t)tok * q_stride + (size_t)(kvh * G + r) * DH + c * 8 : q, ok);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+
+    if (warp == 4) {
+        // ------------------------------------------------------------- producer
+        auto page_of = [&](int pi) { return pi - pg_lo < DT_PAGES_CAP ? s_pages[pi - pg_lo] : bt[pi]; };
+        bool ok = true;
+        for (int it = 0; it < n_it; ++it) {
+            const int s = it % DT_STAGES;
+            const uint32_t ph = (uint32_t)(it / DT_STAGES) & 1u;
+            const int j = t_lo + it;
+            int first = j * pages_per_tile, last = first + pages_per_tile;      // pages with a readable key
+            while (first < last && (first + 1) * page_size <= key_lo) ++first;
+            while (last > first && (last - 1) * page_size >= key_hi) --last;
+            ok = __all_sync(0xffffffffu, ok && dt_wait(smem_u32(&bars[DT_STAGES + s]), ph ^ 1u));
+            if (!ok) break;
+            const uint32_t full = smem_u32(&bars[s]);
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
+                             ::"r"(full), "r"((uint32_t)(last - first) * (uint32_t)page_size * 512u) : "memory");
+            __syncwarp();
+            for (int pi = first + lane; pi < last; pi += 32) {
+                const int row = (page_of(pi) * Hkv + kvh) * page_size;
+                const uint32_t dst = smem_u32(ring + s * DT_STAGE_BYTES) + (uint32_t)((pi - j * pages_per_tile) * page_size * 128);
+                dt_tma(dst, &map_k, 0, row, full);
+                dt_tma(dst + DT_HALF_BYTES, &map_k, 64, row, full);
+                dt_tma(dst + DT_TILE_BYTES, &map_v, 0, row, full);
+                dt_tma(dst + DT_TILE_BYTES + DT_HALF_BYTES, &map_v, 64, row, full);
+            }
+        }
+        // the producer takes no part in the sums below, but in the barriers
+    }
+
+    float o[DH / 8][4];
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    const bool row_lo_ok = r_lo < G, row_hi_ok = r_hi < G;
+
+    if (warp < 4) {
+        uint32_t qa[KS][4];
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+            ldmatrix_x4(qa[ks], sq + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDQ + ks * 16 + (lane >> 4) * 8);
+        bool ok = true;
+        for (int it = 0; it < n_it; ++it) {
+            const int s = it % DT_STAGES;
+            const uint32_t ph = (uint32_t)(it / DT_STAGES) & 1u;
+            const int t = t_lo + it;
+            if (ok) ok = dt_wait(smem_u32(&bars[s]), ph);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const uint32_t kt = smem_u32(ring + s * DT_STAGE_BYTES);
+            const uint32_t vt = kt + DT_TILE_BYTES;
+            const int my_key0 = t * DT_BN + warp * 16;
+            // this warp's V rows that nobody may read: zeros (P is zero there; the page may hold anything)
+            if (my_key0 + 16 > key_hi || my_key0 < key_lo) {
+                for (int i = lane; i < 16 * 16; i += 32) {
+                    const int r = i >> 4, c = i & 15;
+                    const int key = my_key0 + r;
+                    if (key >= key_hi || key < key_lo)
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(vt + dt_at(warp * 16 + r, c)), "r"(0u) : "memory");
+                }
+                __syncwarp();
+            }
+            float sc[2][4];
+            sc[0][0] = sc[0][1] = sc[0][2] = sc[0][3] = 0.f;
+            sc[1][0] = sc[1][1] = sc[1][2] = sc[1][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                uint32_t kb[4];
+                const int r = warp * 16 + (lane & 7) + (lane >> 4) * 8, c = ks * 2 + ((lane >> 3) & 1);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(kb[0]), "=r"(kb[1]), "=r"(kb[2]), "=r"(kb[3]) : "r"(kt + dt_at(r, c)));
+                mma_bf16(sc[0], qa[ks], kb[0], kb[1]);
+                mma_bf16(sc[1], qa[ks], kb[2], kb[3]);
+            }
+            const int kbase = my_key0 + (lane & 3) * 2;
+            float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = kbase + i * 8 + e;
+                    const bool vis = j >= key_lo && j < key_hi;
+                    sc[i][e] = (vis && row_lo_ok) ? sc[i][e] * scale_log2 : -INFINITY;
+                    sc[i][2 + e] = (vis && row_hi_ok) ? sc[i][2 + e] * scale_log2 : -INFINITY;
+                    mx_lo = fmaxf(mx_lo, sc[i][e]);
+                    mx_hi = fmaxf(mx_hi, sc[i][2 + e]);
+                }
+            }
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+            const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo;
+            const float base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+            const float corr_lo = exp2f(m_lo - base_lo), corr_hi = exp2f(m_hi - base_hi);
+            m_lo = mn_lo;
+            m_hi = mn_hi;
+            float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                sc[i][0] = exp2f(sc[i][0] - base_lo);
+                sc[i][1] = exp2f(sc[i][1] - base_lo);
+                sc[i][2] = exp2f(sc[i][2] - base_hi);
+                sc[i][3] = exp2f(sc[i][3] - base_hi);
+                sum_lo += sc[i][0] + sc[i][1];
+                sum_hi += sc[i][2] + sc[i][3];
+            }
+            l_lo = l_lo * corr_lo + sum_lo;
+            l_hi = l_hi * corr_hi + sum_hi;
+            uint32_t pa[4];
+            pa[0] = pack_bf16(sc[0][0], sc[0][1]);
+            pa[1] = pack_bf16(sc[0][2], sc[0][3]);
+            pa[2] = pack_bf16(sc[1][0], sc[1][1]);
+            pa[3] = pack_bf16(sc[1][2], sc[1][3]);
+#pragma unroll
+            for (int dp = 0; dp < DH / 16; ++dp) {
+                uint32_t vb[4];
+                const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = dp * 2 + (lane >> 4);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(vb[0]), "=r"(vb[1]), "=r"(vb[2]), "=r"(vb[3]) : "r"(vt + dt_at(r, c)));
+                o[2 * dp][0] *= corr_lo; o[2 * dp][1] *= corr_lo;
+                o[2 * dp][2] *= corr_hi; o[2 * dp][3] *= corr_hi;
+                o[2 * dp + 1][0] *= corr_lo; o[2 * dp + 1][1] *= corr_lo;
+                o[2 * dp + 1][2] *= corr_hi; o[2 * dp + 1][3] *= corr_hi;
+                mma_bf16(o[2 * dp], pa, vb[0], vb[1]);
+                mma_bf16(o[2 * dp + 1], pa, vb[2], vb[3]);
+            }
+            __syncwarp();                      // every lane has read the stage
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars[DT_STAGES + s])) : "memory");
+        }
+    }
+    __syncthreads();                           // all tiles read: the ring is free for the join
+    pdl_launch_late();
+    float* so = (float*)ring;                  // [4][16][DH]
+    if (warp < 4) {
+        l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+        l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+        const int col = (lane & 3) * 2;
+#pragma unroll
+        for (int i = 0; i < DH / 8; ++i) {
+            *(float2*)(so + ((size_t)warp * 16 + r_lo) * DH + i * 8 + col) = make_float2(o[i][0], o[i][1]);
+            *(float2*)(so + ((size_t)warp * 16 + r_hi) * DH + i * 8 + col) = make_float2(o[i][2], o[i][3]);
+        }
+        if ((lane & 3) == 0) {
+            s_ml[(warp * 16 + r_lo) * 2] = m_lo; s_ml[(warp * 16 + r_lo) * 2 + 1] = l_lo;
+            s_ml[(warp * 16 + r_hi) * 2] = m_hi; s_ml[(warp * 16 + r_hi) * 2 + 1] = l_hi;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < G * DH; i += DT_THREADS) {
+        const int r = i / DH, d = i % DH;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, s_ml[(w * 16 + r) * 2]);
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = s_ml[(w * 16 + r) * 2];
+            if (mw != -INFINITY) {
+                const float f = exp2f(mw - m);
+                l += s_ml[(w * 16 + r) * 2 + 1] * f;
+                acc += so[((size_t)w * 16 + r) * DH + d] * f;
+            }
+        }
+        const int head = kvh * G + r;
+        if (n_splits == 1) {
+            out[(size_t)tok * out_stride + (size_t)head * DH + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else {
+            const size_t at = ((size_t)tok * H + head) * n_splits + split;
+            part_o[at * DH + d] = acc;
+            if (d == 0) { part_ml[at * 2] = m; part_ml[at * 2 + 1] = l; }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------ host
+typedef CUresult (*DtEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                               CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                               CUtensorMapFloatOOBfill);
+
+// The tensor map of one layer's K or V pages, [rows, 128] bf16 in boxes of page_size x 64;
+// made once per (address, rows, page size) and kept.
+static const CUtensorMap* dt_map_of(const void* pages, long long rows, int page_size) {
+    static std::mutex lock;
+    static std::unordered_map<uint64_t, CUtensorMap> maps;
+    static DtEncodeFn encode = nullptr;
+    std::lock_guard<std::mutex> hold(lock);
+    if (!encode) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess ||
+            qr != cudaDriverEntryPointSuccess)
+            return nullptr;
+        encode = (DtEncodeFn)p;
+    }
+    const uint64_t key = (uint64_t)(uintptr_t)pages ^ ((uint64_t)rows * 0x9e3779b97f4a7c15ull) ^ ((uint64_t)page_size << 56);
+    auto it = maps.find(key);
+    if (it != maps.end()) return &it->second;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {DT_DH, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {DT_DH * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    const cuuint32_t elem[2] = {1, 1};
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return nullptr;
+    return &maps.emplace(key, map).first->second;
+}
+
+// 1 if this kernel takes the shape: head size 128, at most 16 query heads a kv head, pages of
+// 8, 16, 32 or 64 tokens.
+TGO_API int tgo_attention_decode_tma_supports(int dh, int group, int page_size) {
+    return dh == DT_DH && group >= 1 && group <= 16 &&
+           (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
+}
+
+// Reads (and waits for the device to reach) the flag a wait that ran out sets; 0: none did.
+TGO_API int tgo_attention_decode_tma_error(int* value) {
+    return (int)cudaMemcpyFromSymbol(value, dt_error_flag, sizeof(int));
+}
+
+// One token per request (token t is request seq_ids[t] at positions[t]); n_splits CTAs per
+// (token, kv head) write partial results to part_o [T, H, n_splits, 128] and part_ml
+// [T, H, n_splits, 2] for flash_combine_kernel when n_splits > 1.
+TGO_API int tgo_attention_decode_tma(const void* q, long long q_stride, void* out, long long out_stride,
+                                     const void* k_cache, const void* v_cache, int n_pages, int page_size,
+                                     const int* block_tables, int max_blocks, const int* positions,
+                                     const int* seq_ids, int T, int H, int Hkv, int dh, float scale,
+                                     int window, int n_splits, float* part_o, float* part_ml,
+                                     cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || Hkv <= 0 || H % Hkv || !tgo_attention_decode_tma_supports(dh, H / Hkv, page_size) ||
+        n_pages <= 0 || max_blocks <= 0 || window < 0 || n_splits < 1 || n_splits > 65535 || Hkv > 65535 ||
+        (n_splits > 1 && (!part_o || !part_ml)) || q_stride % 8 || ((uintptr_t)q % 16) ||
+        ((uintptr_t)k_cache % 128) || ((uintptr_t)v_cache % 128))
+        return TGO_E_BAD_ARG;
+    const long long rows = (long long)n_pages * Hkv * page_size;
+    if (rows > 0x7fffffffll) return TGO_E_BAD_ARG;
+    const CUtensorMap* mk = dt_map_of(k_cache, rows, page_size);
+    const CUtensorMap* mv = dt_map_of(v_cache, rows, page_size);
+    if (!mk || !mv) return TGO_E_BAD_ARG;
+    constexpr size_t ring = (size_t)DT_STAGES * DT_STAGE_BYTES;
+    static_assert(ring >= (size_t)4 * 16 * DT_DH * sizeof(float), "the join of the four warps reuses the ring");
+    constexpr size_t smem = 1024 + ring + 2 * DT_STAGES * 8 + 16 * (DT_DH + 8) * sizeof(bf16) +
+                            4 * 16 * 2 * sizeof(float) + DT_PAGES_CAP * sizeof(int);
+    static bool once = false;
+    if (!once) {
+        cudaError_t e = cudaFuncSetAttribute(flash_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        once = true;
+    }
+    int shift = 0;
+    while ((1 << shift) < page_size) ++shift;
+    return tgo_launch_pdl(flash_decode_tma_kernel, dim3(T, Hkv, n_splits), dim3(DT_THREADS), smem, stream, *mk, *mv,
+                          (const bf16*)q, q_stride, (bf16*)out, out_stride, page_size, shift, block_tables,
+                          max_blocks, positions, seq_ids, H, Hkv, scale * 1.4426950408889634f, window, n_splits,
+                          part_o, part_ml);
+}

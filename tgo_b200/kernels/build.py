@@ -32,6 +32,7 @@ LIBRARIES = {
     "attention_generic": (["attention_generic.cu"], []),
     "attention_flash": (["attention_flash.cu"], []),
     "attention_tc": (["attention_tc.cu"], []),
+    "attention_decode_tma": (["attention_decode_tma.cu"], []),
     "sgemm": (["sgemm.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),

@@ -469,6 +469,24 @@ def flash_supports(head_dim: int, group: int) -> bool:
         c_int(head_dim), c_int(group)))
 
 
+USE_TMA_DECODE = True       # decode attention with head size 128: cache pages by TMA
+
+
+def attention_decode_tma_supports(head_dim: int, group: int, page_size: int) -> bool:
+    if head_dim != 128:                  # do not build the library for models that cannot use it
+        return False
+    return bool(load_library("attention_decode_tma").tgo_attention_decode_tma_supports(
+        c_int(head_dim), c_int(group), c_int(page_size)))
+
+
+def attention_decode_tma_error() -> int:
+    """1 if a wait of the TMA-fed decode attention kernel ever ran out, else 0. Synchronises."""
+    value = ctypes.c_int(0)
+    _check(load_library("attention_decode_tma").tgo_attention_decode_tma_error(ctypes.byref(value)),
+           "attention_decode_tma_error")
+    return int(value.value)
+
+
 def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
                     head_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
                     block_tables: torch.Tensor, positions: torch.Tensor, seq_ids: torch.Tensor,
@@ -492,6 +510,23 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
                              device=q.device)
         part_ml = torch.empty((T, num_heads, n_splits, 2), dtype=torch.float32, device=q.device)
     lib = load_library("attention_flash")
+    if tile_tok0 is None and USE_TMA_DECODE and k_cache.dim() == 4 and k_cache.is_contiguous() and \
+            v_cache.is_contiguous() and attention_decode_tma_supports(
+                head_dim, num_heads // num_kv_heads, page_size):
+        # decode with the pages brought in by TMA; the join of the splits is the same kernel
+        _check(load_library("attention_decode_tma").tgo_attention_decode_tma(
+            _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+            c_int(k_cache.shape[0]), c_int(page_size), _ptr(block_tables),
+            c_int(block_tables.shape[1]), _ptr(positions), _ptr(seq_ids), c_int(T), c_int(num_heads),
+            c_int(num_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(n_splits),
+            _ptr(part_o), _ptr(part_ml), _stream()),
+            "attention_decode_tma", f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads})")
+        if n_splits > 1:
+            _check(lib.tgo_attention_flash_combine(
+                _ptr(part_o), _ptr(part_ml), _ptr(out), c_ll(out.stride(0)), c_int(T),
+                c_int(num_heads), c_int(head_dim), c_int(n_splits), _stream()),
+                "attention_flash_combine")
+        return
     _check(lib.tgo_attention_flash(
         _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
         c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(positions),
@@ -733,6 +768,10 @@ def kernel_wait_errors() -> dict:
         code = attention_tc_error()
         if code:
             out["attention_tc"] = code
+    if "attention_decode_tma" in _loaded:
+        code = attention_decode_tma_error()
+        if code:
+            out["attention_decode_tma"] = code
     for key, flag in _tc_err.items():
         code = int(flag.item())
         if code:
