@@ -344,3 +344,42 @@ def test_toy_parts_are_registered_built_and_stepped(toy_registered, tmp_path, dt
             (fam.__name__, worst)
         if fam is tiny.trace_tail:             # single-token steps: captured, unless chatty
             assert eng.use_graphs == (mixer == "test_decay")
+
+
+# --------------------------------------------------------------- the run order is data
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_run_twice_and_borrowed_cache_on_the_gpu(tmp_path, dtype):
+    """Calls [0, 1, 0, 1] over two layers' weights, the last call reading call 1's cache: a
+    prompt in two portions, then tokens one by one (captured decode steps), against the plain
+    implementation of the same order."""
+    import plain_qwen3 as plain
+    from tgo_b200.config.spec import LayerCall
+    from tgo_b200.engine.model import Model
+    from tgo_b200.engine.step import Engine, StepEntry
+    from tgo_b200.registry import model_spec_from_config
+    from tgo_b200.weights.binder import load_weights
+    from tgo_b200.weights.safetensors import SafetensorsRepo
+    cfg, run = tiny.TINIES["A"]
+    d = tiny.make_model_dir(tmp_path / "a", cfg, run["seed"], 0.2)
+    spec = model_spec_from_config(cfg)
+    spec.run_order = [LayerCall(0), LayerCall(1), LayerCall(0), LayerCall(1, cache_from=1)]
+    dt = torch.float32 if dtype == "float32" else torch.bfloat16
+    model = Model(spec, dt, DEV)
+    model.bind(load_weights(model.weight_specs(), SafetensorsRepo(d), dt, DEV, model.tied_alias()))
+    assert [len(g.calls) for g in model.groups] == [3]          # calls 0, 1, 2 own a cache
+    pc, pw = plain.load_model_dir(d)
+    toks = tiny.random_requests(256, [40], seed=5)["r0"]
+    want = tiny.repeated_layers_reference(pc, pw, toks)
+    eng = Engine(model, page_size=8, max_tokens=64, num_slots=2)
+    eng.admit("x")
+    rows = [eng.step([StepEntry("x", toks[:9], list(range(9)))]).float().cpu(),
+            eng.step([StepEntry("x", toks[9:30], list(range(21)))]).float().cpu()]
+    for t in toks[30:]:
+        rows.append(eng.step([StepEntry("x", [t], [0])]).float().cpu())
+    got = torch.cat(rows).numpy()
+    # the bound is a function of the number of layers a token passes: four calls here
+    tol = tiny.tolerance(dict(cfg, num_hidden_layers=len(spec.run_order)), dtype,
+                         float(np.abs(want).max()))
+    assert np.abs(got - want).max() <= tol

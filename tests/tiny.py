@@ -261,3 +261,37 @@ def compare(got, want, config, dtype):
         if err > worst:
             worst, where = err, (rid, pos)
     return worst, where, tolerance(config, dtype, scale)
+
+
+def repeated_layers_reference(pc, pw, tokens):
+    """Plain logits of TINY_A's weights run as calls [0, 1, 0, 1] where the last call reads
+    the cache of call 1 instead of writing its own (keys and values of call 1, queries of
+    its own input)."""
+    import plain_qwen3 as plain
+    eps, T = pc["rms_norm_eps"], len(tokens)
+    pos = np.arange(T)
+    h = plain.embedding(pw["model.embed_tokens.weight"], tokens)
+    kv1 = None
+    for call, layer in enumerate([0, 1, 0, 1]):
+        p = f"model.layers.{layer}."
+        n = plain.rmsnorm(h, pw[p + "input_layernorm.weight"], eps)
+        H, hkv, dh = 4, 2, 16
+        q = plain.rmsnorm(plain.linear(n, pw[p + "self_attn.q_proj.weight"]).reshape(T, H, dh),
+                          pw[p + "self_attn.q_norm.weight"], eps)
+        q = plain.rope_half_split(q, pos, pc["rope_theta"])
+        if call == 3:
+            k, v = kv1
+        else:
+            k = plain.rmsnorm(plain.linear(n, pw[p + "self_attn.k_proj.weight"]).reshape(T, hkv, dh),
+                              pw[p + "self_attn.k_norm.weight"], eps)
+            k = plain.rope_half_split(k, pos, pc["rope_theta"])
+            v = plain.linear(n, pw[p + "self_attn.v_proj.weight"]).reshape(T, hkv, dh)
+            if call == 1:
+                kv1 = (k, v)
+        a = plain.causal_gqa_attention(q, k, v, 0.25).reshape(T, H * dh)
+        h = h + plain.linear(a, pw[p + "self_attn.o_proj.weight"])
+        n = plain.rmsnorm(h, pw[p + "post_attention_layernorm.weight"], eps)
+        h = h + plain.swiglu_mlp(n, pw[p + "mlp.gate_proj.weight"], pw[p + "mlp.up_proj.weight"],
+                                 pw[p + "mlp.down_proj.weight"])
+    return plain.linear(plain.rmsnorm(h, pw["model.norm.weight"], eps),
+                        pw["model.embed_tokens.weight"])
