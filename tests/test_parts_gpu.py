@@ -261,6 +261,38 @@ class ShiftPosition:
                 v[:, :, 0] = (v[:, :, 0].float() + add).to(t.dtype)
 
 
+class RoutedFeedForward:
+    """A feed-forward with routing: float32 router logits x . R^T, each token goes to its one
+    best expert (lowest id on ties), y = D_e . silu(U_e . x). Written with torch on the
+    device, without a trip to the host, so decode steps with it are captured."""
+
+    def __init__(self, spec, hidden, prefix, device=None):
+        self.hidden, self.inter, self.prefix = hidden, spec.intermediate_size, prefix
+        self.experts = dict(spec.extra)["experts"]
+
+    def weight_specs(self):
+        from tgo_b200.weights.binder import WeightSpec
+        p, E = self.prefix, self.experts
+        specs = [WeightSpec(p + "router.weight", (E, self.hidden))]
+        for e in range(E):
+            specs += [WeightSpec(p + f"experts.{e}.up.weight", (self.inter, self.hidden)),
+                      WeightSpec(p + f"experts.{e}.down.weight", (self.hidden, self.inter))]
+        return specs
+
+    def bind(self, weights):
+        p, E = self.prefix, self.experts
+        self.router = weights.pop(p + "router.weight").float()
+        self.up = torch.stack([weights.pop(p + f"experts.{e}.up.weight") for e in range(E)]).float()
+        self.down = torch.stack([weights.pop(p + f"experts.{e}.down.weight") for e in range(E)]).float()
+
+    def forward(self, x, ctx):
+        xf = x.float()
+        choice = torch.argmax(xf @ self.router.t(), dim=1)          # first of equal maxima
+        u = torch.bmm(self.up.index_select(0, choice), xf[:, :, None])[:, :, 0]
+        act = (u * torch.sigmoid(u)).to(x.dtype).float()
+        return torch.bmm(self.down.index_select(0, choice), act[:, :, None])[:, :, 0].to(x.dtype)
+
+
 def toy_spec(raw):
     """config.json -> ModelSpec of a two-layer toy: a decay mixer, then attention with the
     shift encoding. Nothing of it is a model of anyone's."""
@@ -269,9 +301,11 @@ def toy_spec(raw):
     d, V = raw["width"], raw["vocab"]
     norm = NormSpec("rmsnorm", raw["eps"])
     ffn = FeedForwardSpec("swiglu", raw["inner"])
+    ffn0 = FeedForwardSpec("test_routed", raw["inner"], extra=(("experts", raw["experts"]),)) \
+        if raw.get("experts") else ffn
     layers = [LayerSpec("prenorm_residual", "layers.0.",
                         MixerSpec(raw.get("mixer", "test_decay"), extra=(("decay", raw["decay"]),)),
-                        ffn, norm, names=(("mixer", "decay."),)),
+                        ffn0, norm, names=(("mixer", "decay."),)),
               LayerSpec("prenorm_residual", "layers.1.",
                         MixerSpec("gqa_attention", 4, 2, 16, qk_norm=True,
                                   position=PositionSpec("test_shift"), norm_eps=raw["eps"]), ffn, norm)]
@@ -281,13 +315,15 @@ def toy_spec(raw):
 
 @pytest.fixture()
 def toy_registered():
-    from tgo_b200.registry import ARCHITECTURES, MIXERS, POSITIONS
+    from tgo_b200.registry import ARCHITECTURES, FEED_FORWARDS, MIXERS, POSITIONS
     ARCHITECTURES.register("ToyForTests", toy_spec, replace=True)
+    FEED_FORWARDS.register("test_routed", RoutedFeedForward, replace=True)
     MIXERS.register("test_decay", DecayMixer, replace=True)
     MIXERS.register("test_chatty_decay", ChattyDecayMixer, replace=True)
     POSITIONS.register("test_shift", ShiftPosition, replace=True)
     yield
     ARCHITECTURES.unregister("ToyForTests")
+    FEED_FORWARDS.unregister("test_routed")
     MIXERS.unregister("test_decay")
     MIXERS.unregister("test_chatty_decay")
     POSITIONS.unregister("test_shift")
@@ -304,8 +340,16 @@ def toy_plain(w, raw, toks):
         ys.append(s @ w["layers.0.decay.mix.weight"].T)
     h = h + np.stack(ys)
     n = plain.rmsnorm(h, w["layers.0.post_attention_layernorm.weight"], eps)
-    h = h + plain.swiglu_mlp(n, w["layers.0.mlp.gate_proj.weight"], w["layers.0.mlp.up_proj.weight"],
-                             w["layers.0.mlp.down_proj.weight"])
+    if raw.get("experts"):
+        choice = np.argmax(n @ w["layers.0.mlp.router.weight"].T, axis=1)
+        ys = []
+        for t in range(T):
+            u = w[f"layers.0.mlp.experts.{choice[t]}.up.weight"] @ n[t]
+            ys.append(w[f"layers.0.mlp.experts.{choice[t]}.down.weight"] @ (u / (1 + np.exp(-u))))
+        h = h + np.stack(ys)
+    else:
+        h = h + plain.swiglu_mlp(n, w["layers.0.mlp.gate_proj.weight"], w["layers.0.mlp.up_proj.weight"],
+                                 w["layers.0.mlp.down_proj.weight"])
     # layer 1: attention with the shift encoding
     p = "layers.1.self_attn."
     n = plain.rmsnorm(h, w["layers.1.input_layernorm.weight"], eps)
@@ -322,12 +366,16 @@ def toy_plain(w, raw, toks):
     return plain.linear(plain.rmsnorm(h, w["norm.weight"], eps), w["embed.weight"])
 
 
-@pytest.mark.parametrize("dtype,mixer", [("float32", "test_decay"), ("bfloat16", "test_decay"),
-                                         ("float32", "test_chatty_decay")])
-def test_toy_parts_are_registered_built_and_stepped(toy_registered, tmp_path, dtype, mixer):
+@pytest.mark.parametrize("dtype,mixer,experts", [
+    ("float32", "test_decay", 0), ("bfloat16", "test_decay", 0), ("float32", "test_chatty_decay", 0),
+    ("float32", "test_decay", 3)])
+def test_toy_parts_are_registered_built_and_stepped(toy_registered, tmp_path, dtype, mixer, experts):
+    """Parts from outside the package: a mixer with state of its own, a position encoding the
+    kernels do not know, and (last case) a feed-forward that routes each token to one of
+    three experts."""
     import tgo_b200
     raw = dict(architectures=["ToyForTests"], width=48, vocab=90, inner=80, eps=1e-5, decay=0.75,
-               mixer=mixer)
+               mixer=mixer, experts=experts)
     d = tiny.make_model_dir(tmp_path / "toy", raw, seed=2, sigma=0.15)
     model = tgo_b200.open(d, dtype=dtype)
     assert model.model.state_shapes == {0: (48,)} and [g.calls for g in model.model.groups] == [[1]]
