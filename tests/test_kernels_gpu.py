@@ -259,7 +259,7 @@ class Cache:
 
 
 SHAPES = [(4, 2, 16, 16), (6, 2, 32, 8), (8, 8, 64, 16), (32, 8, 128, 16), (5, 1, 48, 4),
-          (3, 3, 128, 32)]
+          (3, 3, 128, 32), (16, 2, 128, 16), (16, 1, 128, 8), (12, 2, 128, 64)]
 
 
 @pytest.mark.parametrize("H,Hkv,dh,ps", SHAPES)

@@ -34,6 +34,9 @@
 #define DT_STAGE_BYTES (2 * DT_TILE_BYTES)     // K and V
 #define DT_THREADS 160
 #define DT_PAGES_CAP 1024
+#ifndef DT_KEYS_ON_M_MAX_GROUP
+#define DT_KEYS_ON_M_MAX_GROUP 8      // up to this many query heads a kv head: the keys take the M axis
+#endif
 #define DT_WAIT_CYCLES 4000000000ll
 
 __device__ int dt_error_flag = 0;
@@ -66,6 +69,7 @@ __device__ __forceinline__ uint32_t dt_at(int r, int c) {
     return (uint32_t)((c >> 3) * DT_HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4));
 }
 
+template <bool KEYS_ON_M>
 __global__ void __launch_bounds__(DT_THREADS, DT_MIN_BLOCKS)
 flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
@@ -166,13 +170,99 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         // the producer takes no part in the sums below, but in the barriers
     }
 
-    float o[DH / 8][4];
+    // Two forms of the arithmetic. With at most 8 query heads a kv head the keys take the M
+    // axis of the products and the heads the N axis (S^T = K Q^T, O^T += V^T P^T): a 16-key
+    // tile of a warp costs 8 + 8 products, 4 exponentials a lane and 32 accumulators to
+    // rescale, where the heads on the M axis (up to 16 of them) cost twice that with three
+    // quarters of the rows empty for a group of four.
+    float o[KEYS_ON_M ? DH / 16 : DH / 8][4];
 #pragma unroll
-    for (int i = 0; i < DH / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    for (int i = 0; i < (KEYS_ON_M ? DH / 16 : DH / 8); ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;      // KEYS_ON_M: heads 2t and 2t+1
     const int r_lo = lane >> 2, r_hi = r_lo + 8;
     const bool row_lo_ok = r_lo < G, row_hi_ok = r_hi < G;
 
+    if constexpr (KEYS_ON_M) {
+      if (warp < 4) {
+        const int g = lane >> 2, t = lane & 3;
+        const bool q0_ok = 2 * t < G, q1_ok = 2 * t + 1 < G;
+        // Q^T as the B operand: for k-steps 2j and 2j+1, b0 and b1 of each
+        uint32_t qb[KS / 2][4];
+#pragma unroll
+        for (int j = 0; j < KS / 2; ++j)
+            ldmatrix_x4(qb[j], sq + (lane & 7) * LDQ + j * 32 + (lane >> 3) * 8);
+        bool ok = true;
+        for (int it = 0; it < n_it; ++it) {
+            const int s = it % DT_STAGES;
+            const uint32_t ph = (uint32_t)(it / DT_STAGES) & 1u;
+            const int tile = t_lo + it;
+            if (ok) ok = dt_wait(smem_u32(&bars[s]), ph);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const uint32_t kt = smem_u32(ring + s * DT_STAGE_BYTES);
+            const uint32_t vt = kt + DT_TILE_BYTES;
+            const int my_key0 = tile * DT_BN + warp * 16;
+            if (my_key0 + 16 > key_hi || my_key0 < key_lo) {       // V rows nobody may read: zeros
+                for (int i = lane; i < 16 * 16; i += 32) {
+                    const int r = i >> 4, c = i & 15;
+                    const int key = my_key0 + r;
+                    if (key >= key_hi || key < key_lo)
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(vt + dt_at(warp * 16 + r, c)), "r"(0u) : "memory");
+                }
+                __syncwarp();
+            }
+            float sc[4] = {0.f, 0.f, 0.f, 0.f};       // keys g, g+8 x heads 2t, 2t+1
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                uint32_t ka[4];
+                const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = ks * 2 + (lane >> 4);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(ka[0]), "=r"(ka[1]), "=r"(ka[2]), "=r"(ka[3]) : "r"(kt + dt_at(r, c)));
+                mma_bf16(sc, ka, qb[ks >> 1][(ks & 1) * 2], qb[ks >> 1][(ks & 1) * 2 + 1]);
+            }
+            const int key_a = my_key0 + g, key_b = key_a + 8;
+            const bool vis_a = key_a >= key_lo && key_a < key_hi, vis_b = key_b >= key_lo && key_b < key_hi;
+            sc[0] = (vis_a && q0_ok) ? sc[0] * scale_log2 : -INFINITY;
+            sc[1] = (vis_a && q1_ok) ? sc[1] * scale_log2 : -INFINITY;
+            sc[2] = (vis_b && q0_ok) ? sc[2] * scale_log2 : -INFINITY;
+            sc[3] = (vis_b && q1_ok) ? sc[3] * scale_log2 : -INFINITY;
+            float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
+#pragma unroll
+            for (int off = 4; off <= 16; off <<= 1) {             // over the keys: lanes of equal t
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+            }
+            const float mn0 = fmaxf(m_lo, mx0), mn1 = fmaxf(m_hi, mx1);
+            const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
+            const float corr0 = exp2f(m_lo - base0), corr1 = exp2f(m_hi - base1);
+            m_lo = mn0;
+            m_hi = mn1;
+            sc[0] = exp2f(sc[0] - base0); sc[1] = exp2f(sc[1] - base1);
+            sc[2] = exp2f(sc[2] - base0); sc[3] = exp2f(sc[3] - base1);
+            l_lo = l_lo * corr0 + sc[0] + sc[2];
+            l_hi = l_hi * corr1 + sc[1] + sc[3];
+            // P^T as the B operand: the two 8 x 8 blocks (keys x heads) transposed
+            uint32_t pb0, pb1;
+            {
+                const uint32_t blk_a = pack_bf16(sc[0], sc[1]), blk_b = pack_bf16(sc[2], sc[3]);
+                asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb0) : "r"(blk_a));
+                asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb1) : "r"(blk_b));
+            }
+#pragma unroll
+            for (int dt = 0; dt < DH / 16; ++dt) {
+                uint32_t va[4];
+                const int r = warp * 16 + (lane & 7) + (lane >> 4) * 8, c = dt * 2 + ((lane >> 3) & 1);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(va[0]), "=r"(va[1]), "=r"(va[2]), "=r"(va[3]) : "r"(vt + dt_at(r, c)));
+                o[dt][0] *= corr0; o[dt][1] *= corr1; o[dt][2] *= corr0; o[dt][3] *= corr1;
+                mma_bf16(o[dt], va, pb0, pb1);
+            }
+            __syncwarp();                      // every lane has read the stage
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars[DT_STAGES + s])) : "memory");
+        }
+      }
+    } else {
     if (warp < 4) {
         uint32_t qa[KS][4];
 #pragma unroll
@@ -270,9 +360,32 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars[DT_STAGES + s])) : "memory");
         }
     }
+    }
     __syncthreads();                           // all tiles read: the ring is free for the join
     pdl_launch_late();
     float* so = (float*)ring;                  // [4][16][DH]
+    if constexpr (KEYS_ON_M) {
+      if (warp < 4) {
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int off = 4; off <= 16; off <<= 1) {
+            l_lo += __shfl_xor_sync(0xffffffffu, l_lo, off);
+            l_hi += __shfl_xor_sync(0xffffffffu, l_hi, off);
+        }
+        // O^T: lane (g, t) holds rows dt*16 + g (+8) of heads 2t and 2t+1
+#pragma unroll
+        for (int dt = 0; dt < DH / 16; ++dt) {
+            so[((size_t)warp * 16 + 2 * t) * DH + dt * 16 + g] = o[dt][0];
+            so[((size_t)warp * 16 + 2 * t + 1) * DH + dt * 16 + g] = o[dt][1];
+            so[((size_t)warp * 16 + 2 * t) * DH + dt * 16 + g + 8] = o[dt][2];
+            so[((size_t)warp * 16 + 2 * t + 1) * DH + dt * 16 + g + 8] = o[dt][3];
+        }
+        if (g == 0) {
+            s_ml[(warp * 16 + 2 * t) * 2] = m_lo; s_ml[(warp * 16 + 2 * t) * 2 + 1] = l_lo;
+            s_ml[(warp * 16 + 2 * t + 1) * 2] = m_hi; s_ml[(warp * 16 + 2 * t + 1) * 2 + 1] = l_hi;
+        }
+      }
+    } else {
     if (warp < 4) {
         l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
         l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
@@ -288,6 +401,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             s_ml[(warp * 16 + r_lo) * 2] = m_lo; s_ml[(warp * 16 + r_lo) * 2 + 1] = l_lo;
             s_ml[(warp * 16 + r_hi) * 2] = m_hi; s_ml[(warp * 16 + r_hi) * 2 + 1] = l_hi;
         }
+    }
     }
     __syncthreads();
     for (int i = tid; i < G * DH; i += DT_THREADS) {
@@ -390,14 +504,21 @@ TGO_API int tgo_attention_decode_tma(const void* q, long long q_stride, void* ou
                             4 * 16 * 2 * sizeof(float) + DT_PAGES_CAP * sizeof(int);
     static bool once = false;
     if (!once) {
-        cudaError_t e = cudaFuncSetAttribute(flash_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(flash_decode_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(flash_decode_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         once = true;
     }
     int shift = 0;
     while ((1 << shift) < page_size) ++shift;
-    return tgo_launch_pdl(flash_decode_tma_kernel, dim3(T, Hkv, n_splits), dim3(DT_THREADS), smem, stream, *mk, *mv,
-                          (const bf16*)q, q_stride, (bf16*)out, out_stride, page_size, shift, block_tables,
-                          max_blocks, positions, seq_ids, H, Hkv, scale * 1.4426950408889634f, window, n_splits,
-                          part_o, part_ml);
+    if (H / Hkv <= DT_KEYS_ON_M_MAX_GROUP)
+        return tgo_launch_pdl(flash_decode_tma_kernel<true>, dim3(T, Hkv, n_splits), dim3(DT_THREADS), smem, stream,
+                              *mk, *mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_size, shift,
+                              block_tables, max_blocks, positions, seq_ids, H, Hkv, scale * 1.4426950408889634f,
+                              window, n_splits, part_o, part_ml);
+    return tgo_launch_pdl(flash_decode_tma_kernel<false>, dim3(T, Hkv, n_splits), dim3(DT_THREADS), smem, stream,
+                          *mk, *mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_size, shift,
+                          block_tables, max_blocks, positions, seq_ids, H, Hkv, scale * 1.4426950408889634f,
+                          window, n_splits, part_o, part_ml);
 }
