@@ -688,3 +688,21 @@ def test_attention_tc_far_key_and_growing_scores():
     ops().paged_attention(q, out, H, Hkv, dh, Cache(case, ps), Ctx(case, False), 1.0, 0)
     assert ops().attention_tc_error() == 0
     assert torch.allclose(out.float().cpu(), want, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("window", [0, 300])
+def test_attention_decode_beyond_the_on_chip_table(window):
+    """One decode token 17000 keys into its request (head size 128, pages of 16): more pages
+    than the kernel keeps of the block table in shared memory, so the rest comes from global
+    memory; with and without key splits."""
+    H, Hkv, dh, ps = 4, 1, 128, 16
+    case = paged_case([1, 1], [17000, 5], H, Hkv, dh, ps, torch.bfloat16, seed=9)
+    scale = 1 / math.sqrt(dh)
+    want = attention_ref(case, H, Hkv, dh, scale, window)
+    for n_splits in (1, 7):
+        out = torch.zeros_like(case["q"])
+        ops().attention_flash(case["q"], out, H, Hkv, dh, case["kc"], case["vc"], ps, case["bt"],
+                              case["pos"], case["seq"], None, None, scale, window, wide=False,
+                              n_splits=n_splits)
+        assert torch.allclose(out.float().cpu(), want, **tol(torch.bfloat16)), n_splits
+    assert ops().attention_decode_tma_error() == 0
