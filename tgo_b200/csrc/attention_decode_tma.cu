@@ -82,8 +82,8 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     extern __shared__ unsigned char dt_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)dt_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* ring = base;                                      // [stage][K | V][2 halves][64][128 B]
-    uint64_t* bars = (uint64_t*)(ring + DT_STAGES * DT_STAGE_BYTES); // full[S], empty[S]
-    bf16* sq = (bf16*)(bars + 2 * DT_STAGES);                        // [16][LDQ]
+    uint64_t* bars = (uint64_t*)(ring + DT_STAGES * DT_STAGE_BYTES); // K full[S], empty[S], V full[S]
+    bf16* sq = (bf16*)(bars + 3 * DT_STAGES);                        // [16][LDQ]
     float* s_ml = (float*)(sq + 16 * LDQ);                           // [4][16][2]
     int* s_pages = (int*)(s_ml + 4 * 16 * 2);                        // [DT_PAGES_CAP]
     pdl_wait();
@@ -127,6 +127,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         for (int s = 0; s < DT_STAGES; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bars[s])));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;" ::"r"(smem_u32(&bars[DT_STAGES + s])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bars[2 * DT_STAGES + s])));
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -153,18 +154,25 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             while (last > first && (last - 1) * page_size >= key_hi) --last;
             ok = __all_sync(0xffffffffu, ok && dt_wait(smem_u32(&bars[DT_STAGES + s]), ph ^ 1u));
             if (!ok) break;
-            const uint32_t full = smem_u32(&bars[s]);
-            if (lane == 0)
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
-                             ::"r"(full), "r"((uint32_t)(last - first) * (uint32_t)page_size * 512u) : "memory");
+            // K and V of a tile have a barrier each: Q K^T starts when K is there
+            const uint32_t k_full = smem_u32(&bars[s]), v_full = smem_u32(&bars[2 * DT_STAGES + s]);
+            if (lane == 0) {
+                const uint32_t bytes = (uint32_t)(last - first) * (uint32_t)page_size * 256u;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(k_full), "r"(bytes) : "memory");
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(v_full), "r"(bytes) : "memory");
+            }
             __syncwarp();
             for (int pi = first + lane; pi < last; pi += 32) {
                 const int row = (page_of(pi) * Hkv + kvh) * page_size;
                 const uint32_t dst = smem_u32(ring + s * DT_STAGE_BYTES) + (uint32_t)((pi - j * pages_per_tile) * page_size * 128);
-                dt_tma(dst, &map_k, 0, row, full);
-                dt_tma(dst + DT_HALF_BYTES, &map_k, 64, row, full);
-                dt_tma(dst + DT_TILE_BYTES, &map_v, 0, row, full);
-                dt_tma(dst + DT_TILE_BYTES + DT_HALF_BYTES, &map_v, 64, row, full);
+                dt_tma(dst, &map_k, 0, row, k_full);
+                dt_tma(dst + DT_HALF_BYTES, &map_k, 64, row, k_full);
+            }
+            for (int pi = first + lane; pi < last; pi += 32) {
+                const int row = (page_of(pi) * Hkv + kvh) * page_size;
+                const uint32_t dst = smem_u32(ring + s * DT_STAGE_BYTES) + (uint32_t)((pi - j * pages_per_tile) * page_size * 128);
+                dt_tma(dst + DT_TILE_BYTES, &map_v, 0, row, v_full);
+                dt_tma(dst + DT_TILE_BYTES + DT_HALF_BYTES, &map_v, 64, row, v_full);
             }
         }
         // the producer takes no part in the sums below, but in the barriers
@@ -196,21 +204,12 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             const int s = it % DT_STAGES;
             const uint32_t ph = (uint32_t)(it / DT_STAGES) & 1u;
             const int tile = t_lo + it;
-            if (ok) ok = dt_wait(smem_u32(&bars[s]), ph);
+            if (ok) ok = dt_wait(smem_u32(&bars[s]), ph);           // K
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             const uint32_t kt = smem_u32(ring + s * DT_STAGE_BYTES);
             const uint32_t vt = kt + DT_TILE_BYTES;
             const int my_key0 = tile * DT_BN + warp * 16;
-            if (my_key0 + 16 > key_hi || my_key0 < key_lo) {       // V rows nobody may read: zeros
-                for (int i = lane; i < 16 * 16; i += 32) {
-                    const int r = i >> 4, c = i & 15;
-                    const int key = my_key0 + r;
-                    if (key >= key_hi || key < key_lo)
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(vt + dt_at(warp * 16 + r, c)), "r"(0u) : "memory");
-                }
-                __syncwarp();
-            }
             float sc[4] = {0.f, 0.f, 0.f, 0.f};       // keys g, g+8 x heads 2t, 2t+1
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
@@ -241,6 +240,18 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             sc[2] = exp2f(sc[2] - base0); sc[3] = exp2f(sc[3] - base1);
             l_lo = l_lo * corr0 + sc[0] + sc[2];
             l_hi = l_hi * corr1 + sc[1] + sc[3];
+            if (ok) ok = dt_wait(smem_u32(&bars[2 * DT_STAGES + s]), ph);        // V
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (my_key0 + 16 > key_hi || my_key0 < key_lo) {       // V rows nobody may read: zeros
+                for (int i = lane; i < 16 * 16; i += 32) {
+                    const int r = i >> 4, c = i & 15;
+                    const int key = my_key0 + r;
+                    if (key >= key_hi || key < key_lo)
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(vt + dt_at(warp * 16 + r, c)), "r"(0u) : "memory");
+                }
+                __syncwarp();
+            }
             // P^T as the B operand: the two 8 x 8 blocks (keys x heads) transposed
             uint32_t pb0, pb1;
             {
@@ -273,7 +284,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             const int s = it % DT_STAGES;
             const uint32_t ph = (uint32_t)(it / DT_STAGES) & 1u;
             const int t = t_lo + it;
-            if (ok) ok = dt_wait(smem_u32(&bars[s]), ph);
+            if (ok) ok = dt_wait(smem_u32(&bars[s]), ph) && dt_wait(smem_u32(&bars[2 * DT_STAGES + s]), ph);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             const uint32_t kt = smem_u32(ring + s * DT_STAGE_BYTES);
@@ -500,7 +511,7 @@ TGO_API int tgo_attention_decode_tma(const void* q, long long q_stride, void* ou
     if (!mk || !mv) return TGO_E_BAD_ARG;
     constexpr size_t ring = (size_t)DT_STAGES * DT_STAGE_BYTES;
     static_assert(ring >= (size_t)4 * 16 * DT_DH * sizeof(float), "the join of the four warps reuses the ring");
-    constexpr size_t smem = 1024 + ring + 2 * DT_STAGES * 8 + 16 * (DT_DH + 8) * sizeof(bf16) +
+    constexpr size_t smem = 1024 + ring + 3 * DT_STAGES * 8 + 16 * (DT_DH + 8) * sizeof(bf16) +
                             4 * 16 * 2 * sizeof(float) + DT_PAGES_CAP * sizeof(int);
     static bool once = false;
     if (!once) {
