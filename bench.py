@@ -26,6 +26,13 @@ CONFIG_8B = dict(architectures=["Qwen3ForCausalLM"], hidden_size=4096, num_hidde
                  intermediate_size=12288, vocab_size=151936, rms_norm_eps=1e-6,
                  rope_theta=1000000.0, tie_word_embeddings=False, max_position_embeddings=40960,
                  attention_bias=False, sliding_window=None, use_sliding_window=False)
+# configs[3] and configs[4]: the 14B and 32B shapes (--shape 14b / 32b; the contract line is
+# the 8B one)
+CONFIG_14B = dict(CONFIG_8B, hidden_size=5120, num_hidden_layers=40, num_attention_heads=40,
+                  intermediate_size=17408)
+CONFIG_32B = dict(CONFIG_8B, hidden_size=5120, num_hidden_layers=64, num_attention_heads=64,
+                  intermediate_size=25600)
+SHAPES = {"8b": (CONFIG_8B, 8), "14b": (CONFIG_14B, 14), "32b": (CONFIG_32B, 32)}
 SEED = 8
 PROMPT = 1024
 CONTEXT_CAP = 8192
@@ -132,6 +139,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the 36 (0: all)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64, and prefill")
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
+                    help="with --only: the 14B or 32B shape of the baseline record instead of the 8B one")
+    ap.add_argument("--prompt", type=int, default=PROMPT, help="with --only decode: prompt length")
     ap.add_argument("--only", default="", choices=["", "prefill", "decode"],
                     help="profiling aid: run just the 2,048-token prefill, or just the decode "
                          "steps, and print a short line instead of the contract line")
@@ -148,23 +158,30 @@ def main():
     import tgo_b200
     from tgo_b200.engine.measure import load_peaks, measure_decode, measure_prefill
 
-    config = dict(CONFIG_8B)
+    if args.shape != "8b" and not args.only:
+        print("bench: the contract line is measured on the 8B shape; give --only with --shape")
+        return 2
+    config, seed = dict(SHAPES[args.shape][0]), SHAPES[args.shape][1]
     if args.layers:
         config["num_hidden_layers"] = args.layers
-    model = tgo_b200.open_random(config, seed=SEED, dtype="bfloat16", sigma=0.02, gain_sigma=0.05)
+    model = tgo_b200.open_random(config, seed=seed, dtype="bfloat16", sigma=0.02, gain_sigma=0.05)
     peaks = load_peaks()
     if args.only == "prefill":
         pre = measure_prefill(model, PREFILL_TOKENS, warmup=2, steps=max(1, min(args.steps, 3)),
                               seed=SEED, page_size=PAGE)
-        print(json.dumps({"only": "prefill", "layers": config["num_hidden_layers"],
-                          "ms": round(pre["ms"], 3), "tflops": round(pre["tflops"], 1)}))
+        print(json.dumps({"only": "prefill", "shape": args.shape, "layers": config["num_hidden_layers"],
+                          "ms": round(pre["ms"], 3), "tokens_per_s": round(pre["tokens_per_s"], 1),
+                          "tflops": round(pre["tflops"], 1),
+                          "frac": round(pre["tflops"] / peaks["bf16_tflops"], 4)}))
         return 0
     if args.only == "decode":
-        r = measure_decode(model, args.batch, PROMPT, args.steps, warmup=warmup, seed=SEED,
+        r = measure_decode(model, args.batch, args.prompt, args.steps, warmup=warmup, seed=SEED,
                            page_size=PAGE)
-        print(json.dumps({"only": "decode", "layers": config["num_hidden_layers"],
-                          "batch": args.batch, "ms_per_step": round(r["ms_per_step"], 4),
-                          "gbs": round(r["gbs"], 1)}))
+        print(json.dumps({"only": "decode", "shape": args.shape, "layers": config["num_hidden_layers"],
+                          "batch": args.batch, "prompt": args.prompt,
+                          "ms_per_step": round(r["ms_per_step"], 4),
+                          "tokens_per_s": round(r["tokens_per_s"], 1), "gbs": round(r["gbs"], 1),
+                          "hbm_frac": round(r["gbs"] / peaks["hbm_gbs"], 3)}))
         return 0
 
     clocks = ClockSampler()

@@ -629,6 +629,9 @@ TC_CASES = [
     ([300], [0], 16, 1, 64, 100),                           # 16 heads a group, window over tiles
     ([513], [0], 8, 4, 128, 0),                             # a page as large as a key tile
     ([40], [1000], 8, 2, 8, 0),                             # small pages, a long context behind
+    ([300, 9], [20, 0], 5, 1, 16, 0),                       # five heads a group: 25 tokens a tile, 3 rows idle
+    ([200], [0], 6, 2, 32, 50),                             # three heads a group
+    ([130], [70], 40, 8, 16, 0),                            # the 14B shape's heads
     ([40], [17000], 4, 1, 16, 0),                           # more pages than the on-chip table slice holds
     ([40], [17000], 4, 1, 16, 300),                         # the same behind a window
 ]

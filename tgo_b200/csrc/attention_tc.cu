@@ -959,10 +959,10 @@ static const CUtensorMap* at_map_of(const void* pages, long long rows, int page_
     return &maps.emplace(key, map).first->second;
 }
 
-// 1 if this kernel takes the shape: head size 128, a group that divides 128, pages of 8, 16,
-// 32, 64 or 128 tokens.
+// 1 if this kernel takes the shape: head size 128, up to 16 query heads a kv head (a tile then
+// holds 128 / group tokens, rounded down), pages of 8, 16, 32, 64 or 128 tokens.
 TGO_API int tgo_attention_tc_supports(int dh, int group, int page_size) {
-    const bool g_ok = group == 1 || group == 2 || group == 4 || group == 8 || group == 16;
+    const bool g_ok = group >= 1 && group <= 16;
     const bool p_ok = page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
     return dh == AT_DH && g_ok && p_ok;
 }
