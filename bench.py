@@ -130,6 +130,38 @@ def e2e_decode(model, batch, steps, warmup):
             "d2h_bytes_per_step": 4 * batch, "ms_per_step": dt / steps * 1e3}
 
 
+def serve_workload(model, config, shape):
+    """The continuous-batching workload of the baseline record's 14B configuration, through
+    the library's generate: 32 requests, prompt lengths uniform in [128, 4096], outputs uniform
+    in [64, 512], prompt portions of 512 tokens, pages of 16, up to 8192 tokens a request.
+    Run twice (the first run also compiles and captures); the second is reported."""
+    import time
+
+    import numpy as np
+    import torch
+
+    from tgo_b200.sampling.policy import Policy
+    rng = np.random.default_rng(14)
+    n = 32
+    plens, olens = rng.integers(128, 4097, n), rng.integers(64, 513, n)
+    prompts = [rng.integers(0, config["vocab_size"], int(p)).tolist() for p in plens]
+    policies = [Policy(max_tokens=int(o)) for o in olens]
+    for _ in range(2):
+        torch.cuda.synchronize()
+        t0 = time.time()
+        outs = model.generate(prompts, policies, slots=n, chunk=512, pool_tokens=n * CONTEXT_CAP,
+                              page_size=PAGE)
+        torch.cuda.synchronize()
+        seconds = time.time() - t0
+    generated = sum(len(o) for o in outs)
+    print(json.dumps({"only": "serve", "shape": shape, "layers": config["num_hidden_layers"],
+                      "requests": n, "prompt_tokens": int(plens.sum()), "generated_tokens": generated,
+                      "seconds": round(seconds, 3),
+                      "generated_tokens_per_s": round(generated / seconds, 1),
+                      "tokens_per_s": round((generated + int(plens.sum())) / seconds, 1)}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -142,7 +174,7 @@ def main():
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
                     help="with --only: the 14B or 32B shape of the baseline record instead of the 8B one")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="with --only decode: prompt length")
-    ap.add_argument("--only", default="", choices=["", "prefill", "decode"],
+    ap.add_argument("--only", default="", choices=["", "prefill", "decode", "serve"],
                     help="profiling aid: run just the 2,048-token prefill, or just the decode "
                          "steps, and print a short line instead of the contract line")
     args = ap.parse_args()
@@ -174,6 +206,8 @@ def main():
                           "tflops": round(pre["tflops"], 1),
                           "frac": round(pre["tflops"] / peaks["bf16_tflops"], 4)}))
         return 0
+    if args.only == "serve":
+        return serve_workload(model, config, args.shape)
     if args.only == "decode":
         r = measure_decode(model, args.batch, args.prompt, args.steps, warmup=warmup, seed=SEED,
                            page_size=PAGE)
