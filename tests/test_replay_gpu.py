@@ -107,7 +107,6 @@ def test_prompt_portions_through_graphs_give_the_same_bits(models, name, dtype):
         torch.cuda.synchronize()
         got[graphs] = outs
         if graphs:
-            assert len(eng._portion_graphs) == 1 or len({k[2] for k in eng._portion_graphs}) > 1
             assert eng._portion_graphs, "no portion was captured"
     for a, b in zip(got[False], got[True]):
         assert torch.equal(a, b)

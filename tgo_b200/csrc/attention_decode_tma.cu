@@ -77,7 +77,8 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ block_tables, int max_blocks,
                         const int* __restrict__ positions, const int* __restrict__ seq_ids, int H,
                         int Hkv, float scale_log2, int window, int n_splits,
-                        float* __restrict__ part_o, float* __restrict__ part_ml) {
+                        float* __restrict__ part_o, float* __restrict__ part_ml,
+                        const int* __restrict__ tok_list) {
     constexpr int DH = DT_DH, KS = DH / 16, CH = DH / 8, LDQ = DH + 8;
     extern __shared__ unsigned char dt_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)dt_raw + 1023) & ~(uintptr_t)1023);
@@ -89,7 +90,11 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     pdl_wait();
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tok = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    // the tokens of the step this launch takes: all of them, or those a list names (the
+    // single tokens of a step that also holds prompt portions); partial results are kept by
+    // place in the list
+    const int slot = blockIdx.x;
+    const int tok = tok_list ? tok_list[slot] : slot, kvh = blockIdx.y, split = blockIdx.z;
     const int G = H / Hkv;
     const int p = positions[tok];
     if (p < 0) {                               // a request that brings nothing: zeros out
@@ -98,7 +103,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 out[(size_t)tok * out_stride + (size_t)(kvh * G) * DH + i] = __float2bfloat16_rn(0.f);
         if (n_splits > 1)
             for (int r = tid; r < G; r += DT_THREADS) {
-                const size_t at = ((size_t)tok * H + kvh * G + r) * n_splits + split;
+                const size_t at = ((size_t)slot * H + kvh * G + r) * n_splits + split;
                 part_ml[at * 2] = -INFINITY;
                 part_ml[at * 2 + 1] = 0.f;
             }
@@ -434,7 +439,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         if (n_splits == 1) {
             out[(size_t)tok * out_stride + (size_t)head * DH + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
         } else {
-            const size_t at = ((size_t)tok * H + head) * n_splits + split;
+            const size_t at = ((size_t)slot * H + head) * n_splits + split;
             part_o[at * DH + d] = acc;
             if (d == 0) { part_ml[at * 2] = m; part_ml[at * 2 + 1] = l; }
         }
@@ -489,6 +494,8 @@ TGO_API int tgo_attention_decode_tma_error(int* value) {
     return (int)cudaMemcpyFromSymbol(value, dt_error_flag, sizeof(int));
 }
 
+// tok_list: null, or T indices into the step's tokens: those are taken instead of 0 .. T-1
+// (q, out, positions and seq_ids are indexed by them; the partial results by 0 .. T-1).
 // One token per request (token t is request seq_ids[t] at positions[t]); n_splits CTAs per
 // (token, kv head) write partial results to part_o [T, H, n_splits, 128] and part_ml
 // [T, H, n_splits, 2] for flash_combine_kernel when n_splits > 1.
@@ -497,7 +504,7 @@ TGO_API int tgo_attention_decode_tma(const void* q, long long q_stride, void* ou
                                      const int* block_tables, int max_blocks, const int* positions,
                                      const int* seq_ids, int T, int H, int Hkv, int dh, float scale,
                                      int window, int n_splits, float* part_o, float* part_ml,
-                                     cudaStream_t stream) {
+                                     const int* tok_list, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv || !tgo_attention_decode_tma_supports(dh, H / Hkv, page_size) ||
         n_pages <= 0 || max_blocks <= 0 || window < 0 || n_splits < 1 || n_splits > 65535 || Hkv > 65535 ||
@@ -527,9 +534,9 @@ TGO_API int tgo_attention_decode_tma(const void* q, long long q_stride, void* ou
         return tgo_launch_pdl(flash_decode_tma_kernel<true>, dim3(T, Hkv, n_splits), dim3(DT_THREADS), smem, stream,
                               *mk, *mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_size, shift,
                               block_tables, max_blocks, positions, seq_ids, H, Hkv, scale * 1.4426950408889634f,
-                              window, n_splits, part_o, part_ml);
+                              window, n_splits, part_o, part_ml, tok_list);
     return tgo_launch_pdl(flash_decode_tma_kernel<false>, dim3(T, Hkv, n_splits), dim3(DT_THREADS), smem, stream,
                           *mk, *mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_size, shift,
                           block_tables, max_blocks, positions, seq_ids, H, Hkv, scale * 1.4426950408889634f,
-                          window, n_splits, part_o, part_ml);
+                          window, n_splits, part_o, part_ml, tok_list);
 }

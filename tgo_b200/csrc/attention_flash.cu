@@ -488,11 +488,14 @@ flash_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
 // A split that saw no key has m = -inf, l = 0 and its O is not read.
 __global__ void flash_combine_kernel(const float* __restrict__ part_o,
                                      const float* __restrict__ part_ml, bf16* __restrict__ out,
-                                     long long out_stride, int H, int DH, int n_splits) {
+                                     long long out_stride, int H, int DH, int n_splits,
+                                     const int* __restrict__ tok_list) {
     pdl_wait();
     pdl_launch();
-    const int t = blockIdx.x, h = blockIdx.y;
-    const size_t base = ((size_t)t * H + h) * n_splits;
+    // partial results lie by place in the launch; the output row is the token the list names
+    const int h = blockIdx.y;
+    const int t = tok_list ? tok_list[blockIdx.x] : blockIdx.x;
+    const size_t base = ((size_t)blockIdx.x * H + h) * n_splits;
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
     float l = 0.f;
@@ -604,15 +607,28 @@ TGO_API int tgo_attention_flash(const void* q, long long q_stride, void* out, lo
     return TGO_E_BAD_ARG;
 }
 
-TGO_API int tgo_attention_flash_combine(const float* part_o, const float* part_ml, void* out,
-                                        long long out_stride, int T, int H, int dh, int n_splits,
-                                        cudaStream_t stream) {
+static int combine_launch(const float* part_o, const float* part_ml, void* out, long long out_stride,
+                          int T, int H, int dh, int n_splits, const int* tok_list, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H > 65535) return TGO_E_BAD_ARG;
     return tgo_launch_pdl(flash_combine_kernel, dim3(T, H),
                           dim3(dh < 128 ? 32 * ((dh + 31) / 32) : 128), 0, stream, part_o, part_ml,
-                          (bf16*)out, out_stride, H, dh, n_splits);
+                          (bf16*)out, out_stride, H, dh, n_splits, tok_list);
 }
+
+// The same for the T tokens that tok_list names (partial results by place in the list).
+TGO_API int tgo_attention_flash_combine_listed(const float* part_o, const float* part_ml, void* out,
+                                               long long out_stride, int T, int H, int dh, int n_splits,
+                                               const int* tok_list, cudaStream_t stream) {
+    return combine_launch(part_o, part_ml, out, out_stride, T, H, dh, n_splits, tok_list, stream);
+}
+
+TGO_API int tgo_attention_flash_combine(const float* part_o, const float* part_ml, void* out,
+                                        long long out_stride, int T, int H, int dh, int n_splits,
+                                        cudaStream_t stream) {
+    return combine_launch(part_o, part_ml, out, out_stride, T, H, dh, n_splits, nullptr, stream);
+}
+
 
 // ------------------------------------------------------------ no-allocation entry point
 // See attention_decode_static.h: the same decode kernels, with the partial outputs of the

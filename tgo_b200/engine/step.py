@@ -59,6 +59,7 @@ class Engine:
         self.use_graphs = graphs and self.device.type == "cuda"
         self.h2d_bytes_last = 0       # bytes of the last step's inputs copied to the device
         self._graphs = {}
+        self._warmed = set()          # kinds of decode step that have run once outside a capture
         self._portion_graphs = {}     # key -> captured graph of a one-request prompt portion
         self._portion_seen = {}       # key -> times the shape came without a graph
 
@@ -272,7 +273,17 @@ class Engine:
 
     # ------------------------------------------------------------- decode graphs
     BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
-    WIDTH_QUANTUM = 64          # block-table columns per graph variant
+    WIDTH_QUANTUM = 64          # block-table columns of the smallest graph variant; then 128, 256, ...
+
+    def _graph_width(self, entries: List[StepEntry]) -> int:
+        """Block-table columns of the graph a step runs through: the smallest of 64, 128,
+        256, ... that holds the longest table of the step (a few variants however long the
+        contexts grow; the kernels read only the columns a request has)."""
+        raw = max(1, max(len(t) for e in entries for t in self.cache.requests[e.request_id].tables))
+        q = self.WIDTH_QUANTUM
+        while q < raw:
+            q *= 2
+        return q
 
     def _graph_step(self, entries: List[StepEntry]) -> torch.Tensor:
         """A decode-only step through a captured graph. The batch is padded to a bucket
@@ -281,17 +292,17 @@ class Engine:
         valid until the next step of the same bucket."""
         B = len(entries)
         bucket = next((b for b in self.BUCKETS if b >= B), B)
-        widths = tuple((max(1, max(len(self.cache.requests[e.request_id].tables[g])
-                                   for e in entries)) + self.WIDTH_QUANTUM - 1)
-                       // self.WIDTH_QUANTUM * self.WIDTH_QUANTUM
-                       for g in range(len(self.cache.groups)))
-        key = (bucket, widths)
+        width = self._graph_width(entries)
+        key = (bucket, width)
         entry = self._graphs.get(key)
         if entry is None:
-            flat, meta = self._pack(entries, pad_to=bucket, width_quantum=self.WIDTH_QUANTUM,
-                                    all_rows=True)
+            flat, meta = self._pack(entries, pad_to=bucket, width_quantum=width, all_rows=True)
+            # a warm-up run only the first time this engine meets a row count that picks other
+            # product kernels (few rows, the library's range, many): later captures just record
+            kind = 0 if bucket <= 8 else 1 if bucket <= 64 else 2
             try:
-                entry = self._capture(flat, meta)
+                entry = self._capture(flat, meta, warm=kind not in self._warmed)
+                self._warmed.add(kind)
             except RuntimeError as e:
                 # a part that talks to the host in its forward (a part from outside the
                 # package may) cannot be captured: run such a model step by step instead
@@ -307,8 +318,8 @@ class Engine:
         # write again only when the last copy out of it has run (a caller that does not read
         # a step's result before the next step would otherwise overwrite it in flight)
         copied.synchronize()
-        _, meta = self._pack(entries, pad_to=bucket, width_quantum=self.WIDTH_QUANTUM,
-                             all_rows=True, out=host.numpy())
+        _, meta = self._pack(entries, pad_to=bucket, width_quantum=width, all_rows=True,
+                             out=host.numpy())
         dev.copy_(host, non_blocking=True)
         copied.record()
         self.h2d_bytes_last = meta["total"] * 4
@@ -332,10 +343,8 @@ class Engine:
         in the shape (positions, slots, block table, token ids) is data in the step's buffer.
         Returns None when the step has to run the ordinary way."""
         e = entries[0]
-        widths = tuple((max(1, len(self.cache.requests[e.request_id].tables[g])) +
-                        self.WIDTH_QUANTUM - 1) // self.WIDTH_QUANTUM * self.WIDTH_QUANTUM
-                       for g in range(len(self.cache.groups)))
-        key = (len(e.tokens), tuple(int(w) for w in e.want), widths)
+        width = self._graph_width(entries)
+        key = (len(e.tokens), tuple(int(w) for w in e.want), width)
         entry = self._portion_graphs.get(key)
         if entry is None:
             seen = self._portion_seen.get(key, 0) + 1
@@ -344,7 +353,7 @@ class Engine:
                 return None
             if len(self._portion_seen) > 64:
                 self._portion_seen.clear()
-            flat, meta = self._pack(entries, width_quantum=self.WIDTH_QUANTUM)
+            flat, meta = self._pack(entries, width_quantum=width)
             try:
                 # the shape has run before, so everything it needs is loaded: no warm-up run
                 entry = self._capture(flat, meta, warm=False)
@@ -359,7 +368,7 @@ class Engine:
             self._portion_graphs[key] = entry
         graph, host, dev, logits, launches, copied, _ = entry
         copied.synchronize()              # see _graph_step
-        _, meta = self._pack(entries, width_quantum=self.WIDTH_QUANTUM, out=host.numpy())
+        _, meta = self._pack(entries, width_quantum=width, out=host.numpy())
         dev.copy_(host, non_blocking=True)
         copied.record()
         self.h2d_bytes_last = meta["total"] * 4

@@ -491,14 +491,17 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
                     head_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
                     block_tables: torch.Tensor, positions: torch.Tensor, seq_ids: torch.Tensor,
                     tile_tok0: Optional[torch.Tensor], tile_ntok: Optional[torch.Tensor],
-                    scale: float, window: int, wide: bool = True, n_splits: int = 1) -> None:
+                    scale: float, window: int, wide: bool = True, n_splits: int = 1,
+                    tok_list: Optional[torch.Tensor] = None) -> None:
     """Paged causal attention on the tensor cores (bfloat16). With tile arrays (int32,
     first token and token count of each tile, tokens of one request, at most
     flash_tile_rows() // group of them) any step; without them every token is a tile of its
     own (decode), and n_splits > 1 cuts each request's keys over that many CTAs and joins
-    them. (`wide` is accepted and ignored.)"""
-    _need_cuda(q, out, k_cache, v_cache, block_tables, positions, seq_ids, tile_tok0, tile_ntok)
-    T = q.shape[0]
+    them. tok_list (int32, decode with head size 128 only): the tokens of the step to take,
+    instead of all. (`wide` is accepted and ignored.)"""
+    _need_cuda(q, out, k_cache, v_cache, block_tables, positions, seq_ids, tile_tok0, tile_ntok,
+               tok_list)
+    T = q.shape[0] if tok_list is None else tok_list.numel()
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert k_cache.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
     assert q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 2 == 0
@@ -519,14 +522,15 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
             c_int(k_cache.shape[0]), c_int(page_size), _ptr(block_tables),
             c_int(block_tables.shape[1]), _ptr(positions), _ptr(seq_ids), c_int(T), c_int(num_heads),
             c_int(num_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(n_splits),
-            _ptr(part_o), _ptr(part_ml), _stream()),
+            _ptr(part_o), _ptr(part_ml), _ptr(tok_list), _stream()),
             "attention_decode_tma", f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads})")
         if n_splits > 1:
-            _check(lib.tgo_attention_flash_combine(
+            _check(lib.tgo_attention_flash_combine_listed(
                 _ptr(part_o), _ptr(part_ml), _ptr(out), c_ll(out.stride(0)), c_int(T),
-                c_int(num_heads), c_int(head_dim), c_int(n_splits), _stream()),
+                c_int(num_heads), c_int(head_dim), c_int(n_splits), _ptr(tok_list), _stream()),
                 "attention_flash_combine")
         return
+    assert tok_list is None, "a token list is taken by the TMA decode kernel only"
     _check(lib.tgo_attention_flash(
         _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
         c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(positions),
@@ -544,6 +548,7 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
 USE_TC_ATTENTION = True     # prompt portions with head size 128 on the tcgen05 kernel
 TC_ATTENTION_MIN_TOKENS = 1  # steps with fewer tokens than this keep the mma.sync kernel
 TC_ATTENTION_PERSISTENT = True   # one CTA per SM drawing items, or one CTA per item
+SPLIT_MIXED_STEPS = True         # single tokens of a mixed step go through the decode kernel
 
 
 def attention_tc_supports(head_dim: int, group: int, page_size: int) -> bool:
@@ -605,15 +610,32 @@ def _tiles(ctx, tokens_per_tile: int):
     return got
 
 
-def decode_splits(ctx, num_kv_heads: int, window: int, ctas_per_sm: int = 3) -> int:
-    """How many CTAs share one request's keys in a decode step. Few (request, kv head) pairs:
-    as many splits as fill the GPU once (measured: one full wave beats more, shorter CTAs),
-    each with at least two 64-key tiles. Pairs that fill half the GPU or more are cut less
-    (measured on B200 with 8 kv heads and 1088 keys: batch 32 best in 3, batch 64 best whole:
-    a CTA that walks a request's keys alone pays its start once)."""
-    reach = min(ctx.max_context, window) if window > 0 else ctx.max_context
+def _tiles_and_singles(ctx, tokens_per_tile: int):
+    """For a step that holds prompt portions and single tokens: tile arrays of the entries
+    with more than one token, and the list of the tokens that are alone in their entry."""
+    key = ("tiles", tokens_per_tile, "split")
+    got = ctx.aux.get(key)
+    if got is None:
+        tok0, ntok, singles, base = [], [], [], 0
+        for n in ctx.extents:
+            if n == 1:
+                singles.append(base)
+            else:
+                for o in range(0, n, tokens_per_tile):
+                    tok0.append(base + o)
+                    ntok.append(min(tokens_per_tile, n - o))
+            base += n
+        dev = torch.tensor(tok0 + ntok + singles, dtype=torch.int32).to(ctx.token_ids.device,
+                                                                         non_blocking=True)
+        k = len(tok0)
+        got = (dev[:k], dev[k:2 * k], dev[2 * k:], len(singles))
+        ctx.aux[key] = got
+    return got
+
+
+def _splits_for(pairs: int, reach: int, window: int, ctas_per_sm: int = 3) -> int:
     tiles = max(1, (reach + 63) // 64 + (1 if window > 0 else 0))
-    pairs = max(1, ctx.num_seqs * num_kv_heads)
+    pairs = max(1, pairs)
     wave = NUM_SMS * ctas_per_sm
     if pairs >= wave:
         s = 1
@@ -624,6 +646,16 @@ def decode_splits(ctx, num_kv_heads: int, window: int, ctas_per_sm: int = 3) -> 
     else:
         s = -(-wave // pairs)
     return max(1, min(s, tiles // 2, 64))
+
+
+def decode_splits(ctx, num_kv_heads: int, window: int, ctas_per_sm: int = 3) -> int:
+    """How many CTAs share one request's keys in a decode step. Few (request, kv head) pairs:
+    as many splits as fill the GPU once (measured: one full wave beats more, shorter CTAs),
+    each with at least two 64-key tiles. Pairs that fill half the GPU or more are cut less
+    (measured on B200 with 8 kv heads and 1088 keys: batch 32 best in 3, batch 64 best whole:
+    a CTA that walks a request's keys alone pays its start once)."""
+    reach = min(ctx.max_context, window) if window > 0 else ctx.max_context
+    return _splits_for(ctx.num_seqs * num_kv_heads, reach, window, ctas_per_sm)
 
 
 def paged_attention(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
@@ -640,6 +672,23 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
         elif USE_TC_ATTENTION and q.shape[0] >= TC_ATTENTION_MIN_TOKENS and \
                 attention_tc_supports(head_dim, group, cache.page_size) and \
                 cache.k.is_contiguous() and cache.v.is_contiguous():
+            if SPLIT_MIXED_STEPS and USE_TMA_DECODE and 1 in ctx.extents and \
+                    attention_decode_tma_supports(head_dim, group, cache.page_size):
+                # prompt portions beside single tokens: the portions through the tile kernel,
+                # the single tokens through the decode kernel (a tile of 128 rows for one
+                # token's few heads would walk that request's whole context almost empty)
+                tok0, ntok, singles, n_single = _tiles_and_singles(ctx, 128 // group)
+                if tok0.numel():
+                    attention_tc_prefill(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
+                                         cache.page_size, cache.block_tables, ctx.positions,
+                                         ctx.seq_ids, tok0, ntok, scale, window)
+                reach = min(ctx.max_context, window) if window > 0 else ctx.max_context
+                attention_flash(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
+                                cache.page_size, cache.block_tables, ctx.positions, ctx.seq_ids,
+                                None, None, scale, window, wide=False,
+                                n_splits=_splits_for(n_single * num_kv_heads, reach, window),
+                                tok_list=singles)
+                return
             tok0, ntok = _tiles(ctx, 128 // group)
             attention_tc_prefill(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
                                  cache.page_size, cache.block_tables, ctx.positions, ctx.seq_ids,
