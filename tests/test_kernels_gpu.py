@@ -519,7 +519,7 @@ def tc_flag():
 @pytest.mark.parametrize("M,N,K,transpose,splits", [
     (128, 128, 64, False, 1), (200, 300, 264, False, 1), (700, 520, 1000, False, 1),
     (1024, 2048, 4096, False, 1), (300, 512, 2048, False, 3), (8, 128, 64, True, 1),
-    (2048, 4096, 192, False, 1), (2048, 6144, 128, False, 1), (130, 1001, 72, False, 1),   # tiles 232 / 240 wide
+    (2048, 4096, 192, False, 1), (2048, 6144, 128, False, 1), (130, 1001, 72, False, 1),
     (33, 200, 264, True, 1), (64, 512, 4096, True, 4), (200, 256, 512, True, 1)])
 def test_gemm_tc(M, N, K, transpose, splits):
     """The tcgen05 kernel in both orientations, with tails in every dimension and K splits."""
@@ -558,11 +558,44 @@ def test_gemm_tc_gated_output(M, f, K, transpose):
     assert torch.allclose(out.float(), want, rtol=2e-2, atol=2e-2 * float(want.abs().max()))
 
 
+@pytest.mark.parametrize("rows,width", [(128, 64), (128, 144), (128, 224), (128, 256), (256, 64),
+                                        (256, 96), (256, 176), (256, 240), (256, 256)])
+@pytest.mark.parametrize("M", [600, 700])
+def test_gemm_tc_tile_shapes(rows, width, M):
+    """Every kind of tile the kernel takes, forced instead of chosen: one accumulator or two
+    (128 or 256 rows), narrow, odd and full widths, with tails in rows and columns (600 rows
+    leave the lower accumulator of the last tile wholly outside, 700 partly); plain, added
+    and gated outputs."""
+    N, K = 1008, 328
+    x = rnd(M, K, dtype=torch.bfloat16, seed=M)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=width)
+    want = x.float() @ w.float().t()
+    ops().gemm_tc_force_tile(rows, width)
+    try:
+        out = torch.zeros(M, N, dtype=torch.float32, device=DEV)
+        ops().gemm_tc(x, w, out, transpose=False)
+        h = rnd(M, N, seed=3)
+        h2 = h.clone()
+        ops().gemm_tc(x, w, h2, accumulate=True, transpose=False)
+        gated = torch.zeros(M, N // 2, dtype=torch.bfloat16, device=DEV)
+        ops().gemm_tc(x, interleave8(w[:N // 2], w[N // 2:]).contiguous(), gated, transpose=False, gated=True)
+        torch.cuda.synchronize()
+    finally:
+        ops().gemm_tc_force_tile(0, 0)
+    assert tc_flag() == 0
+    assert torch.allclose(out, want, rtol=1e-4, atol=1e-3)
+    assert torch.allclose(h2, h + want, rtol=1e-4, atol=1e-3)
+    g = want[:, :N // 2].to(torch.bfloat16).float()
+    u = want[:, N // 2:].to(torch.bfloat16).float()
+    act = g / (1 + torch.exp(-g)) * u
+    assert torch.allclose(gated.float(), act, rtol=2e-2, atol=2e-2 * float(act.abs().max()))
+
+
 def test_linear_picks_by_rows_and_agrees():
-    """1..8 rows: the weight-streaming kernel; 9..64: the library; more: tcgen05. The same
-    product through each differs by bfloat16 rounding only."""
+    """1..8 rows: the weight-streaming kernel; from TC_MIN_ROWS rows: tcgen05; between them
+    the library. The same product through each differs by bfloat16 rounding only."""
     w = rnd(384, 512, dtype=torch.bfloat16, scale=0.1, seed=6)
-    x = rnd(200, 512, dtype=torch.bfloat16, seed=7)
+    x = rnd(ops().TC_MIN_ROWS + 70, 512, dtype=torch.bfloat16, seed=7)
     many = ops().linear(x, w)
     mid = ops().linear(x[:40].contiguous(), w)
     few = ops().linear(x[:5].contiguous(), w)

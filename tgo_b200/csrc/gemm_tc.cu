@@ -2,7 +2,9 @@
 // with K contiguous, as activations [rows, K] and checkpoint weights [out, K] are), float32
 // accumulation in tensor memory.
 //
-// One CTA computes one 128 x BN tile of D. Six warps, three roles:
+// One CTA computes one 128 x BN tile of D at a time (BN, the tile's width, is a run-time
+// argument: a multiple of 16 up to 256, chosen by the host per product). Six warps, three
+// roles:
 //   warp 0, one lane   producer: TMA tile loads (128-byte swizzle) of A [128 x 64] and
 //                      B [BN x 64] into a ring of shared-memory stages, completion counted
 //                      on each stage's `full` mbarrier;
@@ -18,10 +20,17 @@
 // `splits` > 1 cuts K over gridDim.z CTAs, each writing a float32 partial tile; a second
 // kernel adds the partials in split order and applies the output form.
 //
+// A second form of the kernel (DUAL) gives a CTA 256 rows: two accumulators fed by two A
+// tiles and one shared B tile per k-block, and four more epilogue warps. Per product it
+// brings a third fewer operand bytes into the SM, which is what bounds a 128 x 256 tile.
+//
 // Tails: TMA fills out-of-range rows and K with zeros; stores are guarded. K % 8 == 0.
 // No cluster, no multicast. Every mbarrier wait gives up after about two seconds, records
 // where in *err and lets the CTA run to its end (TMEM is freed on every path).
 #include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 
@@ -93,18 +102,20 @@ __device__ __forceinline__ uint64_t umma_desc(const void* tile) {
     return d;
 }
 
-template <int BN>
-struct TcSmem {
-    static constexpr int A_BYTES = TC_BM * TC_BK * 2;
-    static constexpr int B_BYTES = BN * TC_BK * 2;
-    static constexpr int STAGE = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (200 * 1024) / STAGE < 8 ? (200 * 1024) / STAGE : 8;
-    static constexpr size_t TOTAL = (size_t)STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
-    // columns of tensor memory per accumulator and in all: powers of two (an allocation has to be)
-    static constexpr int ACC_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
-    static constexpr int TMEM_COLS = 2 * ACC_COLS;
-    static_assert(BN % 8 == 0 && BN <= 256, "a tile is at most 256 wide, in steps of 8");
-};
+// Shared and tensor memory of a CTA for tiles `bn` wide (a value at run time: the host picks
+// the width that wastes the least of the GPU for the shape at hand).
+#define TC_A_BYTES (TC_BM * TC_BK * 2)
+#define TC_RING_BYTES (200 * 1024)
+#define TC_SMEM_TOTAL ((size_t)TC_RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/)
+__host__ __device__ __forceinline__ int tc_stage_bytes(int bn, bool dual = false) {
+    return (dual ? 2 : 1) * TC_A_BYTES + bn * TC_BK * 2;
+}
+__host__ __device__ __forceinline__ int tc_stages(int bn, bool dual = false) {
+    const int n = TC_RING_BYTES / tc_stage_bytes(bn, dual);
+    return n < 8 ? n : 8;
+}
+// columns of tensor memory per accumulator: a power of two (an allocation has to be)
+__host__ __device__ __forceinline__ int tc_acc_cols(int bn) { return bn <= 32 ? 32 : bn <= 64 ? 64 : bn <= 128 ? 128 : 256; }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(bar)) : "memory");
@@ -208,16 +219,22 @@ __device__ __forceinline__ void tc_store(const uint32_t (&r)[32], void* __restri
 // Persistent: the grid is at most one CTA per SM and each CTA walks tiles blockIdx.x,
 // blockIdx.x + gridDim.x, ... The accumulator is double-buffered in TMEM (2 x BN columns), so
 // the epilogue of one tile runs while the next tile's products are issued.
-template <int BN, int OMODE, bool TRANSPOSE>
-__global__ void __launch_bounds__(TC_THREADS)
+template <int OMODE, bool TRANSPOSE, bool DUAL>
+__global__ void __launch_bounds__(DUAL ? TC_THREADS + 128 : TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                void* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out, int splits,
-               int kb_per_split, int* __restrict__ err) {
-    using L = TcSmem<BN>;
-    constexpr int STAGES = L::STAGES;
+               int kb_per_split, int* __restrict__ err, int BN) {
+    // DUAL: a CTA's tile is 256 rows, two 128-row halves that share every B tile in shared
+    // memory (a third fewer operand bytes per product: one SM cannot be fed the 48 KB that a
+    // 128 x 256 tile wants every 512 tensor cycles); the two accumulators fill the 512
+    // columns of tensor memory, so the next tile waits for the epilogue of this one, which
+    // two warpgroups run, one per half.
+    constexpr int ROWS = DUAL ? 2 * TC_BM : TC_BM;
+    const int STAGES = tc_stages(BN, DUAL), STAGE = tc_stage_bytes(BN, DUAL);
+    const int ACC_COLS = tc_acc_cols(BN), TMEM_COLS = DUAL ? 512 : 2 * ACC_COLS;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)(base + (size_t)STAGES * L::STAGE);
+    uint64_t* full = (uint64_t*)(base + TC_RING_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;       // [2]
     uint64_t* acc_empty = acc_full + 2;        // [2]
@@ -227,7 +244,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // Tile order: the A-row tiles of one group of TC_GROUP_M run first over a B tile, so the
     // CTAs that are resident together share B tiles (and a small set of A tiles) in L2 instead
     // of streaming all of B once per row of tiles.
-    const int tiles_m = (rows_a + TC_BM - 1) / TC_BM;
+    const int tiles_m = (rows_a + ROWS - 1) / ROWS;
     const int tiles_n = (rows_b + BN - 1) / BN;
     const int n_tiles = tiles_m * tiles_n;
     const int total = n_tiles * splits;
@@ -236,13 +253,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], DUAL ? 8 : 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(tc_smem(tmem_slot)), "r"((uint32_t)L::TMEM_COLS) : "memory");
+                     ::"r"(tc_smem(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -256,7 +273,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int tile = w % n_tiles;
         const int group = tile / per_group, within = tile % per_group;
         const int group_m = tiles_m - group * TC_GROUP_M < TC_GROUP_M ? tiles_m - group * TC_GROUP_M : TC_GROUP_M;
-        m0 = (group * TC_GROUP_M + within % group_m) * TC_BM;
+        m0 = (group * TC_GROUP_M + within % group_m) * ROWS;
         n0 = (within / group_m) * BN;
         kb_lo = split * kb_per_split;
         const int kb_hi = kb_lo + kb_per_split < kb_total ? kb_lo + kb_per_split : kb_total;
@@ -274,10 +291,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int s = it % STAGES;
                     ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, err, 1);
                     if (!ok) break;
-                    mbar_expect_tx(&full[s], L::STAGE);
-                    unsigned char* st = base + (size_t)s * L::STAGE;
+                    mbar_expect_tx(&full[s], (uint32_t)STAGE);
+                    unsigned char* st = base + (size_t)s * STAGE;
                     tma_load_2d(st, &map_a, (kb_lo + i) * TC_BK, m0, &full[s]);
-                    tma_load_2d(st + L::A_BYTES, &map_b, (kb_lo + i) * TC_BK, n0, &full[s]);
+                    if (DUAL) tma_load_2d(st + TC_A_BYTES, &map_a, (kb_lo + i) * TC_BK, m0 + TC_BM, &full[s]);
+                    tma_load_2d(st + (DUAL ? 2 : 1) * TC_A_BYTES, &map_b, (kb_lo + i) * TC_BK, n0, &full[s]);
                 }
             }
         }
@@ -291,22 +309,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++local) {
                 int split, m0, n0, kb_lo, n_kb;
                 locate(w, split, m0, n0, kb_lo, n_kb);
-                const uint32_t buf = local & 1;
-                ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, err, 4);   // epilogue let go of it
+                // two accumulators in turn, or (DUAL) the one pair there is
+                const uint32_t buf = DUAL ? 0u : (local & 1);
+                const uint32_t use = DUAL ? local : (local >> 1);
+                ok = mbar_wait(&acc_empty[buf], (use & 1) ^ 1, err, 4);   // epilogue let go of it
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * L::ACC_COLS;
+                const uint32_t d_tmem = tmem_base + buf * ACC_COLS;
                 for (int i = 0; i < n_kb; ++i, ++it) {
                     const int s = it % STAGES;
                     ok = mbar_wait(&full[s], (it / STAGES) & 1, err, 2);
                     if (!ok) break;
                     tc_fence_after();
-                    unsigned char* st = base + (size_t)s * L::STAGE;
-                    const uint64_t da = umma_desc(st), db = umma_desc(st + L::A_BYTES);
+                    unsigned char* st = base + (size_t)s * STAGE;
+                    const uint64_t da = umma_desc(st), db = umma_desc(st + (DUAL ? 2 : 1) * TC_A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k)    // 16 bf16 = 32 bytes = 2 descriptor units
+                    for (int k = 0; k < TC_BK / 16; ++k) {  // 16 bf16 = 32 bytes = 2 descriptor units
                         umma_bf16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
                                   (i > 0 || k > 0) ? 1u : 0u);
+                        if (DUAL)       // the lower 128 rows: the next A tile, accumulator columns 256..
+                            umma_bf16(d_tmem + 256u, da + (uint64_t)(TC_A_BYTES >> 4) + (uint64_t)(2 * k),
+                                      db + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    }
                     umma_commit(&empty[s]);
                 }
                 umma_commit(&acc_full[buf]);    // arrives once every MMA issued above has finished
@@ -314,14 +338,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else {
         const int quarter = warp & 3;                           // TMEM lanes this warp may read
-        const int row = quarter * 32 + lane;                    // row of the tile = TMEM lane
+        const int half = DUAL ? (warp - 2) >> 2 : 0;            // DUAL: warps 2-5 the upper rows, 6-9 the lower
+        const int row = half * TC_BM + quarter * 32 + lane;     // row of the tile (TMEM lane, + 128)
         uint32_t local = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < total; w += gridDim.x, ++local) {
             int split, m0, n0, kb_lo, n_kb;
             locate(w, split, m0, n0, kb_lo, n_kb);
-            const uint32_t buf = local & 1;
-            if (ok) ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, err, 3);
+            const uint32_t buf = DUAL ? 0u : (local & 1);
+            const uint32_t use = DUAL ? local : (local >> 1);
+            if (ok) ok = mbar_wait(&acc_full[buf], use & 1, err, 3);
             tc_fence_after();
 #pragma unroll 1
             // a tile that is not a multiple of 32 wide: its last group of columns is cut at the
@@ -329,7 +355,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int n_edge = n0 + BN < rows_b ? n0 + BN : rows_b;
             for (int c = 0; c < (BN + 31) / 32; ++c) {
                 uint32_t r[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * L::ACC_COLS + (uint32_t)(c * 32);
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * ACC_COLS + (uint32_t)(half * 256) + (uint32_t)(c * 32);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -354,7 +380,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)L::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
     }
 }
 
@@ -391,8 +417,33 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// A [rows, K] bf16 row-major -> tiles of box_rows x 64 with the 128-byte swizzle.
+// A [rows, K] bf16 row-major -> tiles of box_rows x 64 with the 128-byte swizzle. Maps are kept
+// by (address, shape, box): a weight's map is made once, and activations come back to the same
+// addresses step after step (a map describes memory, not its contents).
+static int make_map_uncached(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows);
 static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+    struct Key {
+        const void* ptr; int rows, K, box;
+        bool operator==(const Key& o) const { return ptr == o.ptr && rows == o.rows && K == o.K && box == o.box; }
+    };
+    struct Hash {
+        size_t operator()(const Key& k) const {
+            return (size_t)(uintptr_t)k.ptr * 0x9e3779b97f4a7c15ull ^ ((size_t)k.rows << 40) ^ ((size_t)k.K << 16) ^ (size_t)k.box;
+        }
+    };
+    static std::mutex lock;
+    static std::unordered_map<Key, CUtensorMap, Hash> maps;
+    std::lock_guard<std::mutex> hold(lock);
+    const Key key{ptr, rows, K, box_rows};
+    auto it = maps.find(key);
+    if (it != maps.end()) { *map = it->second; return 0; }
+    const int rc = make_map_uncached(map, ptr, rows, K, box_rows);
+    if (rc) return rc;
+    if (maps.size() > 8192) maps.clear();
+    maps.emplace(key, *map);
+    return 0;
+}
+static int make_map_uncached(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return TGO_E_BAD_ARG;
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -405,14 +456,18 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_
     return r == CUDA_SUCCESS ? 0 : 2000 + (int)r;
 }
 
-template <int BN, int OMODE, bool TRANSPOSE>
-static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int rows_a, int rows_b, int K,
+template <int OMODE, bool TRANSPOSE, bool DUAL>
+static int tc_launch(int BN, const CUtensorMap& ma, const CUtensorMap& mb, void* out, int rows_a, int rows_b, int K,
                      long long ld_out, int splits, int kb_per_split, int* err, cudaStream_t stream) {
-    auto kern = gemm_tc_kernel<BN, OMODE, TRANSPOSE>;
-    const size_t smem = TcSmem<BN>::TOTAL;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    const int total = ((rows_b + BN - 1) / BN) * ((rows_a + TC_BM - 1) / TC_BM) * splits;
+    auto kern = gemm_tc_kernel<OMODE, TRANSPOSE, DUAL>;
+    const size_t smem = TC_SMEM_TOTAL;
+    static bool sized = false;            // per instance of this template
+    if (!sized) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        sized = true;
+    }
+    const int total = ((rows_b + BN - 1) / BN) * ((rows_a + (DUAL ? 2 : 1) * TC_BM - 1) / ((DUAL ? 2 : 1) * TC_BM)) * splits;
     int sms = 148;
     {
         int dev = 0;
@@ -423,20 +478,34 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, in
         }
     }
     const dim3 grid(total < sms ? total : sms);
-    kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err);
+    kern<<<grid, DUAL ? TC_THREADS + 128 : TC_THREADS, smem, stream>>>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, BN);
     return launch_status();
 }
 
-template <int BN, bool TRANSPOSE>
-static int tc_dispatch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int rows_a, int rows_b, int K,
+template <bool TRANSPOSE, bool DUAL = false>
+static int tc_dispatch(int BN, const CUtensorMap& ma, const CUtensorMap& mb, void* out, int rows_a, int rows_b, int K,
                        long long ld_out, int omode, int splits, int kb_per_split, int* err, cudaStream_t s) {
     switch (omode) {
-        case TC_OUT_BF16: return tc_launch<BN, TC_OUT_BF16, TRANSPOSE>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
-        case TC_OUT_F32: return tc_launch<BN, TC_OUT_F32, TRANSPOSE>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
-        case TC_OUT_ADD_F32: return tc_launch<BN, TC_OUT_ADD_F32, TRANSPOSE>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
-        case TC_OUT_SWIGLU: return tc_launch<BN, TC_OUT_SWIGLU, TRANSPOSE>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
-        default: return tc_launch<BN, TC_OUT_PARTIAL, TRANSPOSE>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
+        case TC_OUT_BF16: return tc_launch<TC_OUT_BF16, TRANSPOSE, DUAL>(BN, ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
+        case TC_OUT_F32: return tc_launch<TC_OUT_F32, TRANSPOSE, DUAL>(BN, ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
+        case TC_OUT_ADD_F32: return tc_launch<TC_OUT_ADD_F32, TRANSPOSE, DUAL>(BN, ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
+        case TC_OUT_SWIGLU: return tc_launch<TC_OUT_SWIGLU, TRANSPOSE, DUAL>(BN, ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
+        default: return tc_launch<TC_OUT_PARTIAL, TRANSPOSE, DUAL>(BN, ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
     }
+}
+
+// For tests and tuning: the tile of the non-transposed product is rows x width instead of
+// the cost model's choice (rows 128 or 256; 0 gives the choice back). The width has to be
+// one the instruction takes with 128 rows: a multiple of 16 from 16 to 256. Not for use
+// while other threads launch products.
+static int g_forced_rows = 0, g_forced_width = 0;
+TGO_API int tgo_gemm_tc_force_tile(int rows, int width) {
+    if (rows == 0) { g_forced_rows = g_forced_width = 0; return 0; }
+    if ((rows != 128 && rows != 256) || width < 16 || width > 256 || width % 16)
+        return TGO_E_BAD_ARG;
+    g_forced_rows = rows;
+    g_forced_width = width;
+    return 0;
 }
 
 // out[M, N] (row-major, leading dimension N) = x[M, K] . w[N, K]^T.
@@ -464,39 +533,50 @@ TGO_API int tgo_gemm_tc(const void* x, const void* w, void* out, int M, int N, i
     CUtensorMap ma, mb;
     int rc;
     if (!transpose) {
-        // Tile width: the CTAs walk the tiles in rounds, and the last round is as long as the
-        // others however few tiles it has; among the widths built, the one with the least
-        // rounds x width wins (4096 columns under 2048 rows: 288 tiles of 232 in two rounds
-        // instead of 256 tiles of 256 in two rounds, of which the second is 3/4 empty).
+        // Tile shape. The CTAs walk the tiles in rounds, and a round lasts as long as a whole
+        // tile however few tiles it has. A k-block of a tile costs the larger of its products
+        // (2 cycles a column for 128 rows) and of bringing its operands in (an SM is fed about
+        // 70 bytes a cycle: measured, a 128 x 256 tile's 48 KB keep the tensor pipe at 73 %).
+        // A tile of 256 rows (two accumulators over one B tile) needs a third fewer bytes per
+        // product. Among 128 or 256 rows and widths in multiples of 32 (the kernel takes
+        // multiples of 16, but a sweep over twelve products of three model sizes at 512 to
+        // 4096 rows found the widths between to cost as much as the next multiple of 32 or
+        // more), the cheapest by this count wins: it was 1.2 % behind
+        // the sweep's best shape on average, 9 % at worst. 4096 columns under 2048 rows run
+        // as 128 tiles of 256 x 256 in one round.
         int bn = N >= 256 ? 256 : 128;
-        if (N >= 256 && om != TC_OUT_SWIGLU && om != TC_OUT_PARTIAL) {
-            const int tiles_m = (M + TC_BM - 1) / TC_BM;
-            long long best = -1;
-            const int widths[3] = {256, 240, 232};
-            for (int i = 0; i < 3; ++i) {
-                const long long tiles = (long long)tiles_m * ((N + widths[i] - 1) / widths[i]);
-                const long long cost = ((tiles + 147) / 148) * widths[i];
-                if (best < 0 || cost < best) { best = cost; bn = widths[i]; }
+        bool dual = false;
+        if (g_forced_rows && om != TC_OUT_PARTIAL) {
+            bn = g_forced_width;
+            dual = g_forced_rows == 256;
+        } else if (N >= 256 && om != TC_OUT_PARTIAL) {
+            double best = -1.0;
+            for (int rows = 128; rows <= 256; rows += 128) {
+                if (rows == 256 && M <= 128) break;
+                const long long tiles_m = (M + rows - 1) / rows;
+                for (int width = 256; width >= 64; width -= 32) {
+                    const long long tiles = tiles_m * ((N + width - 1) / width);
+                    const double math = 2.0 * width * (rows / 128);
+                    const double feed = ((rows / 128) * 16384.0 + 128.0 * width) / 70.0;
+                    // + the epilogue, which a 256-row tile cannot hide behind the next tile
+                    const double per_tile = (math > feed ? math : feed) * ((K + 63) / 64) +
+                                            (rows == 256 ? 12.0 * width : 0.0) + 2000.0;
+                    const double cost = (double)((tiles + 147) / 148) * per_tile;
+                    if (best < 0 || cost < best) { best = cost; bn = width; dual = rows == 256; }
+                }
             }
         }
         if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
         if ((rc = make_map(&mb, w, N, K, bn))) return rc;
-        if (bn == 256) rc = tc_dispatch<256, false>(ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream);
-        else if (bn == 240) rc = tc_dispatch<240, false>(ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream);
-        else if (bn == 232) rc = tc_dispatch<232, false>(ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream);
-        else rc = tc_dispatch<128, false>(ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream);
+        rc = dual ? tc_dispatch<false, true>(bn, ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream)
+                  : tc_dispatch<false, false>(bn, ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream);
     } else {
         if (M > 256) return TGO_E_BAD_ARG;
         const int bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
         if ((rc = make_map(&ma, w, N, K, TC_BM))) return rc;
         if ((rc = make_map(&mb, x, M, K, bn))) return rc;
         // A = w (N rows), B = x (M rows); D^T is stored: out[m, n], leading dimension N
-        switch (bn) {
-            case 32: rc = tc_dispatch<32, true>(ma, mb, dst, N, M, K, ld, om, splits, kb_per_split, err, stream); break;
-            case 64: rc = tc_dispatch<64, true>(ma, mb, dst, N, M, K, ld, om, splits, kb_per_split, err, stream); break;
-            case 128: rc = tc_dispatch<128, true>(ma, mb, dst, N, M, K, ld, om, splits, kb_per_split, err, stream); break;
-            default: rc = tc_dispatch<256, true>(ma, mb, dst, N, M, K, ld, om, splits, kb_per_split, err, stream); break;
-        }
+        rc = tc_dispatch<true>(bn, ma, mb, dst, N, M, K, ld, om, splits, kb_per_split, err, stream);
     }
     if (rc || splits == 1) return rc;
     const long long n = (long long)M * N;

@@ -349,13 +349,14 @@ def _skinny_ok(x, w) -> bool:
         x.shape[0] <= SKINNY_MAX_ROWS and w.shape[1] % 8 == 0
 
 
-# Which kernel multiplies, by the number of rows (measured in the running model on B200):
-#   1..8     gemm_skinny (weight streaming, mma.sync)        faster than the library
-#   9..64    the library product (cuBLASLt through torch.mm)  the tcgen05 kernel in its decode
-#            orientation is 3-8 % behind it per product: too few 128-row tiles for 148 SMs
-#   65..     gemm_tc (tcgen05 + TMEM + TMA)                   within 3 % of the library, and it
-#            applies the gate in its epilogue
-TC_MIN_ROWS = 65
+# Which kernel multiplies, by the number of rows (measured in CUDA graphs on B200):
+#   1..8      gemm_skinny (weight streaming, mma.sync)        8-16 % faster than the library
+#   9..1024   the library product (cuBLASLt through torch.mm)  the tcgen05 kernel is 3-8 % behind
+#             it per product up to 64 rows (decode orientation), 1.5-2.5 x at 256-512 rows and
+#             7-36 % at 1024: too few tiles for 148 SMs and no balancing of the last round
+#   1025..    gemm_tc (tcgen05 + TMEM + TMA)                   3-17 % behind the library per
+#             product at 2048 rows, and it applies the gate in its epilogue
+TC_MIN_ROWS = 1025
 USE_TC = True            # False: the library product for every size above 8 rows
 
 
@@ -363,15 +364,6 @@ def _tc_ok(x, w) -> bool:
     return USE_TC and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and \
         x.shape[0] >= TC_MIN_ROWS and w.shape[1] % 8 == 0 and x.is_contiguous() and \
         w.is_contiguous() and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
-
-
-def _tc_splits(M: int, N: int, K: int) -> int:
-    """K splits for the decode orientation: enough work items to give every SM one, while a
-    split keeps at least eight 64-wide k-blocks."""
-    if M > 64:
-        return 1
-    tiles = (N + 127) // 128
-    return max(1, min(NUM_SMS // tiles, (K // 64) // 8))
 
 
 def _dense(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
@@ -383,7 +375,7 @@ def _dense(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Te
         return y
     if _tc_ok(x, w):
         y = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        gemm_tc(x, w, y, splits=_tc_splits(M, N, w.shape[1]))
+        gemm_tc(x, w, y)
         return y
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         return torch.mm(x, w.t()) if out_dtype == torch.bfloat16 else \
@@ -398,9 +390,9 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
     the product is returned for the caller to add (the block hands it to the next norm).
 
     float32: this package's plain-FMA kernel. bfloat16 with few rows (a decode step): this
-    package's weight-streaming kernel. bfloat16 with more rows: this package's tcgen05
-    kernel (TMA-fed, accumulators in tensor memory), in the decode orientation up to 64
-    rows. Both bfloat16 kernels do the residual add in their epilogue; out_dtype float32
+    package's weight-streaming kernel, which does the residual add in its epilogue.
+    bfloat16 with many rows (TC_MIN_ROWS): this package's tcgen05 kernel (TMA-fed,
+    accumulators in tensor memory); between them the library product. out_dtype float32
     keeps the accumulator's width (the logits).
     """
     out_dtype = out_dtype or x.dtype
@@ -418,14 +410,12 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
         gemm_skinny(x, w, out)
         return out
     x = as_rows(x)
-    if residual is not None and _tc_ok(x, w):
-        if x.shape[0] > 64:
-            # many rows: a read-modify-write of the float32 stream from the product's epilogue
-            # is slow (each thread owns a row); hand the product back and let the next norm,
-            # which reads the stream anyway, add it
-            return _dense(x, w, out_dtype)
-        gemm_tc(x, w, residual, accumulate=True, splits=_tc_splits(x.shape[0], w.shape[0], w.shape[1]))
-        return None
+    if residual is not None and x.dtype == torch.bfloat16:
+        # more than a few rows: the library has no add into a float32 stream, and from the
+        # tcgen05 product's epilogue a read-modify-write of the stream is slow (each thread
+        # owns a row); hand the product back and let the next norm, which reads the stream
+        # anyway, add it
+        return _dense(x, w, out_dtype)
     y = _dense(x, w, out_dtype)
     if residual is not None:
         residual_add(residual, y)
@@ -795,6 +785,15 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
                            c_int(1 if transpose else 0), c_int(splits), _ptr(ws),
                            _ptr(gemm_tc_error_flag(x.device)), _stream()), "gemm_tc",
            f"(M={M}, N={N}, K={K})")
+
+
+def gemm_tc_force_tile(rows: int = 0, width: int = 0) -> None:
+    """For tests and tuning: `gemm_tc` (not transposed) runs tiles of rows x width (rows 128
+    or 256; width a multiple of 16, or of 8 above 128) instead of choosing; 0 gives the
+    choice back."""
+    lib = load_library("gemm_tc")
+    _check(lib.tgo_gemm_tc_force_tile(c_int(rows), c_int(width)), "gemm_tc_force_tile",
+           f"(rows={rows}, width={width})")
 
 
 # ------------------------------------------------------------------ chains of products
