@@ -591,6 +591,57 @@ def test_gemm_tc_tile_shapes(rows, width, M):
     assert torch.allclose(gated.float(), act, rtol=2e-2, atol=2e-2 * float(act.abs().max()))
 
 
+@pytest.mark.parametrize("M,N,K,rows,width,parts", [
+    (300, 512, 2048, 128, 256, 4),      # 6 tiles, each cut four ways
+    (300, 512, 2048, 256, 128, 4),      # 8 tiles of two accumulators, cut four ways
+    (2100, 2600, 1024, 128, 256, 2),    # 187 tiles: a full round, then 39 tiles cut in two
+    (2100, 2600, 1024, 256, 256, 1),    # 99 tiles, fewer than SMs: no cut (148 / 99 < 2)
+    (2100, 2600, 1536, 256, 176, 1),    # 135 tiles: no cut
+    (1100, 2608, 1024, 256, 176, 1),    # 75 tiles: no cut
+    (700, 1008, 4096, 256, 240, 8),     # 15 tiles cut eight ways (a part has 8 k-blocks at least)
+    (520, 4000, 1280, 128, 112, 2)])    # 180 tiles: one round, the 32 left cut in two
+def test_gemm_tc_cut_last_round(M, N, K, rows, width, parts):
+    """The tiles of the last round, cut along K over the idle CTAs and joined through the
+    workspace: the same results as without the cut (up to the order of float32 sums), in
+    every output form, and again on a second launch (the flags went back to zero)."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=M)
+    w = rnd(N - N % 16, K, dtype=torch.bfloat16, scale=0.1, seed=width)
+    N = w.shape[0]
+    want = x.float() @ w.float().t()
+    h = rnd(M, N, seed=3)
+    wgu = interleave8(w[:N // 2], w[N // 2:]).contiguous()
+    got = {}
+    for cut in (False, True, True):
+        ops().gemm_tc_force_tile(rows, width, cut_last_round=cut)
+        try:
+            out = torch.zeros(M, N, dtype=torch.float32, device=DEV)
+            ops().gemm_tc(x, w, out, transpose=False)
+            h2 = h.clone()
+            ops().gemm_tc(x, w, h2, accumulate=True, transpose=False)
+            ob = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+            ops().gemm_tc(x, w, ob, transpose=False)
+            gated = torch.zeros(M, N // 2, dtype=torch.bfloat16, device=DEV)
+            ops().gemm_tc(x, wgu, gated, transpose=False, gated=True)
+            torch.cuda.synchronize()
+        finally:
+            ops().gemm_tc_force_tile(0, 0)
+        assert tc_flag() == 0
+        if torch.cuda.get_device_properties(0).multi_processor_count == 148:
+            assert ops().gemm_tc_last_plan() == (rows, width, parts if cut else 1)
+        assert torch.allclose(out, want, rtol=1e-4, atol=1e-3)
+        assert torch.allclose(h2, h + want, rtol=1e-4, atol=1e-3)
+        if cut in got:      # the second launch with the cut: bit for bit the first
+            for a, b in zip(got[cut], (out, h2, ob, gated)):
+                assert torch.equal(a, b)
+        got[cut] = (out, h2, ob, gated)
+    assert torch.allclose(got[True][0], got[False][0], rtol=1e-5, atol=1e-4)
+    assert torch.allclose(got[True][2].float(), got[False][2].float(), rtol=1e-2, atol=2e-2)
+    assert torch.allclose(got[True][3].float(), got[False][3].float(), rtol=2e-2,
+                          atol=2e-2 * float(got[False][3].float().abs().max()))
+    flags = ops()._tc_tail_buffers(DEV)[1]
+    assert int(flags.abs().sum().item()) == 0
+
+
 def test_linear_picks_by_rows_and_agrees():
     """1..8 rows: the weight-streaming kernel; from TC_MIN_ROWS rows: tcgen05; between them
     the library. The same product through each differs by bfloat16 rounding only."""

@@ -24,6 +24,15 @@
 // tiles and one shared B tile per k-block, and four more epilogue warps. Per product it
 // brings a third fewer operand bytes into the SM, which is what bounds a 128 x 256 tile.
 //
+// The last round. CTAs walk whole tiles in rounds of gridDim.x; what is left for the last,
+// partial round (or all there is, when there are fewer tiles than SMs) is cut along K over
+// the CTAs that would otherwise idle (`tail_splits` > 1): split 0 of a tile keeps its part in
+// its accumulator; the others write theirs as float32 into a workspace and count up the
+// tile's flag; split 0 waits for the count (with a time limit), adds the parts in split
+// order while it reads its accumulator, stores the tile and sets the flag back to zero. No
+// CTA waits before its own products are done, so the wait needs no co-residency. One
+// workspace per device: products of one device must not run at the same time.
+//
 // Tails: TMA fills out-of-range rows and K with zeros; stores are guarded. K % 8 == 0.
 // No cluster, no multicast. Every mbarrier wait gives up after about two seconds, records
 // where in *err and lets the CTA run to its end (TMEM is freed on every path).
@@ -223,7 +232,8 @@ template <int OMODE, bool TRANSPOSE, bool DUAL>
 __global__ void __launch_bounds__(DUAL ? TC_THREADS + 128 : TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                void* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out, int splits,
-               int kb_per_split, int* __restrict__ err, int BN) {
+               int kb_per_split, int* __restrict__ err, int BN, int tail_splits,
+               float* __restrict__ tail_ws, int* __restrict__ tail_flags) {
     // DUAL: a CTA's tile is 256 rows, two 128-row halves that share every B tile in shared
     // memory (a third fewer operand bytes per product: one SM cannot be fed the 48 KB that a
     // 128 x 256 tile wants every 512 tensor cycles); the two accumulators fill the 512
@@ -247,9 +257,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int tiles_m = (rows_a + ROWS - 1) / ROWS;
     const int tiles_n = (rows_b + BN - 1) / BN;
     const int n_tiles = tiles_m * tiles_n;
-    const int total = n_tiles * splits;
     const int per_group = TC_GROUP_M * tiles_n;
     const int kb_total = (K + TC_BK - 1) / TC_BK;
+    // whole tiles in full rounds, then the tiles of the last round cut tail_splits ways
+    const int whole = tail_splits > 1 ? n_tiles / (int)gridDim.x * (int)gridDim.x : n_tiles;
+    const int n_tail = n_tiles - whole;
+    const int total = tail_splits > 1 ? whole + n_tail * tail_splits : n_tiles * splits;
+    constexpr int EPI_WARPS = DUAL ? 8 : 4;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -268,15 +282,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
 
     // work item w -> (split, m0, n0, k-block range)
-    auto locate = [&](int w, int& split, int& m0, int& n0, int& kb_lo, int& n_kb) {
-        split = w / n_tiles;
-        const int tile = w % n_tiles;
+    // tail: -1, or which tile of the last round this is, `split` then being its part of K
+    auto locate = [&](int w, int& split, int& m0, int& n0, int& kb_lo, int& n_kb, int& tail) {
+        int tile, kb_hi;
+        if (tail_splits > 1 && w >= whole) {
+            tail = (w - whole) % n_tail;
+            split = (w - whole) / n_tail;
+            tile = whole + tail;
+            kb_lo = (int)((long long)split * kb_total / tail_splits);
+            kb_hi = (int)((long long)(split + 1) * kb_total / tail_splits);
+        } else {
+            tail = -1;
+            split = w / n_tiles;
+            tile = w % n_tiles;
+            kb_lo = split * kb_per_split;
+            kb_hi = kb_lo + kb_per_split < kb_total ? kb_lo + kb_per_split : kb_total;
+        }
         const int group = tile / per_group, within = tile % per_group;
         const int group_m = tiles_m - group * TC_GROUP_M < TC_GROUP_M ? tiles_m - group * TC_GROUP_M : TC_GROUP_M;
         m0 = (group * TC_GROUP_M + within % group_m) * ROWS;
         n0 = (within / group_m) * BN;
-        kb_lo = split * kb_per_split;
-        const int kb_hi = kb_lo + kb_per_split < kb_total ? kb_lo + kb_per_split : kb_total;
         n_kb = kb_hi > kb_lo ? kb_hi - kb_lo : 0;
     };
 
@@ -285,8 +310,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t it = 0;                                    // stage uses so far, over all tiles
             bool ok = true;
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
-                int split, m0, n0, kb_lo, n_kb;
-                locate(w, split, m0, n0, kb_lo, n_kb);
+                int split, m0, n0, kb_lo, n_kb, tail;
+                locate(w, split, m0, n0, kb_lo, n_kb, tail);
                 for (int i = 0; i < n_kb; ++i, ++it) {
                     const int s = it % STAGES;
                     ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, err, 1);
@@ -307,8 +332,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t it = 0, local = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++local) {
-                int split, m0, n0, kb_lo, n_kb;
-                locate(w, split, m0, n0, kb_lo, n_kb);
+                int split, m0, n0, kb_lo, n_kb, tail;
+                locate(w, split, m0, n0, kb_lo, n_kb, tail);
                 // two accumulators in turn, or (DUAL) the one pair there is
                 const uint32_t buf = DUAL ? 0u : (local & 1);
                 const uint32_t use = DUAL ? local : (local >> 1);
@@ -343,16 +368,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t local = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < total; w += gridDim.x, ++local) {
-            int split, m0, n0, kb_lo, n_kb;
-            locate(w, split, m0, n0, kb_lo, n_kb);
+            int split, m0, n0, kb_lo, n_kb, tail;
+            locate(w, split, m0, n0, kb_lo, n_kb, tail);
             const uint32_t buf = DUAL ? 0u : (local & 1);
             const uint32_t use = DUAL ? local : (local >> 1);
             if (ok) ok = mbar_wait(&acc_full[buf], use & 1, err, 3);
             tc_fence_after();
-#pragma unroll 1
+            const bool gathers = tail >= 0 && split == 0, gives = tail >= 0 && split > 0;
+            if (gathers && ok) {
+                // every epilogue warp of the tile's other parts has counted up
+                int seen = 0;
+                if (lane == 0) {
+                    const int want = (tail_splits - 1) * EPI_WARPS;
+                    const long long start = clock64();
+                    for (;;) {
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(tail_flags + tail) : "memory");
+                        if (seen >= want) break;
+                        if (clock64() - start > TC_WAIT_CYCLES) {
+                            if (err) atomicExch(err, 5);
+                            seen = -1;
+                            break;
+                        }
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, seen, 0) >= 0;
+            }
+            // a part of a tile: [tile of the last round][part - 1][group of 4 columns][row] as
+            // float4, so that the 32 lanes of a warp (32 rows) write and read 512 bytes in a row
+            float4* part = tail < 0 ? nullptr : (float4*)tail_ws + ((size_t)tail * (tail_splits - 1)) * ROWS * (BN / 4) + row;
             // a tile that is not a multiple of 32 wide: its last group of columns is cut at the
             // tile's edge (what lies beyond belongs to the next tile)
             const int n_edge = n0 + BN < rows_b ? n0 + BN : rows_b;
+#pragma unroll 1
             for (int c = 0; c < (BN + 31) / 32; ++c) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * ACC_COLS + (uint32_t)(half * 256) + (uint32_t)(c * 32);
@@ -367,6 +414,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                       "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                     : "r"(taddr));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int cols = BN - c * 32 < 32 ? BN - c * 32 : 32;        // 32 or 16
+                if (gives) {
+                    float4* dst = part + ((size_t)(split - 1) * (BN / 4) + c * 8) * ROWS;
+#pragma unroll
+                    for (int v = 0; v < 8; ++v)
+                        if (4 * v < cols)
+                            dst[(size_t)v * ROWS] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                 __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                    continue;
+                }
+                if (gathers && ok) {
+                    for (int p = 0; p < tail_splits - 1; ++p) {
+                        const float4* src = part + ((size_t)p * (BN / 4) + c * 8) * ROWS;
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            if (4 * v < cols) {
+                                const float4 y = __ldcg(src + (size_t)v * ROWS);    // written by another SM: not through L1
+                                r[4 * v] = __float_as_uint(__uint_as_float(r[4 * v]) + y.x);
+                                r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + y.y);
+                                r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) + y.z);
+                                r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) + y.w);
+                            }
+                    }
+                }
                 if (ok && n_kb > 0)
                     tc_store<OMODE, TRANSPOSE>(r, out, m0 + row, n0 + c * 32, rows_a, n_edge, ld_out, split);
             }
@@ -374,6 +445,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (gives) {
+                // this warp's rows of the part are written: make them visible, then count
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicAdd(tail_flags + tail, 1);
+            }
+            if (gathers) {
+                // all epilogue warps have seen the count: the flag goes back to zero for the
+                // next launch
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+                if (warp == 2 && lane == 0) tail_flags[tail] = 0;
+            }
         }
     }
     tc_fence_before();
@@ -456,9 +539,20 @@ static int make_map_uncached(CUtensorMap* map, const void* ptr, int rows, int K,
     return r == CUDA_SUCCESS ? 0 : 2000 + (int)r;
 }
 
+static int tc_sms() {
+    int dev = 0;
+    static int cached[64] = {};
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+        if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+        if (cached[dev] > 0) return cached[dev];
+    }
+    return 148;
+}
+
 template <int OMODE, bool TRANSPOSE, bool DUAL>
 static int tc_launch(int BN, const CUtensorMap& ma, const CUtensorMap& mb, void* out, int rows_a, int rows_b, int K,
-                     long long ld_out, int splits, int kb_per_split, int* err, cudaStream_t stream) {
+                     long long ld_out, int splits, int kb_per_split, int* err, cudaStream_t stream,
+                     int tail_splits, float* tail_ws, int* tail_flags) {
     auto kern = gemm_tc_kernel<OMODE, TRANSPOSE, DUAL>;
     const size_t smem = TC_SMEM_TOTAL;
     static bool sized = false;            // per instance of this template
@@ -468,44 +562,67 @@ static int tc_launch(int BN, const CUtensorMap& ma, const CUtensorMap& mb, void*
         sized = true;
     }
     const int total = ((rows_b + BN - 1) / BN) * ((rows_a + (DUAL ? 2 : 1) * TC_BM - 1) / ((DUAL ? 2 : 1) * TC_BM)) * splits;
-    int sms = 148;
-    {
-        int dev = 0;
-        static int cached[64] = {};
-        if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
-            if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
-            if (cached[dev] > 0) sms = cached[dev];
-        }
-    }
-    const dim3 grid(total < sms ? total : sms);
-    kern<<<grid, DUAL ? TC_THREADS + 128 : TC_THREADS, smem, stream>>>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, BN);
+    const int sms = tc_sms();
+    // with a cut last round the kernel derives the rounds from the grid: it has to be `sms`
+    const dim3 grid(tail_splits > 1 ? tc_sms() : total < sms ? total : sms);
+    kern<<<grid, DUAL ? TC_THREADS + 128 : TC_THREADS, smem, stream>>>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, BN,
+                                                                       tail_splits, tail_ws, tail_flags);
     return launch_status();
 }
 
 template <bool TRANSPOSE, bool DUAL = false>
 static int tc_dispatch(int BN, const CUtensorMap& ma, const CUtensorMap& mb, void* out, int rows_a, int rows_b, int K,
-                       long long ld_out, int omode, int splits, int kb_per_split, int* err, cudaStream_t s) {
+                       long long ld_out, int omode, int splits, int kb_per_split, int* err, cudaStream_t s,
+                       int tail_splits = 1, float* tail_ws = nullptr, int* tail_flags = nullptr) {
+#define TC_CASE(mode) \
+    return tc_launch<mode, TRANSPOSE, DUAL>(BN, ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s, \
+                                            tail_splits, tail_ws, tail_flags)
     switch (omode) {
-        case TC_OUT_BF16: return tc_launch<TC_OUT_BF16, TRANSPOSE, DUAL>(BN, ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
-        case TC_OUT_F32: return tc_launch<TC_OUT_F32, TRANSPOSE, DUAL>(BN, ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
-        case TC_OUT_ADD_F32: return tc_launch<TC_OUT_ADD_F32, TRANSPOSE, DUAL>(BN, ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
-        case TC_OUT_SWIGLU: return tc_launch<TC_OUT_SWIGLU, TRANSPOSE, DUAL>(BN, ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
-        default: return tc_launch<TC_OUT_PARTIAL, TRANSPOSE, DUAL>(BN, ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s);
+        case TC_OUT_BF16: TC_CASE(TC_OUT_BF16);
+        case TC_OUT_F32: TC_CASE(TC_OUT_F32);
+        case TC_OUT_ADD_F32: TC_CASE(TC_OUT_ADD_F32);
+        case TC_OUT_SWIGLU: TC_CASE(TC_OUT_SWIGLU);
+        default: TC_CASE(TC_OUT_PARTIAL);
     }
+#undef TC_CASE
 }
 
 // For tests and tuning: the tile of the non-transposed product is rows x width instead of
 // the cost model's choice (rows 128 or 256; 0 gives the choice back). The width has to be
-// one the instruction takes with 128 rows: a multiple of 16 from 16 to 256. Not for use
-// while other threads launch products.
-static int g_forced_rows = 0, g_forced_width = 0;
-TGO_API int tgo_gemm_tc_force_tile(int rows, int width) {
+// one the instruction takes with 128 rows: a multiple of 16 from 16 to 256. tail: 0 leaves
+// the cut of the last round to the shape, 1 forbids it. Not for use while other threads
+// launch products.
+static int g_forced_rows = 0, g_forced_width = 0, g_forced_tail = 0;
+TGO_API int tgo_gemm_tc_force_tile(int rows, int width, int tail) {
+    g_forced_tail = tail;
     if (rows == 0) { g_forced_rows = g_forced_width = 0; return 0; }
     if ((rows != 128 && rows != 256) || width < 16 || width > 256 || width % 16)
         return TGO_E_BAD_ARG;
     g_forced_rows = rows;
     g_forced_width = width;
     return 0;
+}
+
+// What the last non-transposed product ran as: rows and width of its tiles and the number
+// of parts its last round's tiles were cut into.
+static int g_last_rows = 0, g_last_width = 0, g_last_cut = 0;
+TGO_API void tgo_gemm_tc_last_plan(int* rows, int* width, int* cut) {
+    *rows = g_last_rows; *width = g_last_width; *cut = g_last_cut;
+}
+
+#define TC_TAIL_MIN_KB 8        // k-blocks a part of a cut tile has at least
+// Floats of workspace and flags that a cut last round may use: every CTA but one writes a
+// part of the largest tile.
+TGO_API long long tgo_gemm_tc_tail_floats() { return (long long)(tc_sms() - 1) * 2 * TC_BM * 256; }
+TGO_API int tgo_gemm_tc_tail_flags() { return tc_sms(); }
+
+// How many ways the tiles of the last round are cut along K (1: not at all).
+static int tc_tail_splits(long long tiles, int kb_total, int sms) {
+    const int left = (int)(tiles % sms);
+    if (!left) return 1;
+    int s = sms / left;
+    if (s > kb_total / TC_TAIL_MIN_KB) s = kb_total / TC_TAIL_MIN_KB;
+    return s < 2 ? 1 : s;
 }
 
 // out[M, N] (row-major, leading dimension N) = x[M, K] . w[N, K]^T.
@@ -515,9 +632,13 @@ TGO_API int tgo_gemm_tc_force_tile(int rows, int width) {
 // omode: 0 bfloat16, 1 float32, 2 add into float32, 4 w is a gate/up matrix with rows
 // interleaved in eights and out is silu(gate) * up, bfloat16 [M, N / 2] (no splits).
 // splits > 1: K is cut; `workspace` must hold splits * M * N floats.
+// tail_ws, tail_flags: tgo_gemm_tc_tail_floats() floats and tgo_gemm_tc_tail_flags() zeroed
+// ints of this device for the cut of the last round (transpose == 0, splits == 1); without
+// them the last round is not cut. The kernel leaves the flags zero.
 // err: one int on the device that a timed-out wait sets.
 TGO_API int tgo_gemm_tc(const void* x, const void* w, void* out, int M, int N, int K, int omode,
-                        int transpose, int splits, float* workspace, int* err, cudaStream_t stream) {
+                        int transpose, int splits, float* workspace, float* tail_ws, int* tail_flags,
+                        int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || omode < 0 || omode == TC_OUT_PARTIAL || omode > TC_OUT_SWIGLU || splits < 1 ||
         (splits > 1 && (!workspace || omode == TC_OUT_SWIGLU)) || (omode == TC_OUT_SWIGLU && N % 16) ||
@@ -534,16 +655,17 @@ TGO_API int tgo_gemm_tc(const void* x, const void* w, void* out, int M, int N, i
     int rc;
     if (!transpose) {
         // Tile shape. The CTAs walk the tiles in rounds, and a round lasts as long as a whole
-        // tile however few tiles it has. A k-block of a tile costs the larger of its products
-        // (2 cycles a column for 128 rows) and of bringing its operands in (an SM is fed about
-        // 70 bytes a cycle: measured, a 128 x 256 tile's 48 KB keep the tensor pipe at 73 %).
-        // A tile of 256 rows (two accumulators over one B tile) needs a third fewer bytes per
-        // product. Among 128 or 256 rows and widths in multiples of 32 (the kernel takes
-        // multiples of 16, but a sweep over twelve products of three model sizes at 512 to
-        // 4096 rows found the widths between to cost as much as the next multiple of 32 or
-        // more), the cheapest by this count wins: it was 1.2 % behind
-        // the sweep's best shape on average, 9 % at worst. 4096 columns under 2048 rows run
-        // as 128 tiles of 256 x 256 in one round.
+        // tile however few tiles it has, unless it is the last and its tiles are cut along K.
+        // A k-block of a tile costs the larger of its products (2 cycles a column for 128
+        // rows) and of bringing its operands in (an SM is fed about 70 bytes a cycle:
+        // measured, a 128 x 256 tile's 48 KB keep the tensor pipe at 73 %). A tile of 256
+        // rows (two accumulators over one B tile) needs a third fewer bytes per product.
+        // Among 128 or 256 rows and widths in multiples of 32 (the kernel takes multiples of
+        // 16, but a sweep over twelve products of three model sizes at 512 to 4096 rows found
+        // the widths between to cost as much as the next multiple of 32 or more), the
+        // cheapest by this count wins.
+        const int sms = tc_sms();
+        const bool may_cut = splits == 1 && tail_ws && tail_flags && g_forced_tail != 1;
         int bn = N >= 256 ? 256 : 128;
         bool dual = false;
         if (g_forced_rows && om != TC_OUT_PARTIAL) {
@@ -558,18 +680,28 @@ TGO_API int tgo_gemm_tc(const void* x, const void* w, void* out, int M, int N, i
                     const long long tiles = tiles_m * ((N + width - 1) / width);
                     const double math = 2.0 * width * (rows / 128);
                     const double feed = ((rows / 128) * 16384.0 + 128.0 * width) / 70.0;
+                    const double per_kb = math > feed ? math : feed;
                     // + the epilogue, which a 256-row tile cannot hide behind the next tile
-                    const double per_tile = (math > feed ? math : feed) * ((K + 63) / 64) +
-                                            (rows == 256 ? 12.0 * width : 0.0) + 2000.0;
-                    const double cost = (double)((tiles + 147) / 148) * per_tile;
+                    const double fixed = (rows == 256 ? 12.0 * width : 0.0) + 2000.0;
+                    const int cut = may_cut ? tc_tail_splits(tiles, kb_total, sms) : 1;
+                    double cost;
+                    if (cut > 1)        // + the parts' way through the workspace: written, waited for,
+                                        // read (fitted to measured differences between cut and uncut)
+                        cost = (double)(tiles / sms) * (per_kb * kb_total + fixed) +
+                               per_kb * ((kb_total + cut - 1) / cut) + fixed + cut * rows * width * 4.0 / 35.0 + 8000.0;
+                    else
+                        cost = (double)((tiles + sms - 1) / sms) * (per_kb * kb_total + fixed);
                     if (best < 0 || cost < best) { best = cost; bn = width; dual = rows == 256; }
                 }
             }
         }
+        const long long tiles = (long long)((M + (dual ? 2 : 1) * TC_BM - 1) / ((dual ? 2 : 1) * TC_BM)) * ((N + bn - 1) / bn);
+        const int cut = may_cut && om != TC_OUT_PARTIAL ? tc_tail_splits(tiles, kb_total, sms) : 1;
+        g_last_rows = dual ? 256 : 128; g_last_width = bn; g_last_cut = cut;
         if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
         if ((rc = make_map(&mb, w, N, K, bn))) return rc;
-        rc = dual ? tc_dispatch<false, true>(bn, ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream)
-                  : tc_dispatch<false, false>(bn, ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream);
+        rc = dual ? tc_dispatch<false, true>(bn, ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream, cut, tail_ws, tail_flags)
+                  : tc_dispatch<false, false>(bn, ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream, cut, tail_ws, tail_flags);
     } else {
         if (M > 256) return TGO_E_BAD_ARG;
         const int bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;

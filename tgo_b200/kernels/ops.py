@@ -753,6 +753,25 @@ def gemm_tc_error_flag(device) -> torch.Tensor:
     return _tc_err[key]
 
 
+_tc_tail = {}
+
+
+def _tc_tail_buffers(device):
+    """Per device: the float32 workspace and the zeroed flags through which the CTAs of a
+    product's last round hand each other their parts of a tile (made at first use, outside
+    any stream capture: the engine's first steps run uncaptured). One product at a time
+    per device may use them."""
+    key = torch.device(device).index or 0
+    if key not in _tc_tail:
+        lib = load_library("gemm_tc")
+        lib.tgo_gemm_tc_tail_floats.restype = ctypes.c_longlong
+        with torch.cuda.device(device):
+            n, f = int(lib.tgo_gemm_tc_tail_floats()), int(lib.tgo_gemm_tc_tail_flags())
+        _tc_tail[key] = (torch.empty(n, dtype=torch.float32, device=device),
+                         torch.zeros(f, dtype=torch.int32, device=device))
+    return _tc_tail[key]
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
             transpose: Optional[bool] = None, splits: int = 1, gated: bool = False) -> None:
     """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, float32
@@ -781,19 +800,29 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
         transpose = M <= 64
     ws = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
     lib = load_library("gemm_tc")
+    tail_ws, tail_flags = (None, None) if transpose or splits > 1 else _tc_tail_buffers(x.device)
     _check(lib.tgo_gemm_tc(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_int(omode),
-                           c_int(1 if transpose else 0), c_int(splits), _ptr(ws),
-                           _ptr(gemm_tc_error_flag(x.device)), _stream()), "gemm_tc",
+                           c_int(1 if transpose else 0), c_int(splits), _ptr(ws), _ptr(tail_ws),
+                           _ptr(tail_flags), _ptr(gemm_tc_error_flag(x.device)), _stream()), "gemm_tc",
            f"(M={M}, N={N}, K={K})")
 
 
-def gemm_tc_force_tile(rows: int = 0, width: int = 0) -> None:
+def gemm_tc_force_tile(rows: int = 0, width: int = 0, cut_last_round: bool = True) -> None:
     """For tests and tuning: `gemm_tc` (not transposed) runs tiles of rows x width (rows 128
-    or 256; width a multiple of 16, or of 8 above 128) instead of choosing; 0 gives the
-    choice back."""
+    or 256; width a multiple of 16 up to 256) instead of choosing; 0 gives the choice back.
+    cut_last_round False: the tiles of the last round are not cut along K."""
     lib = load_library("gemm_tc")
-    _check(lib.tgo_gemm_tc_force_tile(c_int(rows), c_int(width)), "gemm_tc_force_tile",
-           f"(rows={rows}, width={width})")
+    _check(lib.tgo_gemm_tc_force_tile(c_int(rows), c_int(width), c_int(0 if cut_last_round else 1)),
+           "gemm_tc_force_tile", f"(rows={rows}, width={width})")
+
+
+def gemm_tc_last_plan() -> tuple:
+    """(rows, width, parts) of the last non-transposed `gemm_tc`: its tile and into how many
+    parts along K the tiles of its last round were cut (1: not cut)."""
+    lib = load_library("gemm_tc")
+    r, w, c = c_int(0), c_int(0), c_int(0)
+    lib.tgo_gemm_tc_last_plan(ctypes.byref(r), ctypes.byref(w), ctypes.byref(c))
+    return r.value, w.value, c.value
 
 
 # ------------------------------------------------------------------ chains of products
