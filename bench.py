@@ -166,6 +166,110 @@ def serve_workload(model, config, shape):
     return 0
 
 
+def exactness_check(config, seed, shape):
+    """Logits at real layer sizes under different ways of cutting the work. Three requests
+    (777, 300 and 65 prompt tokens, then 8 given tokens each) run (a) each alone, the prompt
+    in one step and the rest token by token; (b) together, at most two live at a time in a
+    pool that holds just those two, the prompts in portions of changing size (down to two
+    tokens) beside the single tokens of the others, the third request in pages the second
+    gave back. Both in true float32 and in bfloat16, with the same seeded weights. Compared:
+    float32 (b) with float32 (a); bfloat16 (a) and (b) with float32 (a), against the bound
+    the tests use for bfloat16 (activations rounded to 8 bits about six times a layer, a
+    random walk: 4 * sqrt(6 L + 2) * 2^-9 times the largest logit)."""
+    import math
+
+    import numpy as np
+    import torch
+
+    import tgo_b200
+    from tgo_b200.engine.measure import round_up
+    from tgo_b200.engine.step import Engine, StepEntry
+    V, L = config["vocab_size"], config["num_hidden_layers"]
+    rng = np.random.default_rng(5)
+    lens, extra, tail = [777, 300, 65], 8, 24
+    toks = [rng.integers(0, V, n + extra).tolist() for n in lens]
+
+    def alone(model):
+        eng = Engine(model, page_size=PAGE, max_tokens=round_up(max(lens) + extra, 64), num_slots=1)
+        out = []
+        for rid, (n, t) in enumerate(zip(lens, toks)):
+            eng.admit(rid)
+            rows = [eng.step([StepEntry(rid, t[:n], list(range(n - tail, n)))]).float().cpu()]
+            for j in range(extra):      # a step's logits are only good until the next step
+                rows.append(eng.step([StepEntry(rid, [t[n + j]], [0])]).float().cpu())
+            eng.finish(rid)
+            out.append(torch.cat(rows))
+        eng.check_kernels()
+        return out
+
+    def together(model):
+        eng = Engine(model, page_size=PAGE, num_slots=2,
+                     max_tokens=round_up(lens[0] + extra, 64) + round_up(lens[1] + extra, 64))
+        sizes = [129, 2, 300, 64, 33, 500, 7]
+        fed, turn, rows = [0, 0, 0], [0, 1, 2], [[], [], []]
+        live, waiting = [0, 1], [2]
+        for rid in live:
+            eng.admit(rid)
+        while live:
+            entries, owners = [], []
+            for rid in live:
+                n, t, at = lens[rid], toks[rid], fed[rid]
+                if at < n:
+                    k = min(sizes[turn[rid] % len(sizes)], n - at)
+                    turn[rid] += 1
+                    want = [p - at for p in range(max(at, n - tail), at + k) if p < n]
+                else:
+                    k, want = 1, [0]
+                entries.append(StepEntry(rid, t[at:at + k], want))
+                owners += [rid] * len(want)
+                fed[rid] = at + k
+            logits = eng.step(entries).float().cpu()
+            for row, rid in zip(logits, owners):
+                rows[rid].append(row)
+            for rid in list(live):
+                if fed[rid] == lens[rid] + extra:
+                    eng.finish(rid)
+                    live.remove(rid)
+                    if waiting:
+                        nxt = waiting.pop(0)
+                        eng.admit(nxt)
+                        live.append(nxt)
+        eng.check_kernels()
+        return [torch.stack(r) for r in rows]
+
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        model = tgo_b200.open_random(config, seed=seed, dtype=dtype, sigma=0.02, gain_sigma=0.05)
+        got[dtype] = (alone(model.model), together(model.model))
+        del model
+        torch.cuda.empty_cache()
+    ref = got["float32"][0]
+    scale = max(float(r.abs().max()) for r in ref)
+    rms = math.sqrt(sum(float((r.double() ** 2).sum()) for r in ref) / sum(r.numel() for r in ref))
+
+    def worst(a, b):
+        return max(float((x.double() - y.double()).abs().max()) for x, y in zip(a, b))
+
+    def top1(a, b):
+        same = sum(int((x.argmax(-1) == y.argmax(-1)).sum()) for x, y in zip(a, b))
+        return same / sum(x.shape[0] for x in a)
+    bound_bf16 = 4 * math.sqrt(6 * L + 2) * 2.0 ** -9 * max(scale, 1.0)
+    bound_f32 = 8 * (2 * L + 1) * math.sqrt(config["hidden_size"]) * 2.0 ** -24 * 10 * max(scale, 1.0)
+    line = {"only": "check", "shape": shape, "layers": L, "positions": sum(r.shape[0] for r in ref),
+            "vocab": V, "largest_logit": round(scale, 4), "logit_rms": round(rms, 4),
+            "float32_cut_vs_alone_max_abs": worst(got["float32"][1], ref), "float32_bound": bound_f32,
+            "bfloat16_alone_vs_float32_max_abs": round(worst(got["bfloat16"][0], ref), 5),
+            "bfloat16_cut_vs_float32_max_abs": round(worst(got["bfloat16"][1], ref), 5),
+            "bfloat16_cut_vs_alone_max_abs": round(worst(got["bfloat16"][1], got["bfloat16"][0]), 5),
+            "bfloat16_bound": round(bound_bf16, 5),
+            "bfloat16_top1_agrees_with_float32": round(top1(got["bfloat16"][1], ref), 4)}
+    line["ok"] = bool(line["float32_cut_vs_alone_max_abs"] <= bound_f32 and
+                      line["bfloat16_alone_vs_float32_max_abs"] <= bound_bf16 and
+                      line["bfloat16_cut_vs_float32_max_abs"] <= bound_bf16)
+    print(json.dumps(line))
+    return 0 if line["ok"] else 1
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -178,9 +282,12 @@ def main():
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
                     help="with --only: the 14B or 32B shape of the baseline record instead of the 8B one")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="with --only decode: prompt length")
-    ap.add_argument("--only", default="", choices=["", "prefill", "decode", "serve"],
-                    help="profiling aid: run just the 2,048-token prefill, or just the decode "
-                         "steps, and print a short line instead of the contract line")
+    ap.add_argument("--only", default="", choices=["", "prefill", "decode", "serve", "check"],
+                    help="run just the 2,048-token prefill, just the decode steps, the "
+                         "continuous-batching workload, or the exactness check at real layer "
+                         "sizes (float32 against bfloat16, alone against cut and mixed; 4 layers "
+                         "unless --layers says otherwise), and print a short line instead of "
+                         "the contract line")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -200,6 +307,10 @@ def main():
     config, seed = dict(SHAPES[args.shape][0]), SHAPES[args.shape][1]
     if args.layers:
         config["num_hidden_layers"] = args.layers
+    if args.only == "check":
+        if not args.layers:
+            config["num_hidden_layers"] = 4
+        return exactness_check(config, seed, args.shape)
     model = tgo_b200.open_random(config, seed=seed, dtype="bfloat16", sigma=0.02, gain_sigma=0.05)
     peaks = load_peaks()
     if args.only == "prefill":

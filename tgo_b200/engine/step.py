@@ -248,7 +248,9 @@ class Engine:
 
     def step(self, entries: List[StepEntry]) -> torch.Tensor:
         """Run one batch; returns logits [number of wanted places, vocab], float32, on the
-        device, in the order of the entries and of their `want`."""
+        device, in the order of the entries and of their `want`. The tensor is good until
+        the next step: a step replayed from a CUDA graph writes its logits where the last
+        replay of that graph did. Copy it (`.clone()`, `.cpu()`) to keep it longer."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         if not entries:
             raise ValueError("step: an empty batch carries nothing")
