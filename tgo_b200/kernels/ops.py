@@ -627,23 +627,23 @@ def _splits_for(pairs: int, reach: int, window: int, ctas_per_sm: int = 3) -> in
     tiles = max(1, (reach + 63) // 64 + (1 if window > 0 else 0))
     pairs = max(1, pairs)
     wave = NUM_SMS * ctas_per_sm
-    if pairs >= wave:
-        s = 1
-    elif 4 * pairs >= 3 * wave:
-        s = 2
-    elif 2 * pairs >= wave:
-        s = 3
-    else:
-        s = -(-wave // pairs)
-    return max(1, min(s, tiles // 2, 64))
+    best, best_cost = 1, None
+    for s in range(1, max(1, min(tiles // 2, 64)) + 1):
+        rounds = -(-pairs * s // wave)
+        cost = rounds * (tiles / s * 1.0 + 5.0) + (10.0 if s > 1 else 0.0)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 def decode_splits(ctx, num_kv_heads: int, window: int, ctas_per_sm: int = 3) -> int:
-    """How many CTAs share one request's keys in a decode step. Few (request, kv head) pairs:
-    as many splits as fill the GPU once (measured: one full wave beats more, shorter CTAs),
-    each with at least two 64-key tiles. Pairs that fill half the GPU or more are cut less
-    (measured on B200 with 8 kv heads and 1088 keys: batch 32 best in 3, batch 64 best whole:
-    a CTA that walks a request's keys alone pays its start once)."""
+    """How many CTAs share one request's keys in a decode step: the count that is cheapest by
+    a small model fitted on B200 (8 kv heads, contexts of 1024 and 4096, batches 8 to 128):
+    the CTAs run in rounds of as many as the GPU holds, a CTA costs 1 unit per 64-key tile
+    and 5 to start, joining the splits costs 10 once. So a few requests are cut until they
+    fill the GPU once (batch 8: 7 ways), 32 or 64 requests of 1024 keys are not cut (the
+    start is paid once), and 64 requests of 4096 keys are cut in 3 or 4, because the second,
+    nearly empty round of whole requests would cost a whole request's time."""
     reach = min(ctx.max_context, window) if window > 0 else ctx.max_context
     return _splits_for(ctx.num_seqs * num_kv_heads, reach, window, ctas_per_sm)
 
