@@ -312,15 +312,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
                 int split, m0, n0, kb_lo, n_kb, tail;
                 locate(w, split, m0, n0, kb_lo, n_kb, tail);
+                // Decode orientation: A is the weight matrix, read once from DRAM, and its row
+                // pitch is often a power of two, so CTAs that all walk K from the same end
+                // keep hitting the same few memory channels together (measured: the busiest
+                // channel carried twice the traffic of the idlest). Each tile starts its walk
+                // somewhere else; the sum over k takes another order, fixed per tile.
+                const int rot = TRANSPOSE && n_kb > 1 ? (int)(((unsigned)(m0 / TC_BM) * 13u + (unsigned)split * 5u) % (unsigned)n_kb) : 0;
                 for (int i = 0; i < n_kb; ++i, ++it) {
                     const int s = it % STAGES;
                     ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, err, 1);
                     if (!ok) break;
                     mbar_expect_tx(&full[s], (uint32_t)STAGE);
                     unsigned char* st = base + (size_t)s * STAGE;
-                    tma_load_2d(st, &map_a, (kb_lo + i) * TC_BK, m0, &full[s]);
-                    if (DUAL) tma_load_2d(st + TC_A_BYTES, &map_a, (kb_lo + i) * TC_BK, m0 + TC_BM, &full[s]);
-                    tma_load_2d(st + (DUAL ? 2 : 1) * TC_A_BYTES, &map_b, (kb_lo + i) * TC_BK, n0, &full[s]);
+                    const int kb = kb_lo + (i + rot < n_kb ? i + rot : i + rot - n_kb);
+                    tma_load_2d(st, &map_a, kb * TC_BK, m0, &full[s]);
+                    if (DUAL) tma_load_2d(st + TC_A_BYTES, &map_a, kb * TC_BK, m0 + TC_BM, &full[s]);
+                    tma_load_2d(st + (DUAL ? 2 : 1) * TC_A_BYTES, &map_b, kb * TC_BK, n0, &full[s]);
                 }
             }
         }
@@ -633,8 +640,8 @@ static int tc_tail_splits(long long tiles, int kb_total, int sms) {
 // interleaved in eights and out is silu(gate) * up, bfloat16 [M, N / 2] (no splits).
 // splits > 1: K is cut; `workspace` must hold splits * M * N floats.
 // tail_ws, tail_flags: tgo_gemm_tc_tail_floats() floats and tgo_gemm_tc_tail_flags() zeroed
-// ints of this device for the cut of the last round (transpose == 0, splits == 1); without
-// them the last round is not cut. The kernel leaves the flags zero.
+// ints of this device for the cut of the last round (splits == 1); without them the last
+// round is not cut. The kernel leaves the flags zero.
 // err: one int on the device that a timed-out wait sets.
 TGO_API int tgo_gemm_tc(const void* x, const void* w, void* out, int M, int N, int K, int omode,
                         int transpose, int splits, float* workspace, float* tail_ws, int* tail_flags,
@@ -705,10 +712,14 @@ TGO_API int tgo_gemm_tc(const void* x, const void* w, void* out, int M, int N, i
     } else {
         if (M > 256) return TGO_E_BAD_ARG;
         const int bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+        // the 128-row tiles of the weight matrix seldom fill the SMs a whole number of times
+        // (192 tiles of a gate/up matrix: a round and 44): the last round is cut along K
+        const bool may_cut = splits == 1 && tail_ws && tail_flags && g_forced_tail != 1;
+        const int cut = may_cut ? tc_tail_splits((N + TC_BM - 1) / TC_BM, kb_total, tc_sms()) : 1;
         if ((rc = make_map(&ma, w, N, K, TC_BM))) return rc;
         if ((rc = make_map(&mb, x, M, K, bn))) return rc;
         // A = w (N rows), B = x (M rows); D^T is stored: out[m, n], leading dimension N
-        rc = tc_dispatch<true>(bn, ma, mb, dst, N, M, K, ld, om, splits, kb_per_split, err, stream);
+        rc = tc_dispatch<true>(bn, ma, mb, dst, N, M, K, ld, om, splits, kb_per_split, err, stream, cut, tail_ws, tail_flags);
     }
     if (rc || splits == 1) return rc;
     const long long n = (long long)M * N;

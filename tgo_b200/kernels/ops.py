@@ -800,7 +800,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
         transpose = M <= 64
     ws = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
     lib = load_library("gemm_tc")
-    tail_ws, tail_flags = (None, None) if transpose or splits > 1 else _tc_tail_buffers(x.device)
+    tail_ws, tail_flags = (None, None) if splits > 1 else _tc_tail_buffers(x.device)
     _check(lib.tgo_gemm_tc(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_int(omode),
                            c_int(1 if transpose else 0), c_int(splits), _ptr(ws), _ptr(tail_ws),
                            _ptr(tail_flags), _ptr(gemm_tc_error_flag(x.device)), _stream()), "gemm_tc",
