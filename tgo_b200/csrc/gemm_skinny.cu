@@ -9,7 +9,7 @@
 // multiplies the other; the sets are small enough (80 registers a thread) for three CTAs on
 // an SM. MEASURED on B200, Qwen3-8B layer shapes at 8 rows, the four products of a layer:
 // one set of 8 loads, 92 us; two sets of 8 (110 registers, two CTAs), 100 us; two sets of 4,
-// 83 us; 16 warps a CTA for the narrow matrices, 89 us; W through TMA boxes of 16 rows x 128
+// 83 us (and 82 with sets of 8 for the matrices of 4096 rows only: see gs_launch); 16 warps a CTA for the narrow matrices, 89 us; W through TMA boxes of 16 rows x 128
 // bytes into per-warp rings, 92-121 us (the vocabulary product fell from 5.8 to 3.2 TB/s). Both operands go from global memory straight into fragments with
 // 16-byte loads: the sum over k may run in any order as long as W and x agree on it, so a
 // thread's eight consecutive k values serve as the (2t, 2t+1) and (2t+8, 2t+9) pairs of two
@@ -25,7 +25,10 @@
 #include "common.cuh"
 
 #ifndef GS_UNROLL
-#define GS_UNROLL 2
+#define GS_UNROLL 2             // 16-byte loads per row half in one register set
+#endif
+#ifndef GS_NARROW_UNROLL
+#define GS_NARROW_UNROLL 4      // the same for a matrix with too few rows to fill the GPU
 #endif
 
 #define GS_X_BF16 0
@@ -70,7 +73,7 @@ __device__ __forceinline__ uint4 load_x(const void* __restrict__ x, const float*
     return z;
 }
 
-template <int MT, int XMODE, int OMODE, int GS_WARPS>
+template <int MT, int XMODE, int OMODE, int GS_WARPS, int UNROLL>
 __global__ void __launch_bounds__(GS_WARPS * 32)
 gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, float eps,
                    const bf16* __restrict__ w, void* __restrict__ y, int M, int N, int K) {
@@ -87,26 +90,26 @@ gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, f
     const bf16* w_lo = w + (size_t)(row_lo < N ? row_lo : 0) * K;
     const bf16* w_hi = w + (size_t)(row_hi < N ? row_hi : 0) * K;
     const bool ok_lo = row_lo < N, ok_hi = row_hi < N;
-    constexpr int STEP = 32 * GS_UNROLL;
+    constexpr int STEP = 32 * UNROLL;
 
     float acc[MT][4];
     float ss[MT];
 #pragma unroll
     for (int j = 0; j < MT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; ss[j] = 0.f; }
 
-    uint4 a_lo[GS_UNROLL], a_hi[GS_UNROLL], b_lo[GS_UNROLL], b_hi[GS_UNROLL];
-    auto load_w = [&](uint4 (&lo)[GS_UNROLL], uint4 (&hi)[GS_UNROLL], int k) {
+    uint4 a_lo[UNROLL], a_hi[UNROLL], b_lo[UNROLL], b_hi[UNROLL];
+    auto load_w = [&](uint4 (&lo)[UNROLL], uint4 (&hi)[UNROLL], int k) {
 #pragma unroll
-        for (int u = 0; u < GS_UNROLL; ++u) {
+        for (int u = 0; u < UNROLL; ++u) {
             const int kk = k + u * 32 + 8 * t;
             const bool v = kk < k_end;
             lo[u] = (v && ok_lo) ? ldg_stream(w_lo + kk) : make_uint4(0u, 0u, 0u, 0u);
             hi[u] = (v && ok_hi) ? ldg_stream(w_hi + kk) : make_uint4(0u, 0u, 0u, 0u);
         }
     };
-    auto multiply = [&](const uint4 (&lo)[GS_UNROLL], const uint4 (&hi)[GS_UNROLL], int k) {
+    auto multiply = [&](const uint4 (&lo)[UNROLL], const uint4 (&hi)[UNROLL], int k) {
 #pragma unroll
-        for (int u = 0; u < GS_UNROLL; ++u) {
+        for (int u = 0; u < UNROLL; ++u) {
             const int kk = k + u * 32 + 8 * t;
             const bool v = kk < k_end;
 #pragma unroll
@@ -190,31 +193,48 @@ gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, f
     }
 }
 
-template <int MT, int XMODE, int WARPS>
+template <int MT, int XMODE, int WARPS, int UNROLL>
 static int gs_launch_o(const void* x, const float* gain, float eps, const bf16* w, void* y, int M,
                        int N, int K, int omode, cudaStream_t s) {
     const dim3 grid((N + 15) / 16), block(WARPS * 32);
     switch (omode) {
         case GS_OUT_BF16:
-            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_BF16, WARPS>, grid, block, 0,
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_BF16, WARPS, UNROLL>, grid, block, 0,
                                   s, x, gain, eps, w, y, M, N, K);
         case GS_OUT_F32:
-            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_F32, WARPS>, grid, block, 0,
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_F32, WARPS, UNROLL>, grid, block, 0,
                                   s, x, gain, eps, w, y, M, N, K);
         case GS_OUT_ADD_F32:
-            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_ADD_F32, WARPS>, grid, block,
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_ADD_F32, WARPS, UNROLL>, grid, block,
                                   0, s, x, gain, eps, w, y, M, N, K);
         default:
-            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_SWIGLU, WARPS>, grid, block,
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_SWIGLU, WARPS, UNROLL>, grid, block,
                                   0, s, x, gain, eps, w, y, M, N, K);
     }
 }
 
+// A CTA has 2 x UNROLL x 2 loads of 16 bytes a thread on their way, 32 KB with UNROLL 2, and
+// what bounds the kernel is how many bytes the whole GPU has on their way (about 15 MB hide
+// the latency of HBM at its full rate). A matrix of 4096 rows is only 256 CTAs: 8 MB. For
+// such a matrix (its CTAs all fit on the GPU at two an SM) each thread keeps twice the loads
+// in flight, at 110 registers; where there are more CTAs than that, three an SM with the
+// smaller sets are better.
 template <int MT>
 static int gs_launch(const void* x, const float* gain, float eps, const bf16* w, void* y, int M,
                      int N, int K, int xmode, int omode, cudaStream_t s) {
-    if (xmode == GS_X_BF16) return gs_launch_o<MT, GS_X_BF16, 8>(x, gain, eps, w, y, M, N, K, omode, s);
-    return gs_launch_o<MT, GS_X_NORM, 8>(x, gain, eps, w, y, M, N, K, omode, s);
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    const bool narrow = MT == 1 && GS_NARROW_UNROLL != GS_UNROLL && (N + 15) / 16 <= 2 * sms && K >= 2048;
+    if (xmode == GS_X_BF16) {
+        if (narrow) return gs_launch_o<MT, GS_X_BF16, 8, GS_NARROW_UNROLL>(x, gain, eps, w, y, M, N, K, omode, s);
+        return gs_launch_o<MT, GS_X_BF16, 8, GS_UNROLL>(x, gain, eps, w, y, M, N, K, omode, s);
+    }
+    return gs_launch_o<MT, GS_X_NORM, 8, GS_UNROLL>(x, gain, eps, w, y, M, N, K, omode, s);
 }
 
 // Most rows this kernel takes; K must be a multiple of 8 (16-byte loads).
