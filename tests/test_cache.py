@@ -8,9 +8,21 @@ from tgo_b200.cache.pages import (NULL_PAGE, CacheManager, GroupLayout, PagePool
                                   SlotPool, SlotsExhausted)
 
 
-def manager(pages=(12, 12), page=4, slots=3, window=10):
+def make_manager(kind, pages=(12, 12), page=4, slots=3, window=10):
     groups = [GroupLayout("full", None, 2, 8, [0, 2]), GroupLayout("window", window, 2, 8, [1])]
+    if kind == "native":
+        from tgo_b200.cache.native import NativeCacheManager
+        return NativeCacheManager(groups, page, list(pages), slots)
     return CacheManager(groups, page, list(pages), slots)
+
+
+@pytest.fixture(params=["plain", "native"])
+def manager(request):
+    """The books in Python (the plain statement of the rules) and the native ones the engine
+    uses: every test of the manager runs against both."""
+    def make(**kw):
+        return make_manager(request.param, **kw)
+    return make
 
 
 def test_pool_hands_out_lowest_first_and_refuses_misuse():
@@ -43,7 +55,7 @@ def test_slots():
         s.give(5)
 
 
-def test_grow_commit_finish():
+def test_grow_commit_finish(manager):
     cm = manager()
     cm.admit("a")
     cm.grow("a", 9)                              # positions 0..8 -> 3 pages in both groups
@@ -63,7 +75,7 @@ def test_grow_commit_finish():
     assert cm.slots.free_count == 3
 
 
-def test_growth_is_all_or_nothing_across_groups():
+def test_growth_is_all_or_nothing_across_groups(manager):
     cm = manager(pages=(12, 2))
     cm.admit("a")
     with pytest.raises(PagesExhausted) as e:
@@ -73,7 +85,7 @@ def test_growth_is_all_or_nothing_across_groups():
     cm.check_invariants()
 
 
-def test_admission_reserves_full_groups_together_or_not_at_all():
+def test_admission_reserves_full_groups_together_or_not_at_all(manager):
     cm = manager(pages=(4, 12))
     cm.admit("a", reserve_tokens=12)             # 3 of 4 pages
     with pytest.raises(PagesExhausted):
@@ -84,7 +96,7 @@ def test_admission_reserves_full_groups_together_or_not_at_all():
     assert cm.can_hold(16) and not cm.can_hold(17)
 
 
-def test_freed_pages_are_used_again():
+def test_freed_pages_are_used_again(manager):
     cm = manager(pages=(3, 3))
     cm.admit("a")
     cm.grow("a", 12)
@@ -97,7 +109,7 @@ def test_freed_pages_are_used_again():
 
 
 @pytest.mark.parametrize("seed", range(5))
-def test_random_orders_keep_the_books(seed):
+def test_random_orders_keep_the_books(manager, seed):
     rng = random.Random(seed)
     cm = manager(pages=(40, 40), page=4, slots=4, window=10)
     live, counter = {}, 0
@@ -138,3 +150,79 @@ def test_random_orders_keep_the_books(seed):
     assert all(p.taken_total == p.given_total for p in cm.pools)
     with pytest.raises(KeyError):
         cm.finish("r1" if "r1" not in cm.requests else "nobody")
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_native_books_follow_the_plain_ones(seed):
+    """The same random life of requests through both managers: the same slots, tables,
+    refusals and released pages at every turn, and the same packed step."""
+    import numpy as np
+
+    from tgo_b200.engine.step import Engine, StepEntry
+    rng = random.Random(100 + seed)
+    plain_cm = make_manager("plain", pages=(30, 30), page=4, slots=4, window=10)
+    native_cm = make_manager("native", pages=(30, 30), page=4, slots=4, window=10)
+    packer = Engine.__new__(Engine)              # only its packing, over the plain books
+    packer.cache, packer.page_size = plain_cm, 4
+    live, counter = {}, 0
+
+    def both(call, *args):
+        out = []
+        for cm in (plain_cm, native_cm):
+            try:
+                out.append(("ok", getattr(cm, call)(*args)))
+            except (PagesExhausted, SlotsExhausted, ValueError, KeyError) as e:
+                out.append((type(e).__name__, None))
+        assert out[0][0] == out[1][0], (call, args, out)
+        return out
+
+    for turn in range(400):
+        action = rng.random()
+        if action < 0.25:
+            counter += 1
+            rid = f"r{counter}"
+            got = both("admit", rid, rng.choice([0, 5, 17]))
+            if got[0][0] == "ok":
+                assert got[0][1].slot == got[1][1].slot
+                live[rid] = 0
+        elif action < 0.8 and live:
+            # a step: some of the live requests bring tokens, packed by both and compared
+            chosen = [r for r in live if rng.random() < 0.7] or [rng.choice(list(live))]
+            extents = [rng.choice([1, 1, 2, 7, 13]) for _ in chosen]
+            ok = True
+            for rid, n in zip(chosen, extents):
+                got = both("grow", rid, live[rid] + n)
+                ok = ok and got[0][0] == "ok"
+            if ok:
+                tokens = [[rng.randrange(50) for _ in range(n)] for n in extents]
+                wants = [sorted(rng.sample(range(n), rng.randrange(0, min(n, 3) + 1))) for n in extents]
+                pad = rng.choice([0, 0, len(chosen) + 2])
+                quantum = rng.choice([1, 4])
+                all_rows = rng.random() < 0.2
+                entries = [StepEntry(r, t, w) for r, t, w in zip(chosen, tokens, wants)]
+                flat, meta = packer._pack(entries, pad_to=pad, width_quantum=quantum, all_rows=all_rows)
+                out = np.full(meta["total"] + 5, -7, dtype=np.int32)
+                nmeta, total = native_cm.step_pack(chosen, tokens, wants, pad, quantum, all_rows, out)
+                assert total == meta["total"] and (out[total:] == -7).all()
+                assert np.array_equal(out[:total], flat[:total])
+                for key in ("T", "B", "n_rows", "widths", "firsts", "max_context"):
+                    assert nmeta[key] == meta[key], key
+                small, needed = native_cm.step_pack(chosen, tokens, wants, pad, quantum, all_rows,
+                                                    np.zeros(3, dtype=np.int32))
+                assert small is None and needed == total
+                for rid, n in zip(chosen, extents):
+                    got = both("commit", rid, live[rid] + n)
+                    assert sorted(got[0][1]) == sorted(got[1][1])
+                    live[rid] += n
+        elif live:
+            rid = rng.choice(list(live))
+            got = both("finish", rid)
+            assert sorted(got[0][1]) == sorted(got[1][1])
+            del live[rid]
+        plain_cm.check_invariants()
+        native_cm.check_invariants()
+        for rid in live:
+            a, b = plain_cm.requests[rid], native_cm.requests[rid]
+            assert a.tables == b.tables and a.length == b.length and a.slot == b.slot
+        for pa, pb in zip(plain_cm.pools, native_cm.pools):
+            assert (pa.free_count, pa.taken_total, pa.given_total) == (pb.free_count, pb.taken_total, pb.given_total)

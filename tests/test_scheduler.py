@@ -174,3 +174,26 @@ def test_single_request_that_outgrows_the_pool_raises():
     runner.submit(Request([1], Policy(max_tokens=20)))
     with pytest.raises(PagesExhausted):
         runner.run()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_native_policy_decides_as_the_plain_one(seed):
+    """next_step and victim of the native host library against the Python statement of them,
+    over random slots, chunks and budgets."""
+    import random
+
+    from tgo_b200.engine.scheduler import next_step_native, victim_native
+    rng = random.Random(seed)
+    for _ in range(300):
+        slots = []
+        for i in range(rng.randrange(1, 9)):
+            n = rng.randrange(1, 40)
+            done = rng.choice([0, rng.randrange(0, n + 1), n])
+            feed = rng.choice([None, rng.randrange(100)])
+            slots.append(slot([rng.randrange(100) for _ in range(n)], done, feed,
+                              arrived=rng.randrange(50), live=rng.random() < 0.8))
+        chunk, budget = rng.randrange(1, 20), rng.randrange(1, 40)
+        assert next_step_native(slots, chunk, budget) == next_step(slots, chunk, budget)
+        assert victim_native(slots) == victim(slots)
+    with pytest.raises(ValueError, match="chunk"):
+        next_step_native([slot([1, 2])], 0, 4)

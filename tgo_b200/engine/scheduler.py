@@ -104,6 +104,57 @@ def victim(slots: Sequence[SlotState]) -> int:
     return best
 
 
+def _policy_arrays(slots: Sequence[SlotState]):
+    import numpy as np
+    n = len(slots)
+    live = np.fromiter((1 if s.live else 0 for s in slots), dtype=np.int32, count=n)
+    plen = np.fromiter((len(s.prompt) for s in slots), dtype=np.int64, count=n)
+    done = np.fromiter((s.prefilled for s in slots), dtype=np.int64, count=n)
+    return n, live, plen, done
+
+
+def next_step_native(slots: Sequence[SlotState], chunk: int, budget: int) -> List[Work]:
+    """`next_step` decided by the native host library (csrc/host_runtime.cpp): the same
+    work for the same slots, which the tests check over random states."""
+    import numpy as np
+
+    from ..kernels.build import load_library
+    if chunk <= 0 or budget <= 0:
+        return next_step(slots, chunk, budget)          # raises, naming the number
+    lib = load_library("host_runtime")
+    n, live, plen, done = _policy_arrays(slots)
+    feed = np.fromiter((0 if s.feed is None else 1 for s in slots), dtype=np.int32, count=n)
+    out_slot, out_pre = np.empty(n, dtype=np.int32), np.empty(n, dtype=np.int32)
+    out_count = np.empty(n, dtype=np.int64)
+    from ctypes import c_int, c_longlong, c_void_p
+    k = lib.tgo_schedule_next_step(c_int(n), c_void_p(live.ctypes.data), c_void_p(plen.ctypes.data),
+                                   c_void_p(done.ctypes.data), c_void_p(feed.ctypes.data),
+                                   c_longlong(chunk), c_longlong(budget),
+                                   c_void_p(out_slot.ctypes.data), c_void_p(out_count.ctypes.data),
+                                   c_void_p(out_pre.ctypes.data))
+    work = []
+    for j in range(k):
+        s = slots[int(out_slot[j])]
+        if out_pre[j]:
+            work.append(Work(int(out_slot[j]), s.prompt[s.prefilled:s.prefilled + int(out_count[j])], True))
+        else:
+            work.append(Work(int(out_slot[j]), [s.feed], False))
+    return work
+
+
+def victim_native(slots: Sequence[SlotState]) -> int:
+    import numpy as np
+    from ctypes import c_int, c_void_p
+
+    from ..kernels.build import load_library
+    lib = load_library("host_runtime")
+    n, live, plen, done = _policy_arrays(slots)
+    in_prompt = (done < plen).astype(np.int32)
+    arrived = np.fromiter((s.arrived for s in slots), dtype=np.int64, count=n)
+    return int(lib.tgo_schedule_victim(c_int(n), c_void_p(live.ctypes.data),
+                                       c_void_p(in_prompt.ctypes.data), c_void_p(arrived.ctypes.data)))
+
+
 # ------------------------------------------------------------------------ scheduler
 
 
@@ -143,6 +194,8 @@ class Scheduler:
         self.reserve = reserve
         self.budget = max_batched_tokens or (self.chunk + slots)
         self.slots = [SlotState() for _ in range(slots)]
+        # the policy is decided natively, as the engine's books are (TGO_NATIVE_HOST=0: here)
+        self.native = bool(getattr(engine, "_native", False))
         self._arrivals = 0
         self._ids = 0
 
@@ -192,7 +245,7 @@ class Scheduler:
     def evict(self) -> int:
         """Drop the victim's pages and free its slot; the caller re-admits it later with
         its prompt and what it produced, to be computed again. -1 if nothing is live."""
-        v = victim(self.slots)
+        v = (victim_native if self.native else victim)(self.slots)
         if v >= 0:
             self.finish(v)
         return v
@@ -224,7 +277,7 @@ class Scheduler:
         """Plan with `next_step`, run the batch, advance the slots that worked.
         Raises PagesExhausted before anything ran if a slot cannot get its pages."""
         from .step import StepEntry
-        work = next_step(self.slots, self.chunk, self.budget)
+        work = (next_step_native if self.native else next_step)(self.slots, self.chunk, self.budget)
         if not work:
             return StepResult([], None)
         entries, produced, row = [], [], 0
@@ -298,7 +351,7 @@ class Runner:
             self.by_slot[slot] = req
 
     def _evict_one(self) -> None:
-        v = victim(self.sched.slots)
+        v = (victim_native if self.sched.native else victim)(self.sched.slots)
         if v < 0:
             raise PagesExhausted(-1, 0, 0)
         req = self.by_slot.pop(v)

@@ -9,6 +9,7 @@ model/batch.go:66-152 are the reference's descriptor and commit rule).
 """
 from __future__ import annotations
 
+import os
 import sys
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
@@ -16,6 +17,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
+from ..cache.native import NativeCacheManager
 from ..cache.pages import NULL_PAGE, CacheManager
 from ..cache.storage import CacheStorage
 from ..kernels import ops
@@ -52,7 +54,16 @@ class Engine:
         self.device = model.device
         self.page_size = page_size
         pages = [num_pages for _ in model.groups]
-        self.cache = CacheManager(model.groups, page_size, pages, num_slots)
+        # the books and the packing of a step are kept by the native host library;
+        # TGO_NATIVE_HOST=0 keeps them in Python (cache/pages.py and _pack below, the plain
+        # statement that the tests hold the native ones against)
+        self._native = os.environ.get("TGO_NATIVE_HOST", "1") != "0"
+        if self._native:
+            self.cache = NativeCacheManager(model.groups, page_size, pages, num_slots)
+            self._stage = np.empty(4096, dtype=np.int32)
+            self._begun = None                   # (request ids, what step_begin returned)
+        else:
+            self.cache = CacheManager(model.groups, page_size, pages, num_slots)
         self.storage = CacheStorage(model.groups, page_size, pages, num_slots, model.dtype,
                                     model.device, model.state_shapes)
         self.steps_run = 0
@@ -128,6 +139,8 @@ class Engine:
         slots[T] table[B*width]. With pad_to > B, requests that bring nothing fill the batch:
         one token each at position -1 (the kernels read and write nothing for it).
         Written into `out` if it is given and large enough."""
+        if getattr(self, "_native", False):
+            return self._pack_native(entries, pad_to, width_quantum, all_rows, out)
         cm = self.cache
         ps = self.page_size
         reqs = [cm.requests[e.request_id] for e in entries]
@@ -213,6 +226,27 @@ class Engine:
                     max_context=int(ctx_lens[:n_real].max()), total=total)
         return buf, meta
 
+    def _pack_native(self, entries, pad_to, width_quantum, all_rows, out):
+        """`_pack` by the native host library: the same buffer and the same meta."""
+        ids = [e.request_id for e in entries]
+        tokens = [e.tokens for e in entries]
+        wants = [e.want for e in entries]
+        buf = out if out is not None else self._stage
+        begun = self._begun if self._begun is not None and self._begun[0] == ids else None
+        begun = begun[1] if begun else None
+        meta, total = self.cache.step_pack(ids, tokens, wants, pad_to, width_quantum, all_rows, buf,
+                                           begun)
+        if meta is None:                         # too small: a buffer of its own, as _pack does
+            buf = np.empty(total, dtype=np.int32)
+            if out is None:
+                self._stage = np.empty(2 * total, dtype=np.int32)
+            meta, total = self.cache.step_pack(ids, tokens, wants, pad_to, width_quantum, all_rows,
+                                               buf, begun)
+        elif out is None:
+            buf = buf[:total].copy()             # the staging buffer is written again next step
+        meta["extents"] = [len(t) for t in tokens]
+        return buf, meta
+
     def _views(self, dev: torch.Tensor, meta: dict):
         """Device views into a flat buffer laid out by `_pack`."""
         T, B, widths = meta["T"], meta["B"], meta["widths"]
@@ -255,9 +289,13 @@ class Engine:
         if not entries:
             raise ValueError("step: an empty batch carries nothing")
         self._validate(entries)
-        for e in entries:
-            r = self.cache.requests[e.request_id]
-            self.cache.grow(e.request_id, r.length + len(e.tokens))
+        if self._native:
+            ids = [e.request_id for e in entries]
+            self._begun = (ids, self.cache.step_begin(ids, [len(e.tokens) for e in entries]))
+        else:
+            for e in entries:
+                r = self.cache.requests[e.request_id]
+                self.cache.grow(e.request_id, r.length + len(e.tokens))
         if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
             logits = self._graph_step(entries)
         elif self.use_graphs and len(entries) == 1 and \
@@ -267,9 +305,13 @@ class Engine:
         else:
             ctx, tables, slots = self.build_context(entries)
             logits = self.model.forward(ctx, self.storage, tables, slots)
-        for e in entries:
-            r = self.cache.requests[e.request_id]
-            self.cache.commit(e.request_id, r.length + len(e.tokens))
+        if self._native:
+            self.cache.step_commit(self._begun[1])
+            self._begun = None
+        else:
+            for e in entries:
+                r = self.cache.requests[e.request_id]
+                self.cache.commit(e.request_id, r.length + len(e.tokens))
         self.steps_run += 1
         return logits
 
@@ -281,7 +323,12 @@ class Engine:
         """Block-table columns of the graph a step runs through: the smallest of 64, 128,
         256, ... that holds the longest table of the step (a few variants however long the
         contexts grow; the kernels read only the columns a request has)."""
-        raw = max(1, max(len(t) for e in entries for t in self.cache.requests[e.request_id].tables))
+        if self._native and self._begun is not None:
+            raw = max(1, self._begun[1][2])
+        elif self._native:
+            raw = max(1, self.cache.step_widest_table([e.request_id for e in entries]))
+        else:
+            raw = max(1, max(len(t) for e in entries for t in self.cache.requests[e.request_id].tables))
         q = self.WIDTH_QUANTUM
         while q < raw:
             q *= 2

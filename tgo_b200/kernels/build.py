@@ -38,7 +38,10 @@ LIBRARIES = {
     "gemm_tc": (["gemm_tc.cu"], []),
     "gemm_chain": (["gemm_chain.cu"], []),
     "sampling": (["sampling.cu"], []),
+    # host code only (no kernel): the cache books and the packing of a step
+    "host_runtime": (["host_runtime.cpp"], []),
 }
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden"]
 
 _loaded = {}
 _lock = threading.Lock()
@@ -61,6 +64,15 @@ def find_nvcc() -> str:
     raise KernelBuildError("nvcc was not found (looked at $TGO_NVCC, $CUDA_HOME/bin, "
                            "/usr/local/cuda/bin and PATH); the CUDA kernels cannot be built "
                            "and there is no other path")
+
+
+def find_host_compiler():
+    """A C++ compiler for the libraries without kernels, or None (nvcc compiles them then)."""
+    for cand in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        path = shutil.which(cand) if cand else None
+        if path:
+            return path
+    return None
 
 
 def _build_dir() -> str:
@@ -87,7 +99,8 @@ def _digest(sources, link_flags) -> str:
     for src in sources:
         with open(os.path.join(CSRC, src), "rb") as f:
             h.update(src.encode() + b"\0" + f.read())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + list(link_flags)).encode())
+    flags = HOST_FLAGS if all(src.endswith(".cpp") for src in sources) else ARCH_FLAGS + NVCC_FLAGS
+    h.update(" ".join(flags + list(link_flags)).encode())
     return h.hexdigest()[:16]
 
 
@@ -104,13 +117,19 @@ def compile_library(name: str, verbose: bool = True, ptxas_info: bool = False) -
     out = library_path(name)
     if os.path.exists(out) and not ptxas_info:
         return out
-    nvcc = find_nvcc()
     tmp = f"{out}.{os.getpid()}.tmp"
-    cmd = [nvcc] + ARCH_FLAGS + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + \
-        ["-I", CSRC, "-o", tmp] + [os.path.join(CSRC, s) for s in sources] + list(link_flags)
+    host_only = all(src.endswith(".cpp") for src in sources)
+    cxx = find_host_compiler() if host_only else None
+    if cxx:
+        cmd = [cxx] + HOST_FLAGS + ["-I", CSRC, "-o", tmp] + \
+            [os.path.join(CSRC, s) for s in sources] + list(link_flags)
+    else:
+        nvcc = find_nvcc()
+        cmd = [nvcc] + ARCH_FLAGS + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + \
+            ["-I", CSRC, "-o", tmp] + [os.path.join(CSRC, s) for s in sources] + list(link_flags)
     if verbose:
-        print(f"[tgo_b200] compiling {name} ({', '.join(sources)}) for sm_100a ...",
-              file=sys.stderr, flush=True)
+        print(f"[tgo_b200] compiling {name} ({', '.join(sources)})"
+              f"{' for the host' if host_only else ' for sm_100a'} ...", file=sys.stderr, flush=True)
     t0 = time.time()
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
@@ -127,7 +146,7 @@ def compile_library(name: str, verbose: bool = True, ptxas_info: bool = False) -
     if proc.returncode != 0:
         if os.path.exists(tmp):
             os.unlink(tmp)
-        raise KernelBuildError(f"nvcc failed on {name}:\n{' '.join(cmd)}\n{text}")
+        raise KernelBuildError(f"the compiler failed on {name}:\n{' '.join(cmd)}\n{text}")
     os.replace(tmp, out)
     # older builds of the same library (other source hashes) are of no use any more
     prefix = f"libtgo_{name}_"
