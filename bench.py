@@ -147,10 +147,11 @@ def serve_workload(model, config, shape):
     plens, olens = rng.integers(128, 4097, n), rng.integers(64, 513, n)
     prompts = [rng.integers(0, config["vocab_size"], int(p)).tolist() for p in plens]
     policies = [Policy(max_tokens=int(o)) for o in olens]
-    # a step's tokens (a prompt portion and one token per decoding request) stay within 512:
-    # four row tiles of the products, none partly filled
+    # prompt portions of 512 tokens as the record says; a step carries up to 1024 tokens (two
+    # portions, or one and the decoding requests' tokens): measured 5.59 s against 5.88 s with
+    # steps of 512, and 5.56 s with 1536
     scheduler = model.new_scheduler(n, chunk=512, reserve=int(olens.max()), pool_tokens=n * CONTEXT_CAP,
-                                    page_size=PAGE, max_batched_tokens=512)
+                                    page_size=PAGE, max_batched_tokens=1024)
     for _ in range(2):
         torch.cuda.synchronize()
         t0 = time.time()
