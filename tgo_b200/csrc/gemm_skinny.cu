@@ -231,7 +231,9 @@ static int gs_launch(const void* x, const float* gain, float eps, const bf16* w,
     }
     const bool narrow = MT == 1 && GS_NARROW_UNROLL != GS_UNROLL && (N + 15) / 16 <= 2 * sms && K >= 2048;
     if (xmode == GS_X_BF16) {
-        if (narrow) return gs_launch_o<MT, GS_X_BF16, 8, GS_NARROW_UNROLL>(x, gain, eps, w, y, M, N, K, omode, s);
+        if constexpr (MT == 1) {        // only this one is built with the larger sets
+            if (narrow) return gs_launch_o<MT, GS_X_BF16, 8, GS_NARROW_UNROLL>(x, gain, eps, w, y, M, N, K, omode, s);
+        }
         return gs_launch_o<MT, GS_X_BF16, 8, GS_UNROLL>(x, gain, eps, w, y, M, N, K, omode, s);
     }
     return gs_launch_o<MT, GS_X_NORM, 8, GS_UNROLL>(x, gain, eps, w, y, M, N, K, omode, s);

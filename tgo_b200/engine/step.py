@@ -53,6 +53,8 @@ class Engine:
         self.model = model
         self.device = model.device
         self.page_size = page_size
+        if self.device.type == "cuda":
+            ops.prebuild_for(model.dtype, [(g.head_dim, page_size) for g in model.groups])
         pages = [num_pages for _ in model.groups]
         # the books and the packing of a step are kept by the native host library;
         # TGO_NATIVE_HOST=0 keeps them in Python (cache/pages.py and _pack below, the plain

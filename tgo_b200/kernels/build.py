@@ -182,6 +182,20 @@ def load_library(name: str) -> ctypes.CDLL:
     return lib
 
 
+def compile_together(names, verbose: bool = True) -> None:
+    """Build several libraries at once, a compiler process each (a model's first step would
+    otherwise build the ones it needs one after the other as it reaches them)."""
+    from concurrent.futures import ThreadPoolExecutor
+    todo = [n for n in dict.fromkeys(names) if n not in _loaded and not os.path.exists(library_path(n))]
+    if len(todo) <= 1:
+        for n in todo:
+            compile_library(n, verbose=verbose)
+        return
+    with ThreadPoolExecutor(max_workers=min(len(todo), os.cpu_count() or 2, 8)) as pool:
+        for f in [pool.submit(compile_library, n, verbose) for n in todo]:
+            f.result()
+
+
 def build_all(verbose: bool = True) -> None:
     for name in sorted(LIBRARIES):
         compile_library(name, verbose=verbose)

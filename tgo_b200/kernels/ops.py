@@ -459,6 +459,22 @@ def flash_supports(head_dim: int, group: int) -> bool:
         c_int(head_dim), c_int(group)))
 
 
+def prebuild_for(dtype: torch.dtype, head_dims_and_pages) -> None:
+    """Compile, side by side, the libraries that a model of this storage type and these head
+    sizes is sure to use in its first steps (each would otherwise be built when the first
+    step reaches it, one after the other). What a model may never need (the product for more
+    than 1024 rows, sampling) is left to its first use."""
+    from .build import compile_together
+    names = ["host_runtime", "elementwise"]
+    if dtype == torch.float32:
+        names += ["sgemm", "attention_generic"]
+    else:
+        names += ["gemm_skinny", "attention_flash"]
+        if any(dh == 128 for dh, _ in head_dims_and_pages):
+            names += ["attention_tc", "attention_decode_tma"]
+    compile_together(names)
+
+
 USE_TMA_DECODE = True       # decode attention with head size 128: cache pages by TMA
 
 
