@@ -51,6 +51,12 @@ class KernelBuildError(RuntimeError):
     pass
 
 
+def _say(line: str) -> None:
+    """One whole line to stderr (several libraries may be compiling side by side)."""
+    sys.stderr.write(line + "\n")
+    sys.stderr.flush()
+
+
 def register_library(name: str, sources, link_flags=()) -> None:
     LIBRARIES[name] = (list(sources), list(link_flags))
 
@@ -128,8 +134,8 @@ def compile_library(name: str, verbose: bool = True, ptxas_info: bool = False) -
         cmd = [nvcc] + ARCH_FLAGS + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + \
             ["-I", CSRC, "-o", tmp] + [os.path.join(CSRC, s) for s in sources] + list(link_flags)
     if verbose:
-        print(f"[tgo_b200] compiling {name} ({', '.join(sources)})"
-              f"{' for the host' if host_only else ' for sm_100a'} ...", file=sys.stderr, flush=True)
+        _say(f"[tgo_b200] compiling {name} ({', '.join(sources)})"
+             f"{' for the host' if host_only else ' for sm_100a'} ...")
     t0 = time.time()
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
@@ -140,8 +146,7 @@ def compile_library(name: str, verbose: bool = True, ptxas_info: bool = False) -
             break
         except subprocess.TimeoutExpired:
             if verbose:
-                print(f"[tgo_b200]   still compiling {name} ({time.time() - t0:.0f} s)",
-                      file=sys.stderr, flush=True)
+                _say(f"[tgo_b200]   still compiling {name} ({time.time() - t0:.0f} s)")
     text = output.decode(errors="replace")
     if proc.returncode != 0:
         if os.path.exists(tmp):
@@ -158,8 +163,7 @@ def compile_library(name: str, verbose: bool = True, ptxas_info: bool = False) -
             except OSError:
                 pass
     if verbose:
-        print(f"[tgo_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s",
-              file=sys.stderr, flush=True)
+        _say(f"[tgo_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s")
     if ptxas_info:
         print(text)
     return out
