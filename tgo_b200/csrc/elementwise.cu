@@ -534,17 +534,24 @@ qk_norm_rope_cache_dh128_wide_kernel(
     }
     // every half-warp runs the same number of rounds, so that the shuffles below are complete
     const int rounds = (total + 15) / 16;
+    // the vector of round r for this half-warp: read one round ahead of its use
+    auto fetch = [&](int r) {
+        const int hh = r * 16 + half_id;
+        if (hh >= total) return make_uint4(0u, 0u, 0u, 0u);
+        const bf16* src = hh < H ? q + (size_t)t * q_stride + (size_t)hh * dh
+                          : hh >= H + nk ? v + (size_t)t * v_stride + (size_t)(hh - H - nk) * dh
+                                         : k + (size_t)t * k_stride + (size_t)(hh - H) * dh;
+        return *(const uint4*)(src + 8 * hl);
+    };
+    uint4 ahead = fetch(0);
     for (int r = 0; r < rounds; ++r) {
         const int hh = r * 16 + half_id;
         const bool live = hh < total;
         const bool is_v = live && hh >= H + nk;
         const bool is_q = live && hh < H;
         const int head = !live ? 0 : is_q ? hh : is_v ? hh - H - nk : hh - H;
-        const bf16* src = !live ? q : is_q ? q + (size_t)t * q_stride + (size_t)head * dh
-                          : is_v ? v + (size_t)t * v_stride + (size_t)head * dh
-                                 : k + (size_t)t * k_stride + (size_t)head * dh;
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        if (live) raw = *(const uint4*)(src + 8 * hl);
+        const uint4 raw = ahead;
+        if (r + 1 < rounds) ahead = fetch(r + 1);
         if (is_v) {
             if (slot >= 0) *(uint4*)(v_cache + (((size_t)page * Hkv + head) * page_size + off) * dh + 8 * hl) = raw;
             continue;                                        // no shuffles on this path ...
