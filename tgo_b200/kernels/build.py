@@ -201,5 +201,6 @@ def compile_together(names, verbose: bool = True) -> None:
 
 
 def build_all(verbose: bool = True) -> None:
-    for name in sorted(LIBRARIES):
+    compile_together(sorted(LIBRARIES), verbose=verbose)
+    for name in sorted(LIBRARIES):           # whatever was there already is checked to exist
         compile_library(name, verbose=verbose)
