@@ -121,3 +121,18 @@ def test_run_order_is_validated():
         spec.validate()
     spec.run_order = [LayerCall(0), LayerCall(1), LayerCall(0, cache_from=0)]
     spec.validate()
+
+
+def test_build_folder_is_one_for_all_threads():
+    """Several libraries compile side by side: every thread must get the same folder (a
+    probe file shared by name once sent some of them to the fallback folder)."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    from tgo_b200.kernels import build as kb
+    kb._build_dir_found = None
+    with ThreadPoolExecutor(max_workers=8) as pool:
+        got = set(pool.map(lambda _: kb._build_dir(), range(64)))
+    assert len(got) == 1
+    # and the host library, which needs no CUDA compiler, builds and loads
+    lib = kb.load_library("host_runtime")
+    assert lib.tgo_cache_create

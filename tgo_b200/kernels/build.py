@@ -45,6 +45,7 @@ HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden"]
 
 _loaded = {}
 _lock = threading.Lock()
+_dir_lock = threading.Lock()
 
 
 class KernelBuildError(RuntimeError):
@@ -81,19 +82,29 @@ def find_host_compiler():
     return None
 
 
+_build_dir_found = None
+
+
 def _build_dir() -> str:
-    here = os.path.join(os.path.dirname(__file__), "_build")
-    try:
-        os.makedirs(here, exist_ok=True)
-        probe = os.path.join(here, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.unlink(probe)
-        return here
-    except OSError:
-        alt = os.path.join(tempfile.gettempdir(), f"tgo_b200_build_{os.getuid()}")
-        os.makedirs(alt, exist_ok=True)
-        return alt
+    """Where the libraries go: decided once per process (several threads may be compiling)."""
+    global _build_dir_found
+    if _build_dir_found is not None:
+        return _build_dir_found
+    with _dir_lock:
+        if _build_dir_found is None:
+            here = os.path.join(os.path.dirname(__file__), "_build")
+            try:
+                os.makedirs(here, exist_ok=True)
+                probe = os.path.join(here, f".w{os.getpid()}.{threading.get_ident()}")
+                with open(probe, "w"):
+                    pass
+                os.unlink(probe)
+                _build_dir_found = here
+            except OSError:
+                alt = os.path.join(tempfile.gettempdir(), f"tgo_b200_build_{os.getuid()}")
+                os.makedirs(alt, exist_ok=True)
+                _build_dir_found = alt
+    return _build_dir_found
 
 
 def _digest(sources, link_flags) -> str:
