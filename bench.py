@@ -90,7 +90,7 @@ def reference_arm():
     print(json.dumps({"impl": "reference", "unavailable":
                       "latere-ai/tgo is Go (no setup.py/pyproject; needs Go 1.27 and the "
                       "external golang.design/x/accel module, neither present offline); "
-                      "pip install of /root/reference fails"}))
+                      "pip install of the reference checkout fails"}))
     return 0
 
 
