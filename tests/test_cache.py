@@ -1,5 +1,6 @@
 """Cache manager (no GPU): no page lost, held twice or freed twice, under random orders of
 requests; windows give pages back; all-or-nothing growth; state slots."""
+import os
 import random
 
 import pytest
@@ -226,3 +227,46 @@ def test_native_books_follow_the_plain_ones(seed):
             assert a.tables == b.tables and a.length == b.length and a.slot == b.slot
         for pa, pb in zip(plain_cm.pools, native_cm.pools):
             assert (pa.free_count, pa.taken_total, pa.given_total) == (pb.free_count, pb.taken_total, pb.given_total)
+
+
+def test_host_runtime_from_plain_c(tmp_path):
+    """The native books through their C header, from a C program: admit, grow, a packed
+    step, commit, finish."""
+    import shutil
+    import subprocess
+
+    from tgo_b200.kernels import build as kb
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if not cc:
+        pytest.skip("no C compiler")
+    lib = kb.compile_library("host_runtime", verbose=False)
+    src = tmp_path / "use.c"
+    src.write_text(r'''
+#include <stdio.h>
+#include "host_runtime.h"
+int main(void) {
+    int kinds[1] = {0}, windows[1] = {0}, pages[1] = {8}, slot = -1, refused = -1, widest = 0;
+    void* c = tgo_cache_create(1, kinds, windows, 4, pages, 2);
+    if (!c) return 1;
+    if (tgo_cache_admit(c, 7, 0, &slot) != TGO_HOST_OK) return 2;
+    long long h[1] = {7};
+    int extents[1] = {5}, tokens[5] = {3, 1, 4, 1, 5}, n_want[1] = {1}, want[1] = {4}, meta[7];
+    if (tgo_step_grow(c, 1, h, extents, &refused, &widest) != TGO_HOST_OK || widest != 2) return 3;
+    int32_t out[64];
+    if (tgo_step_pack(c, 1, h, extents, tokens, n_want, want, 0, 1, 0, out, 64, meta) != TGO_HOST_OK) return 4;
+    if (meta[0] != 5 || meta[1] != 1 || meta[2] != 1 || out[4] != 5 || out[5 + 4] != 4) return 5;
+    if (tgo_step_commit(c, 1, h, extents) != TGO_HOST_OK || tgo_cache_request(c, 7, 0) != 5) return 6;
+    if (tgo_cache_grow(c, 7, 100) != TGO_HOST_PAGES_EXHAUSTED) return 7;
+    if (tgo_cache_check(c) != TGO_HOST_OK) return 8;
+    int n = 0;
+    if (tgo_cache_finish(c, 7, 0, 0, &n) != TGO_HOST_OK || n != 2 || tgo_cache_pool(c, 0, 0) != 8) return 9;
+    tgo_cache_destroy(c);
+    printf("ok\n");
+    return 0;
+}
+''')
+    exe = tmp_path / "use"
+    subprocess.run([cc, "-std=c99", "-Wall", "-I", kb.CSRC, "-o", str(exe), str(src), lib,
+                    f"-Wl,-rpath,{os.path.dirname(lib)}"], check=True)
+    got = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert got.returncode == 0 and got.stdout.strip() == "ok", (got.returncode, got.stderr)

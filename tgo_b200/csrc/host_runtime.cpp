@@ -22,6 +22,8 @@
 #include <unordered_map>
 #include <vector>
 
+#include "host_runtime.h"      // the declarations: a mismatch with a definition below fails to compile
+
 #define TGO_HOST_API extern "C" __attribute__((visibility("default")))
 
 namespace {
