@@ -112,8 +112,6 @@ def paged_attention(q, out, num_heads, num_kv_heads, head_dim, cache, ctx, scale
 
 
 def linear(x, w, out_dtype=None, residual=None):
-    from tgo_b200.kernels import ops
-    x = ops.as_rows(x)
     y = x.float() @ w.float().t()
     if residual is not None:
         residual += y
@@ -122,8 +120,6 @@ def linear(x, w, out_dtype=None, residual=None):
 
 
 def gated_linear(x, w_gate_up, interleaved):
-    from tgo_b200.kernels import ops
-    x = ops.as_rows(x)
     gu = (x.float() @ w_gate_up.float().t()).to(x.dtype)
     out = torch.empty((x.shape[0], w_gate_up.shape[0] // 2), dtype=x.dtype)
     swiglu(gu, out, interleaved)
@@ -163,12 +159,13 @@ def logits_adjust(row, bias_ids, bias, ids, counts, repetition, presence, freque
 
 
 NAMES = ["rope_table", "argmax", "sample", "logits_adjust", "embed", "add_rmsnorm", "residual_add", "swiglu", "qk_norm_rope_cache",
-         "attention_generic", "paged_attention", "linear", "gated_linear", "sgemm_tn"]
+         "attention_generic", "linear", "gated_linear", "sgemm_tn"]
 
 
 def install(monkeypatch):
     from tgo_b200.kernels import ops
-    monkeypatch.setattr(ops, "USE_CHAINS", False)
+    from tgo_b200.parts import attention
     here = globals()
     for name in NAMES:
         monkeypatch.setattr(ops, name, here[name])
+    monkeypatch.setattr(attention, "paged_attention", paged_attention)

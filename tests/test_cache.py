@@ -5,12 +5,13 @@ import random
 
 import pytest
 
-from tgo_b200.cache.pages import (NULL_PAGE, CacheManager, GroupLayout, PagePool, PagesExhausted,
-                                  SlotPool, SlotsExhausted)
+from plain_cache import CacheManager, PagePool, SlotPool
+from plain_pack import plain_pack
+from tgo_b200.cache.pages import NULL_PAGE, GroupLayout, PagesExhausted, SlotsExhausted
 
 
 def make_manager(kind, pages=(12, 12), page=4, slots=3, window=10):
-    groups = [GroupLayout("full", None, 2, 8, [0, 2]), GroupLayout("window", window, 2, 8, [1])]
+    groups = [GroupLayout("full", None, 2, (2, 8), [0, 2]), GroupLayout("window", window, 2, (2, 8), [1])]
     if kind == "native":
         from tgo_b200.cache.native import NativeCacheManager
         return NativeCacheManager(groups, page, list(pages), slots)
@@ -159,12 +160,10 @@ def test_native_books_follow_the_plain_ones(seed):
     refusals and released pages at every turn, and the same packed step."""
     import numpy as np
 
-    from tgo_b200.engine.step import Engine, StepEntry
+    from tgo_b200.engine.step import StepEntry
     rng = random.Random(100 + seed)
     plain_cm = make_manager("plain", pages=(30, 30), page=4, slots=4, window=10)
     native_cm = make_manager("native", pages=(30, 30), page=4, slots=4, window=10)
-    packer = Engine.__new__(Engine)              # only its packing, over the plain books
-    packer.cache, packer.page_size = plain_cm, 4
     live, counter = {}, 0
 
     def both(call, *args):
@@ -201,7 +200,7 @@ def test_native_books_follow_the_plain_ones(seed):
                 quantum = rng.choice([1, 4])
                 all_rows = rng.random() < 0.2
                 entries = [StepEntry(r, t, w) for r, t, w in zip(chosen, tokens, wants)]
-                flat, meta = packer._pack(entries, pad_to=pad, width_quantum=quantum, all_rows=all_rows)
+                flat, meta = plain_pack(plain_cm, entries, pad_to=pad, width_quantum=quantum, all_rows=all_rows)
                 out = np.full(meta["total"] + 5, -7, dtype=np.int32)
                 nmeta, total = native_cm.step_pack(chosen, tokens, wants, pad, quantum, all_rows, out)
                 assert total == meta["total"] and (out[total:] == -7).all()
@@ -270,3 +269,33 @@ int main(void) {
                     f"-Wl,-rpath,{os.path.dirname(lib)}"], check=True)
     got = subprocess.run([str(exe)], capture_output=True, text=True)
     assert got.returncode == 0 and got.stdout.strip() == "ok", (got.returncode, got.stderr)
+
+
+def test_a_window_only_pool_counts_the_steps_own_tokens(manager):
+    """A window group gives pages back only when a step has landed: while a step of c tokens
+    runs it holds the window and those c tokens. `can_hold` is asked with the largest step
+    the scheduler cuts, so a pool sized for the window alone refuses at submission what it
+    could never run, instead of running out of pages mid-run."""
+    def make(pages):
+        groups = [GroupLayout("window", 8, 2, (2, 8), [0])]
+        if "Native" in type(manager()).__name__:
+            from tgo_b200.cache.native import NativeCacheManager
+            return NativeCacheManager(groups, 4, [pages], 2)
+        return CacheManager(groups, 4, [pages], 2)
+    cm = make(3)                                    # pages_for(window) + 1
+    assert cm.can_hold(1000, 1)                     # token by token it fits for ever
+    assert not cm.can_hold(1000, 16)                # a 16-token portion needs 7 pages at once
+    assert cm.can_hold(10, 16)                      # a request shorter than that needs only its own
+    big = make(7)
+    assert big.can_hold(1000, 16)
+    big.admit("r")
+    length = 0
+    for n in (16, 16, 16, 3, 16):
+        big.grow("r", length + n)
+        big.commit("r", length + n)
+        length += n
+        big.check_invariants()
+    small = make(3)
+    small.admit("r")
+    with pytest.raises(PagesExhausted):
+        small.grow("r", 16)

@@ -150,3 +150,131 @@ def test_session_and_context_limits(emulated, tmp_path):
     stop = plain.greedy_generate(pc, pw, prompt, 3)[2]
     s2 = loaded.new_session(context=48, stop_ids=[stop])
     assert len(list(s2.complete(prompt, Policy(max_tokens=5)))) <= 2
+
+
+# ----------------------------------------------- a toy architecture defined here, on the CPU
+
+
+class CountingMixer:
+    """A mixer with fixed-size state and a one-plane paged cache of its own row shape, written
+    with torch: state s <- s + sum of the step's inputs per request; it stores each token's
+    input row in its cache plane and returns x + (mean of all cached rows so far) + s. It can
+    be told to fail after it has advanced its state."""
+    fail_next = False
+
+    def __init__(self, spec, hidden, prefix, device=None):
+        self.hidden = hidden
+
+    def weight_specs(self):
+        return []
+
+    def bind(self, weights):
+        pass
+
+    def cache_need(self):
+        from tgo_b200.parts.base import CacheNeed
+        return CacheNeed("full", None, 1, (self.hidden,))
+
+    def state_need(self):
+        from tgo_b200.parts.base import StateNeed
+        return StateNeed((self.hidden,))
+
+    def forward(self, x, ctx, cache):
+        plane = cache.planes[0]                        # [pages, page_size, hidden]
+        rows = plane.view(-1, self.hidden)
+        out = torch.empty_like(x)
+        base = 0
+        for b, n in enumerate(ctx.extents):
+            slot = int(ctx.state_slots[b])
+            first = int(ctx.context_lens[b]) - n
+            for t in range(n):
+                rows[int(cache.slots[base + t])] = x[base + t]
+                cache.state[slot] += x[base + t].float()
+                table = cache.block_tables[b]
+                held = torch.stack([plane[int(table[p // cache.page_size]), p % cache.page_size]
+                                    for p in range(first + t + 1)])
+                out[base + t] = x[base + t] + held.float().mean(0) + cache.state[slot]
+            base += n
+        if CountingMixer.fail_next:
+            CountingMixer.fail_next = False
+            raise RuntimeError("the mixer gave up after it had advanced its state")
+        return out
+
+
+def counting_spec(raw):
+    from tgo_b200.config.spec import (FeedForwardSpec, LayerCall, LayerSpec, MixerSpec, ModelSpec,
+                                      NormSpec)
+    from tgo_b200.config.qwen3 import BLOCK_TENSORS, FEED_FORWARD_TENSORS
+    norm = NormSpec("rmsnorm", 1e-5)
+    layer = LayerSpec("prenorm_residual", "l0.", MixerSpec("test_counting"),
+                      FeedForwardSpec("swiglu", raw["inner"], tensors=FEED_FORWARD_TENSORS), norm,
+                      BLOCK_TENSORS)
+    return ModelSpec("CountingToy", raw["width"], raw["vocab"], [layer], [LayerCall(0)], norm,
+                     "embed.weight", "norm.weight", None, source=dict(raw))
+
+
+@pytest.fixture()
+def counting_registered():
+    from tgo_b200.registry import ARCHITECTURES, MIXERS
+    ARCHITECTURES.register("CountingToy", counting_spec, replace=True)
+    MIXERS.register("test_counting", CountingMixer, replace=True)
+    yield
+    ARCHITECTURES.unregister("CountingToy")
+    MIXERS.unregister("test_counting")
+
+
+def test_a_step_that_fails_leaves_lengths_and_state_where_they_were(emulated, counting_registered,
+                                                                   tmp_path):
+    """A mixer from outside the package, with state of its own and a cache whose rows are not
+    keys and values (one plane of [hidden]): built, stepped in two cuts with equal results,
+    and a step that raises after the mixer advanced its state is undone."""
+    from tgo_b200.engine.step import StepEntry
+    raw = dict(architectures=["CountingToy"], width=24, vocab=40, inner=32)
+    d = tiny.make_model_dir(tmp_path / "toy", raw, seed=5, sigma=0.2)
+    loaded = cpu_model(d, raw)
+    assert [(g.planes, g.row_shape) for g in loaded.model.groups] == [(1, (24,))]
+    toks = [3, 9, 1, 30, 7, 7, 12, 5, 0, 39, 8]
+    whole = loaded.new_engine(page_size=4, max_tokens=64, num_slots=2)
+    assert whole.storage.kv[0].shape == (1, 1, 17, 4, 24)
+    whole.admit("w")
+    want = whole.step([StepEntry("w", toks, list(range(len(toks))))]).clone()
+    eng = loaded.new_engine(page_size=4, max_tokens=64, num_slots=2)
+    eng.admit("a")
+    first = eng.step([StepEntry("a", toks[:6], list(range(6)))]).clone()
+    state = {c: t.clone() for c, t in eng.storage.state.items()}
+    CountingMixer.fail_next = True
+    with pytest.raises(RuntimeError, match="gave up"):
+        eng.step([StepEntry("a", toks[6:], list(range(5)))])
+    assert eng.length("a") == 6
+    for c, t in state.items():
+        assert torch.equal(eng.storage.state[c], t)
+    rest = eng.step([StepEntry("a", toks[6:], list(range(5)))])
+    assert torch.allclose(torch.cat([first, rest]), want, atol=1e-5)
+    # the toy counts no flops and reads no cache by its own account: measurement still adds up
+    assert loaded.model.flops([5], [0]) == 2.0 * 5 * 24 * 3 * 32 + 2.0 * 24 * 40
+    assert loaded.model.cache_bytes_read(100) == 0.0
+
+
+def test_parts_count_their_own_flops_and_bytes(tmp_path):
+    """Model.flops sums what the parts report: for the tiny configurations it is the count
+    written out by hand here."""
+    from tgo_b200.engine.model import Model
+    from tgo_b200.registry import model_spec_from_config
+    for name in ("A", "B"):
+        cfg, _ = tiny.TINIES[name]
+        model = Model(model_spec_from_config(cfg), torch.float32, "cpu")
+        d, H, Hkv, dh = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], \
+            cfg["head_dim"]
+        f, V, L = cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+        n, first = 37, 11
+        windows = [cfg.get("sliding_window") if (cfg.get("layer_types") or ["full_attention"] * L)[i]
+                   == "sliding_attention" else None for i in range(L)]
+        want = 2.0 * d * V
+        for w in windows:
+            want += 2.0 * n * d * (H * dh + 2 * Hkv * dh) + 2.0 * n * H * dh * d + 2.0 * n * d * 3 * f
+            keys = sum(min(first + t + 1, w) if w else first + t + 1 for t in range(n))
+            want += 4.0 * H * dh * keys
+        assert model.flops([n], [first]) == want
+        per_token = sum(2 * Hkv * dh * 4 * (min(100, w) if w else 100) for w in windows)
+        assert model.cache_bytes_read(100) == per_token
+        assert model.cache_bytes_per_token() == L * 2 * Hkv * dh * 4

@@ -17,6 +17,12 @@ def ops():
     return o
 
 
+def attention_part():
+    """The module that picks the attention kernel for a step."""
+    from tgo_b200.parts import attention
+    return attention
+
+
 def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
     g = torch.Generator(device="cpu").manual_seed(seed)
     return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
@@ -272,7 +278,7 @@ def test_attention_mixed_batch(H, Hkv, dh, ps, window, dtype):
     scale = 1 / math.sqrt(dh)
     want = attention_ref(case, H, Hkv, dh, scale, window)
     out = torch.zeros_like(case["q"])
-    ops().paged_attention(case["q"], out, H, Hkv, dh, Cache(case, ps), Ctx(case, False), scale,
+    attention_part().paged_attention(case["q"], out, H, Hkv, dh, Cache(case, ps), Ctx(case, False), scale,
                           window)
     assert torch.allclose(out.float().cpu(), want, **tol(dtype))
     out2 = torch.zeros_like(case["q"])
@@ -317,13 +323,13 @@ def test_attention_far_key_stands_out(far, dtype):
     case["q"] = q
     scale = 1 / math.sqrt(dh)
     out = torch.zeros_like(q)
-    ops().paged_attention(q, out, H, Hkv, dh, Cache(case, ps), Ctx(case, False), scale, 0)
+    attention_part().paged_attention(q, out, H, Hkv, dh, Cache(case, ps), Ctx(case, False), scale, 0)
     sees = case["pos"] >= far                # rows before the far key cannot read it
     assert sees.any()
     assert torch.allclose(out[sees].float(), torch.full_like(out[sees], 7.0).float(), atol=0.05)
     out = torch.zeros_like(q[:1])
     case1 = dict(case, q=q[:1], pos=case["pos"][:1], seq=case["seq"][:1], extents=[1], firsts=[499])
-    ops().paged_attention(q[:1], out, H, Hkv, dh, Cache(case, ps), Ctx(case1, True), scale, 0)
+    attention_part().paged_attention(q[:1], out, H, Hkv, dh, Cache(case, ps), Ctx(case1, True), scale, 0)
     assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05)
 
 
@@ -344,7 +350,7 @@ def test_attention_window_edge(dtype):
         q[:, 0::dh] = 8.0
         for decode in (True, False):
             out = torch.zeros_like(q)
-            ops().paged_attention(q, out, H, Hkv, dh, Cache(case, ps), Ctx(case, decode),
+            attention_part().paged_attention(q, out, H, Hkv, dh, Cache(case, ps), Ctx(case, decode),
                                   1 / math.sqrt(dh), W)
             assert torch.allclose(out.float(), torch.full_like(out, expect).float(), atol=0.05)
 
@@ -355,7 +361,7 @@ def test_attention_unusual_head_size_falls_back():
     case = paged_case([33, 1], [0, 50], H, Hkv, dh, ps, torch.bfloat16)
     want = attention_ref(case, H, Hkv, dh, 0.1, 0)
     out = torch.zeros_like(case["q"])
-    ops().paged_attention(case["q"], out, H, Hkv, dh, Cache(case, ps), Ctx(case, False), 0.1, 0)
+    attention_part().paged_attention(case["q"], out, H, Hkv, dh, Cache(case, ps), Ctx(case, False), 0.1, 0)
     assert torch.allclose(out.float().cpu(), want, **tol(torch.bfloat16))
 
 
@@ -487,26 +493,6 @@ def test_gemm_skinny_gated_output(M, f, K):
     # and gated_linear picks either
     got = ops().gated_linear(x, w, True)
     assert torch.allclose(got.float(), want, rtol=2e-2, atol=2e-2)
-
-
-@pytest.mark.parametrize("M,N,K", [(1, 48, 64), (7, 100, 96), (16, 33, 4096)])
-def test_gemm_skinny_folds_the_norm(M, N, K):
-    h = rnd(M, K, seed=8, scale=3.0)
-    gain = 1 + 0.1 * rnd(K, seed=9)
-    w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=10)
-    eps = 1e-5
-    normed = (h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps)) * gain
-    want = normed @ w.float().t()
-    x = ops().NormedRows(h, gain, eps, torch.bfloat16)
-    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
-    ops().gemm_skinny(x, w, out)
-    # K products of two bfloat16-rounded factors (relative error 2^-9 each, random sign):
-    # three standard deviations of their sum
-    atol = 3 * 2.0 ** -8.5 * math.sqrt(K) * float(normed.pow(2).mean().sqrt()) * 0.1
-    assert torch.allclose(out, want, rtol=0, atol=atol)
-    # and the unfolded route agrees
-    y = ops().linear(x.materialize(), w, out_dtype=torch.float32)
-    assert torch.allclose(y, want, rtol=0, atol=atol)
 
 
 # ------------------------------------------------------------------ tcgen05 product
@@ -655,51 +641,6 @@ def test_linear_picks_by_rows_and_agrees():
     assert tc_flag() == 0
 
 
-# --------------------------------------------------------------------- chain of products
-
-
-@pytest.mark.parametrize("M,d,a_w,f,qkv_n", [(1, 64, 64, 128, 128), (3, 96, 192, 224, 320),
-                                              (5, 1000, 520, 1008, 776), (8, 2048, 1024, 3072, 1536)])
-def test_gemm_chain(M, d, a_w, f, qkv_n):
-    """o-projection into the stream, norm + gate/up + gate, down into the stream, norm + the
-    next q/k/v, as one kernel, against float32 matrix products with the same roundings.
-    Run twice: the barrier's state carries over from launch to launch."""
-    o = ops()
-
-    def bf(*s, seed):
-        return rnd(*s, scale=0.05, seed=seed).to(torch.bfloat16)
-
-    eps = 1e-6
-    h = rnd(M, d, scale=2.0, seed=1)
-    g1, g2 = 1 + 0.1 * rnd(d, seed=2), 1 + 0.1 * rnd(d, seed=3)
-    wqkv, wo = bf(qkv_n, d, seed=4), bf(d, a_w, seed=5)
-    wg, wu, wd = bf(f, d, seed=6), bf(f, d, seed=7), bf(d, f, seed=8)
-    wgu = torch.stack([wg.view(f // 8, 8, d), wu.view(f // 8, 8, d)], dim=1).reshape(2 * f, d).contiguous()
-    a = rnd(M, a_w, seed=9).to(torch.bfloat16)
-
-    def norm(x, g):
-        return ((x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)) * g).to(torch.bfloat16).float()
-
-    h_want = h + a.float() @ wo.float().t()
-    n2 = norm(h_want, g2)
-    gt = (n2 @ wg.float().t()).to(torch.bfloat16).float()
-    up = (n2 @ wu.float().t()).to(torch.bfloat16).float()
-    act_want = (gt / (1 + torch.exp(-gt)) * up).to(torch.bfloat16).float()
-    h_want = h_want + act_want @ wd.float().t()
-    qkv_want = norm(h_want, g1) @ wqkv.float().t()
-    for _ in range(2):
-        hh = h.clone()
-        act = torch.zeros(M, f, dtype=torch.bfloat16, device=DEV)
-        qkv = torch.zeros(M, qkv_n, dtype=torch.bfloat16, device=DEV)
-        o.gemm_chain([(a, wo, hh, "add"), (o.NormedRows(hh, g2, eps, torch.bfloat16), wgu, act, "gated"),
-                      (act, wd, hh, "add"), (o.NormedRows(hh, g1, eps, torch.bfloat16), wqkv, qkv, "bf16")], M)
-        torch.cuda.synchronize()
-        assert int(o.gemm_chain_error_flag(DEV).item()) == 0
-        assert torch.allclose(act.float(), act_want, rtol=3e-2, atol=3e-2 * act_want.abs().max().item())
-        assert torch.allclose(hh, h_want, rtol=1e-2, atol=1e-2 * h_want.abs().max().item())
-        assert torch.allclose(qkv.float(), qkv_want, rtol=3e-2, atol=3e-2 * qkv_want.abs().max().item())
-
-
 # --------------------------------------------------------------------- attention on tcgen05
 
 
@@ -734,7 +675,7 @@ def test_attention_tc_prefill(extents, firsts, H, Hkv, ps, window, persistent, m
     scale = 1 / math.sqrt(dh)
     want = attention_ref(case, H, Hkv, dh, scale, window)
     out = torch.full_like(case["q"], float("nan"))
-    tok0, ntok = o._tiles(Ctx(case, False), 128 // (H // Hkv))
+    tok0, ntok = attention_part().step_tiles(Ctx(case, False), 128 // (H // Hkv))
     o.attention_tc_prefill(case["q"], out, H, Hkv, dh, case["kc"], case["vc"], ps, case["bt"],
                            case["pos"], case["seq"], tok0, ntok, scale, window)
     torch.cuda.synchronize()
@@ -758,7 +699,7 @@ def test_attention_tc_far_key_and_growing_scores():
         q[:, 0::dh] = 8.0
         case["q"] = q
         out = torch.zeros_like(q)
-        ops().paged_attention(q, out, H, Hkv, dh, Cache(case, ps), Ctx(case, False), 1 / math.sqrt(dh), 0)
+        attention_part().paged_attention(q, out, H, Hkv, dh, Cache(case, ps), Ctx(case, False), 1 / math.sqrt(dh), 0)
         sees = case["pos"] >= far
         assert torch.allclose(out[sees].float(), torch.full_like(out[sees], 7.0).float(), atol=0.05), far
 
@@ -772,7 +713,7 @@ def test_attention_tc_far_key_and_growing_scores():
     case["q"] = q
     want = attention_ref(case, H, Hkv, dh, 1.0, 0)
     out = torch.zeros_like(q)
-    ops().paged_attention(q, out, H, Hkv, dh, Cache(case, ps), Ctx(case, False), 1.0, 0)
+    attention_part().paged_attention(q, out, H, Hkv, dh, Cache(case, ps), Ctx(case, False), 1.0, 0)
     assert ops().attention_tc_error() == 0
     assert torch.allclose(out.float().cpu(), want, **tol(torch.bfloat16))
 

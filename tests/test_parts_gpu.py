@@ -43,8 +43,6 @@ def test_rmsnorm_part(dtype):
     want = plain.rmsnorm((h + delta).double().numpy(), gain.double().numpy(), eps)
     assert np.abs(out.float().cpu().numpy() - want).max() < tol(dtype, np.abs(want).max())
     assert torch.allclose(hd.cpu(), h + delta, atol=1e-6)          # the add stays in the stream
-    lazy = part.lazy(hd, None, dtype)
-    assert torch.equal(lazy.materialize(), part.forward(hd, None, dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -72,9 +70,12 @@ def test_rope_part(dtype, dh, rot):
 def test_swiglu_part(dtype, T, d, f):
     from tgo_b200.config.spec import FeedForwardSpec
     from tgo_b200.parts.feed_forward import SwiGLU
-    part = SwiGLU(FeedForwardSpec("swiglu", f), d, "mlp.")
+    from tgo_b200.config.qwen3 import FEED_FORWARD_TENSORS
+    part = SwiGLU(FeedForwardSpec("swiglu", f, tensors=FEED_FORWARD_TENSORS), d, "")
     assert {w.name: w.shape for w in part.weight_specs()} == {
         "mlp.gate_proj.weight": (f, d), "mlp.up_proj.weight": (f, d), "mlp.down_proj.weight": (d, f)}
+    with pytest.raises(ValueError, match="names no tensor for the role 'down'"):
+        SwiGLU(FeedForwardSpec("swiglu", f, tensors=FEED_FORWARD_TENSORS[:2]), d, "")
     w = {n: bf16_exact(rnd(*s.shape, scale=0.2, seed=i)) for i, (n, s) in
          enumerate((s.name, s) for s in part.weight_specs())}
     part.bind({n: t.to(dtype).to(DEV) for n, t in w.items()})
@@ -99,9 +100,13 @@ def test_swiglu_part(dtype, T, d, f):
 def attention_setup(dtype, window, H=6, Hkv=2, dh=32, d=96, theta=1e4, eps=1e-5):
     from tgo_b200.config.spec import MixerSpec, PositionSpec
     from tgo_b200.parts.attention import GQAAttention
+    names = tuple((role, "a." + role + ("_norm.weight" if role.endswith("norm") else "_proj.weight"))
+                  for role in ("q", "k", "v", "o")) + (("q_norm", "a.q_norm.weight"),
+                                                      ("k_norm", "a.k_norm.weight"))
     spec = MixerSpec("gqa_attention", H, Hkv, dh, qk_norm=True, window=window,
-                     position=PositionSpec("rope_half_split", dh, theta), norm_eps=eps)
-    part = GQAAttention(spec, d, "a.", DEV)
+                     position=PositionSpec("rope_half_split", dh, theta), norm_eps=eps,
+                     tensors=names)
+    part = GQAAttention(spec, d, "", DEV)
     w = {}
     for i, s in enumerate(part.weight_specs()):
         t = rnd(*s.shape, scale=0.15, seed=20 + i)
@@ -119,15 +124,14 @@ def test_attention_part_whole_and_in_portions(dtype, window):
     portions beside another request's single tokens."""
     from tgo_b200.parts.base import CacheNeed, LayerCache, StepContext
     part, w, cfg = attention_setup(dtype, window)
-    assert part.cache_need() == CacheNeed("window" if window else "full", window, 2, 32)
+    assert part.cache_need() == CacheNeed("window" if window else "full", window, 2, (2, 32))
     assert part.state_need() is None
     T, ps, d = 45, 8, 96
     x = bf16_exact(rnd(T, d, seed=3))
     want = plain.attention_block(x.double().numpy(), np.arange(T),
                                  {k: v.double().numpy() for k, v in w.items()}, "a.", cfg, window)
     pages = 16
-    kc = torch.zeros(pages, 2, ps, 32, dtype=dtype, device=DEV)
-    vc = torch.zeros_like(kc)
+    planes = torch.zeros(2, pages, 2, ps, 32, dtype=dtype, device=DEV)      # keys, values
     table = torch.tensor([[9, 3, 12, 1, 7, 5], [2, 4, 6, 8, 10, 11]], dtype=torch.int32, device=DEV)
 
     def step(chunks):
@@ -146,7 +150,7 @@ def test_attention_part_whole_and_in_portions(dtype, window):
                           max_context=max(c[1] + c[2].shape[0] for c in chunks),
                           decode_only=all(c[2].shape[0] == 1 for c in chunks))
         tb = torch.stack([table[c[0]] for c in chunks]).contiguous()
-        cache = LayerCache(kc, vc, ps, tb, i32(slots), True)
+        cache = LayerCache(planes, ps, tb, i32(slots), True)
         out = part.forward(torch.cat(rows).to(dtype).to(DEV), ctx, cache)
         return out.float().cpu().numpy()
     got = step([(0, 0, x)])
@@ -201,16 +205,17 @@ class DecayMixer:
     (a test part; the package's own mixers use its kernels)."""
 
     def __init__(self, spec, hidden, prefix, device=None):
-        self.hidden, self.prefix = hidden, prefix
+        self.hidden = hidden
+        self.name = prefix + dict(spec.tensors)["mix"]
         self.decay = dict(spec.extra)["decay"]
         self.w = None
 
     def weight_specs(self):
         from tgo_b200.weights.binder import WeightSpec
-        return [WeightSpec(self.prefix + "mix.weight", (self.hidden, self.hidden))]
+        return [WeightSpec(self.name, (self.hidden, self.hidden))]
 
     def bind(self, weights):
-        self.w = weights.pop(self.prefix + "mix.weight")
+        self.w = weights.pop(self.name)
 
     def cache_need(self):
         return None
@@ -267,7 +272,8 @@ class RoutedFeedForward:
     device, without a trip to the host, so decode steps with it are captured."""
 
     def __init__(self, spec, hidden, prefix, device=None):
-        self.hidden, self.inter, self.prefix = hidden, spec.intermediate_size, prefix
+        self.hidden, self.inter = hidden, spec.intermediate_size
+        self.prefix = prefix + dict(spec.tensors)["root"]
         self.experts = dict(spec.extra)["experts"]
 
     def weight_specs(self):
@@ -300,15 +306,23 @@ def toy_spec(raw):
                                       NormSpec, PositionSpec)
     d, V = raw["width"], raw["vocab"]
     norm = NormSpec("rmsnorm", raw["eps"])
-    ffn = FeedForwardSpec("swiglu", raw["inner"])
-    ffn0 = FeedForwardSpec("test_routed", raw["inner"], extra=(("experts", raw["experts"]),)) \
-        if raw.get("experts") else ffn
+    # the toy checkpoint has names of its own, and ships q, k and v as one matrix in layer 1
+    # and gate and up as one matrix in both layers: the package's parts take the tables as given
+    ffn = FeedForwardSpec("swiglu", raw["inner"],
+                          tensors=(("gate_up", "ff.gu.weight"), ("down", "ff.out.weight")))
+    ffn0 = FeedForwardSpec("test_routed", raw["inner"], tensors=(("root", "moe."),),
+                           extra=(("experts", raw["experts"]),)) if raw.get("experts") else ffn
+    block = (("mixer_norm", "n1.weight"), ("ffn_norm", "n2.weight"))
     layers = [LayerSpec("prenorm_residual", "layers.0.",
-                        MixerSpec(raw.get("mixer", "test_decay"), extra=(("decay", raw["decay"]),)),
-                        ffn0, norm, names=(("mixer", "decay."),)),
+                        MixerSpec(raw.get("mixer", "test_decay"), tensors=(("mix", "decay.mix.weight"),),
+                                  extra=(("decay", raw["decay"]),)),
+                        ffn0, norm, block),
               LayerSpec("prenorm_residual", "layers.1.",
                         MixerSpec("gqa_attention", 4, 2, 16, qk_norm=True,
-                                  position=PositionSpec("test_shift"), norm_eps=raw["eps"]), ffn, norm)]
+                                  position=PositionSpec("test_shift"), norm_eps=raw["eps"],
+                                  tensors=(("qkv", "att.qkv.weight"), ("o", "att.out.weight"),
+                                           ("q_norm", "att.qn.weight"), ("k_norm", "att.kn.weight"))),
+                        ffn, norm, block)]
     return ModelSpec("ToyForTests", d, V, layers, [LayerCall(0), LayerCall(1)], norm, "embed.weight",
                      "norm.weight", None, source=dict(raw))
 
@@ -333,36 +347,40 @@ def toy_plain(w, raw, toks):
     eps, T = raw["eps"], len(toks)
     h = w["embed.weight"][np.asarray(toks)]
     # layer 0: the decay mixer
-    n = plain.rmsnorm(h, w["layers.0.input_layernorm.weight"], eps)
+    n = plain.rmsnorm(h, w["layers.0.n1.weight"], eps)
     s, ys = np.zeros(raw["width"]), []
     for t in range(T):
         s = raw["decay"] * s + n[t]
         ys.append(s @ w["layers.0.decay.mix.weight"].T)
     h = h + np.stack(ys)
-    n = plain.rmsnorm(h, w["layers.0.post_attention_layernorm.weight"], eps)
+    f = raw["inner"]
+
+    def joined_ffn(layer, x):
+        gu = w[f"layers.{layer}.ff.gu.weight"]
+        return plain.swiglu_mlp(x, gu[:f], gu[f:], w[f"layers.{layer}.ff.out.weight"])
+    n = plain.rmsnorm(h, w["layers.0.n2.weight"], eps)
     if raw.get("experts"):
-        choice = np.argmax(n @ w["layers.0.mlp.router.weight"].T, axis=1)
+        choice = np.argmax(n @ w["layers.0.moe.router.weight"].T, axis=1)
         ys = []
         for t in range(T):
-            u = w[f"layers.0.mlp.experts.{choice[t]}.up.weight"] @ n[t]
-            ys.append(w[f"layers.0.mlp.experts.{choice[t]}.down.weight"] @ (u / (1 + np.exp(-u))))
+            u = w[f"layers.0.moe.experts.{choice[t]}.up.weight"] @ n[t]
+            ys.append(w[f"layers.0.moe.experts.{choice[t]}.down.weight"] @ (u / (1 + np.exp(-u))))
         h = h + np.stack(ys)
     else:
-        h = h + plain.swiglu_mlp(n, w["layers.0.mlp.gate_proj.weight"], w["layers.0.mlp.up_proj.weight"],
-                                 w["layers.0.mlp.down_proj.weight"])
-    # layer 1: attention with the shift encoding
-    p = "layers.1.self_attn."
-    n = plain.rmsnorm(h, w["layers.1.input_layernorm.weight"], eps)
-    q = plain.rmsnorm(plain.linear(n, w[p + "q_proj.weight"]).reshape(T, 4, 16), w[p + "q_norm.weight"], eps)
-    k = plain.rmsnorm(plain.linear(n, w[p + "k_proj.weight"]).reshape(T, 2, 16), w[p + "k_norm.weight"], eps)
-    v = plain.linear(n, w[p + "v_proj.weight"]).reshape(T, 2, 16)
+        h = h + joined_ffn(0, n)
+    # layer 1: attention with the shift encoding, q, k, v from one joined matrix
+    p = "layers.1.att."
+    n = plain.rmsnorm(h, w["layers.1.n1.weight"], eps)
+    qkv = plain.linear(n, w[p + "qkv.weight"])
+    q = plain.rmsnorm(qkv[:, :64].reshape(T, 4, 16), w[p + "qn.weight"], eps)
+    k = plain.rmsnorm(qkv[:, 64:96].reshape(T, 2, 16), w[p + "kn.weight"], eps)
+    v = qkv[:, 96:].reshape(T, 2, 16)
     q[:, :, 0] += np.arange(T)[:, None] / 64
     k[:, :, 0] += np.arange(T)[:, None] / 64
     a = plain.causal_gqa_attention(q, k, v, 0.25).reshape(T, 64)
-    h = h + plain.linear(a, w[p + "o_proj.weight"])
-    n = plain.rmsnorm(h, w["layers.1.post_attention_layernorm.weight"], eps)
-    h = h + plain.swiglu_mlp(n, w["layers.1.mlp.gate_proj.weight"], w["layers.1.mlp.up_proj.weight"],
-                             w["layers.1.mlp.down_proj.weight"])
+    h = h + plain.linear(a, w[p + "out.weight"])
+    n = plain.rmsnorm(h, w["layers.1.n2.weight"], eps)
+    h = h + joined_ffn(1, n)
     return plain.linear(plain.rmsnorm(h, w["norm.weight"], eps), w["embed.weight"])
 
 

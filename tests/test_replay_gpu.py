@@ -56,23 +56,6 @@ def test_float32_cuts_agree_bit_for_bit(models, name):
             assert np.array_equal(row, base[k]), f"{name}: {fam} differs from whole at {k}"
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
-def test_decode_with_chained_products_matches_plain(models, name, monkeypatch):
-    """The optional one-kernel chain of a decode step's products (off by default) gives the
-    plain implementation's logits too: the last 32 tokens of each request come one by one."""
-    import tgo_b200
-    from tgo_b200.kernels import ops
-    monkeypatch.setattr(ops, "USE_CHAINS", True)
-    d, cfg, run, reqs, want = models[name]
-    model = tgo_b200.open(d, dtype="bfloat16")
-    trace = tiny.trace_tail(reqs)
-    eng = model.new_engine(page_size=run["page_size"], max_tokens=tiny.max_tokens_of(trace), num_slots=4)
-    got = tiny.run_trace_engine(eng, trace)
-    worst, where, tol = tiny.compare(got, want, cfg, "bfloat16")
-    assert worst <= tol, f"{name}: error {worst:.3e} at {where}, allowed {tol:.3e}"
-    assert int(ops.gemm_chain_error_flag("cuda:0").item()) == 0
-
-
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["B", "C"])
 def test_prompt_portions_through_graphs_give_the_same_bits(models, name, dtype):

@@ -3,7 +3,9 @@ the runner over a fake engine (schedule_test.go:42-220 tests the reference's pol
 same way)."""
 import pytest
 
-from tgo_b200.cache.pages import CacheManager, GroupLayout, PagesExhausted
+from plain_cache import CacheManager
+from plain_schedule import next_step as plain_next_step, victim as plain_victim
+from tgo_b200.cache.pages import GroupLayout, PagesExhausted
 from tgo_b200.engine.scheduler import (ContextExhausted, NoSlot, Request, Runner, Scheduler,
                                        SlotState, next_step, victim)
 from tgo_b200.sampling.policy import Policy
@@ -62,7 +64,7 @@ class FakeEngine:
         pass
 
     def __init__(self, pages, page=4, slots=4):
-        self.cache = CacheManager([GroupLayout("full", None, 1, 8, [0])], page, [pages], slots)
+        self.cache = CacheManager([GroupLayout("full", None, 2, (1, 8), [0])], page, [pages], slots)
         self.model = self._Model()
         self.model.spec = self._Spec()
         self.steps = []
@@ -182,7 +184,6 @@ def test_native_policy_decides_as_the_plain_one(seed):
     over random slots, chunks and budgets."""
     import random
 
-    from tgo_b200.engine.scheduler import next_step_native, victim_native
     rng = random.Random(seed)
     for _ in range(300):
         slots = []
@@ -193,7 +194,7 @@ def test_native_policy_decides_as_the_plain_one(seed):
             slots.append(slot([rng.randrange(100) for _ in range(n)], done, feed,
                               arrived=rng.randrange(50), live=rng.random() < 0.8))
         chunk, budget = rng.randrange(1, 20), rng.randrange(1, 40)
-        assert next_step_native(slots, chunk, budget) == next_step(slots, chunk, budget)
-        assert victim_native(slots) == victim(slots)
+        assert next_step(slots, chunk, budget) == plain_next_step(slots, chunk, budget)
+        assert victim(slots) == plain_victim(slots)
     with pytest.raises(ValueError, match="chunk"):
-        next_step_native([slot([1, 2])], 0, 4)
+        next_step([slot([1, 2])], 0, 4)

@@ -157,8 +157,12 @@ class NativeCacheManager:
     def pages_for(self, n_tokens: int) -> int:
         return (n_tokens + self.page_size - 1) // self.page_size
 
-    def can_hold(self, n_tokens: int) -> bool:
-        return bool(self._lib.tgo_cache_can_hold(self._h, c_longlong(n_tokens)))
+    def can_hold(self, n_tokens: int, step_tokens: int = 1) -> bool:
+        """Could a request of this many tokens ever fit, with the pools empty, when it is run
+        in steps of at most `step_tokens` tokens (a window group holds the window and the
+        step's own tokens until the step has landed)?"""
+        return bool(self._lib.tgo_cache_can_hold(self._h, c_longlong(n_tokens),
+                                                 c_longlong(step_tokens)))
 
     # ------------------------------------------------------------------- lifecycle
     def admit(self, request_id, reserve_tokens: int = 0) -> NativeRequest:

@@ -205,11 +205,24 @@ def _layer_windows(raw: dict, L: int) -> tuple:
     return tuple([None] * L)
 
 
+# The checkpoint's tensor names below a layer's prefix, by the role each part asks for
+# (model/qwen3.go:57-67 is the reference's table for this architecture).
+ATTENTION_TENSORS = (("q", "self_attn.q_proj.weight"), ("k", "self_attn.k_proj.weight"),
+                     ("v", "self_attn.v_proj.weight"), ("o", "self_attn.o_proj.weight"),
+                     ("q_norm", "self_attn.q_norm.weight"), ("k_norm", "self_attn.k_norm.weight"))
+FEED_FORWARD_TENSORS = (("gate", "mlp.gate_proj.weight"), ("up", "mlp.up_proj.weight"),
+                        ("down", "mlp.down_proj.weight"))
+BLOCK_TENSORS = (("mixer_norm", "input_layernorm.weight"),
+                 ("ffn_norm", "post_attention_layernorm.weight"))
+
+
 def qwen3_model_spec(raw: dict) -> ModelSpec:
     """config.json (as a dict) -> ModelSpec. The weight names are the checkpoint's own
     (model/qwen3.go:18-26, :76-148): per layer input_layernorm, self_attn.{q,k,v,o}_proj,
     self_attn.{q,k}_norm, post_attention_layernorm, mlp.{gate,up,down}_proj."""
     c = Qwen3Config.from_dict(raw)
+    attention_tensors, ffn_tensors, block_tensors = \
+        ATTENTION_TENSORS, FEED_FORWARD_TENSORS, BLOCK_TENSORS
     norm = NormSpec("rmsnorm", c.rms_norm_eps)
     pos = PositionSpec("rope_half_split", rotary_dim=c.head_dim, theta=c.rope_theta)
     layers = []
@@ -217,9 +230,11 @@ def qwen3_model_spec(raw: dict) -> ModelSpec:
         mixer = MixerSpec("gqa_attention", num_heads=c.num_attention_heads,
                           num_kv_heads=c.num_key_value_heads, head_dim=c.head_dim,
                           qk_norm=True, window=c.layer_windows[i], position=pos,
-                          norm_eps=c.rms_norm_eps)
-        ffn = FeedForwardSpec("swiglu", intermediate_size=c.intermediate_size)
-        layers.append(LayerSpec("prenorm_residual", f"model.layers.{i}.", mixer, ffn, norm))
+                          norm_eps=c.rms_norm_eps, tensors=attention_tensors)
+        ffn = FeedForwardSpec("swiglu", intermediate_size=c.intermediate_size,
+                              tensors=ffn_tensors)
+        layers.append(LayerSpec("prenorm_residual", f"model.layers.{i}.", mixer, ffn, norm,
+                                block_tensors))
     spec = ModelSpec(
         architecture=c.architecture, hidden_size=c.hidden_size, vocab_size=c.vocab_size,
         layers=layers, run_order=[LayerCall(i) for i in range(c.num_hidden_layers)],

@@ -12,7 +12,22 @@ model/layerkind.go:21-59).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Optional
+from typing import Dict, Iterable, Optional
+
+
+def tensor_names(tensors, prefix: str, roles: Iterable[str], what: str) -> Dict[str, str]:
+    """The checkpoint names a part asks for: `tensors` is the (role, name) table its spec
+    carries (names relative to the layer's prefix), `roles` the roles the part needs. A role
+    the table does not name is an error of the architecture's config reader, which owns the
+    table (model/qwen3.go:57-67 keeps it per architecture in the same way)."""
+    table = dict(tensors)
+    out = {}
+    for role in roles:
+        if role not in table:
+            raise ValueError(f"{what}: the spec names no tensor for the role {role!r}; "
+                             f"it names {sorted(table) or 'none'}")
+        out[role] = prefix + table[role]
+    return out
 
 
 @dataclass(frozen=True)
@@ -37,7 +52,9 @@ class MixerSpec:
 
     For attention kinds: `window` is None when a query reads every earlier key,
     else the number of most recent keys (its own included) that it reads.
-    `extra` carries what a mixer kind outside this package needs.
+    `tensors` is the (role, checkpoint name relative to the layer's prefix) table of the
+    mixer's weights; the roles are the mixer kind's own (attention: q, k, v or qkv joined, o,
+    q_norm, k_norm). `extra` carries what a mixer kind outside this package needs.
     """
     kind: str
     num_heads: int = 0
@@ -48,27 +65,32 @@ class MixerSpec:
     scale: Optional[float] = None        # None: 1/sqrt(head_dim)
     position: Optional[PositionSpec] = None
     norm_eps: float = 0.0                # eps of the per-head q/k norm
+    tensors: tuple = ()
     extra: tuple = ()
 
 
 @dataclass(frozen=True)
 class FeedForwardSpec:
-    """The per-token part of a layer. kind names a registered feed-forward."""
+    """The per-token part of a layer. kind names a registered feed-forward. `tensors` as in
+    MixerSpec (gated feed-forward: gate, up or gate_up joined, down)."""
     kind: str
     intermediate_size: int = 0
+    tensors: tuple = ()
     extra: tuple = ()
 
 
 @dataclass(frozen=True)
 class LayerSpec:
     """One layer: which block arrangement, and the parts inside it.
-    `prefix` is the tensor-name prefix of the layer's weights ("model.layers.3.")."""
+    `prefix` is the tensor-name prefix of the layer's weights ("model.layers.3."); every
+    part of the layer gets it and adds the names of its own spec's `tensors` table.
+    `tensors` names the block's own weights (pre-norm block: mixer_norm, ffn_norm)."""
     block: str
     prefix: str
     mixer: MixerSpec
     feed_forward: FeedForwardSpec
     norm: NormSpec
-    names: tuple = ()      # (role, tensor-name suffix) pairs that differ from the block's own
+    tensors: tuple = ()
 
 
 @dataclass(frozen=True)

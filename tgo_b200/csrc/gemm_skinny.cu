@@ -15,10 +15,9 @@
 // thread's eight consecutive k values serve as the (2t, 2t+1) and (2t+8, 2t+9) pairs of two
 // k-steps. W is read with a no-allocate hint (each byte is used once); x stays cached.
 //
-// Input forms:  x bfloat16 [M,K];  or the float32 residual stream h [M,K] with a gain [K],
-// in which case the product is taken with bf16(h * gain) and each row of the result is
-// scaled by rsqrt(mean(h^2) + eps) at the end: RMSNorm without a kernel of its own (every
-// CTA forms the row sums itself, in a fixed order).
+// Input: x bfloat16 [M,K]. (Taking the float32 residual stream and a gain instead, RMSNorm
+// folded into the product, was measured slower at every batch size: every CTA re-reads the
+// stream and the gain.)
 // Output forms:  bfloat16 or float32 [M,N];  added into a float32 [M,N] (the residual);  or,
 // for a gate/up matrix whose rows are interleaved in eights (8 gate rows, the 8 matching up
 // rows, ...), silu(gate) * up as bfloat16 [M, N/2].
@@ -31,8 +30,6 @@
 #define GS_NARROW_UNROLL 4      // the same for a matrix with too few rows to fill the GPU
 #endif
 
-#define GS_X_BF16 0
-#define GS_X_NORM 1
 #define GS_OUT_BF16 0
 #define GS_OUT_F32 1
 #define GS_OUT_ADD_F32 2
@@ -55,30 +52,17 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *(uint32_t*)&v;
 }
 
-template <int XMODE>
-__device__ __forceinline__ uint4 load_x(const void* __restrict__ x, const float* __restrict__ gain,
-                                        int m, int M, int K, int kk, bool valid_k, float& ss) {
-    uint4 z = make_uint4(0u, 0u, 0u, 0u);
-    if (m >= M || !valid_k) return z;
-    if (XMODE == GS_X_BF16) return *(const uint4*)((const bf16*)x + (size_t)m * K + kk);
-    const float* row = (const float*)x + (size_t)m * K + kk;
-    const float4 h0 = *(const float4*)row, h1 = *(const float4*)(row + 4);
-    const float4 g0 = *(const float4*)(gain + kk), g1 = *(const float4*)(gain + kk + 4);
-    ss += h0.x * h0.x + h0.y * h0.y + h0.z * h0.z + h0.w * h0.w + h1.x * h1.x + h1.y * h1.y +
-          h1.z * h1.z + h1.w * h1.w;
-    z.x = pack2(h0.x * g0.x, h0.y * g0.y);
-    z.y = pack2(h0.z * g0.z, h0.w * g0.w);
-    z.z = pack2(h1.x * g1.x, h1.y * g1.y);
-    z.w = pack2(h1.z * g1.z, h1.w * g1.w);
-    return z;
+__device__ __forceinline__ uint4 load_x(const bf16* __restrict__ x, int m, int M, int K, int kk,
+                                        bool valid_k) {
+    if (m >= M || !valid_k) return make_uint4(0u, 0u, 0u, 0u);
+    return *(const uint4*)(x + (size_t)m * K + kk);
 }
 
-template <int MT, int XMODE, int OMODE, int GS_WARPS, int UNROLL>
+template <int MT, int OMODE, int GS_WARPS, int UNROLL>
 __global__ void __launch_bounds__(GS_WARPS * 32)
-gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, float eps,
-                   const bf16* __restrict__ w, void* __restrict__ y, int M, int N, int K) {
+gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void* __restrict__ y,
+                   int M, int N, int K) {
     __shared__ float red[GS_WARPS][16][MT * 8 + 1];
-    __shared__ float red_ss[GS_WARPS][MT * 8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * 16;
@@ -93,9 +77,8 @@ gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, f
     constexpr int STEP = 32 * UNROLL;
 
     float acc[MT][4];
-    float ss[MT];
 #pragma unroll
-    for (int j = 0; j < MT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; ss[j] = 0.f; }
+    for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
     uint4 a_lo[UNROLL], a_hi[UNROLL], b_lo[UNROLL], b_hi[UNROLL];
     auto load_w = [&](uint4 (&lo)[UNROLL], uint4 (&hi)[UNROLL], int k) {
@@ -114,7 +97,7 @@ gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, f
             const bool v = kk < k_end;
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
-                const uint4 b = load_x<XMODE>(x, gain, j * 8 + g, M, K, kk, v, ss[j]);
+                const uint4 b = load_x(x, j * 8 + g, M, K, kk, v);
                 mma_bf16_16816(acc[j], lo[u].x, hi[u].x, lo[u].y, hi[u].y, b.x, b.y);
                 mma_bf16_16816(acc[j], lo[u].z, hi[u].z, lo[u].w, hi[u].w, b.z, b.w);
             }
@@ -139,12 +122,6 @@ gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, f
         red[warp][g][j * 8 + 2 * t + 1] = acc[j][1];
         red[warp][g + 8][j * 8 + 2 * t] = acc[j][2];
         red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
-        if (XMODE == GS_X_NORM) {
-            float s = ss[j];
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            if (t == 0) red_ss[warp][j * 8 + g] = s;
-        }
     }
     __syncthreads();
     if (OMODE == GS_OUT_SWIGLU) {
@@ -156,14 +133,6 @@ gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, f
             float gt = 0.f, up = 0.f;
 #pragma unroll
             for (int wv = 0; wv < GS_WARPS; ++wv) { gt += red[wv][r][m]; up += red[wv][r + 8][m]; }
-            if (XMODE == GS_X_NORM) {
-                float tot = 0.f;
-#pragma unroll
-                for (int wv = 0; wv < GS_WARPS; ++wv) tot += red_ss[wv][m];
-                const float sc = rsqrtf(tot / (float)K + eps);
-                gt *= sc;
-                up *= sc;
-            }
             // the gate and up values pass through bfloat16 as they do when the product is
             // stored before the gate is applied
             gt = __bfloat162float(__float2bfloat16_rn(gt));
@@ -180,12 +149,6 @@ gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, f
         float s = 0.f;
 #pragma unroll
         for (int wv = 0; wv < GS_WARPS; ++wv) s += red[wv][r][m];
-        if (XMODE == GS_X_NORM) {
-            float tot = 0.f;
-#pragma unroll
-            for (int wv = 0; wv < GS_WARPS; ++wv) tot += red_ss[wv][m];
-            s *= rsqrtf(tot / (float)K + eps);
-        }
         const size_t at = (size_t)m * N + n;
         if (OMODE == GS_OUT_BF16) ((bf16*)y)[at] = __float2bfloat16_rn(s);
         else if (OMODE == GS_OUT_F32) ((float*)y)[at] = s;
@@ -193,23 +156,23 @@ gemm_skinny_kernel(const void* __restrict__ x, const float* __restrict__ gain, f
     }
 }
 
-template <int MT, int XMODE, int WARPS, int UNROLL>
-static int gs_launch_o(const void* x, const float* gain, float eps, const bf16* w, void* y, int M,
-                       int N, int K, int omode, cudaStream_t s) {
+template <int MT, int WARPS, int UNROLL>
+static int gs_launch_o(const bf16* x, const bf16* w, void* y, int M, int N, int K, int omode,
+                       cudaStream_t s) {
     const dim3 grid((N + 15) / 16), block(WARPS * 32);
     switch (omode) {
         case GS_OUT_BF16:
-            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_BF16, WARPS, UNROLL>, grid, block, 0,
-                                  s, x, gain, eps, w, y, M, N, K);
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, GS_OUT_BF16, WARPS, UNROLL>, grid, block, 0, s,
+                                  x, w, y, M, N, K);
         case GS_OUT_F32:
-            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_F32, WARPS, UNROLL>, grid, block, 0,
-                                  s, x, gain, eps, w, y, M, N, K);
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, GS_OUT_F32, WARPS, UNROLL>, grid, block, 0, s,
+                                  x, w, y, M, N, K);
         case GS_OUT_ADD_F32:
-            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_ADD_F32, WARPS, UNROLL>, grid, block,
-                                  0, s, x, gain, eps, w, y, M, N, K);
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, GS_OUT_ADD_F32, WARPS, UNROLL>, grid, block, 0,
+                                  s, x, w, y, M, N, K);
         default:
-            return tgo_launch_pdl(gemm_skinny_kernel<MT, XMODE, GS_OUT_SWIGLU, WARPS, UNROLL>, grid, block,
-                                  0, s, x, gain, eps, w, y, M, N, K);
+            return tgo_launch_pdl(gemm_skinny_kernel<MT, GS_OUT_SWIGLU, WARPS, UNROLL>, grid, block, 0,
+                                  s, x, w, y, M, N, K);
     }
 }
 
@@ -220,8 +183,8 @@ static int gs_launch_o(const void* x, const float* gain, float eps, const bf16* 
 // in flight, at 110 registers; where there are more CTAs than that, three an SM with the
 // smaller sets are better.
 template <int MT>
-static int gs_launch(const void* x, const float* gain, float eps, const bf16* w, void* y, int M,
-                     int N, int K, int xmode, int omode, cudaStream_t s) {
+static int gs_launch(const bf16* x, const bf16* w, void* y, int M, int N, int K, int omode,
+                     cudaStream_t s) {
     static int sms = 0;
     if (!sms) {
         int dev = 0;
@@ -230,27 +193,23 @@ static int gs_launch(const void* x, const float* gain, float eps, const bf16* w,
             sms = 148;
     }
     const bool narrow = MT == 1 && GS_NARROW_UNROLL != GS_UNROLL && (N + 15) / 16 <= 2 * sms && K >= 2048;
-    if (xmode == GS_X_BF16) {
-        if constexpr (MT == 1) {        // only this one is built with the larger sets
-            if (narrow) return gs_launch_o<MT, GS_X_BF16, 8, GS_NARROW_UNROLL>(x, gain, eps, w, y, M, N, K, omode, s);
-        }
-        return gs_launch_o<MT, GS_X_BF16, 8, GS_UNROLL>(x, gain, eps, w, y, M, N, K, omode, s);
+    if constexpr (MT == 1) {        // only this one is built with the larger sets
+        if (narrow) return gs_launch_o<MT, 8, GS_NARROW_UNROLL>(x, w, y, M, N, K, omode, s);
     }
-    return gs_launch_o<MT, GS_X_NORM, 8, GS_UNROLL>(x, gain, eps, w, y, M, N, K, omode, s);
+    return gs_launch_o<MT, 8, GS_UNROLL>(x, w, y, M, N, K, omode, s);
 }
 
 // Most rows this kernel takes; K must be a multiple of 8 (16-byte loads).
 TGO_API int tgo_gemm_skinny_max_rows() { return 64; }
 
-TGO_API int tgo_gemm_skinny(const void* x, const float* gain, float eps, const void* w, void* y,
-                            int M, int N, int K, int xmode, int omode, cudaStream_t stream) {
+TGO_API int tgo_gemm_skinny(const void* x, const void* w, void* y, int M, int N, int K, int omode,
+                            cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 || M > 64 || xmode < 0 || xmode > 1 || omode < 0 || omode > 3 ||
-        (xmode == GS_X_NORM && !gain) || (omode == GS_OUT_SWIGLU && N % 16))
+    if (K <= 0 || K % 8 || M > 64 || omode < 0 || omode > 3 || (omode == GS_OUT_SWIGLU && N % 16))
         return TGO_E_BAD_ARG;
-    const bf16* wp = (const bf16*)w;
-    if (M <= 8) return gs_launch<1>(x, gain, eps, wp, y, M, N, K, xmode, omode, stream);
-    if (M <= 16) return gs_launch<2>(x, gain, eps, wp, y, M, N, K, xmode, omode, stream);
-    if (M <= 32) return gs_launch<4>(x, gain, eps, wp, y, M, N, K, xmode, omode, stream);
-    return gs_launch<8>(x, gain, eps, wp, y, M, N, K, xmode, omode, stream);
+    const bf16 *xp = (const bf16*)x, *wp = (const bf16*)w;
+    if (M <= 8) return gs_launch<1>(xp, wp, y, M, N, K, omode, stream);
+    if (M <= 16) return gs_launch<2>(xp, wp, y, M, N, K, omode, stream);
+    if (M <= 32) return gs_launch<4>(xp, wp, y, M, N, K, omode, stream);
+    return gs_launch<8>(xp, wp, y, M, N, K, omode, stream);
 }

@@ -326,12 +326,16 @@ TGO_HOST_API int tgo_cache_page_is_held(void* p, int group, int page) {
 TGO_HOST_API int tgo_cache_free_slots(void* p) { return (int)M(p)->free_slots.size(); }
 TGO_HOST_API int tgo_cache_live_requests(void* p) { return (int)M(p)->requests.size(); }
 
-// Could a request of this many tokens ever fit, with the pools empty?
-TGO_HOST_API int tgo_cache_can_hold(void* p, long long n_tokens) {
+// Could a request of this many tokens ever fit, with the pools empty, when it is run in steps
+// of at most step_tokens tokens? A window group gives pages back only when a step has landed,
+// so during a step it holds the window and the step's own tokens.
+TGO_HOST_API int tgo_cache_can_hold(void* p, long long n_tokens, long long step_tokens) {
     Manager* m = M(p);
+    if (step_tokens < 1) step_tokens = 1;
     for (int g = 0; g < (int)m->kind.size(); ++g) {
         long long need = m->pages_for(n_tokens);
-        if (m->kind[g] == KIND_WINDOW) need = std::min(need, m->pages_for(m->window[g]) + 1);
+        if (m->kind[g] == KIND_WINDOW)
+            need = std::min(need, m->pages_for(m->window[g] - 1 + step_tokens) + 1);
         if (need > m->pools[g].num_pages) return 0;
     }
     return 1;

@@ -45,7 +45,7 @@ long long tgo_cache_pool(void* cache, int group, int what);
 int tgo_cache_page_is_held(void* cache, int group, int page);
 int tgo_cache_free_slots(void* cache);
 int tgo_cache_live_requests(void* cache);
-int tgo_cache_can_hold(void* cache, long long n_tokens);          /* 1 or 0 */
+int tgo_cache_can_hold(void* cache, long long n_tokens, long long step_tokens);   /* 1 or 0 */
 long long tgo_cache_slot_of(void* cache, long long handle, int group, long long position); /* row, or -1 */
 int tgo_cache_check(void* cache);
 

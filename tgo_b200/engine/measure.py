@@ -26,38 +26,17 @@ def round_up(n: int, m: int) -> int:
 
 def model_flops(model, n_tokens: int, first_position: int = 0, n_logit_rows: int = 1) -> float:
     """Floating-point operations of one step that runs `n_tokens` tokens of one request
-    starting at `first_position`: 2 per multiply-add of every matrix product, and of
-    q.K and w.V over the keys each token may read."""
-    spec = model.spec
-    d = spec.hidden_size
-    total = 0.0
-    for call in spec.run_order:
-        ls = spec.layers[call.layer]
-        m, f = ls.mixer, ls.feed_forward
-        H, Hkv, dh = m.num_heads, m.num_kv_heads, m.head_dim
-        kv = 0 if call.cache_from is not None else 2 * Hkv * dh
-        total += 2.0 * n_tokens * d * (H * dh + kv) + 2.0 * n_tokens * H * dh * d
-        total += 2.0 * n_tokens * d * 2 * f.intermediate_size + 2.0 * n_tokens * \
-            f.intermediate_size * d
-        keys = 0
-        for t in range(n_tokens):
-            p = first_position + t
-            keys += min(p + 1, m.window) if m.window else p + 1
-        total += 4.0 * H * dh * keys
-    total += 2.0 * n_logit_rows * d * spec.vocab_size
-    return total
+    starting at `first_position`: what every part of every call counts for itself (2 per
+    multiply-add of its matrix products, and of q.K and w.V over the keys each token may
+    read), plus the head's product. A part that counts nothing adds nothing."""
+    return model.flops([n_tokens], [first_position], n_logit_rows)
 
 
 def decode_bytes(model, context_lens) -> float:
-    """Bytes a decode step has to read: every weight it uses once, and the cached keys
-    and values of the live requests (window layers: at most the window)."""
-    width = 4 if model.dtype == torch.float32 else 2
-    kv = 0.0
-    for g in model.groups:
-        per_tok = 2 * len(g.calls) * g.num_kv_heads * g.head_dim * width
-        for c in context_lens:
-            kv += per_tok * (min(c, g.window) if g.kind == "window" else c)
-    return model.weight_bytes() + kv
+    """Bytes a decode step has to read: every weight it uses once, and what every mixer says
+    it reads of the live requests' cache (attention: keys and values, a window layer at most
+    its window)."""
+    return model.weight_bytes() + sum(model.cache_bytes_read(c) for c in context_lens)
 
 
 def load_peaks(path: Optional[str] = None) -> Dict[str, object]:

@@ -15,7 +15,7 @@ from ..cache.pages import GroupLayout
 from ..cache.storage import CacheStorage
 from ..config.spec import ModelSpec
 from ..kernels import ops
-from ..parts.base import LayerCache, StepContext
+from ..parts.base import LayerCache, StepContext, offered
 from ..registry import BLOCKS, NORMS
 from ..weights.binder import WeightSpec
 
@@ -67,7 +67,7 @@ class Model:
         seen, total = set(), 0
         tensors = [self.head]
         for b in self.blocks:
-            for part in b.parts():
+            for part in (b.parts() if hasattr(b, "parts") else [b]):
                 tensors += [v for v in vars(part).values() if isinstance(v, torch.Tensor)]
         for t in tensors:
             if t is None or t.dtype not in (torch.float32, torch.bfloat16):
@@ -92,11 +92,11 @@ class Model:
             mixer = self.blocks[call.layer].mixer
             need = mixer.cache_need() if hasattr(mixer, "cache_need") else None
             if need is not None:
-                key = (need.kind, need.window, need.num_kv_heads, need.head_dim)
+                key = (need.kind, need.window, need.planes, tuple(need.row_shape))
                 if key not in by_key:
                     by_key[key] = len(self.groups)
-                    self.groups.append(GroupLayout(need.kind, need.window, need.num_kv_heads,
-                                                   need.head_dim, []))
+                    self.groups.append(GroupLayout(need.kind, need.window, need.planes,
+                                                   need.row_shape, []))
                 self.groups[by_key[key]].calls.append(ci)
                 self.call_group[ci] = by_key[key]
             st = mixer.state_need() if hasattr(mixer, "state_need") else None
@@ -104,9 +104,41 @@ class Model:
                 self.state_shapes[ci] = tuple(st.shape)
 
     def cache_bytes_per_token(self) -> int:
-        """Bytes of keys and values one token adds over all full groups."""
+        """Bytes one token adds to the cache over all groups."""
         width = 4 if self.dtype == torch.float32 else 2
-        return sum(2 * len(g.calls) * g.num_kv_heads * g.head_dim * width for g in self.groups)
+        return sum(g.planes * len(g.calls) * g.row_elements * width for g in self.groups)
+
+    # ------------------------------------------------------- what the parts report
+    def libraries(self, page_size: int) -> List[str]:
+        """Kernel libraries the model's parts say they will call, without repeats."""
+        names = ["elementwise", "sgemm" if self.dtype == torch.float32 else "gemm_skinny"]
+        for b in self.blocks:
+            names += offered(b, "libraries")(self.dtype, page_size)
+        names += offered(self.final_norm, "libraries")(self.dtype, page_size)
+        return list(dict.fromkeys(names))
+
+    def prepare_capture(self, ctx: StepContext, storage: CacheStorage, group_tables,
+                        group_slots) -> None:
+        """Before a CUDA-graph capture of this step: every part makes what its forward would
+        otherwise make on the host."""
+        for ci, call in enumerate(self.spec.run_order):
+            cache = self.layer_cache(ci, ctx, storage, group_tables, group_slots)
+            offered(self.blocks[call.layer], "prepare_capture")(ctx, cache)
+
+    def flops(self, extents, first_positions, n_logit_rows: int = 1) -> float:
+        """Floating-point operations of one step, as the parts count their own, plus the
+        head's product."""
+        total = 0.0
+        for call in self.spec.run_order:
+            total += offered(self.blocks[call.layer], "flops")(extents, first_positions,
+                                                               call.cache_from is None)
+        return total + 2.0 * n_logit_rows * self.spec.hidden_size * self.spec.vocab_size
+
+    def cache_bytes_read(self, context_len: float) -> float:
+        """Bytes of cache one decoded token of a request at this context length reads."""
+        width = 4 if self.dtype == torch.float32 else 2
+        return sum(offered(self.blocks[call.layer], "cache_bytes_read")(context_len, width)
+                   for call in self.spec.run_order)
 
     # ------------------------------------------------------------------- forward
     def layer_cache(self, ci: int, ctx: StepContext, storage: CacheStorage,
@@ -115,7 +147,7 @@ class Model:
         owner = ci if call.cache_from is None else call.cache_from
         lc = LayerCache(writable=call.cache_from is None, page_size=storage.page_size)
         if owner in storage.where:
-            lc.k, lc.v, g = storage.layer(owner)
+            lc.planes, g = storage.layer(owner)
             lc.group = g
             lc.block_tables = group_tables[g]
             lc.slots = group_slots[g]
@@ -130,19 +162,9 @@ class Model:
         h = torch.empty((ctx.num_tokens, s.hidden_size), dtype=torch.float32, device=self.device)
         ops.embed(self.embedding, ctx.token_ids, h)
         pending = None
-        # a decode step of a few rows: the products of consecutive parts (and layers) are
-        # collected and run as chains in one persistent kernel each, if every block keeps to
-        # the kernels of this package
-        chained = ctx.decode_only and self.dtype == torch.bfloat16 and \
-            all(getattr(b, "chain_safe", False) for b in self.blocks) and \
-            ops.begin_chain(ctx.num_tokens)
-        try:
-            for ci, call in enumerate(s.run_order):
-                cache = self.layer_cache(ci, ctx, storage, group_tables, group_slots)
-                h, pending = self.blocks[call.layer].forward(h, pending, ctx, cache)
-        finally:
-            if chained:
-                ops.end_chain()
+        for ci, call in enumerate(s.run_order):
+            cache = self.layer_cache(ci, ctx, storage, group_tables, group_slots)
+            h, pending = self.blocks[call.layer].forward(h, pending, ctx, cache)
         n_want = ctx.logit_rows.numel()
         if n_want == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=self.device)

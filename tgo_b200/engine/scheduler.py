@@ -1,7 +1,7 @@
 """Continuous batching above the step function.
 
 Two layers, as in the reference: a pure policy that only looks at integers
-(`next_step`, `victim`: schedule.go:80-150) and a Scheduler that owns slots and drives
+(`next_step`, `victim`: schedule.go:80-150; decided in the native host library) and a Scheduler that owns slots and drives
 the engine (`admit / step / feed / finish / evict / feasible`: scheduler.go:72-390).
 Above them `Runner` keeps a waiting list and runs requests to completion.
 
@@ -56,54 +56,6 @@ class Work:
     prefill: bool
 
 
-def next_step(slots: Sequence[SlotState], chunk: int, budget: int) -> List[Work]:
-    """Which tokens the next step carries.
-
-    Pass 1: every live slot still in its prompt brings min(chunk, what is left of the
-    prompt, what is left of the budget), in slot order. Pass 2: every slot past its
-    prompt brings its one fed token. A slot left out just waits. The result is in slot
-    order. Unlike the reference, whose budget is the whole pool and never binds, the
-    budget here is a real limit on a step's tokens, so one token is set aside for every
-    decoding slot before the prompts share the rest: a long prompt cannot stall the
-    requests that are already producing.
-    """
-    if chunk <= 0:
-        raise ValueError(f"scheduler: the prefill chunk is {chunk}; a chunk is at least one token")
-    if budget <= 0:
-        raise ValueError(f"scheduler: a step of {budget} tokens carries nothing")
-    decoders = sum(1 for s in slots if s.live and not s.in_prompt() and s.feed is not None)
-    work, left = [], max(budget - decoders, 0)
-    for i, s in enumerate(slots):
-        if not s.live or not s.in_prompt():
-            continue
-        n = min(chunk, len(s.prompt) - s.prefilled, left)
-        if n <= 0:
-            continue
-        work.append(Work(i, s.prompt[s.prefilled:s.prefilled + n], True))
-        left -= n
-    left += min(decoders, budget)
-    for i, s in enumerate(slots):
-        if not s.live or s.in_prompt() or s.feed is None or left <= 0:
-            continue
-        work.append(Work(i, [s.feed], False))
-        left -= 1
-    work.sort(key=lambda w: w.slot)
-    return work
-
-
-def victim(slots: Sequence[SlotState]) -> int:
-    """The slot to evict: the latest arrival, one still in its prompt before any that
-    decodes (it has the least work to lose). -1 if none is live."""
-    best, best_key = -1, None
-    for i, s in enumerate(slots):
-        if not s.live:
-            continue
-        key = (1 if s.in_prompt() else 0, s.arrived)
-        if best_key is None or key > best_key:
-            best, best_key = i, key
-    return best
-
-
 def _policy_arrays(slots: Sequence[SlotState]):
     import numpy as np
     n = len(slots)
@@ -113,14 +65,25 @@ def _policy_arrays(slots: Sequence[SlotState]):
     return n, live, plen, done
 
 
-def next_step_native(slots: Sequence[SlotState], chunk: int, budget: int) -> List[Work]:
-    """`next_step` decided by the native host library (csrc/host_runtime.cpp): the same
-    work for the same slots, which the tests check over random states."""
+def next_step(slots: Sequence[SlotState], chunk: int, budget: int) -> List[Work]:
+    """Which tokens the next step carries, decided by the native host library
+    (tgo_schedule_next_step in csrc/host_runtime.cpp).
+
+    Pass 1: every live slot still in its prompt brings min(chunk, what is left of the
+    prompt, what is left of the budget), in slot order. Pass 2: every slot past its
+    prompt brings its one fed token. A slot left out just waits. The result is in slot
+    order. Unlike the reference, whose budget is the whole pool and never binds, the
+    budget here is a real limit on a step's tokens, so one token is set aside for every
+    decoding slot before the prompts share the rest: a long prompt cannot stall the
+    requests that are already producing.
+    """
     import numpy as np
 
     from ..kernels.build import load_library
-    if chunk <= 0 or budget <= 0:
-        return next_step(slots, chunk, budget)          # raises, naming the number
+    if chunk <= 0:
+        raise ValueError(f"scheduler: the prefill chunk is {chunk}; a chunk is at least one token")
+    if budget <= 0:
+        raise ValueError(f"scheduler: a step of {budget} tokens carries nothing")
     lib = load_library("host_runtime")
     n, live, plen, done = _policy_arrays(slots)
     feed = np.fromiter((0 if s.feed is None else 1 for s in slots), dtype=np.int32, count=n)
@@ -142,7 +105,10 @@ def next_step_native(slots: Sequence[SlotState], chunk: int, budget: int) -> Lis
     return work
 
 
-def victim_native(slots: Sequence[SlotState]) -> int:
+def victim(slots: Sequence[SlotState]) -> int:
+    """The slot to evict: the latest arrival, one still in its prompt before any that
+    decodes (it has the least work to lose). -1 if none is live. Decided by the native host
+    library (tgo_schedule_victim)."""
     import numpy as np
     from ctypes import c_int, c_void_p
 
@@ -194,8 +160,6 @@ class Scheduler:
         self.reserve = reserve
         self.budget = max_batched_tokens or (self.chunk + slots)
         self.slots = [SlotState() for _ in range(slots)]
-        # the policy is decided natively, as the engine's books are (TGO_NATIVE_HOST=0: here)
-        self.native = bool(getattr(engine, "_native", False))
         self._arrivals = 0
         self._ids = 0
 
@@ -208,7 +172,7 @@ class Scheduler:
         if prompt_len <= 0:
             raise ValueError("scheduler: the prompt is empty; there is nothing to condition on")
         reserve = self._reserve_for(reserve)
-        if not self.engine.cache.can_hold(prompt_len + reserve):
+        if not self.engine.cache.can_hold(prompt_len + reserve, min(self.chunk, self.budget)):
             raise ContextExhausted(f"scheduler: a {prompt_len}-token prompt with a reserve of "
                                    f"{reserve} needs more pages than the pool holds")
 
@@ -245,7 +209,7 @@ class Scheduler:
     def evict(self) -> int:
         """Drop the victim's pages and free its slot; the caller re-admits it later with
         its prompt and what it produced, to be computed again. -1 if nothing is live."""
-        v = (victim_native if self.native else victim)(self.slots)
+        v = victim(self.slots)
         if v >= 0:
             self.finish(v)
         return v
@@ -277,7 +241,7 @@ class Scheduler:
         """Plan with `next_step`, run the batch, advance the slots that worked.
         Raises PagesExhausted before anything ran if a slot cannot get its pages."""
         from .step import StepEntry
-        work = (next_step_native if self.native else next_step)(self.slots, self.chunk, self.budget)
+        work = next_step(self.slots, self.chunk, self.budget)
         if not work:
             return StepResult([], None)
         entries, produced, row = [], [], 0
@@ -351,7 +315,7 @@ class Runner:
             self.by_slot[slot] = req
 
     def _evict_one(self) -> None:
-        v = (victim_native if self.sched.native else victim)(self.sched.slots)
+        v = victim(self.sched.slots)
         if v < 0:
             raise PagesExhausted(-1, 0, 0)
         req = self.by_slot.pop(v)

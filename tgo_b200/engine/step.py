@@ -9,8 +9,8 @@ model/batch.go:66-152 are the reference's descriptor and commit rule).
 """
 from __future__ import annotations
 
-import os
 import sys
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -18,9 +18,9 @@ import numpy as np
 import torch
 
 from ..cache.native import NativeCacheManager
-from ..cache.pages import NULL_PAGE, CacheManager
 from ..cache.storage import CacheStorage
 from ..kernels import ops
+from ..kernels.build import compile_together
 from ..parts.base import StepContext
 from .model import Model
 
@@ -54,18 +54,14 @@ class Engine:
         self.device = model.device
         self.page_size = page_size
         if self.device.type == "cuda":
-            ops.prebuild_for(model.dtype, [(g.head_dim, page_size) for g in model.groups])
+            # the libraries the model's parts say they call, compiled side by side (each
+            # would otherwise be built when the first step reaches it, one after the other)
+            compile_together(["host_runtime"] + model.libraries(page_size))
         pages = [num_pages for _ in model.groups]
-        # the books and the packing of a step are kept by the native host library;
-        # TGO_NATIVE_HOST=0 keeps them in Python (cache/pages.py and _pack below, the plain
-        # statement that the tests hold the native ones against)
-        self._native = os.environ.get("TGO_NATIVE_HOST", "1") != "0"
-        if self._native:
-            self.cache = NativeCacheManager(model.groups, page_size, pages, num_slots)
-            self._stage = np.empty(4096, dtype=np.int32)
-            self._begun = None                   # (request ids, what step_begin returned)
-        else:
-            self.cache = CacheManager(model.groups, page_size, pages, num_slots)
+        # the books and the packing of a step are kept by the native host library
+        self.cache = NativeCacheManager(model.groups, page_size, pages, num_slots)
+        self._stage = np.empty(4096, dtype=np.int32)
+        self._begun = None                       # (request ids, what step_begin returned)
         self.storage = CacheStorage(model.groups, page_size, pages, num_slots, model.dtype,
                                     model.device, model.state_shapes)
         self.steps_run = 0
@@ -73,7 +69,8 @@ class Engine:
         self.h2d_bytes_last = 0       # bytes of the last step's inputs copied to the device
         self._graphs = {}
         self._warmed = set()          # kinds of decode step that have run once outside a capture
-        self._portion_graphs = {}     # key -> captured graph of a one-request prompt portion
+        self._portion_graphs = OrderedDict()   # key -> captured graph of a one-request prompt
+                                               # portion, least recently used first
         self._portion_seen = {}       # key -> times the shape came without a graph
 
     # ------------------------------------------------------------------ requests
@@ -125,111 +122,13 @@ class Engine:
                     raise ValueError(f"step: request {e.request_id!r} wants the logits of "
                                      f"place {w} among {len(e.tokens)} tokens")
 
-    def _table_array(self, req, g):
-        """A request's block table of group g as an int32 array, rebuilt only when it changed."""
-        cache = req.__dict__.setdefault("_np_tables", {})
-        got = cache.get(g)
-        if got is None or got[0] != req.version:
-            got = (req.version, np.asarray(req.tables[g], dtype=np.int32))
-            cache[g] = got
-        return got[1]
-
     def _pack(self, entries: List[StepEntry], pad_to: int = 0, width_quantum: int = 1,
               all_rows: bool = False, out: Optional[np.ndarray] = None):
-        """Host data of one step, laid out as one flat int32 array:
+        """Host data of one step, laid out by the native host library as one flat int32 array:
         ids[T] pos[T] seq[T] q_start[B+1] ctx[B] state_slot[B] rows[n] then, per group,
         slots[T] table[B*width]. With pad_to > B, requests that bring nothing fill the batch:
         one token each at position -1 (the kernels read and write nothing for it).
         Written into `out` if it is given and large enough."""
-        if getattr(self, "_native", False):
-            return self._pack_native(entries, pad_to, width_quantum, all_rows, out)
-        cm = self.cache
-        ps = self.page_size
-        reqs = [cm.requests[e.request_id] for e in entries]
-        n_real = len(entries)
-        extents = [len(e.tokens) for e in entries]
-        firsts = [r.length for r in reqs]
-        n_pad = max(0, pad_to - n_real)
-        B = n_real + n_pad
-        T = sum(extents) + n_pad
-        rows = []
-        if all_rows:
-            n_rows = T
-        else:
-            base = 0
-            for e, n in zip(entries, extents):
-                rows += [base + int(w) for w in e.want]
-                base += n
-            n_rows = len(rows)
-        n_groups = len(cm.groups)
-        widths = []
-        for g in range(n_groups):
-            width = max(1, max(len(r.tables[g]) for r in reqs))
-            widths.append((width + width_quantum - 1) // width_quantum * width_quantum)
-        total = 3 * T + (B + 1) + 2 * B + n_rows + sum(T + B * w for w in widths)
-        buf = out if out is not None and out.size >= total else np.empty(total, dtype=np.int32)
-        ids, pos, seq = buf[0:T], buf[T:2 * T], buf[2 * T:3 * T]
-        o = 3 * T
-        q_start = buf[o:o + B + 1]
-        o += B + 1
-        ctx_lens = buf[o:o + B]
-        o += B
-        st_slots = buf[o:o + B]
-        o += B
-        rows_v = buf[o:o + n_rows]
-        o += n_rows
-        ext = np.asarray(extents, dtype=np.int64)
-        fst = np.asarray(firsts, dtype=np.int64)
-        starts = np.zeros(n_real + 1, dtype=np.int64)
-        np.cumsum(ext, out=starts[1:])
-        n_tok = int(starts[-1])
-        if n_tok == n_real:                      # every request brings one token
-            ids[:n_real] = [e.tokens[0] for e in entries]
-            pos[:n_real] = fst
-            seq[:n_real] = np.arange(n_real)
-        else:
-            for b, e in enumerate(entries):
-                a, z = int(starts[b]), int(starts[b + 1])
-                ids[a:z] = e.tokens
-                pos[a:z] = np.arange(firsts[b], firsts[b] + extents[b])
-                seq[a:z] = b
-        q_start[:n_real + 1] = starts
-        ctx_lens[:n_real] = fst + ext
-        st_slots[:n_real] = [r.slot for r in reqs]
-        if n_pad:
-            ids[n_tok:] = 0
-            pos[n_tok:] = -1
-            seq[n_tok:] = np.arange(n_real, B)
-            q_start[n_real + 1:] = n_tok + 1 + np.arange(n_pad)
-            ctx_lens[n_real:] = 0
-            st_slots[n_real:] = cm.slots.num_slots      # the spare slot nobody owns
-        rows_v[:] = np.arange(T) if all_rows else rows
-        token_pos = pos[:n_tok].astype(np.int64)
-        for g in range(n_groups):
-            width = widths[g]
-            slots = buf[o:o + T]
-            o += T
-            table = buf[o:o + B * width].reshape(B, width)
-            o += B * width
-            table[:] = NULL_PAGE
-            for b, r in enumerate(reqs):
-                arr = self._table_array(r, g)
-                table[b, :arr.size] = arr
-            tok_seq = seq[:n_tok].astype(np.int64)
-            pages = table[tok_seq, token_pos // ps]
-            if (pages == NULL_PAGE).any():
-                bad = int(np.argmax(pages == NULL_PAGE))
-                raise ValueError(f"cache: position {int(token_pos[bad])} of request "
-                                 f"{entries[int(tok_seq[bad])].request_id!r} has no page in "
-                                 f"group {g}")
-            slots[:n_tok] = pages.astype(np.int64) * ps + token_pos % ps
-            slots[n_tok:] = -1
-        meta = dict(T=T, B=B, n_rows=n_rows, widths=widths, extents=extents, firsts=firsts,
-                    max_context=int(ctx_lens[:n_real].max()), total=total)
-        return buf, meta
-
-    def _pack_native(self, entries, pad_to, width_quantum, all_rows, out):
-        """`_pack` by the native host library: the same buffer and the same meta."""
         ids = [e.request_id for e in entries]
         tokens = [e.tokens for e in entries]
         wants = [e.want for e in entries]
@@ -238,7 +137,7 @@ class Engine:
         begun = begun[1] if begun else None
         meta, total = self.cache.step_pack(ids, tokens, wants, pad_to, width_quantum, all_rows, buf,
                                            begun)
-        if meta is None:                         # too small: a buffer of its own, as _pack does
+        if meta is None:                         # too small: a buffer of its own
             buf = np.empty(total, dtype=np.int32)
             if out is None:
                 self._stage = np.empty(2 * total, dtype=np.int32)
@@ -291,29 +190,32 @@ class Engine:
         if not entries:
             raise ValueError("step: an empty batch carries nothing")
         self._validate(entries)
-        if self._native:
-            ids = [e.request_id for e in entries]
-            self._begun = (ids, self.cache.step_begin(ids, [len(e.tokens) for e in entries]))
-        else:
-            for e in entries:
-                r = self.cache.requests[e.request_id]
-                self.cache.grow(e.request_id, r.length + len(e.tokens))
-        if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
-            logits = self._graph_step(entries)
-        elif self.use_graphs and len(entries) == 1 and \
-                len(entries[0].tokens) >= self.PORTION_GRAPH_MIN_TOKENS and \
-                (logits := self._portion_graph_step(entries)) is not None:
-            pass
-        else:
-            ctx, tables, slots = self.build_context(entries)
-            logits = self.model.forward(ctx, self.storage, tables, slots)
-        if self._native:
-            self.cache.step_commit(self._begun[1])
+        ids = [e.request_id for e in entries]
+        self._begun = (ids, self.cache.step_begin(ids, [len(e.tokens) for e in entries]))
+        # fixed-size state is advanced in place by the mixers that own it: a step that fails
+        # half-way must leave it where it was, as it leaves the lengths
+        saved = None
+        if self.storage.state:
+            rows = torch.tensor([self.cache.requests[i].slot for i in ids], dtype=torch.int64,
+                                device=self.device)
+            saved = (rows, self.storage.save_state(rows))
+        try:
+            if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
+                logits = self._graph_step(entries)
+            elif self.use_graphs and len(entries) == 1 and \
+                    len(entries[0].tokens) >= self.PORTION_GRAPH_MIN_TOKENS and \
+                    (logits := self._portion_graph_step(entries)) is not None:
+                pass
+            else:
+                ctx, tables, slots = self.build_context(entries)
+                logits = self.model.forward(ctx, self.storage, tables, slots)
+        except BaseException:
+            if saved is not None:
+                self.storage.restore_state(*saved)
             self._begun = None
-        else:
-            for e in entries:
-                r = self.cache.requests[e.request_id]
-                self.cache.commit(e.request_id, r.length + len(e.tokens))
+            raise
+        self.cache.step_commit(self._begun[1])
+        self._begun = None
         self.steps_run += 1
         return logits
 
@@ -325,12 +227,10 @@ class Engine:
         """Block-table columns of the graph a step runs through: the smallest of 64, 128,
         256, ... that holds the longest table of the step (a few variants however long the
         contexts grow; the kernels read only the columns a request has)."""
-        if self._native and self._begun is not None:
+        if self._begun is not None:
             raw = max(1, self._begun[1][2])
-        elif self._native:
-            raw = max(1, self.cache.step_widest_table([e.request_id for e in entries]))
         else:
-            raw = max(1, max(len(t) for e in entries for t in self.cache.requests[e.request_id].tables))
+            raw = max(1, self.cache.step_widest_table([e.request_id for e in entries]))
         q = self.WIDTH_QUANTUM
         while q < raw:
             q *= 2
@@ -350,7 +250,7 @@ class Engine:
             flat, meta = self._pack(entries, pad_to=bucket, width_quantum=width, all_rows=True)
             # a warm-up run only the first time this engine meets a row count that picks other
             # product kernels (few rows, the library's range, many): later captures just record
-            kind = 0 if bucket <= 8 else 1 if bucket <= 64 else 2
+            kind = ops.product_regime(bucket)
             try:
                 entry = self._capture(flat, meta, warm=kind not in self._warmed)
                 self._warmed.add(kind)
@@ -397,7 +297,9 @@ class Engine:
         width = self._graph_width(entries)
         key = (len(e.tokens), tuple(int(w) for w in e.want), width)
         entry = self._portion_graphs.get(key)
-        if entry is None:
+        if entry is not None:
+            self._portion_graphs.move_to_end(key)
+        else:
             seen = self._portion_seen.get(key, 0) + 1
             self._portion_seen[key] = seen
             if seen < 2:
@@ -415,7 +317,10 @@ class Engine:
                 torch.cuda.synchronize(self.device)
                 return None
             while len(self._portion_graphs) >= self.PORTION_GRAPHS_KEPT:
-                self._portion_graphs.pop(next(iter(self._portion_graphs)))     # the oldest
+                # the least recently used goes, with its pool; its shape starts over (it is
+                # captured again only when it has come twice more)
+                gone, _ = self._portion_graphs.popitem(last=False)
+                self._portion_seen.pop(gone, None)
             self._portion_graphs[key] = entry
         graph, host, dev, logits, launches, copied, _ = entry
         copied.synchronize()              # see _graph_step
@@ -448,18 +353,10 @@ class Engine:
             for call, t in saved.items():
                 self.storage.state[call].copy_(t)
             torch.cuda.synchronize(self.device)
-        elif not ctx.decode_only:
-            # the attention tile lists are made on the host, which a capture cannot do: make
-            # them now, for every number of tokens a tile may hold
-            groups = set()
-            for ls in self.model.spec.layers:
-                heads = getattr(ls.mixer, "num_heads", None)
-                kv_heads = getattr(ls.mixer, "num_kv_heads", None)
-                if heads and kv_heads:
-                    groups.add(max(1, heads // kv_heads))
-            for g in groups:
-                ops._tiles(ctx, max(1, 128 // g))
-            torch.cuda.synchronize(self.device)
+        # what a part's forward would make on the host (lists derived from the step's shape)
+        # is made now: a capture cannot do it
+        self.model.prepare_capture(ctx, self.storage, tables, slots)
+        torch.cuda.synchronize(self.device)
         # what an eager run cached per step (tables made from its inputs) must be made again
         # inside the capture, or the replays would keep reading the first step's; the tile
         # lists depend on the step's shape alone and are kept

@@ -36,7 +36,6 @@ LIBRARIES = {
     "sgemm": (["sgemm.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
-    "gemm_chain": (["gemm_chain.cu"], []),
     "sampling": (["sampling.cu"], []),
     # host code only (no kernel): the cache books and the packing of a step
     "host_runtime": (["host_runtime.cpp"], []),

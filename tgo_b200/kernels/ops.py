@@ -24,84 +24,6 @@ class KernelError(RuntimeError):
     pass
 
 
-class _Chain:
-    """Products of a decode step that have been asked for and not launched yet."""
-
-    def __init__(self, rows: int):
-        self.rows = rows
-        self.phases = []
-
-
-_CHAIN = None
-CHAIN_MAX_ROWS = 8
-CHAIN_MAX_PHASES = 4
-USE_CHAINS = False     # measured slower than separate launches (see gemm_chain.cu); kept tested, off
-
-
-def begin_chain(rows: int) -> bool:
-    """From now until end_chain, small-batch products asked of `linear` / `gated_linear` are
-    collected and run, up to four at a time, as one persistent kernel (gemm_chain). Every
-    other kernel wrapper of this module launches what has been collected first, so the
-    order of effects stays the order of the calls. Code between begin and end must touch
-    device data through this module only (or call flush_chain first)."""
-    global _CHAIN
-    if not USE_CHAINS or rows > CHAIN_MAX_ROWS or rows <= 0:
-        return False
-    _CHAIN = _Chain(rows)
-    return True
-
-
-def flush_chain() -> None:
-    if _CHAIN is not None and _CHAIN.phases:
-        phases, _CHAIN.phases = _CHAIN.phases, []
-        gemm_chain(phases, _CHAIN.rows)
-
-
-def end_chain() -> None:
-    global _CHAIN
-    try:
-        flush_chain()
-    finally:
-        _CHAIN = None
-
-
-def _chain_take(x, w: torch.Tensor, mode: str, out_dtype, residual) -> Optional[tuple]:
-    """Collect the product if a chain is open and the kernel takes it. Returns (result,) or
-    None when the caller has to run it the ordinary way."""
-    if _CHAIN is None:
-        return None
-    normed = isinstance(x, NormedRows)
-    xt = x.h if normed else x
-    N, K = w.shape
-    M = xt.shape[0]
-    ok = (M == _CHAIN.rows and w.dtype == torch.bfloat16 and w.is_contiguous() and K % 8 == 0
-          and xt.is_contiguous() and xt.shape[1] == K and K <= 12288 and xt.data_ptr() % 16 == 0
-          and w.data_ptr() % 16 == 0)
-    if normed:
-        ok = ok and x.delta is None and x._done is None and x.dtype == torch.bfloat16
-    else:
-        ok = ok and xt.dtype == torch.bfloat16
-    if mode == "gated":
-        ok = ok and N % 16 == 0
-    elif mode == "add":
-        ok = ok and residual is not None and residual.dtype == torch.float32 and \
-            residual.is_contiguous() and residual.shape == (M, N)
-    else:
-        ok = ok and out_dtype == torch.bfloat16
-    if not ok:
-        return None
-    if len(_CHAIN.phases) >= CHAIN_MAX_PHASES:
-        flush_chain()
-    if mode == "add":
-        out = residual
-    elif mode == "gated":
-        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=xt.device)
-    else:
-        out = torch.empty((M, N), dtype=torch.bfloat16, device=xt.device)
-    _CHAIN.phases.append((x, w, out, mode))
-    return (None if mode == "add" else out,)
-
-
 def dtype_code(dt: torch.dtype) -> int:
     try:
         return _CODES[dt]
@@ -118,8 +40,6 @@ def _stream():
 
 
 def _need_cuda(*tensors) -> None:
-    if _CHAIN is not None and _CHAIN.phases:
-        flush_chain()          # every kernel wrapper comes through here first
     for t in tensors:
         if t is not None and not t.is_cuda:
             raise KernelError("the kernels run on a CUDA device only; got a tensor on "
@@ -271,62 +191,18 @@ def sgemm_tn(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 
 SKINNY_MAX_ROWS = 8
-FOLD_NORM = False     # folding RMSNorm into the product re-reads h and the gain in every CTA;
-                      # measured slower than the separate norm kernel at every batch size
 
-
-class NormedRows:
-    """rmsnorm(h) * gain, not computed yet: a mixer or feed-forward whose first step is a
-    matrix product can hand this to `linear`, which folds the norm into the product when
-    the weight-streaming kernel runs it, and computes it with the norm kernel otherwise."""
-
-    def __init__(self, h: torch.Tensor, gain: torch.Tensor, eps: float, dtype: torch.dtype,
-                 delta: Optional[torch.Tensor] = None):
-        """`delta`, if given, is still to be added to h (and stays added): the norm kernel
-        does that add on its way."""
-        self.h, self.gain, self.eps, self.dtype = h, gain, float(eps), dtype
-        self.delta = delta
-        self._done = None
-
-    @property
-    def shape(self):
-        return self.h.shape
-
-    @property
-    def device(self):
-        return self.h.device
-
-    def materialize(self) -> torch.Tensor:
-        if self._done is None:
-            out = torch.empty(self.h.shape, dtype=self.dtype, device=self.h.device)
-            add_rmsnorm(self.h, self.delta, self.gain, self.eps, out)      # launches a pending chain first
-            self.delta = None
-            self._done = out
-        return self._done
-
-
-def as_rows(x) -> torch.Tensor:
-    """The tensor behind `x`, computing a pending norm if there is one."""
-    return x.materialize() if isinstance(x, NormedRows) else x
-
-
-def gemm_skinny(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
                 gated: bool = False) -> None:
-    """out = x . w^T for at most 64 rows, bfloat16 weights, the weight-streaming kernel.
-    x: bfloat16 [M, K], or NormedRows over a float32 [M, K] (the norm is folded in).
-    out: bfloat16 or float32 [M, N]; with `accumulate` (float32) the product is added to it;
-    with `gated`, w is a gate/up matrix with rows interleaved in eights and out is
-    silu(gate) * up, bfloat16 [M, N / 2]."""
-    normed = isinstance(x, NormedRows)
-    if normed and x.delta is not None:
-        residual_add(x.h, x.delta)
-        x.delta = None
-    xt = x.h if normed else x
-    _need_cuda(xt, w, out)
-    M, N, K = xt.shape[0], w.shape[0], w.shape[1]
-    assert w.dtype == torch.bfloat16 and xt.dtype == (torch.float32 if normed else torch.bfloat16)
-    assert xt.is_contiguous() and w.is_contiguous() and out.is_contiguous()
-    assert xt.shape[1] == K and xt.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+    """out = x . w^T for at most 64 rows, bfloat16 [M, K] by bfloat16 [N, K], the
+    weight-streaming kernel. out: bfloat16 or float32 [M, N]; with `accumulate` (float32) the
+    product is added to it; with `gated`, w is a gate/up matrix with rows interleaved in
+    eights and out is silu(gate) * up, bfloat16 [M, N / 2]."""
+    _need_cuda(x, w, out)
+    M, N, K = x.shape[0], w.shape[0], w.shape[1]
+    assert w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+    assert x.is_contiguous() and w.is_contiguous() and out.is_contiguous()
+    assert x.shape[1] == K and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
     if gated:
         assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2) and N % 16 == 0
         omode = 3
@@ -337,10 +213,8 @@ def gemm_skinny(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
         assert out.dtype in (torch.bfloat16, torch.float32) and out.shape == (M, N)
         omode = 0 if out.dtype == torch.bfloat16 else 1
     lib = load_library("gemm_skinny")
-    _check(lib.tgo_gemm_skinny(_ptr(xt), _ptr(x.gain if normed else None),
-                               c_float(x.eps if normed else 0.0), _ptr(w), _ptr(out), c_int(M),
-                               c_int(N), c_int(K), c_int(1 if normed else 0), c_int(omode),
-                               _stream()), "gemm_skinny", f"(M={M}, N={N}, K={K})")
+    _check(lib.tgo_gemm_skinny(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
+                               c_int(omode), _stream()), "gemm_skinny", f"(M={M}, N={N}, K={K})")
 
 
 def _skinny_ok(x, w) -> bool:
@@ -358,6 +232,13 @@ def _skinny_ok(x, w) -> bool:
 #             product at 2048 rows, and it applies the gate in its epilogue
 TC_MIN_ROWS = 1025
 USE_TC = True            # False: the library product for every size above 8 rows
+
+
+def product_regime(rows: int) -> int:
+    """Which of the three product kernels a bfloat16 product of this many rows takes
+    (0 weight streaming, 1 the library, 2 tcgen05): an engine warms each one up once before
+    it captures a graph that holds it."""
+    return 0 if rows <= SKINNY_MAX_ROWS else 1 if rows < TC_MIN_ROWS else 2
 
 
 def _tc_ok(x, w) -> bool:
@@ -383,11 +264,11 @@ def _dense(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Te
     raise KernelError(f"linear: x is {x.dtype} and w is {w.dtype}")
 
 
-def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
            residual: Optional[torch.Tensor] = None):
-    """y = x . w^T with w stored [out, in]. x is a tensor or NormedRows. residual: a float32
-    [M, N] tensor the product belongs to: either it is added there and None is returned, or
-    the product is returned for the caller to add (the block hands it to the next norm).
+    """y = x . w^T with w stored [out, in]. residual: a float32 [M, N] tensor the product
+    belongs to: either it is added there and None is returned, or the product is returned
+    for the caller to add (the block hands it to the next norm).
 
     float32: this package's plain-FMA kernel. bfloat16 with few rows (a decode step): this
     package's weight-streaming kernel, which does the residual add in its epilogue.
@@ -396,11 +277,6 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
     keeps the accumulator's width (the logits).
     """
     out_dtype = out_dtype or x.dtype
-    taken = _chain_take(x, w, "add" if residual is not None else "bf16", out_dtype, residual)
-    if taken is not None:
-        return taken[0]
-    if isinstance(x, NormedRows) and not FOLD_NORM:
-        x = x.materialize()
     if _skinny_ok(x, w):
         M, N = x.shape[0], w.shape[0]
         if residual is not None:
@@ -409,7 +285,6 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         gemm_skinny(x, w, out)
         return out
-    x = as_rows(x)
     if residual is not None and x.dtype == torch.bfloat16:
         # more than a few rows: the library has no add into a float32 stream, and from the
         # tcgen05 product's epilogue a read-modify-write of the stream is slow (each thread
@@ -423,33 +298,34 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
     return y
 
 
-def gated_linear(x, w_gate_up: torch.Tensor, interleaved: bool) -> torch.Tensor:
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool) -> torch.Tensor:
     """silu(x . Wg^T) * (x . Wu^T) as [M, f] in x's dtype. w_gate_up is [2f, K]: the gate
     rows then the up rows, or (`interleaved`) eight gate rows and the eight matching up rows
     in turn, which lets the bfloat16 kernels apply the gate in their epilogue."""
     M, f = x.shape[0], w_gate_up.shape[0] // 2
-    if interleaved:
-        taken = _chain_take(x, w_gate_up, "gated", torch.bfloat16, None)
-        if taken is not None:
-            return taken[0]
-    if isinstance(x, NormedRows) and not FOLD_NORM:
-        x = x.materialize()
     if interleaved and _skinny_ok(x, w_gate_up):
         out = torch.empty((M, f), dtype=torch.bfloat16, device=x.device)
         gemm_skinny(x, w_gate_up, out, gated=True)
         return out
-    xt = as_rows(x)
-    if interleaved and _tc_ok(xt, w_gate_up) and f % 8 == 0:
-        out = torch.empty((M, f), dtype=torch.bfloat16, device=xt.device)
-        gemm_tc(xt, w_gate_up, out, gated=True)
+    if interleaved and _tc_ok(x, w_gate_up) and f % 8 == 0:
+        out = torch.empty((M, f), dtype=torch.bfloat16, device=x.device)
+        gemm_tc(x, w_gate_up, out, gated=True)
         return out
-    gu = _dense(xt, w_gate_up, xt.dtype)
-    out = torch.empty((M, f), dtype=xt.dtype, device=xt.device)
+    gu = _dense(x, w_gate_up, x.dtype)
+    out = torch.empty((M, f), dtype=x.dtype, device=x.device)
     swiglu(gu, out, interleaved)
     return out
 
 
-NUM_SMS = 148
+_num_sms = {}
+
+
+def num_sms(device) -> int:
+    """Streaming multiprocessors of the device (asked once per device)."""
+    key = torch.device(device).index or 0
+    if key not in _num_sms:
+        _num_sms[key] = int(torch.cuda.get_device_properties(key).multi_processor_count)
+    return _num_sms[key]
 
 
 def flash_supports(head_dim: int, group: int) -> bool:
@@ -457,22 +333,6 @@ def flash_supports(head_dim: int, group: int) -> bool:
     group (others go to the generic kernel)."""
     return bool(load_library("attention_flash").tgo_attention_flash_supports(
         c_int(head_dim), c_int(group)))
-
-
-def prebuild_for(dtype: torch.dtype, head_dims_and_pages) -> None:
-    """Compile, side by side, the libraries that a model of this storage type and these head
-    sizes is sure to use in its first steps (each would otherwise be built when the first
-    step reaches it, one after the other). What a model may never need (the product for more
-    than 1024 rows, sampling) is left to its first use."""
-    from .build import compile_together
-    names = ["host_runtime", "elementwise"]
-    if dtype == torch.float32:
-        names += ["sgemm", "attention_generic"]
-    else:
-        names += ["gemm_skinny", "attention_flash"]
-        if any(dh == 128 for dh, _ in head_dims_and_pages):
-            names += ["attention_tc", "attention_decode_tma"]
-    compile_together(names)
 
 
 USE_TMA_DECODE = True       # decode attention with head size 128: cache pages by TMA
@@ -497,14 +357,14 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
                     head_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
                     block_tables: torch.Tensor, positions: torch.Tensor, seq_ids: torch.Tensor,
                     tile_tok0: Optional[torch.Tensor], tile_ntok: Optional[torch.Tensor],
-                    scale: float, window: int, wide: bool = True, n_splits: int = 1,
+                    scale: float, window: int, n_splits: int = 1,
                     tok_list: Optional[torch.Tensor] = None) -> None:
     """Paged causal attention on the tensor cores (bfloat16). With tile arrays (int32,
     first token and token count of each tile, tokens of one request, at most
     flash_tile_rows() // group of them) any step; without them every token is a tile of its
     own (decode), and n_splits > 1 cuts each request's keys over that many CTAs and joins
     them. tok_list (int32, decode with head size 128 only): the tokens of the step to take,
-    instead of all. (`wide` is accepted and ignored.)"""
+    instead of all."""
     _need_cuda(q, out, k_cache, v_cache, block_tables, positions, seq_ids, tile_tok0, tile_ntok,
                tok_list)
     T = q.shape[0] if tok_list is None else tok_list.numel()
@@ -551,10 +411,7 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
             "attention_flash_combine")
 
 
-USE_TC_ATTENTION = True     # prompt portions with head size 128 on the tcgen05 kernel
-TC_ATTENTION_MIN_TOKENS = 1  # steps with fewer tokens than this keep the mma.sync kernel
 TC_ATTENTION_PERSISTENT = True   # one CTA per SM drawing items, or one CTA per item
-SPLIT_MIXED_STEPS = True         # single tokens of a mixed step go through the decode kernel
 
 
 def attention_tc_supports(head_dim: int, group: int, page_size: int) -> bool:
@@ -596,118 +453,6 @@ def attention_tc_prefill(q: torch.Tensor, out: torch.Tensor, num_heads: int, num
 def flash_tile_rows() -> int:
     """Query rows (token x head of the group) one prefill tile of the attention kernel holds."""
     return int(load_library("attention_flash").tgo_attention_flash_tile_rows())
-
-
-def _tiles(ctx, tokens_per_tile: int):
-    """Tile arrays of a step for the wide kernel, made once per step and group size."""
-    key = ("tiles", tokens_per_tile)
-    got = ctx.aux.get(key)
-    if got is None:
-        tok0, ntok, base = [], [], 0
-        for n in ctx.extents:
-            for o in range(0, n, tokens_per_tile):
-                tok0.append(base + o)
-                ntok.append(min(tokens_per_tile, n - o))
-            base += n
-        dev = torch.tensor([tok0, ntok], dtype=torch.int32).to(ctx.token_ids.device,
-                                                               non_blocking=True)
-        got = (dev[0], dev[1])
-        ctx.aux[key] = got
-    return got
-
-
-def _tiles_and_singles(ctx, tokens_per_tile: int):
-    """For a step that holds prompt portions and single tokens: tile arrays of the entries
-    with more than one token, and the list of the tokens that are alone in their entry."""
-    key = ("tiles", tokens_per_tile, "split")
-    got = ctx.aux.get(key)
-    if got is None:
-        tok0, ntok, singles, base = [], [], [], 0
-        for n in ctx.extents:
-            if n == 1:
-                singles.append(base)
-            else:
-                for o in range(0, n, tokens_per_tile):
-                    tok0.append(base + o)
-                    ntok.append(min(tokens_per_tile, n - o))
-            base += n
-        dev = torch.tensor(tok0 + ntok + singles, dtype=torch.int32).to(ctx.token_ids.device,
-                                                                         non_blocking=True)
-        k = len(tok0)
-        got = (dev[:k], dev[k:2 * k], dev[2 * k:], len(singles))
-        ctx.aux[key] = got
-    return got
-
-
-def _splits_for(pairs: int, reach: int, window: int, ctas_per_sm: int = 3) -> int:
-    tiles = max(1, (reach + 63) // 64 + (1 if window > 0 else 0))
-    pairs = max(1, pairs)
-    wave = NUM_SMS * ctas_per_sm
-    best, best_cost = 1, None
-    for s in range(1, max(1, min(tiles // 2, 64)) + 1):
-        rounds = -(-pairs * s // wave)
-        cost = rounds * (tiles / s * 1.0 + 5.0) + (10.0 if s > 1 else 0.0)
-        if best_cost is None or cost < best_cost - 1e-9:
-            best, best_cost = s, cost
-    return best
-
-
-def decode_splits(ctx, num_kv_heads: int, window: int, ctas_per_sm: int = 3) -> int:
-    """How many CTAs share one request's keys in a decode step: the count that is cheapest by
-    a small model fitted on B200 (8 kv heads, contexts of 1024 and 4096, batches 8 to 128):
-    the CTAs run in rounds of as many as the GPU holds, a CTA costs 1 unit per 64-key tile
-    and 5 to start, joining the splits costs 10 once. So a few requests are cut until they
-    fill the GPU once (batch 8: 7 ways), 32 or 64 requests of 1024 keys are not cut (the
-    start is paid once), and 64 requests of 4096 keys are cut in 3 or 4, because the second,
-    nearly empty round of whole requests would cost a whole request's time."""
-    reach = min(ctx.max_context, window) if window > 0 else ctx.max_context
-    return _splits_for(ctx.num_seqs * num_kv_heads, reach, window, ctas_per_sm)
-
-
-def paged_attention(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
-                    head_dim: int, cache, ctx, scale: float, window: int) -> None:
-    """Attention of every token of the step over its request's cached keys and values.
-    Picks the kernel by storage type, head size and what the step holds."""
-    group = num_heads // num_kv_heads
-    if q.dtype == torch.bfloat16 and flash_supports(head_dim, group):
-        if ctx.decode_only:
-            attention_flash(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
-                            cache.page_size, cache.block_tables, ctx.positions, ctx.seq_ids,
-                            None, None, scale, window, wide=False,
-                            n_splits=decode_splits(ctx, num_kv_heads, window))
-        elif USE_TC_ATTENTION and q.shape[0] >= TC_ATTENTION_MIN_TOKENS and \
-                attention_tc_supports(head_dim, group, cache.page_size) and \
-                cache.k.is_contiguous() and cache.v.is_contiguous():
-            if SPLIT_MIXED_STEPS and USE_TMA_DECODE and 1 in ctx.extents and \
-                    attention_decode_tma_supports(head_dim, group, cache.page_size):
-                # prompt portions beside single tokens: the portions through the tile kernel,
-                # the single tokens through the decode kernel (a tile of 128 rows for one
-                # token's few heads would walk that request's whole context almost empty)
-                tok0, ntok, singles, n_single = _tiles_and_singles(ctx, 128 // group)
-                if tok0.numel():
-                    attention_tc_prefill(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
-                                         cache.page_size, cache.block_tables, ctx.positions,
-                                         ctx.seq_ids, tok0, ntok, scale, window)
-                reach = min(ctx.max_context, window) if window > 0 else ctx.max_context
-                attention_flash(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
-                                cache.page_size, cache.block_tables, ctx.positions, ctx.seq_ids,
-                                None, None, scale, window, wide=False,
-                                n_splits=_splits_for(n_single * num_kv_heads, reach, window),
-                                tok_list=singles)
-                return
-            tok0, ntok = _tiles(ctx, 128 // group)
-            attention_tc_prefill(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
-                                 cache.page_size, cache.block_tables, ctx.positions, ctx.seq_ids,
-                                 tok0, ntok, scale, window)
-        else:
-            tok0, ntok = _tiles(ctx, flash_tile_rows() // group)
-            attention_flash(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
-                            cache.page_size, cache.block_tables, ctx.positions, ctx.seq_ids,
-                            tok0, ntok, scale, window, wide=True)
-        return
-    attention_generic(q, out, num_heads, num_kv_heads, head_dim, cache.k, cache.v,
-                      cache.page_size, cache.block_tables, ctx.seq_ids, ctx.positions, scale,
-                      window)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
@@ -841,24 +586,6 @@ def gemm_tc_last_plan() -> tuple:
     return r.value, w.value, c.value
 
 
-# ------------------------------------------------------------------ chains of products
-_chain_state = {}
-
-
-def _chain_buffers(device):
-    """Per device: the grid barrier's two counters (they reset themselves) and an error flag."""
-    key = torch.device(device).index or 0
-    if key not in _chain_state:
-        _chain_state[key] = (torch.zeros(2, dtype=torch.int32, device=device),
-                             torch.zeros(1, dtype=torch.int32, device=device))
-    return _chain_state[key]
-
-
-def gemm_chain_error_flag(device) -> torch.Tensor:
-    """Set to 7 if a grid barrier of a product chain ever gave up waiting."""
-    return _chain_buffers(device)[1]
-
-
 def kernel_wait_errors() -> dict:
     """Which kernels of this package gave up a wait (on an mbarrier or a grid barrier) since
     the process began: {kernel: code}, empty when none did. Their results are then not to be
@@ -877,50 +604,4 @@ def kernel_wait_errors() -> dict:
         code = int(flag.item())
         if code:
             out[f"gemm_tc (device {key})"] = code
-    for key, state in _chain_state.items():
-        code = int(state[1].item())
-        if code:
-            out[f"gemm_chain ({key})"] = code
     return out
-
-
-def gemm_chain(phases, M: int) -> None:
-    """Run up to four small-batch products back to back in one persistent kernel.
-
-    phases: list of (x, w, out, mode) with
-      x     bfloat16 [M, K], or NormedRows over the float32 [M, K] stream (norm folded in);
-      w     bfloat16 [N, K];
-      out   per mode: "bf16" -> bfloat16 [M, N]; "add" -> float32 [M, N] the product is added
-            to; "gated" -> bfloat16 [M, N / 2] = silu(gate) * up, w interleaved in eights.
-    A phase may read what an earlier phase of the same chain wrote (a grid barrier stands
-    between phases). M <= 8."""
-    import struct
-    rows = []
-    dev = None
-    for x, w, out, mode in phases:
-        normed = isinstance(x, NormedRows)
-        xt = x.h if normed else x
-        _need_cuda(xt, w, out)
-        dev = xt.device
-        N, K = w.shape
-        assert xt.shape == (M, K) and xt.is_contiguous() and w.is_contiguous() and out.is_contiguous()
-        assert w.dtype == torch.bfloat16 and xt.dtype == (torch.float32 if normed else torch.bfloat16)
-        if mode == "bf16":
-            assert out.dtype == torch.bfloat16 and out.shape == (M, N)
-            ok = 0
-        elif mode == "add":
-            assert out.dtype == torch.float32 and out.shape == (M, N)
-            ok = 2
-        elif mode == "gated":
-            assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2) and N % 16 == 0
-            ok = 3
-        else:
-            raise KernelError(f"gemm_chain: unknown output mode {mode!r}")
-        eps_bits = struct.unpack("<I", struct.pack("<f", x.eps if normed else 0.0))[0]
-        rows += [xt.data_ptr(), x.gain.data_ptr() if normed else 0, w.data_ptr(), out.data_ptr(),
-                 eps_bits, 0 if normed else 1, ok, N, K]
-    arr = (ctypes.c_longlong * len(rows))(*rows)
-    barrier, err = _chain_buffers(dev)
-    lib = load_library("gemm_chain")
-    _check(lib.tgo_gemm_chain(arr, c_int(len(phases)), c_int(M), _ptr(barrier), _ptr(err), _stream()),
-           "gemm_chain", f"({len(phases)} phases, M={M})")

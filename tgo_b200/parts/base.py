@@ -21,6 +21,23 @@ Interfaces (duck-typed; `Part` only supplies the defaults):
   feed-forward    forward(x, ctx) -> [T, d]; `residual` as for the mixer.
   block           forward(h, pending, ctx, cache) -> (h, pending): `pending` is a delta
                   not yet added to h, so the add can be fused into the next norm.
+
+A part's constructor gets (its spec, the hidden width, the layer's tensor-name prefix, the
+device); the checkpoint names of its weights are in its spec's `tensors` table, which the
+architecture's config reader writes: no part carries a checkpoint's names in its code.
+
+What a part may also offer, each with a default in `Part` (a part from outside the package
+that offers none of them still runs):
+
+  libraries(dtype, page_size) -> names of the kernel libraries (kernels/build.py) it will
+                  call, so that an engine compiles them side by side before its first step;
+  prepare_capture(ctx, cache) -> make, outside a CUDA-graph capture, whatever its forward
+                  would otherwise make on the host during the step (lists derived from the
+                  step's shape), leaving it in ctx.aux under a key that starts with "tiles";
+  flops(extents, first_positions, writes_cache) -> floating-point operations of one forward
+                  over requests bringing `extents` tokens from `first_positions` on;
+  cache_bytes_read(context_len, width) -> bytes of cache one decoded token at that context
+                  length reads (mixers that own a cache).
 """
 from __future__ import annotations
 
@@ -34,11 +51,22 @@ from ..weights.binder import WeightSpec
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """Keys and values a mixer keeps per token: every one of them, or a window."""
+    """What a mixer keeps per token in the paged cache: `planes` tensors (keys and values
+    are two) of one row of `row_shape` each, for every token or for a window of them. The
+    books only see kind and window; the storage gives every call of the group
+    [planes, pages, page layout], where a row of two or more axes is laid out with its
+    first axis outermost ([heads, page_size, head_dim]: one head's rows of a page lie
+    together) and a row of one axis as [page_size, width]."""
     kind: str                     # "full" | "window"
     window: Optional[int]
-    num_kv_heads: int
-    head_dim: int
+    planes: int
+    row_shape: Tuple[int, ...]
+
+    @staticmethod
+    def keys_and_values(window: Optional[int], num_kv_heads: int, head_dim: int) -> "CacheNeed":
+        kind = "full" if window is None else "window"
+        return CacheNeed(kind, None if window is None else int(window), 2,
+                         (int(num_kv_heads), int(head_dim)))
 
 
 @dataclass(frozen=True)
@@ -50,14 +78,22 @@ class StateNeed:
 @dataclass
 class LayerCache:
     """What a layer call may touch of the cache during one step."""
-    k: Optional[torch.Tensor] = None            # [pages, kv_heads, page_size, head_dim]
-    v: Optional[torch.Tensor] = None
+    planes: Optional[torch.Tensor] = None       # [planes, pages, *page layout] of this call
     page_size: int = 0
     block_tables: Optional[torch.Tensor] = None  # int32 [B, max_blocks] of this layer's group
     slots: Optional[torch.Tensor] = None         # int32 [T], row of the storage per token
     writable: bool = True                        # False: the cache belongs to another call
     state: Optional[torch.Tensor] = None         # [num_slots, *StateNeed.shape] float32
     group: int = -1
+
+    @property
+    def k(self) -> Optional[torch.Tensor]:
+        """Plane 0: for keys and values, the keys [pages, kv_heads, page_size, head_dim]."""
+        return None if self.planes is None else self.planes[0]
+
+    @property
+    def v(self) -> Optional[torch.Tensor]:
+        return None if self.planes is None else self.planes[1]
 
 
 @dataclass
@@ -92,3 +128,27 @@ class Part:
 
     def bind(self, weights: Dict[str, torch.Tensor]) -> None:
         pass
+
+    def libraries(self, dtype: torch.dtype, page_size: int) -> List[str]:
+        return []
+
+    def prepare_capture(self, ctx: StepContext, cache: Optional[LayerCache]) -> None:
+        pass
+
+    def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
+        return 0.0
+
+    def cache_bytes_read(self, context_len: float, width: int) -> float:
+        return 0.0
+
+
+def offered(part, name: str):
+    """A part's optional method, or Part's default when it has none (duck-typed parts from
+    outside the package need not derive from Part)."""
+    fn = getattr(part, name, None)
+    if fn is not None:
+        return fn
+    return getattr(_DEFAULTS, name)
+
+
+_DEFAULTS = Part()

@@ -3,40 +3,28 @@
     h = h + mixer(norm1(h));  h = h + feed_forward(norm2(h))
 
 (model/qwen3_graph.go:76-100). The residual stream h is float32. Each add is left
-pending and handed to the next norm, which does it in its own kernel.
+pending and handed to the next norm, which does it in its own kernel. The two norms'
+checkpoint names come from the layer spec's `tensors` table (roles mixer_norm, ffn_norm).
 """
 from __future__ import annotations
 
 import inspect
 
-from ..config.spec import LayerSpec
+from ..config.spec import LayerSpec, tensor_names
 from ..registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
-from .base import Part
-
-DEFAULT_NAMES = {
-    "mixer_norm": "input_layernorm.weight",
-    "ffn_norm": "post_attention_layernorm.weight",
-    "mixer": "self_attn.",
-    "feed_forward": "mlp.",
-}
+from .base import Part, offered
 
 
 class PreNormResidual(Part):
     def __init__(self, spec: LayerSpec, hidden: int, device=None):
-        names = dict(DEFAULT_NAMES)
-        names.update(dict(spec.names))
         p = spec.prefix
-        self.norm1 = NORMS.get(spec.norm.kind)(spec.norm, hidden, p + names["mixer_norm"])
-        self.norm2 = NORMS.get(spec.norm.kind)(spec.norm, hidden, p + names["ffn_norm"])
-        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, hidden, p + names["mixer"], device)
+        names = tensor_names(spec.tensors, p, ["mixer_norm", "ffn_norm"], "pre-norm block")
+        self.norm1 = NORMS.get(spec.norm.kind)(spec.norm, hidden, names["mixer_norm"])
+        self.norm2 = NORMS.get(spec.norm.kind)(spec.norm, hidden, names["ffn_norm"])
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, hidden, p, device)
         self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(
-            spec.feed_forward, hidden, p + names["feed_forward"], device)
+            spec.feed_forward, hidden, p, device)
         # a part whose forward takes `residual` may add its result to the stream itself
-        # every part reaches the device through the package's kernels only: its products may
-        # be collected into chains (see kernels/ops.py begin_chain)
-        self.chain_safe = all(getattr(part, "chain_safe", False)
-                              for part in (self.mixer, self.feed_forward)) and \
-            hasattr(self.norm1, "lazy") and hasattr(self.norm2, "lazy")
         self._mixer_adds = "residual" in inspect.signature(self.mixer.forward).parameters
         self._ffn_adds = "residual" in inspect.signature(self.feed_forward.forward).parameters
 
@@ -53,18 +41,30 @@ class PreNormResidual(Part):
         for part in self.parts():
             part.bind(weights)
 
-    def _normed(self, norm, part, h, pending, ctx):
-        if getattr(part, "takes_normed_rows", False) and hasattr(norm, "lazy"):
-            return norm.lazy(h, pending, ctx.act_dtype)
-        return norm.forward(h, pending, ctx.act_dtype)
+    def libraries(self, dtype, page_size):
+        out = []
+        for part in self.parts():
+            out += offered(part, "libraries")(dtype, page_size)
+        return out
+
+    def prepare_capture(self, ctx, cache):
+        for part in self.parts():
+            offered(part, "prepare_capture")(ctx, cache)
+
+    def flops(self, extents, first_positions, writes_cache=True):
+        return sum(offered(part, "flops")(extents, first_positions, writes_cache)
+                   for part in self.parts())
+
+    def cache_bytes_read(self, context_len, width):
+        return offered(self.mixer, "cache_bytes_read")(context_len, width)
 
     def forward(self, h, pending, ctx, cache):
-        n = self._normed(self.norm1, self.mixer, h, pending, ctx)
+        n = self.norm1.forward(h, pending, ctx.act_dtype)
         if self._mixer_adds:
             a = self.mixer.forward(n, ctx, cache, residual=h)
         else:
             a = self.mixer.forward(n, ctx, cache)
-        n = self._normed(self.norm2, self.feed_forward, h, a, ctx)
+        n = self.norm2.forward(h, a, ctx.act_dtype)
         if self._ffn_adds:
             return h, self.feed_forward.forward(n, ctx, residual=h)
         return h, self.feed_forward.forward(n, ctx)

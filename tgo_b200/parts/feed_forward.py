@@ -1,11 +1,15 @@
 """Dense SiLU-gated feed-forward: (SiLU(x Wg^T) * (x Wu^T)) Wd^T, no bias
 (nn/blocks.go:57-66). The gate and up matrices are joined at bind time so that one
-matrix product makes both, and one kernel applies the gate."""
+matrix product makes both, and one kernel applies the gate. The checkpoint names of the
+three matrices come from the spec's `tensors` table (roles gate, up or gate_up for a
+matrix that is shipped joined, gate rows first; down)."""
 from __future__ import annotations
+
+from typing import List
 
 import torch
 
-from ..config.spec import FeedForwardSpec
+from ..config.spec import FeedForwardSpec, tensor_names
 from ..kernels import ops
 from ..registry import FEED_FORWARDS
 from ..weights.binder import WeightSpec
@@ -16,33 +20,45 @@ class SwiGLU(Part):
     def __init__(self, spec: FeedForwardSpec, hidden: int, prefix: str, device=None):
         self.hidden = hidden
         self.inter = spec.intermediate_size
-        self.prefix = prefix
+        self.joined = "gate_up" in dict(spec.tensors)
+        roles = (["gate_up"] if self.joined else ["gate", "up"]) + ["down"]
+        self.names = tensor_names(spec.tensors, prefix, roles, "feed-forward")
         self.w_gate_up = None
         self.w_down = None
         self.interleaved = False
 
     def weight_specs(self):
-        p = self.prefix
-        return [WeightSpec(p + "gate_proj.weight", (self.inter, self.hidden)),
-                WeightSpec(p + "up_proj.weight", (self.inter, self.hidden)),
-                WeightSpec(p + "down_proj.weight", (self.hidden, self.inter))]
-
-    takes_normed_rows = True      # its first step is a matrix product: the norm may fold in
-    chain_safe = True             # touches device data through kernels/ops.py only
+        n = self.names
+        if self.joined:
+            first = [WeightSpec(n["gate_up"], (2 * self.inter, self.hidden))]
+        else:
+            first = [WeightSpec(n["gate"], (self.inter, self.hidden)),
+                     WeightSpec(n["up"], (self.inter, self.hidden))]
+        return first + [WeightSpec(n["down"], (self.hidden, self.inter))]
 
     def bind(self, weights):
-        p = self.prefix
-        gate, up = weights.pop(p + "gate_proj.weight"), weights.pop(p + "up_proj.weight")
+        n = self.names
         f, d = self.inter, self.hidden
+        if self.joined:
+            both = weights.pop(n["gate_up"])
+            gate, up = both[:f], both[f:]
+        else:
+            gate, up = weights.pop(n["gate"]), weights.pop(n["up"])
         # eight gate rows, then the eight matching up rows, and so on: one 16-row tile of the
         # weight-streaming product then holds a gate column and its up column together
         self.interleaved = f % 8 == 0
         if self.interleaved:
-            self.w_gate_up = torch.stack([gate.view(f // 8, 8, d), up.view(f // 8, 8, d)],
+            self.w_gate_up = torch.stack([gate.reshape(f // 8, 8, d), up.reshape(f // 8, 8, d)],
                                          dim=1).reshape(2 * f, d).contiguous()
         else:
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
-        self.w_down = weights.pop(p + "down_proj.weight").contiguous()
+        self.w_down = weights.pop(n["down"]).contiguous()
+
+    def libraries(self, dtype, page_size) -> List[str]:
+        return ["sgemm"] if dtype == torch.float32 else ["gemm_skinny"]
+
+    def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
+        return 2.0 * sum(extents) * self.hidden * 3 * self.inter
 
     def forward(self, x: torch.Tensor, ctx, residual=None):
         """With `residual` (the float32 stream) the result may be added to it, and None is

@@ -27,6 +27,9 @@ class RMSNorm(Part):
     def bind(self, weights):
         self.gain = weights[self.name].contiguous()
 
+    def libraries(self, dtype, page_size):
+        return ["elementwise"]
+
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = h.shape[0] if rows is None else rows.numel()
@@ -36,12 +39,3 @@ class RMSNorm(Part):
 
 
 NORMS.register("rmsnorm", RMSNorm)
-
-
-def _lazy(self, h, delta, out_dtype):
-    """The norm of h (+ delta, which the norm kernel adds to h on its way), to be computed
-    by whoever consumes it."""
-    return ops.NormedRows(h, self.gain, self.eps, out_dtype, delta)
-
-
-RMSNorm.lazy = _lazy
