@@ -169,7 +169,8 @@ def serve_workload(model, config, shape):
 
 def exactness_check(config, seed, shape):
     """Logits at real layer sizes under different ways of cutting the work. Three requests
-    (777, 300 and 65 prompt tokens, then 8 given tokens each) run (a) each alone, the prompt
+    (1500, 300 and 65 prompt tokens, then 8 given tokens each; 1500 rows in a step take the
+    tcgen05 product) run (a) each alone, the prompt
     in one step and the rest token by token; (b) together, at most two live at a time in a
     pool that holds just those two, the prompts in portions of changing size (down to two
     tokens) beside the single tokens of the others, the third request in pages the second
@@ -187,7 +188,7 @@ def exactness_check(config, seed, shape):
     from tgo_b200.engine.step import Engine, StepEntry
     V, L = config["vocab_size"], config["num_hidden_layers"]
     rng = np.random.default_rng(5)
-    lens, extra, tail = [777, 300, 65], 8, 24
+    lens, extra, tail = [1500, 300, 65], 8, 24
     toks = [rng.integers(0, V, n + extra).tolist() for n in lens]
 
     def alone(model):
@@ -206,7 +207,7 @@ def exactness_check(config, seed, shape):
     def together(model):
         eng = Engine(model, page_size=PAGE, num_slots=2,
                      max_tokens=round_up(lens[0] + extra, 64) + round_up(lens[1] + extra, 64))
-        sizes = [129, 2, 300, 64, 33, 500, 7]
+        sizes = [129, 2, 1100, 64, 33, 300, 7]
         fed, turn, rows = [0, 0, 0], [0, 1, 2], [[], [], []]
         live, waiting = [0, 1], [2]
         for rid in live:
@@ -254,7 +255,7 @@ def exactness_check(config, seed, shape):
     def top1(a, b):
         same = sum(int((x.argmax(-1) == y.argmax(-1)).sum()) for x, y in zip(a, b))
         return same / sum(x.shape[0] for x in a)
-    bound_bf16 = 4 * math.sqrt(6 * L + 2) * 2.0 ** -9 * max(scale, 1.0)
+    bound_bf16 = 4 * math.sqrt(6 * L + 2) * 2.0 ** -9 * scale
     bound_f32 = 8 * (2 * L + 1) * math.sqrt(config["hidden_size"]) * 2.0 ** -24 * 10 * max(scale, 1.0)
     line = {"only": "check", "shape": shape, "layers": L, "positions": sum(r.shape[0] for r in ref),
             "vocab": V, "largest_logit": round(scale, 4), "logit_rms": round(rms, 4),

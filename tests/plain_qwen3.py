@@ -101,12 +101,12 @@ def rope_half_split(x, positions, theta, rotary_dim=None):
     return out
 
 
-def causal_gqa_attention(q, k, v, scale, window=None):
+def causal_gqa_attention(q, k, v, scale, window=None, round_weights=None):
     """q [T,H,dh], k/v [T,Hkv,dh] of one whole sequence. Query row t of head h
     reads kv head floor(h / (H/Hkv)) over keys 0..t (those with t - j < window if
     a window is given); softmax with the maximum subtracted; masking is by
     shortening the key range (internal/oracle/attention.go:6-95;
-    nn/attention.go:234-264)."""
+    nn/attention.go:234-264). round_weights: see forward_rounded."""
     T, H, dh = q.shape
     hkv = k.shape[1]
     group = H // hkv
@@ -117,7 +117,10 @@ def causal_gqa_attention(q, k, v, scale, window=None):
             g = h // group
             s = (k[lo:t + 1, g, :] @ q[t, h, :]) * scale
             w = np.exp(s - s.max())
-            w = w / w.sum()
+            if round_weights is None:
+                w = w / w.sum()
+            else:           # the weights that multiply the values are rounded, their sum is not
+                w = round_weights(w) / w.sum()
             out[t, h, :] = w @ v[lo:t + 1, g, :]
     return out
 
@@ -178,6 +181,54 @@ def forward(cfg, w, token_ids):
         h = h + swiglu_mlp(n, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                            w[p + "mlp.down_proj.weight"])
     n = rmsnorm(h, w["model.norm.weight"], eps)
+    head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) \
+        else w["lm_head.weight"]
+    return linear(n, head)
+
+
+# ------------------------------------------------- the same model with rounded activations
+
+
+def round_bfloat16(x):
+    """Every value rounded to the nearest bfloat16 (8 significant bits, ties to even), as
+    float64."""
+    bits = np.asarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    bits = (bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000
+    return bits.astype(np.uint32).view(np.float32).astype(np.float64)
+
+
+def forward_rounded(cfg, w, token_ids, rnd=round_bfloat16):
+    """`forward`, with every activation that an engine computing in bfloat16 stores in
+    bfloat16 rounded by `rnd`: the norms' outputs, q, k and v before and after the q/k norm
+    and rotation, the softmax weights that multiply the values, the attention's output, each
+    product's output before it joins the (unrounded) residual sum, gate, up and their gated
+    product. Softmax sums, norms, angles and the residual sum stay exact. The difference from
+    `forward` is what rounding alone does to this model's logits on this input: the tests
+    hold a bfloat16 engine's error against it."""
+    eps = cfg["rms_norm_eps"]
+    H = cfg["num_attention_heads"]
+    hkv = cfg.get("num_key_value_heads", H)
+    dh = cfg.get("head_dim", cfg["hidden_size"] // H)
+    T = len(token_ids)
+    positions = np.arange(T)
+    h = embedding(w["model.embed_tokens.weight"], token_ids)
+    windows = layer_windows(cfg)
+    for l in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{l}."
+        a = p + "self_attn."
+        n = rnd(rmsnorm(h, w[p + "input_layernorm.weight"], eps))
+        q = rnd(linear(n, w[a + "q_proj.weight"])).reshape(T, H, dh)
+        k = rnd(linear(n, w[a + "k_proj.weight"])).reshape(T, hkv, dh)
+        v = rnd(linear(n, w[a + "v_proj.weight"])).reshape(T, hkv, dh)
+        q = rnd(rope_half_split(rmsnorm(q, w[a + "q_norm.weight"], eps), positions, cfg["rope_theta"]))
+        k = rnd(rope_half_split(rmsnorm(k, w[a + "k_norm.weight"], eps), positions, cfg["rope_theta"]))
+        att = rnd(causal_gqa_attention(q, k, v, 1.0 / math.sqrt(dh), windows[l], round_weights=rnd))
+        h = h + rnd(linear(att.reshape(T, H * dh), w[a + "o_proj.weight"]))
+        n = rnd(rmsnorm(h, w[p + "post_attention_layernorm.weight"], eps))
+        gate = rnd(linear(n, w[p + "mlp.gate_proj.weight"]))
+        up = rnd(linear(n, w[p + "mlp.up_proj.weight"]))
+        h = h + rnd(linear(rnd(silu(gate) * up), w[p + "mlp.down_proj.weight"]))
+    n = rnd(rmsnorm(h, w["model.norm.weight"], eps))
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) \
         else w["lm_head.weight"]
     return linear(n, head)

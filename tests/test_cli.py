@@ -9,8 +9,9 @@ from tgo_b200.sampling.policy import DrawStream, Policy
 
 
 class FakeSession:
-    def __init__(self, context):
+    def __init__(self, context, **kw):
         self.context = context
+        self.kw = kw
         self.calls = []
 
     def complete(self, prompt, policy):
@@ -24,12 +25,19 @@ class FakeModel:
         vocab_size = 1000
     info = {"architecture": "Qwen3ForCausalLM", "weight_bytes": 10 ** 9}
 
+    stop_ids = [7, 9]
+
     def __init__(self):
         self.sessions = []
+        self.generated = []
 
-    def new_session(self, context=4096):
-        self.sessions.append(FakeSession(context))
+    def new_session(self, context=4096, **kw):
+        self.sessions.append(FakeSession(context, **kw))
         return self.sessions[-1]
+
+    def generate(self, prompts, policies, **kw):
+        self.generated.append((prompts, policies, kw))
+        return [[200 + i] * policies[i].max_tokens for i in range(len(prompts))]
 
 
 def run(argv):
@@ -62,7 +70,29 @@ def test_defaults_are_the_references():
     assert (a.max_tokens, a.temp, a.top_k, a.top_p, a.repeat_penalty, a.seed, a.precision,
             a.context, a.device) == (128, 0.0, 0, 0.0, 1.0, 0, "auto", 4096, "auto")
     b = cli.bench_parser().parse_args(["m"])
-    assert (b.tokens, b.prompt_tokens, b.batch, b.warmup, b.json) == (128, 128, 1, 8, "")
+    assert (b.tokens, b.prompt_tokens, b.batch, b.warmup, b.json) == (128, 128, "1", 8, "")
+    assert (a.page_size, a.kv_pages, a.stop_ids, a.prompt, a.prompt_len) == (16, 0, "auto", None, 0)
+
+
+def test_stop_ids_page_size_and_several_prompts():
+    """What goes beyond the reference's flags: stop ids (the model folder's by default), the
+    page size, and several prompts, which run together through the scheduler."""
+    rc, out, err, _, model = run(["run", "--max-tokens", "2", "--page-size", "8", "m"])
+    assert rc == 0 and model.sessions[0].kw == {"page_size": 8, "stop_ids": [7, 9]}
+    assert model.sessions[0].calls[0][0] == [1, 2, 3, 4, 5, 6, 7, 8]
+    rc, out, err, _, model = run(["run", "--max-tokens", "2", "--stop-ids", "3,4", "m"])
+    assert model.sessions[0].kw["stop_ids"] == [3, 4]
+    rc, out, err, _, model = run(["run", "--max-tokens", "2", "--stop-ids", "none", "m"])
+    assert model.sessions[0].kw["stop_ids"] == []
+    rc, out, err, _, model = run(["run", "--prompt", "1 2", "--prompt", "3,4,5", "--max-tokens", "3",
+                                  "--seed", "5", "--kv-pages", "40", "--context", "64", "m"])
+    assert rc == 0 and not model.sessions
+    prompts, policies, kw = model.generated[0]
+    assert prompts == [[1, 2], [3, 4, 5]] and [p.seed for p in policies] == [5, 6]
+    assert kw == {"slots": 2, "pool_tokens": 640, "page_size": 16, "stop_ids": [7, 9]}
+    assert out.splitlines() == ["200 200 200", "201 201 201"] and "2 prompts" in err
+    rc, out, err, _, model = run(["run", "--prompt-len", "11", "--max-tokens", "1", "m"])
+    assert rc == 0 and len(model.sessions[0].calls[0][0]) == 11
 
 
 @pytest.mark.parametrize("argv,needle", [
@@ -77,6 +107,12 @@ def test_defaults_are_the_references():
     (["bench", "--tokens", "100", "--prompt-tokens", "100", "--context", "150", "m"], "more than"),
     (["bench", "--warmup", "-1", "m"], "warmup"),
     (["bench", "--batch", "0", "m"], "batch"),
+    (["bench", "--batch", "1,x", "m"], "batch"),
+    (["run", "--stop-ids", "eos", "m"], "stop-ids"),
+    (["run", "--prompt", "1", "--prompt-len", "4", "m"], "prompt-len"),
+    (["run", "--config", "c.json", "m"], "go together"),
+    (["run"], "<model-dir> is needed"),
+    (["run", "--prompt", "1 2 3", "--prompt", "4", "--max-tokens", "60", "--context", "62", "m"], "exceed"),
 ])
 def test_usage_errors_name_the_flag(argv, needle):
     rc, out, err, opened, _ = run(argv)

@@ -300,17 +300,20 @@ def test_attention_decode_split(H, Hkv, dh, ps, window):
         if not ops().flash_supports(dh, H // Hkv):
             pytest.skip("no tensor-core instance for this head size")
         ops().attention_flash(case["q"], out, H, Hkv, dh, case["kc"], case["vc"], ps, case["bt"],
-                              case["pos"], case["seq"], None, None, scale, window, wide=False,
+                              case["pos"], case["seq"], None, None, scale, window,
                               n_splits=n_splits)
         assert torch.allclose(out.float().cpu(), want, **tol(torch.bfloat16)), n_splits
 
 
 @pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 127, 128, 499])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_attention_far_key_stands_out(far, dtype):
+@pytest.mark.parametrize("dh", [64, 128])
+def test_attention_far_key_stands_out(far, dtype, dh):
     """One key among 500 is made to carry nearly all the weight; a kernel that skips it (a
-    tile's or a page's edge) returns something else entirely."""
-    H, Hkv, dh, ps = 8, 2, 64, 16
+    tile's or a page's edge) returns something else entirely. Head size 64 goes through the
+    mma.sync kernels, 128 (in bfloat16) through the tcgen05 kernel for the portion and the
+    TMA-fed kernel for the single token."""
+    H, Hkv, ps = 8, 2, 16
 
     def crafted(b, K, V):
         K *= 0.05
@@ -334,10 +337,12 @@ def test_attention_far_key_stands_out(far, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_attention_window_edge(dtype):
+@pytest.mark.parametrize("H,Hkv,dh,ps", [(4, 2, 32, 8), (8, 2, 128, 16), (32, 8, 128, 16)])
+def test_attention_window_edge(dtype, H, Hkv, dh, ps):
     """The key just outside the window carries a huge score and must not be read; the key
-    just inside must be."""
-    H, Hkv, dh, ps, W = 4, 2, 32, 8, 40
+    just inside must be. (Head size 128 in bfloat16: the TMA-fed decode kernel, and the
+    tcgen05 kernel when the token comes as a portion.)"""
+    W = 40
     p = 200
     for edge, expect in ((p - W, 1.0), (p - W + 1, 7.0)):
         def crafted(b, K, V, edge=edge):
@@ -353,6 +358,33 @@ def test_attention_window_edge(dtype):
             attention_part().paged_attention(q, out, H, Hkv, dh, Cache(case, ps), Ctx(case, decode),
                                   1 / math.sqrt(dh), W)
             assert torch.allclose(out.float(), torch.full_like(out, expect).float(), atol=0.05)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,Hkv,dh,ps", [(4, 2, 32, 8), (8, 2, 128, 16), (32, 8, 128, 16), (6, 2, 64, 32)])
+def test_attention_window_edge_inside_a_portion(dtype, H, Hkv, dh, ps):
+    """A prompt portion of 121 tokens at positions 140..260 with a window of 40, so the
+    window's start moves through the kernel's key tiles row by row. Key 170 carries a huge
+    score and the value 7, every other value is 1: exactly the rows at positions 170..209
+    may read it (earlier rows are before it, later rows' windows have passed it)."""
+    W, first, n, edge = 40, 140, 121, 170
+
+    def crafted(b, K, V):
+        K *= 0.01
+        V[:] = 1.0
+        K[edge, :, 0] = 50.0
+        V[edge] = 7.0
+    case = paged_case([n], [first], H, Hkv, dh, ps, dtype, seed=4, crafted=crafted)
+    q = torch.zeros_like(case["q"])
+    q[:, 0::dh] = 8.0
+    out = torch.zeros_like(q)
+    attention_part().paged_attention(q, out, H, Hkv, dh, Cache(case, ps), Ctx(case, False),
+                                     1 / math.sqrt(dh), W)
+    pos = torch.arange(first, first + n, device=DEV)
+    sees = (pos >= edge) & (pos - W + 1 <= edge)
+    want = torch.where(sees, 7.0, 1.0)[:, None].expand_as(out)
+    bad = (out.float() - want).abs().amax(dim=1) > 0.05
+    assert not bad.any(), f"wrong at positions {pos[bad].tolist()}"
 
 
 def test_attention_unusual_head_size_falls_back():
@@ -730,7 +762,7 @@ def test_attention_decode_beyond_the_on_chip_table(window):
     for n_splits in (1, 7):
         out = torch.zeros_like(case["q"])
         ops().attention_flash(case["q"], out, H, Hkv, dh, case["kc"], case["vc"], ps, case["bt"],
-                              case["pos"], case["seq"], None, None, scale, window, wide=False,
+                              case["pos"], case["seq"], None, None, scale, window,
                               n_splits=n_splits)
         assert torch.allclose(out.float().cpu(), want, **tol(torch.bfloat16)), n_splits
     assert ops().attention_decode_tma_error() == 0

@@ -446,6 +446,7 @@ def test_layer_run_twice_and_borrowed_cache_on_the_gpu(tmp_path, dtype):
         rows.append(eng.step([StepEntry("x", [t], [0])]).float().cpu())
     got = torch.cat(rows).numpy()
     # the bound is a function of the number of layers a token passes: four calls here
-    tol = tiny.tolerance(dict(cfg, num_hidden_layers=len(spec.run_order)), dtype,
-                         float(np.abs(want).max()))
+    tol = tiny.tolerance(dict(cfg, num_hidden_layers=len(spec.run_order)), dtype, want,
+                         tiny.repeated_layers_reference(pc, pw, toks, plain.round_bfloat16))
+    tiny.note(f"run_twice/{dtype}", float(np.abs(got - want).max()), tol)
     assert np.abs(got - want).max() <= tol

@@ -113,3 +113,182 @@ def test_tiny_forward_is_causal_and_tied(tmp_path):
     assert full.shape == (6, 256)
     assert np.allclose(plain.forward(c, w, toks[:4]), full[:4])      # no cache, still causal
     assert "lm_head.weight" not in w
+
+
+# ------------------------------------------------- the reference's own inputs and expected values
+# Each test below takes its inputs and its expected numbers from the reference's oracle tests
+# (internal/oracle/*_test.go), which its authors computed outside their package. Where the
+# reference draws inputs from its own generator (randf) and asserts a relation rather than
+# numbers, the relation is asserted here on inputs drawn here.
+
+TOL_ULP = 4 * 2.0 ** -52          # oracle_test.go: a few units in the last place of a float64
+
+
+def close(got, want, tol=TOL_ULP):
+    got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
+    return np.all(np.abs(got - want) <= tol * np.maximum(1.0, np.abs(want)))
+
+
+def test_reference_rmsnorm_vectors():
+    """internal/oracle/oracle_test.go:69-77 (hand computed), :79-88 (eps inside the root),
+    :90-106 (each row of width len(gain) on its own: the per-head q/k norm)."""
+    x = np.array([[1.0, 2.0, 3.0, 4.0]])
+    want = [0.3651483716701107, 1.4605934866804429, 0.5477225575051661, -1.4605934866804429]
+    assert close(plain.rmsnorm(x, np.array([1.0, 2.0, 0.5, -1.0]), 0.0)[0], want)
+    want = [0.3651483473268884, 0.7302966946537768, 1.0954450419806652, 1.4605933893075536]
+    assert close(plain.rmsnorm(x, np.ones(4), 1e-6)[0], want)
+    heads = np.array([[1.0, 1.0], [100.0, 100.0]])              # two heads of width 2
+    assert close(plain.rmsnorm(heads, np.ones(2), 0.0), [[1, 1], [1, 1]])
+    wide = plain.rmsnorm(heads.reshape(1, 4), np.ones(4), 0.0)
+    assert abs(wide[0, 0] - 1) > 1e-3                           # one row of 4 would mix the heads
+
+
+def test_reference_matmul_vectors():
+    """internal/oracle/oracle_test.go:112-118, :120-128, :130-137. The reference multiplies
+    x [m,k] by w [k,n]; `linear` takes the weight as the checkpoint stores it, [n,k]."""
+    x = np.array([[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]])
+    w = np.array([[1.0, 2.0], [3.0, 4.0], [5.0, 6.0]])
+    assert close(plain.linear(x, w.T), [[22, 28], [49, 64]])
+    row = np.array([[1.0, -2.0, 3.5, 0.0, 7.0]])
+    assert close(plain.linear(row, np.eye(5)), row)
+    w = np.array([[1.0, 10.0, 100.0], [1.0, 10.0, 100.0]])
+    assert close(plain.linear(np.array([[2.0, 3.0]]), w.T), [[5, 50, 500]])
+
+
+def test_reference_silu_and_swiglu_vectors():
+    """internal/oracle/oracle_test.go:155-160 (values), :162-174 (saturation), :176-186
+    (the gate multiplies the up branch)."""
+    assert close(plain.silu(np.array([0.0, 1.0, -2.0])), [0, 0.7310585786300049, -0.2384058440442351])
+    with np.errstate(over="ignore"):
+        big = plain.silu(np.array([800.0, -800.0]))
+    assert big[0] == 800 and big[1] == 0
+    gate, up = np.array([0.0, 1.0, -2.0, 3.0]), np.array([5.0, -1.0, 2.0, 0.5])
+    want = [0 * 5, 0.7310585786300049 * -1, -0.2384058440442351 * 2, 3 / (1 + math.exp(-3)) * 0.5]
+    assert close(plain.silu(gate) * up, want)
+    # through the feed-forward: a one-channel input of 1 makes x Wg^T = gate and x Wu^T = up
+    got = plain.swiglu_mlp(np.array([[1.0]]), gate[:, None], up[:, None], np.eye(4))
+    assert close(got[0], want)
+
+
+def one_head(q, k, v, scale, base=None):
+    """The reference's Attention(q, k, v, qSeq, 1, 1, headDim, kvLen, scale, causalBase) for
+    the cases below: the queries are the last rows of a sequence whose keys are k."""
+    q, k, v = (np.asarray(a, dtype=np.float64) for a in (q, k, v))
+    n_q, n_k = q.shape[0], k.shape[0]
+    first = n_k - n_q if base is None else base
+    pad = np.zeros((first, q.shape[1]))
+    out = plain.causal_gqa_attention(np.concatenate([pad, q])[:, None, :][:first + n_q],
+                                     k[:first + n_q, None, :], v[:first + n_q, None, :], scale)
+    return out[first:, 0, :]
+
+
+def test_reference_attention_vectors():
+    """internal/oracle/attention_test.go:21-35 (one key returns the value, exactly), :37-61
+    (floor grouping: four query heads over two kv heads read 0,0,1,1), :194-207 (scale 0 is
+    the mean of the values), :209-224 (a softmax computed by hand)."""
+    got = one_head([[0.5, -2, 100]], [[1, 1, 1]], [[7, 8, 9]], 0.125)
+    assert np.array_equal(got[0], [7, 8, 9])
+    rng = np.random.default_rng(21)
+    q, k = rng.normal(size=(2, 4, 2)), rng.normal(size=(2, 2, 2))
+    v = np.empty((2, 2, 2))
+    v[:, 0, :], v[:, 1, :] = 10.0, 20.0                      # the value names the kv head read
+    got = plain.causal_gqa_attention(q, k, v, 0.7)[1]
+    assert close(got, [[10, 10], [10, 10], [20, 20], [20, 20]], 4 * TOL_ULP)
+    rng = np.random.default_rng(71)
+    v = [[1, 10], [2, 20], [3, 30], [4, 40]]
+    got = one_head(rng.normal(size=(1, 2)), rng.normal(size=(4, 2)), v, 0.0)
+    assert close(got[0], [2.5, 25], 8 * TOL_ULP)
+    got = one_head([[1, 0]], [[1, 0], [0, 1]], [[1, 2], [3, 4]], 2.0)
+    e0, e1 = math.exp(2.0), math.exp(0.0)
+    w0, w1 = e0 / (e0 + e1), e1 / (e0 + e1)
+    assert close(got[0], [w0 * 1 + w1 * 3, w0 * 2 + w1 * 4], 4 * TOL_ULP)
+
+
+def test_reference_attention_relations():
+    """internal/oracle/attention_test.go:63-101 (heads of a group read the same keys),
+    :103-134 (the future is masked, bit for bit), :136-149 (the first query reads only its
+    own key), :151-168 (decode equals the last row of prefill)."""
+    rng = np.random.default_rng(91)
+    k, v = rng.normal(size=(3, 2, 3)), rng.normal(size=(3, 2, 3))
+    q = np.tile(rng.normal(size=(1, 1, 3)), (3, 4, 1))
+    got = plain.causal_gqa_attention(q, k, v, 0.6)[2]
+    assert np.array_equal(got[0], got[1]) and np.array_equal(got[2], got[3])
+    assert not np.array_equal(got[0], got[2])
+    q, k, v = rng.normal(size=(3, 1, 2)), rng.normal(size=(3, 1, 2)), rng.normal(size=(3, 1, 2))
+    before = plain.causal_gqa_attention(q, k, v, 0.5)
+    k2, v2 = k.copy(), v.copy()
+    k2[2] += 5
+    v2[2] += 5
+    after = plain.causal_gqa_attention(q, k2, v2, 0.5)
+    assert np.array_equal(before[:2], after[:2]) and not np.array_equal(before[2], after[2])
+    q, k, v = rng.normal(size=(4, 1, 3)), rng.normal(size=(4, 1, 3)), rng.normal(size=(4, 1, 3))
+    assert np.array_equal(plain.causal_gqa_attention(q, k, v, 0.3)[0, 0], v[0, 0])
+    q, k, v = rng.normal(size=(3, 4, 5)), rng.normal(size=(3, 2, 5)), rng.normal(size=(3, 2, 5))
+    whole = plain.causal_gqa_attention(q, k, v, 0.44)
+    assert np.array_equal(plain.causal_gqa_attention(q, k, v, 0.44)[2], whole[2])
+
+
+def test_reference_rope_vectors():
+    """internal/oracle/rope_test.go:198-215 (the angle: pair i at position m turns by
+    m * base^(-2i/rotary_dim); pair 0 by m radians), :217-250 (theta divides by rotary_dim,
+    not by the head's width), :170-181 (channels past rotary_dim are left alone). The
+    reference's vectors are laid out for its interleaved kernel, pairs (2i, 2i+1); the same
+    pairs in half-split layout are (i, i + rotary_dim/2)."""
+    m, base = 2.0, 1e6
+    # interleaved x = [1, 0, 1, 0]: pair 0 = (1, 0), pair 1 = (1, 0); half-split: [1, 1, 0, 0]
+    got = plain.rope_half_split(np.array([[[1.0, 1.0, 0.0, 0.0]]]), np.array([2]), base)[0, 0]
+    assert close([got[0], got[2]], [math.cos(m), math.sin(m)])
+    theta1 = base ** -0.5
+    assert close([got[1], got[3]], [math.cos(m * theta1), math.sin(m * theta1)])
+    # width 8, rotary_dim 4: pair 1 turns by base^(-2/4), not base^(-2/8)
+    x = np.array([[[1.0, 1.0, 0.0, 0.0, 9.0, 9.0, 9.0, 9.0]]])
+    got = plain.rope_half_split(x, np.array([2]), base, rotary_dim=4)[0, 0]
+    want_theta, wrong_theta = base ** (-2.0 / 4.0), base ** (-2.0 / 8.0)
+    assert close([got[1], got[3]], [math.cos(m * want_theta), math.sin(m * want_theta)])
+    assert abs(got[1] - math.cos(m * wrong_theta)) > 1e-6
+    assert np.array_equal(got[4:], [9, 9, 9, 9])
+    x = np.array([[[1.0, 2.0, 3.0, 4.0, 5.0, 6.0]]])
+    got = plain.rope_half_split(x, np.array([9]), base, rotary_dim=4)[0, 0]
+    assert got[4] == 5 and got[5] == 6 and not (got[0] == 1 and got[1] == 2)
+
+
+def test_reference_rope_relations():
+    """internal/oracle/rope_test.go:139-168 (a rotation keeps each pair's norm, at positions
+    0, 1, 17, 512, 4095 with base 1e6), :183-196 (each row turns by its own position)."""
+    rng = np.random.default_rng(5)
+    rows, width, rot = 5, 8, 6
+    x = rng.normal(size=(rows, 1, width))
+    pos = np.array([0, 1, 17, 512, 4095])
+    got = plain.rope_half_split(x, pos, 1e6, rotary_dim=rot)
+    for i in range(rot // 2):
+        before = x[:, 0, i] ** 2 + x[:, 0, i + rot // 2] ** 2
+        after = got[:, 0, i] ** 2 + got[:, 0, i + rot // 2] ** 2
+        assert close(after, before, 4 * TOL_ULP)
+    same = np.tile(np.array([[[1.0, 2.0]]]), (3, 1, 1))
+    got = plain.rope_half_split(same, np.array([0, 1, 1]), 1e6)
+    assert np.array_equal(got[1], got[2]) and not np.array_equal(got[0], got[1])
+
+
+def test_reference_sampling_vectors():
+    """sample/stages_test.go:67-89 (the penalty's arithmetic, exact in float32), :93-105 (a
+    negative logit is multiplied, not divided), :110-116 (zero is in the multiply branch),
+    :120-130 (once per token, however often it came), :247-255 and :260-266 (ties at the edge
+    of the nucleus and of top-k go to the lower id), :365-374 (greedy is one-hot), :376-380
+    (argmax ties go to the lowest id)."""
+    r, alpha, beta = 2.0, 0.5, 0.25
+    logits = [3.0, -3.0, 0.0, 5.0]
+    got = plain.penalize(logits, [0, 0, 1], rep=r, presence=alpha, frequency=beta)
+    want = np.array([3 / r - alpha - beta * 2, -3 * r - alpha - beta * 1, 0.0, 5.0], dtype=np.float32)
+    assert np.array_equal(np.asarray(got, dtype=np.float32), want)
+    assert plain.penalize([-4.0], [0], rep=2.0)[0] == -8.0
+    assert plain.penalize([0.0], [0], rep=4.0)[0] == 0.0
+    assert plain.penalize([8.0], [0], rep=2.0)[0] == plain.penalize([8.0], [0, 0, 0, 0], rep=2.0)[0]
+    ids, _, _ = plain.policy_distribution(np.array([1, 0, 0], np.float32), temperature=1.0, top_p=0.7)
+    assert ids == [0, 1]
+    ids, _, _ = plain.policy_distribution(np.array([0, 0, 0], np.float32), temperature=1.0, top_k=2)
+    assert ids == [0, 1]
+    ids, w, total = plain.policy_distribution(np.array([1, 9, 3], np.float32))
+    assert ids == [1] and float(w[0]) == float(total)
+    assert plain.argmax_lowest(np.array([2.0, 7.0, 7.0, 1.0])) == 1
+    ids, _, _ = plain.policy_distribution(np.array([3, 2, 1, 0, -1], np.float32), temperature=1.0, top_k=10)
+    assert ids == [0, 1, 2, 3, 4]                   # sample/stages_test.go:294-303

@@ -20,7 +20,7 @@ def models(tmp_path_factory):
         d = tiny.make_model_dir(tmp_path_factory.mktemp(f"tiny{name}"), cfg, run["seed"],
                                 run["sigma"])
         reqs = tiny.random_requests(cfg["vocab_size"], LENGTHS[name], seed=10 + run["seed"])
-        out[name] = (d, cfg, run, reqs, tiny.plain_logits(d, reqs))
+        out[name] = (d, cfg, run, reqs, tiny.plain_logits(d, reqs), tiny.plain_logits_rounded(d, reqs))
     return out
 
 
@@ -28,12 +28,12 @@ def models(tmp_path_factory):
 @pytest.mark.parametrize("family", list(FAMILIES))
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_replay_matches_plain(models, tmp_path, name, family, dtype):
-    d, cfg, run, reqs, want = models[name]
+    d, cfg, run, reqs, want, rounded = models[name]
     trace = FAMILIES[family](reqs)
     got = tiny.run_trace_program(d, dtype, trace, tmp_path / "out", cfg["vocab_size"],
                                  extra=["--page-size", str(run["page_size"])])
     assert len(got) == sum(len(t) for t in reqs.values())
-    worst, where, tol = tiny.compare(got, want, cfg, dtype)
+    worst, where, tol = tiny.compare(got, want, cfg, dtype, f"replay/{name}/{family}/{dtype}", rounded)
     assert worst <= tol, f"{name}/{family}/{dtype}: error {worst:.3e} at {where}, allowed {tol:.3e}"
 
 
@@ -42,7 +42,7 @@ def test_float32_cuts_agree_bit_for_bit(models, name):
     """In float32 every sum's order depends on the position alone, so the four ways of
     cutting give the same bits, not just close values."""
     import tgo_b200
-    d, cfg, run, reqs, _ = models[name]
+    d, cfg, run, reqs, _, _ = models[name]
     model = tgo_b200.open(d, dtype="float32")
     results = {}
     for fam, make in FAMILIES.items():
@@ -66,7 +66,7 @@ def test_prompt_portions_through_graphs_give_the_same_bits(models, name, dtype):
     import torch
     import tgo_b200
     from tgo_b200.engine.step import StepEntry
-    d, cfg, run, reqs, _ = models[name]
+    d, cfg, run, reqs, _, _ = models[name]
     model = tgo_b200.open(d, dtype=dtype)
     rng = np.random.default_rng(5)
     long_a = rng.integers(0, cfg["vocab_size"], 200).tolist()

@@ -110,8 +110,34 @@ def test_one_error_lists_missing_unexpected_and_wrong(tmp_path):
     msg = str(e.value)
     assert "2 missing" in msg and "model.layers.1.mlp.up_proj.weight" in msg
     assert "1 unexpected" in msg and "q_proj.bias" in msg
-    assert "2 of the wrong shape" in msg and "[383, 96], declared [384, 96]" in msg
-    assert "k_norm.weight is [16], declared [32]" in msg
+    assert "2 of the wrong shape" in msg and "k_norm.weight is [16], declared [32]" in msg
+    # the embedding's row count is the vocabulary: the message names the config's field
+    assert "vocab_size is 384 and model.embed_tokens.weight has 383 rows" in msg
+
+
+def test_errors_for_rank_empty_and_values_that_do_not_survive(tmp_path):
+    """weights/weights.go:756-762 (a weight is a matrix or a gain vector), :605-610 (an empty
+    tensor), :450-458 (values the 16-bit storage type cannot hold); and the rounding of
+    float16 to bfloat16 is said once."""
+    specs = [WeightSpec("m", (2, 3), "matrix"), WeightSpec("g", (3,), "gain")]
+    with pytest.raises(WeightError) as e:
+        check_weights(specs, {"m": ("BF16", (2, 3, 1)), "g": ("F32", (0,))})
+    assert "m has rank 3" in str(e.value) and "g is empty" in str(e.value)
+    write_safetensors(str(tmp_path / "model.safetensors"),
+                      {"m": torch.tensor([[1.0, 2.0, 0.3337], [4.0, 5.0, 6.0]], dtype=torch.float16),
+                       "g": torch.ones(3)})
+    logs = []
+    got = load_weights(specs, SafetensorsRepo(str(tmp_path)), torch.bfloat16, "cpu", None, logs.append)
+    assert got["m"].dtype == torch.bfloat16
+    assert len(logs) == 1 and "1 tensors are stored as float16" in logs[0] and "m" in logs[0]
+    logs.clear()
+    load_weights(specs, SafetensorsRepo(str(tmp_path)), torch.float32, "cpu", None, logs.append)
+    assert not logs                                  # widening loses nothing and says nothing
+    write_safetensors(str(tmp_path / "model.safetensors"),
+                      {"m": torch.tensor([[1.0, float("inf"), 0.0], [4.0, 5.0, 6.0]],
+                                         dtype=torch.float16), "g": torch.ones(3)})
+    with pytest.raises(WeightError, match="not finite"):
+        load_weights(specs, SafetensorsRepo(str(tmp_path)), torch.bfloat16, "cpu", None, logs.append)
 
 
 def test_declared_names_are_the_checkpoints_own(tmp_path):
@@ -173,6 +199,11 @@ def test_random_weights_are_seeded_per_tensor(tmp_path):
     assert torch.equal(w1["a"], w2["a"]) and torch.equal(w1["g"], w2["g"])
     assert not torch.equal(w1["a"], random_weights(specs, 4, dtype=torch.float32)["a"])
     assert abs(float(w1["g"].mean()) - 1) < 0.3
+    from tgo_b200.weights.random_init import seeded_normal
+    x = seeded_normal(200000, 7)
+    assert abs(float(x.mean())) < 0.01 and abs(float(x.std()) - 1) < 0.01
+    assert abs(float((x ** 4).mean()) - 3) < 0.1 and float(x.abs().max()) < 4.4
+    assert torch.equal(x[:1000], seeded_normal(1000, 7))       # a stream's start does not depend on its length
     write_random_model(str(tmp_path / "r"), tiny.TINY_A, seed=0)
     assert sorted(os.listdir(tmp_path / "r")) == ["config.json", "model.safetensors"]
     with open(tmp_path / "r" / "config.json") as f:

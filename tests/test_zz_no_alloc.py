@@ -6,8 +6,11 @@ that must not take the device-wide stall of cudaMalloc and cudaFree, or C code w
 tensor allocator. For them the scratch of the split-key decode attention is an array
 inside the library. This test calls that entry point through its exported C symbol, with
 ctypes and raw pointers, twice in a row, and compares each result with the ordinary entry
-point's, which takes its scratch from torch. The second call uses other inputs and another
-split count, so what the first call left in the shared array must not show.
+point's, which takes its scratch from torch, and with a dense float32 attention written
+with torch over the same keys and values (the two entry points share their kernels, so
+agreeing with each other alone would not show an error in the arithmetic). The second call
+uses other inputs and another split count, so what the first call left in the shared array
+must not show.
 
 The file sorts last on purpose: a run that stops at the first failure has then already run
 every other test.
@@ -43,16 +46,17 @@ def call_static(fn, case, out, H, Hkv, dh, ps, scale, window, n_splits):
 
 
 def test_static_scratch_entry_matches_the_allocating_one():
-    from test_kernels_gpu import paged_case
+    from test_kernels_gpu import attention_ref, paged_case
     from tgo_b200.kernels import ops
     fn = static_entry()
     H, Hkv, dh, ps = 8, 2, 64, 16
     scale = 1 / math.sqrt(dh)
     for seed, firsts, n_splits, window in ((1, [700, 63, 0, 300], 5, 0), (2, [511, 64, 129, 5], 3, 100)):
         case = paged_case([1, 1, 1, 1], firsts, H, Hkv, dh, ps, torch.bfloat16, seed=seed)
+        dense = attention_ref(case, H, Hkv, dh, scale, window)
         want = torch.zeros_like(case["q"])
         ops.attention_flash(case["q"], want, H, Hkv, dh, case["kc"], case["vc"], ps, case["bt"],
-                            case["pos"], case["seq"], None, None, scale, window, wide=False,
+                            case["pos"], case["seq"], None, None, scale, window,
                             n_splits=n_splits)
         got = torch.full_like(case["q"], float("nan"))
         torch.cuda.synchronize()
@@ -62,11 +66,32 @@ def test_static_scratch_entry_matches_the_allocating_one():
         assert rc == 0
         assert torch.cuda.memory_allocated() == before          # torch was asked for nothing
         assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+        assert torch.allclose(got.float().cpu(), dense, rtol=2e-2, atol=2e-2)
     # one split needs no scratch at all and still works
     got = torch.zeros_like(case["q"])
     assert call_static(fn, case, got, H, Hkv, dh, ps, scale, window, 1) == 0
     torch.cuda.synchronize()
     assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    assert torch.allclose(got.float().cpu(), dense, rtol=2e-2, atol=2e-2)
+
+
+def test_static_scratch_entry_takes_the_largest_request_that_fits():
+    """209 tokens x 8 heads x 19 splits x (64 + 2) floats = 2 096 688 of the array's 2 097 152:
+    the largest request of this shape that fits (one more split would not). Every split's
+    partial result lies in the array, the last one ends 464 floats before its end."""
+    from test_kernels_gpu import attention_ref, paged_case
+    fn = static_entry()
+    H, Hkv, dh, ps, T, n_splits = 8, 2, 64, 16, 209, 19
+    assert T * H * n_splits * (dh + 2) <= SCRATCH_FLOATS < T * H * (n_splits + 1) * (dh + 2)
+    firsts = [(37 * i) % 150 for i in range(T)]
+    case = paged_case([1] * T, firsts, H, Hkv, dh, ps, torch.bfloat16, seed=7)
+    scale = 1 / math.sqrt(dh)
+    dense = attention_ref(case, H, Hkv, dh, scale, 0)
+    got = torch.full_like(case["q"], float("nan"))
+    assert call_static(fn, case, got, H, Hkv, dh, ps, scale, 0, n_splits) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(got.float().cpu(), dense, rtol=2e-2, atol=2e-2)
+    assert call_static(fn, case, got, H, Hkv, dh, ps, scale, 0, n_splits + 1) == E_TOO_SMALL
 
 
 def test_static_scratch_entry_refuses_what_does_not_fit():

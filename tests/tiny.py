@@ -9,9 +9,10 @@ Two configurations of the one architecture that differ in every size and option:
 In A the q width equals the hidden size and layers equal kv heads, so a confusion of
 those two pairs passes there; B is the configuration that tells them apart.
 
-A third, TINY_C, has the head size (128) that the tcgen05 attention kernel takes, a window
-layer, and prompts long enough for the tcgen05 product, so that replay in bfloat16 goes
-through those kernels too:
+A third, TINY_C, has the head size (128) that the tcgen05 attention kernel and the TMA-fed
+decode kernel take, and a window layer, so that replay in bfloat16 goes through those
+kernels too. (The tcgen05 product starts above 1024 rows: tests/test_schedules_gpu.py runs
+Tiny C with a 1200-token request, and with the threshold lowered to 65 rows.)
 
   TINY_C      2    160     4    2   128       512      272   320   5e5    1e-5   no    40 (layer 0)  16
 """
@@ -180,11 +181,34 @@ def trace_mixed(requests, seed=0, max_live=4, tail=32):
 # ----------------------------------------------------------------------- running
 
 
-def run_trace_engine(engine, trace):
-    """Drive an Engine in-process; {(id, position): logits row (numpy float32)}."""
+def held_pages(engine):
+    """Per group, {page: request id} over the live requests' block tables."""
+    out = [dict() for _ in engine.cache.groups]
+    for rid, req in engine.cache.requests.items():
+        for g in range(len(out)):
+            for p in req.held(g):
+                out[g][p] = rid
+    return out
+
+
+def poison_unheld(engine):
+    """NaN into every page no live request holds: pages never handed out, pages of finished
+    requests, pages a window has passed."""
+    for g, held in enumerate(held_pages(engine)):
+        n = engine.cache.pools[g].num_pages
+        engine.storage.poison_pages(g, [p for p in range(1, n + 1) if p not in held])
+
+
+def run_trace_engine(engine, trace, poison=False, owners=None):
+    """Drive an Engine in-process; {(id, position): logits row (numpy float32)}.
+    poison: before the first step, and after every step and every end of a request, every
+    page that no live request holds is filled with NaN. owners: a list (one dict per cache
+    group) that collects {page: set of request ids that ever held it}."""
     from tgo_b200.engine.step import StepEntry
     keys = keys_of(trace)
     out = {}
+    if poison:
+        poison_unheld(engine)
     for st in trace:
         entries = []
         for e in st["entries"]:
@@ -197,8 +221,14 @@ def run_trace_engine(engine, trace):
             assert arr.shape[0] == len(keys[st["step"]])
             for row, k in zip(arr, keys[st["step"]]):
                 out[k] = row
+        if owners is not None:
+            for g, held in enumerate(held_pages(engine)):
+                for p, rid in held.items():
+                    owners[g].setdefault(p, set()).add(rid)
         for rid in st["end"]:
             engine.finish(rid)
+        if poison:
+            poison_unheld(engine)
         engine.cache.check_invariants()
     return out
 
@@ -235,63 +265,100 @@ def plain_logits(model_dir, requests):
     return {rid: plain.forward(cfg, w, toks) for rid, toks in requests.items()}
 
 
-def tolerance(config, dtype, scale):
+def plain_logits_rounded(model_dir, requests):
+    """The plain implementation with bfloat16-rounded activations: the scale of the bound
+    for a bfloat16 engine (see `tolerance`)."""
+    import plain_qwen3 as plain
+    cfg, w = plain.load_model_dir(model_dir)
+    return {rid: plain.forward_rounded(cfg, w, toks) for rid, toks in requests.items()}
+
+
+def tolerance(config, dtype, reference, rounded=None):
     """Allowed absolute difference between engine logits and the float64 yardstick.
+    `reference`: the yardstick's logits (an array or several).
 
     float32: the reference's derived bound for a float32 graph against its float64 oracle,
-    8 * (2L+1) * sqrt(d) * 2^-24 * 10 (model/graph_rig_test.go:538-549), times the logits'
-    magnitude. bfloat16: activations are rounded to 8 significant bits about six times a
-    layer (norm output, q/k/v, attention output, projection output, gate, feed-forward
-    output) and the errors add like a random walk: 4 * sqrt(6L + 2) * 2^-9.
-    """
+    8 * (2L+1) * sqrt(d) * 2^-24 * 10 (model/graph_rig_test.go:538-549), times the largest
+    logit (at least 1).
+
+    bfloat16: `rounded` holds the logits of the plain implementation run with every
+    activation rounded to bfloat16 where a bfloat16 engine stores one
+    (plain_qwen3.forward_rounded), for the same inputs as `reference`. Its largest
+    difference from `reference` is what rounding alone does to this model on these inputs;
+    an engine may differ from the yardstick by twice that (its sums run in another order, it
+    rounds a few more intermediate values, and the largest of some 10^5 errors varies from
+    one draw to the next). The bound therefore follows the model: it is small where the
+    model damps rounding errors and larger where large weights amplify them, and it has no
+    floor."""
     L, d = config["num_hidden_layers"], config["hidden_size"]
+    arrays = reference if isinstance(reference, (list, tuple)) else [reference]
     if dtype == "float32":
-        return 8 * (2 * L + 1) * math.sqrt(d) * 2.0 ** -24 * 10 * max(scale, 1.0)
-    return 4 * math.sqrt(6 * L + 2) * 2.0 ** -9 * max(scale, 1.0)
+        top = max(float(np.abs(np.asarray(a)).max()) for a in arrays)
+        return 8 * (2 * L + 1) * math.sqrt(d) * 2.0 ** -24 * 10 * max(top, 1.0)
+    if rounded is None:
+        raise ValueError("tolerance: the bfloat16 bound needs the rounded plain logits")
+    others = rounded if isinstance(rounded, (list, tuple)) else [rounded]
+    return 2.0 * max(float(np.abs(np.asarray(r, dtype=np.float64) - a).max())
+                     for r, a in zip(others, arrays))
 
 
-def compare(got, want, config, dtype):
-    """got: {(id, pos): row}; want: {id: [T, V]}. Returns the worst (error, key)."""
+def note(what, worst, allowed):
+    """With TGO_TOLERANCE_LOG=<file>: append how much of its bound a comparison used."""
+    path = os.environ.get("TGO_TOLERANCE_LOG")
+    if path:
+        with open(path, "a") as f:
+            f.write(f"{what}\t{worst:.4e}\t{allowed:.4e}\t{worst / allowed if allowed else 0:.3f}\n")
+
+
+def compare(got, want, config, dtype, what="", rounded=None):
+    """got: {(id, pos): row}; want: {id: [T, V]}; rounded: {id: [T, V]} of the rounded plain
+    implementation (bfloat16 only). Returns the worst (error, key) and the allowed error."""
     worst, where = 0.0, None
-    scale = max(float(np.abs(v).max()) for v in want.values())
+    ids = list(want)
+    allowed = tolerance(config, dtype, [want[i] for i in ids],
+                        None if dtype == "float32" else [rounded[i] for i in ids])
     for (rid, pos), row in sorted(got.items()):
         err = float(np.abs(row.astype(np.float64) - want[rid][pos]).max())
         if not np.isfinite(err):
-            return float("inf"), (rid, pos), tolerance(config, dtype, scale)
+            return float("inf"), (rid, pos), allowed
         if err > worst:
             worst, where = err, (rid, pos)
-    return worst, where, tolerance(config, dtype, scale)
+    note(what or f"compare/{dtype}/L{config['num_hidden_layers']}", worst, allowed)
+    return worst, where, allowed
 
 
-def repeated_layers_reference(pc, pw, tokens):
+def repeated_layers_reference(pc, pw, tokens, rnd=None):
     """Plain logits of TINY_A's weights run as calls [0, 1, 0, 1] where the last call reads
     the cache of call 1 instead of writing its own (keys and values of call 1, queries of
-    its own input)."""
+    its own input). rnd: round the activations a bfloat16 engine stores (see
+    plain_qwen3.forward_rounded)."""
     import plain_qwen3 as plain
+    rnd = rnd or (lambda x: x)
     eps, T = pc["rms_norm_eps"], len(tokens)
     pos = np.arange(T)
     h = plain.embedding(pw["model.embed_tokens.weight"], tokens)
     kv1 = None
     for call, layer in enumerate([0, 1, 0, 1]):
         p = f"model.layers.{layer}."
-        n = plain.rmsnorm(h, pw[p + "input_layernorm.weight"], eps)
+        n = rnd(plain.rmsnorm(h, pw[p + "input_layernorm.weight"], eps))
         H, hkv, dh = 4, 2, 16
-        q = plain.rmsnorm(plain.linear(n, pw[p + "self_attn.q_proj.weight"]).reshape(T, H, dh),
+        q = plain.rmsnorm(rnd(plain.linear(n, pw[p + "self_attn.q_proj.weight"])).reshape(T, H, dh),
                           pw[p + "self_attn.q_norm.weight"], eps)
-        q = plain.rope_half_split(q, pos, pc["rope_theta"])
+        q = rnd(plain.rope_half_split(q, pos, pc["rope_theta"]))
         if call == 3:
             k, v = kv1
         else:
-            k = plain.rmsnorm(plain.linear(n, pw[p + "self_attn.k_proj.weight"]).reshape(T, hkv, dh),
+            k = plain.rmsnorm(rnd(plain.linear(n, pw[p + "self_attn.k_proj.weight"])).reshape(T, hkv, dh),
                               pw[p + "self_attn.k_norm.weight"], eps)
-            k = plain.rope_half_split(k, pos, pc["rope_theta"])
-            v = plain.linear(n, pw[p + "self_attn.v_proj.weight"]).reshape(T, hkv, dh)
+            k = rnd(plain.rope_half_split(k, pos, pc["rope_theta"]))
+            v = rnd(plain.linear(n, pw[p + "self_attn.v_proj.weight"])).reshape(T, hkv, dh)
             if call == 1:
                 kv1 = (k, v)
-        a = plain.causal_gqa_attention(q, k, v, 0.25).reshape(T, H * dh)
-        h = h + plain.linear(a, pw[p + "self_attn.o_proj.weight"])
-        n = plain.rmsnorm(h, pw[p + "post_attention_layernorm.weight"], eps)
-        h = h + plain.swiglu_mlp(n, pw[p + "mlp.gate_proj.weight"], pw[p + "mlp.up_proj.weight"],
-                                 pw[p + "mlp.down_proj.weight"])
-    return plain.linear(plain.rmsnorm(h, pw["model.norm.weight"], eps),
+        a = rnd(plain.causal_gqa_attention(q, k, v, 0.25, round_weights=rnd)).reshape(T, H * dh)
+        h = h + rnd(plain.linear(a, pw[p + "self_attn.o_proj.weight"]))
+        n = rnd(plain.rmsnorm(h, pw[p + "post_attention_layernorm.weight"], eps))
+        gate = rnd(plain.linear(n, pw[p + "mlp.gate_proj.weight"]))
+        up = rnd(plain.linear(n, pw[p + "mlp.up_proj.weight"]))
+        h = h + rnd(plain.linear(rnd(plain.silu(gate) * up), pw[p + "mlp.down_proj.weight"]))
+    return plain.linear(rnd(plain.rmsnorm(h, pw["model.norm.weight"], eps)),
                         pw["model.embed_tokens.weight"])

@@ -63,6 +63,25 @@ class LoadedModel:
         return self.model.spec
 
     @property
+    def stop_ids(self):
+        """Token ids that end a completion without being part of it, as the model folder
+        states them: `eos_token_id` (a number or a list) of generation_config.json, else of
+        config.json. The reference takes them from its tokenizer's end-of-turn and
+        end-of-text markers (decode.go:151-155); this engine has no tokenizer."""
+        raw = None
+        path = os.path.join(self.source, "generation_config.json") if self.source else ""
+        if path and os.path.isfile(path):
+            with builtins.open(path) as f:
+                raw = json.load(f).get("eos_token_id")
+        if raw is None:
+            raw = self.config.get("eos_token_id")
+        if raw is None:
+            return []
+        ids = raw if isinstance(raw, list) else [raw]
+        V = self.spec.vocab_size
+        return [int(i) for i in ids if isinstance(i, int) and not isinstance(i, bool) and 0 <= i < V]
+
+    @property
     def info(self) -> dict:
         s = self.model.spec
         return {"architecture": s.architecture, "layers": len(s.layers),

@@ -9,6 +9,10 @@ reference has them.
 
 Text is outside this engine (no tokenizer, no chat template), so --prompt holds token
 ids ("5,17,3" or "5 17 3") and --raw is accepted for compatibility and changes nothing.
+Beyond the reference's flags, `run` and `bench` take `--config cfg.json --random SEED` in
+place of a model folder (random weights made on the device), `run` takes --prompt several
+times (the prompts then run together through the scheduler), --prompt-len, --stop-ids,
+--page-size and --kv-pages, and `bench` takes a list of batch sizes.
 """
 from __future__ import annotations
 
@@ -42,13 +46,28 @@ def _common(ap):
     ap.add_argument("--temp", type=float, default=0.0,
                     help="sampling temperature; 0 is greedy (default 0)")
     ap.add_argument("--seed", type=int, default=0, help="the sampler seed (default 0)")
-    ap.add_argument("model_dir", metavar="<model-dir>")
+    ap.add_argument("--config", default="",
+                    help="with --random: a config.json to build a random-weights model from, "
+                         "in place of <model-dir>")
+    ap.add_argument("--random", type=int, default=None, metavar="SEED",
+                    help="seed of the random weights of the --config model")
+    ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (default 16)")
+    ap.add_argument("model_dir", metavar="<model-dir>", nargs="?", default="")
 
 
 def run_parser():
     ap = _parser("run")
-    ap.add_argument("--prompt", default="1 2 3 4 5 6 7 8",
-                    help="the prompt, as token ids separated by commas or spaces")
+    ap.add_argument("--prompt", action="append", default=None,
+                    help="the prompt, as token ids separated by commas or spaces (default "
+                         "\"1 2 3 4 5 6 7 8\"); given several times, the prompts run together "
+                         "through the scheduler")
+    ap.add_argument("--prompt-len", type=int, default=0,
+                    help="in place of --prompt: a seeded random prompt of N token ids")
+    ap.add_argument("--stop-ids", default="auto",
+                    help="token ids that end a completion without being part of it; auto "
+                         "(default): eos_token_id of the model folder; none: no stop ids")
+    ap.add_argument("--kv-pages", type=int, default=0,
+                    help="pages in the cache pool (default: enough for --context per prompt)")
     ap.add_argument("--raw", action="store_true",
                     help="accepted for compatibility; prompts are always token ids")
     ap.add_argument("--max-tokens", type=int, default=128,
@@ -68,7 +87,10 @@ def bench_parser():
     ap.add_argument("--tokens", type=int, default=128, help="decode steps to measure (default 128)")
     ap.add_argument("--prompt-tokens", type=int, default=128,
                     help="synthetic prompt length in tokens (default 128)")
-    ap.add_argument("--batch", type=int, default=1, help="sequences in flight (default 1)")
+    ap.add_argument("--batch", default="1",
+                    help="sequences in flight; a list (1,8,64) measures each (default 1)")
+    ap.add_argument("--prefill-tokens", type=int, default=0,
+                    help="length of the measured prefill (default: --prompt-tokens)")
     ap.add_argument("--warmup", type=int, default=8,
                     help="steps to run and discard before measuring (default 8)")
     ap.add_argument("--json", default="", help="write the machine-readable record here")
@@ -107,28 +129,74 @@ def _ids(text):
                          "this engine has no tokenizer") from None
 
 
+def _open(args, dtype, device, opener):
+    """The model of a command: a folder, or (--config with --random) random weights."""
+    import tgo_b200
+    if args.random is not None or args.config:
+        if args.random is None or not args.config:
+            raise UsageError("--config and --random SEED go together: a config.json to take the "
+                             "sizes from and the seed of the weights")
+        if args.model_dir:
+            raise UsageError("give a <model-dir> or --config with --random, not both")
+        with open(args.config) as f:
+            config = json.load(f)
+        return tgo_b200.open_random(config, args.random, dtype=dtype, device=device)
+    if not args.model_dir:
+        raise UsageError("a <model-dir> is needed (or --config cfg.json --random SEED)")
+    return (opener or tgo_b200.open)(args.model_dir, dtype=dtype, device=device)
+
+
+def _stop_ids(text, model):
+    if text == "auto":
+        return list(getattr(model, "stop_ids", ()))
+    if text in ("none", ""):
+        return []
+    try:
+        return [int(p) for p in re.split(r"[,\s]+", text.strip()) if p]
+    except ValueError:
+        raise UsageError(f"--stop-ids {text}: token ids, auto or none") from None
+
+
 def cmd_run(argv, out=sys.stdout, err=sys.stderr, opener=None):
     args = run_parser().parse_args(argv)
     dtype, device = _precision(args.precision), _device(args.device)
     _positive("max-tokens", args.max_tokens)
     _positive("context", args.context)
+    _positive("page-size", args.page_size)
     if args.max_tokens > args.context:
         raise UsageError(f"--max-tokens {args.max_tokens} is more than the --context "
                          f"{args.context} the cache holds")
-    prompt = _ids(args.prompt)
+    if args.prompt_len < 0 or (args.prompt_len and args.prompt):
+        raise UsageError("--prompt-len N stands in place of --prompt and is positive")
+    if args.kv_pages < 0:
+        raise UsageError(f"--kv-pages {args.kv_pages}: it cannot be negative")
+    prompts = [_ids(p) for p in (args.prompt or ([] if args.prompt_len else ["1 2 3 4 5 6 7 8"]))]
     from .sampling.policy import Policy
     policy = Policy(temperature=args.temp, top_k=args.top_k, top_p=args.top_p,
                     repetition_penalty=args.repeat_penalty, seed=args.seed,
                     max_tokens=args.max_tokens)
-    import tgo_b200
-    model = (opener or tgo_b200.open)(args.model_dir, dtype=dtype, device=device)
+    model = _open(args, dtype, device, opener)
     try:
         policy.check(model.spec.vocab_size)
     except ValueError as e:
         raise UsageError(str(e)) from None
+    if args.prompt_len:
+        from .engine.measure import random_prompts
+        prompts = random_prompts(model.spec.vocab_size, 1, args.prompt_len, args.seed)
+    stop_ids = _stop_ids(args.stop_ids, model)
     print(f"tgo: {model.info['architecture']} {dtype} context={args.context} "
-          f"temp={args.temp} seed={args.seed} prompt={len(prompt)} tokens", file=err)
-    session = model.new_session(context=args.context)
+          f"temp={args.temp} seed={args.seed} prompt={' + '.join(str(len(p)) for p in prompts)} "
+          f"tokens stop_ids={stop_ids}", file=err)
+    if len(prompts) > 1:
+        return _run_together(args, model, prompts, policy, stop_ids, out, err)
+    prompt = prompts[0]
+    if args.kv_pages:
+        if args.kv_pages * args.page_size < len(prompt) + 1:
+            raise UsageError(f"--kv-pages {args.kv_pages} of {args.page_size} tokens do not hold "
+                             f"the prompt")
+        args.context = min(args.context, args.kv_pages * args.page_size)
+        policy.max_tokens = min(policy.max_tokens, args.context - len(prompt))
+    session = model.new_session(context=args.context, page_size=args.page_size, stop_ids=stop_ids)
     t0 = time.perf_counter()
     first = None
     n = 0
@@ -145,36 +213,74 @@ def cmd_run(argv, out=sys.stdout, err=sys.stderr, opener=None):
     return 0
 
 
+def _run_together(args, model, prompts, policy, stop_ids, out, err):
+    """Several prompts: continuous batching through the scheduler; one line of ids each."""
+    import copy
+    need = max(len(p) for p in prompts) + args.max_tokens
+    if need > args.context:
+        raise UsageError(f"a prompt of {need - args.max_tokens} tokens and --max-tokens "
+                         f"{args.max_tokens} exceed the --context {args.context}")
+    pool = args.kv_pages * args.page_size if args.kv_pages else None
+    policies = []
+    for i in range(len(prompts)):           # each request draws from a stream of its own
+        pol = copy.copy(policy)
+        pol.seed = policy.seed + i
+        policies.append(pol)
+    t0 = time.perf_counter()
+    outs = model.generate(prompts, policies, slots=min(len(prompts), 64), pool_tokens=pool,
+                          page_size=args.page_size, stop_ids=stop_ids)
+    dt = time.perf_counter() - t0
+    for o in outs:
+        print(" ".join(str(t) for t in o), file=out)
+    n = sum(len(o) for o in outs)
+    runner = getattr(model, "last_runner", None)
+    print(f"tgo: {len(prompts)} prompts, {sum(len(p) for p in prompts)} prompt tokens, {n} "
+          f"generated in {getattr(runner, 'steps', 0)} steps "
+          f"({getattr(runner, 'evictions', 0)} evictions), {n / dt:.2f} tokens/s overall", file=err)
+    return 0
+
+
 def cmd_bench(argv, out=sys.stdout, err=sys.stderr, opener=None):
     args = bench_parser().parse_args(argv)
     dtype, device = _precision(args.precision), _device(args.device)
-    for name in ("tokens", "prompt_tokens", "context", "batch"):
+    try:
+        batches = [int(b) for b in re.split(r"[,\s]+", str(args.batch).strip()) if b]
+    except ValueError:
+        raise UsageError(f"--batch {args.batch}: a number or a list like 1,8,64") from None
+    if not batches or min(batches) <= 0:
+        raise UsageError(f"--batch {args.batch}: it must be positive")
+    for name in ("tokens", "prompt_tokens", "context", "page_size"):
         _positive(name.replace("_", "-"), getattr(args, name))
     if args.warmup < 0:
         raise UsageError(f"--warmup {args.warmup}: it cannot be negative")
     if args.prompt_tokens + args.tokens > args.context:
         raise UsageError(f"--prompt-tokens {args.prompt_tokens} plus --tokens {args.tokens} is "
                          f"more than the --context {args.context} the cache holds")
-    import tgo_b200
     from .engine.measure import measure_decode, measure_prefill
-    model = (opener or tgo_b200.open)(args.model_dir, dtype=dtype, device=device)
-    pre = measure_prefill(model, args.prompt_tokens, warmup=min(args.warmup, 3), steps=3,
-                          seed=args.seed)
-    dec = measure_decode(model, args.batch, args.prompt_tokens, args.tokens, warmup=args.warmup,
-                         seed=args.seed)
+    model = _open(args, dtype, device, opener)
+    pre = measure_prefill(model, args.prefill_tokens or args.prompt_tokens,
+                          warmup=min(args.warmup, 3), steps=3, seed=args.seed,
+                          page_size=args.page_size)
+    decs = [measure_decode(model, b, args.prompt_tokens, args.tokens, warmup=args.warmup,
+                           seed=args.seed, page_size=args.page_size) for b in batches]
+    dec = decs[0]
     record = {"model": model.info, "conditions": {
-        "precision": dtype, "context": args.context, "batch": args.batch,
+        "precision": dtype, "context": args.context, "batch": batches[0],
         "prompt_tokens": args.prompt_tokens, "tokens": args.tokens, "warmup": args.warmup,
-        "temp": args.temp, "seed": args.seed, "prompt": "seeded uniform-random token ids"},
+        "temp": args.temp, "seed": args.seed, "prompt": "seeded uniform-random token ids",
+        "page_size": args.page_size},
         "prefill": pre, "decode": dec}
+    if len(decs) > 1:
+        record["decode_by_batch"] = {str(b): d for b, d in zip(batches, decs)}
     print(f"model      {model.info['architecture']}  {dtype}  weights "
           f"{model.info['weight_bytes'] / 1e9:.2f} GB", file=out)
     print(f"conditions batch={args.batch} prompt={args.prompt_tokens} tokens={args.tokens} "
           f"warmup={args.warmup} context={args.context}", file=out)
     print(f"prefill    {pre['tokens_per_s']:.1f} tokens/s  ({pre['tokens']} tokens in "
           f"{pre['ms']:.2f} ms)", file=out)
-    print(f"decode     {dec['tokens_per_s']:.1f} tokens/s  (p50 {dec['p50_ms']:.3f} ms, p90 "
-          f"{dec['p90_ms']:.3f} ms, p99 {dec['p99_ms']:.3f} ms per step)", file=out)
+    for b, d in zip(batches, decs):
+        print(f"decode     {d['tokens_per_s']:.1f} tokens/s  batch {b}  (p50 {d['p50_ms']:.3f} ms, "
+              f"p90 {d['p90_ms']:.3f} ms, p99 {d['p99_ms']:.3f} ms per step)", file=out)
     if args.json:
         with open(args.json, "w") as f:
             json.dump(record, f, indent=1)
@@ -185,11 +291,11 @@ def cmd_info(argv, out=sys.stdout, err=sys.stderr, opener=None):
     ap = _parser("info")
     ap.add_argument("--precision", default="auto")
     ap.add_argument("--device", default="auto")
-    ap.add_argument("model_dir", metavar="<model-dir>")
+    ap.add_argument("--config", default="")
+    ap.add_argument("--random", type=int, default=None, metavar="SEED")
+    ap.add_argument("model_dir", metavar="<model-dir>", nargs="?", default="")
     args = ap.parse_args(argv)
-    import tgo_b200
-    model = (opener or tgo_b200.open)(args.model_dir, dtype=_precision(args.precision),
-                                      device=_device(args.device))
+    model = _open(args, _precision(args.precision), _device(args.device), opener)
     for k, v in model.info.items():
         print(f"{k:24s}{v}", file=out)
     return 0

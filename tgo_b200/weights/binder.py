@@ -67,8 +67,21 @@ def check_weights(expected: Iterable[WeightSpec], have: Dict[str, Tuple[str, Tup
     for n in sorted(want):
         if n in have:
             dt, shape = have[n]
-            if tuple(shape) != tuple(want[n].shape):
-                wrong.append(f"{n} is {list(shape)}, declared {list(want[n].shape)}")
+            shape, declared = tuple(shape), tuple(want[n].shape)
+            if any(int(s) == 0 for s in shape) and shape != declared:
+                # weights/weights.go:605-610: a tensor without elements is a broken file
+                wrong.append(f"{n} is empty (shape {list(shape)})")
+            elif want[n].role != "other" and len(shape) not in (1, 2):
+                # weights/weights.go:756-762: a weight is a matrix or a gain vector
+                wrong.append(f"{n} has rank {len(shape)} (shape {list(shape)}); a weight is a "
+                             "matrix or a gain vector")
+            elif want[n].role == "table" and len(shape) == 2 and len(declared) == 2 and \
+                    shape[1] == declared[1] and shape[0] != declared[0]:
+                # model/weights.go:224-234: the field to change is in config.json, so name it
+                wrong.append(f"config: vocab_size is {declared[0]} and {n} has {shape[0]} rows; "
+                             "the config and the weights are from different models")
+            elif shape != declared:
+                wrong.append(f"{n} is {list(shape)}, declared {list(declared)}")
             elif dt not in ("BF16", "F16", "F32") and want[n].role != "other":
                 wrong.append(f"{n} is stored as {dt}; BF16, F16 or F32 is needed")
     if missing or extra or wrong:
@@ -85,7 +98,7 @@ def check_weights(expected: Iterable[WeightSpec], have: Dict[str, Tuple[str, Tup
 
 
 def _place(t: torch.Tensor, role: str, compute_dtype: torch.dtype, device, name: str,
-           log) -> torch.Tensor:
+           log, narrowed=None) -> torch.Tensor:
     if not t.dtype.is_floating_point:
         return t.to(device=device, dtype=torch.int32)
     if role == "gain":
@@ -93,7 +106,17 @@ def _place(t: torch.Tensor, role: str, compute_dtype: torch.dtype, device, name:
     if role in ("matrix", "table"):
         if t.dtype == torch.float32 and compute_dtype != torch.float32 and log:
             log(f"weights: {name} is stored in 32-bit and is narrowed to {compute_dtype}")
-        return t.to(device=device, dtype=compute_dtype)
+        out = t.to(device=device, dtype=compute_dtype)
+        if t.dtype == torch.float16 and compute_dtype == torch.bfloat16:
+            # float16 has three mantissa bits more than bfloat16: the values are rounded.
+            # What must not happen silently is a value that does not survive at all
+            # (weights/weights.go:450-458 refuses a checkpoint its 16-bit type cannot hold)
+            if not torch.isfinite(out).all():
+                raise WeightError(f"weights: {name} holds values that are not finite in "
+                                  f"{compute_dtype}")
+            if narrowed is not None:
+                narrowed.append(name)
+        return out
     if t.dtype == torch.float32:
         return t.to(device=device)
     return t.to(device=device, dtype=compute_dtype)
@@ -115,7 +138,11 @@ def load_weights(expected: Iterable[WeightSpec], repo: SafetensorsRepo,
                 a.view(torch.uint8), b.view(torch.uint8)):
             raise WeightError(f"weights: the config ties the head to {target} and the checkpoint "
                               f"ships a different {alias}")
-    out = {}
+    out, narrowed = {}, []
     for w in expected:
-        out[w.name] = _place(repo.tensor(w.name), w.role, compute_dtype, device, w.name, log)
+        out[w.name] = _place(repo.tensor(w.name), w.role, compute_dtype, device, w.name, log,
+                             narrowed)
+    if narrowed and log:
+        log(f"weights: {len(narrowed)} tensors are stored as float16 and were rounded to "
+            f"bfloat16 (8 significant bits instead of 11): {_listing(narrowed, 3)}")
     return out
