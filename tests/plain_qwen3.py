@@ -51,6 +51,28 @@ def read_safetensors(path):
     return out
 
 
+def write_safetensors(path, arrays, bfloat16=True):
+    """Write {name: float array} in the layout `read_safetensors` describes, as BF16 (values
+    rounded to the nearest, ties to even) or F32. Written here from the format's description,
+    sharing nothing with the product's writer."""
+    header, planes, at = {}, [], 0
+    for name in sorted(arrays):
+        a = np.ascontiguousarray(arrays[name], dtype=np.float32)
+        if bfloat16:
+            bits = a.view(np.uint32).astype(np.uint64)
+            plane = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype("<u2").tobytes()
+        else:
+            plane = a.astype("<f4").tobytes()
+        header[name] = {"dtype": "BF16" if bfloat16 else "F32", "shape": list(a.shape),
+                        "data_offsets": [at, at + len(plane)]}
+        planes.append(plane)
+        at += len(plane)
+    blob = json.dumps(header, separators=(",", ":")).encode("utf-8")
+    blob += b" " * (-len(blob) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(blob)) + blob + b"".join(planes))
+
+
 def load_model_dir(model_dir):
     with open(os.path.join(model_dir, "config.json")) as f:
         cfg = json.load(f)

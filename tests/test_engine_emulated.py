@@ -278,3 +278,47 @@ def test_parts_count_their_own_flops_and_bytes(tmp_path):
         per_token = sum(2 * Hkv * dh * 4 * (min(100, w) if w else 100) for w in windows)
         assert model.cache_bytes_read(100) == per_token
         assert model.cache_bytes_per_token() == L * 2 * Hkv * dh * 4
+
+
+def test_a_model_folder_written_by_plain_code(emulated, tmp_path):
+    """The tiny configurations' folders are written by the product's own writer. This one is
+    written by the plain code of the tests (names spelled out here, the container written
+    from its description), so a fault that the product's writer and reader share cannot
+    hide: the engine reads it and gives the plain implementation's logits."""
+    import json
+    import os
+    cfg = dict(tiny.TINY_B)
+    rng = np.random.default_rng(44)
+    d, H, Hkv, dh, f, V = 96, 6, 2, 32, 224, 384
+    arrays = {"model.embed_tokens.weight": rng.normal(0, 0.05, (V, d)),
+              "lm_head.weight": rng.normal(0, 0.05, (V, d)),
+              "model.norm.weight": 1 + rng.normal(0, 0.1, d)}
+    for i in range(3):
+        p = f"model.layers.{i}."
+        arrays.update({
+            p + "input_layernorm.weight": 1 + rng.normal(0, 0.1, d),
+            p + "post_attention_layernorm.weight": 1 + rng.normal(0, 0.1, d),
+            p + "self_attn.q_proj.weight": rng.normal(0, 0.05, (H * dh, d)),
+            p + "self_attn.k_proj.weight": rng.normal(0, 0.05, (Hkv * dh, d)),
+            p + "self_attn.v_proj.weight": rng.normal(0, 0.05, (Hkv * dh, d)),
+            p + "self_attn.o_proj.weight": rng.normal(0, 0.05, (d, H * dh)),
+            p + "self_attn.q_norm.weight": 1 + rng.normal(0, 0.1, dh),
+            p + "self_attn.k_norm.weight": 1 + rng.normal(0, 0.1, dh),
+            p + "mlp.gate_proj.weight": rng.normal(0, 0.05, (f, d)),
+            p + "mlp.up_proj.weight": rng.normal(0, 0.05, (f, d)),
+            p + "mlp.down_proj.weight": rng.normal(0, 0.05, (d, f))})
+    folder = tmp_path / "by_hand"
+    os.makedirs(folder)
+    with open(folder / "config.json", "w") as fh:
+        json.dump(cfg, fh)
+    plain.write_safetensors(str(folder / "model.safetensors"), arrays, bfloat16=True)
+    pc, pw = plain.load_model_dir(str(folder))
+    assert np.abs(pw["model.layers.1.mlp.up_proj.weight"] -
+                  arrays["model.layers.1.mlp.up_proj.weight"]).max() < 0.05 * 2 ** -7 * 6
+    loaded = cpu_model(str(folder), cfg)
+    toks = tiny.random_requests(V, [50], seed=1)["r0"]
+    want = plain.forward(pc, pw, toks)
+    eng = loaded.new_engine(page_size=8, max_tokens=64, num_slots=1)
+    got = tiny.run_trace_engine(eng, tiny.trace_portions({"r0": toks}))
+    worst, where, tol = tiny.compare(got, {"r0": want}, cfg, "float32")
+    assert worst <= tol, (worst, where)

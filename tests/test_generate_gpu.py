@@ -154,3 +154,16 @@ def test_command_line(lively, tmp_path):
     assert "decode" in r.stdout and "prefill" in r.stdout
     r = subprocess.run([sys.executable, tgo, "info", d], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "Qwen3ForCausalLM" in r.stdout
+
+
+def test_one_seed_gives_one_model_on_the_cpu_and_on_the_gpu():
+    """The random-weights mode makes a model folder on the CPU and, for large models, makes
+    the tensors on the device: one seed gives the same bits either way."""
+    import torch
+    from tgo_b200.weights.binder import WeightSpec
+    from tgo_b200.weights.random_init import random_tensor
+    for spec in (WeightSpec("w", (300, 129)), WeightSpec("g", (1000,), "gain")):
+        for dtype in (torch.float32, torch.bfloat16):
+            a = random_tensor(spec, 11, 0.02, 0.1, dtype, "cpu")
+            b = random_tensor(spec, 11, 0.02, 0.1, dtype, "cuda:0")
+            assert torch.equal(a, b.cpu())

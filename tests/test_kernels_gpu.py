@@ -295,7 +295,7 @@ def test_attention_decode_split(H, Hkv, dh, ps, window):
     case = paged_case(extents, firsts, H, Hkv, dh, ps, torch.bfloat16, seed=3)
     scale = 1 / math.sqrt(dh)
     want = attention_ref(case, H, Hkv, dh, scale, window)
-    for n_splits in (1, 2, 5, 16):
+    for n_splits in (1, 2, 5, 8, 16):
         out = torch.zeros_like(case["q"])
         if not ops().flash_supports(dh, H // Hkv):
             pytest.skip("no tensor-core instance for this head size")

@@ -93,3 +93,34 @@ def test_prompt_portions_through_graphs_give_the_same_bits(models, name, dtype):
             assert eng._portion_graphs, "no portion was captured"
     for a, b in zip(got[False], got[True]):
         assert torch.equal(a, b)
+
+
+def test_more_portion_shapes_than_graphs_are_kept(models):
+    """Five portion shapes in turn, again and again, with room for four captured graphs: the
+    least recently used graph goes and its shape starts over, and whatever is replayed,
+    captured or run directly, the logits are those of an engine that never captures."""
+    import torch
+    import tgo_b200
+    from tgo_b200.engine.step import StepEntry
+    d, cfg, run, _, _, _ = models["B"]
+    model = tgo_b200.open(d, dtype="bfloat16")
+    rng = np.random.default_rng(9)
+    sizes = [33, 34, 35, 36, 37]
+    rounds = 4
+    toks = rng.integers(0, cfg["vocab_size"], sum(sizes) * rounds).tolist()
+    got = {}
+    for graphs in (False, True):
+        eng = model.new_engine(page_size=run["page_size"], max_tokens=1024, num_slots=1, graphs=graphs)
+        eng.PORTION_GRAPH_MIN_TOKENS = 32
+        eng.admit("a")
+        outs, at = [], 0
+        for _ in range(rounds):
+            for n in sizes:
+                outs.append(eng.step([StepEntry("a", toks[at:at + n], [n - 1])]).clone())
+                at += n
+        torch.cuda.synchronize()
+        got[graphs] = outs
+        if graphs:
+            assert 1 <= len(eng._portion_graphs) <= eng.PORTION_GRAPHS_KEPT
+    for a, b in zip(got[False], got[True]):
+        assert torch.equal(a, b)

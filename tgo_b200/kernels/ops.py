@@ -373,16 +373,17 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
     assert q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 2 == 0
     assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
     n_tiles = T if tile_tok0 is None else tile_tok0.numel()
+    tma = tile_tok0 is None and USE_TMA_DECODE and k_cache.dim() == 4 and k_cache.is_contiguous() and \
+        v_cache.is_contiguous() and attention_decode_tma_supports(
+            head_dim, num_heads // num_kv_heads, page_size)
     part_o = part_ml = None
     if n_splits > 1:
         part_o = torch.empty((T, num_heads, n_splits, head_dim), dtype=torch.float32,
                              device=q.device)
         part_ml = torch.empty((T, num_heads, n_splits, 2), dtype=torch.float32, device=q.device)
     lib = load_library("attention_flash")
-    if tile_tok0 is None and USE_TMA_DECODE and k_cache.dim() == 4 and k_cache.is_contiguous() and \
-            v_cache.is_contiguous() and attention_decode_tma_supports(
-                head_dim, num_heads // num_kv_heads, page_size):
-        # decode with the pages brought in by TMA; the join of the splits is the same kernel
+    if tma:
+        # decode with the pages brought in by TMA
         _check(load_library("attention_decode_tma").tgo_attention_decode_tma(
             _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
             c_int(k_cache.shape[0]), c_int(page_size), _ptr(block_tables),
