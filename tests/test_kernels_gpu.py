@@ -534,20 +534,18 @@ def tc_flag():
     return int(ops().gemm_tc_error_flag(DEV).item())
 
 
-@pytest.mark.parametrize("M,N,K,transpose,splits", [
-    (128, 128, 64, False, 1), (200, 300, 264, False, 1), (700, 520, 1000, False, 1),
-    (1024, 2048, 4096, False, 1), (300, 512, 2048, False, 3), (8, 128, 64, True, 1),
-    (2048, 4096, 192, False, 1), (2048, 6144, 128, False, 1), (130, 1001, 72, False, 1),
-    (33, 200, 264, True, 1), (64, 512, 4096, True, 4), (200, 256, 512, True, 1)])
-def test_gemm_tc(M, N, K, transpose, splits):
-    """The tcgen05 kernel in both orientations, with tails in every dimension and K splits."""
+@pytest.mark.parametrize("M,N,K", [
+    (128, 128, 64), (200, 300, 264), (700, 520, 1000), (1024, 2048, 4096), (300, 512, 2048),
+    (2048, 4096, 192), (2048, 6144, 128), (130, 1001, 72), (33, 200, 264), (8, 128, 64)])
+def test_gemm_tc(M, N, K):
+    """The tcgen05 kernel with tails in every dimension."""
     x = rnd(M, K, dtype=torch.bfloat16, seed=M + K)
     w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=N + K)
     want = x.float() @ w.float().t()
     atol = 3 * 2.0 ** -8.5 * math.sqrt(K) * 0.1 + 1e-3         # float32 accumulation of exact bf16 products
     for dt in (torch.float32, torch.bfloat16):
         out = torch.zeros(M, N, dtype=dt, device=DEV)
-        ops().gemm_tc(x, w, out, transpose=transpose, splits=splits)
+        ops().gemm_tc(x, w, out)
         torch.cuda.synchronize()
         assert tc_flag() == 0
         if dt == torch.float32:
@@ -556,13 +554,12 @@ def test_gemm_tc(M, N, K, transpose, splits):
             assert torch.allclose(out.float(), want, rtol=1e-2, atol=atol + 2e-2)
     h = rnd(M, N, seed=3)
     h2 = h.clone()
-    ops().gemm_tc(x, w, h2, accumulate=True, transpose=transpose, splits=splits)
+    ops().gemm_tc(x, w, h2, accumulate=True)
     assert torch.allclose(h2, h + want, rtol=1e-4, atol=1e-3) and tc_flag() == 0
 
 
-@pytest.mark.parametrize("M,f,K,transpose", [(300, 512, 264, False), (1000, 1000, 512, False),
-                                             (24, 256, 512, True), (64, 1008, 264, True)])
-def test_gemm_tc_gated_output(M, f, K, transpose):
+@pytest.mark.parametrize("M,f,K", [(300, 512, 264), (1000, 1000, 512), (24, 256, 512), (64, 1008, 264)])
+def test_gemm_tc_gated_output(M, f, K):
     x = rnd(M, K, dtype=torch.bfloat16, seed=4)
     wg = rnd(f, K, dtype=torch.bfloat16, scale=0.2, seed=5)
     wu = rnd(f, K, dtype=torch.bfloat16, scale=0.2, seed=6)
@@ -570,7 +567,7 @@ def test_gemm_tc_gated_output(M, f, K, transpose):
     u = (x.float() @ wu.float().t()).to(torch.bfloat16).float()
     want = g / (1 + torch.exp(-g)) * u
     out = torch.zeros(M, f, dtype=torch.bfloat16, device=DEV)
-    ops().gemm_tc(x, interleave8(wg, wu).contiguous(), out, transpose=transpose, gated=True)
+    ops().gemm_tc(x, interleave8(wg, wu).contiguous(), out, gated=True)
     torch.cuda.synchronize()
     assert tc_flag() == 0
     assert torch.allclose(out.float(), want, rtol=2e-2, atol=2e-2 * float(want.abs().max()))
@@ -591,12 +588,12 @@ def test_gemm_tc_tile_shapes(rows, width, M):
     ops().gemm_tc_force_tile(rows, width)
     try:
         out = torch.zeros(M, N, dtype=torch.float32, device=DEV)
-        ops().gemm_tc(x, w, out, transpose=False)
+        ops().gemm_tc(x, w, out)
         h = rnd(M, N, seed=3)
         h2 = h.clone()
-        ops().gemm_tc(x, w, h2, accumulate=True, transpose=False)
+        ops().gemm_tc(x, w, h2, accumulate=True)
         gated = torch.zeros(M, N // 2, dtype=torch.bfloat16, device=DEV)
-        ops().gemm_tc(x, interleave8(w[:N // 2], w[N // 2:]).contiguous(), gated, transpose=False, gated=True)
+        ops().gemm_tc(x, interleave8(w[:N // 2], w[N // 2:]).contiguous(), gated, gated=True)
         torch.cuda.synchronize()
     finally:
         ops().gemm_tc_force_tile(0, 0)
@@ -633,13 +630,13 @@ def test_gemm_tc_cut_last_round(M, N, K, rows, width, parts):
         ops().gemm_tc_force_tile(rows, width, cut_last_round=cut)
         try:
             out = torch.zeros(M, N, dtype=torch.float32, device=DEV)
-            ops().gemm_tc(x, w, out, transpose=False)
+            ops().gemm_tc(x, w, out)
             h2 = h.clone()
-            ops().gemm_tc(x, w, h2, accumulate=True, transpose=False)
+            ops().gemm_tc(x, w, h2, accumulate=True)
             ob = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
-            ops().gemm_tc(x, w, ob, transpose=False)
+            ops().gemm_tc(x, w, ob)
             gated = torch.zeros(M, N // 2, dtype=torch.bfloat16, device=DEV)
-            ops().gemm_tc(x, wgu, gated, transpose=False, gated=True)
+            ops().gemm_tc(x, wgu, gated, gated=True)
             torch.cuda.synchronize()
         finally:
             ops().gemm_tc_force_tile(0, 0)
@@ -694,14 +691,12 @@ TC_CASES = [
 ]
 
 
-@pytest.mark.parametrize("persistent", [True, False])
 @pytest.mark.parametrize("extents,firsts,H,Hkv,ps,window", TC_CASES)
-def test_attention_tc_prefill(extents, firsts, H, Hkv, ps, window, persistent, monkeypatch):
-    """The tcgen05 attention kernels alone (head size 128; one CTA per SM drawing items, and
-    one CTA per item) over a scattered paged cache whose unwritten rows hold NaN, against
-    the plain float32 attention."""
+def test_attention_tc_prefill(extents, firsts, H, Hkv, ps, window):
+    """The tcgen05 attention kernel alone (head size 128; one CTA per SM drawing items) over a
+    scattered paged cache whose unwritten rows hold NaN, against the plain float32
+    attention."""
     o, dh = ops(), 128
-    monkeypatch.setattr(o, "TC_ATTENTION_PERSISTENT", persistent)
     assert o.attention_tc_supports(dh, H // Hkv, ps)
     case = paged_case(extents, firsts, H, Hkv, dh, ps, torch.bfloat16, seed=len(extents) + ps)
     scale = 1 / math.sqrt(dh)

@@ -1,39 +1,35 @@
 // Paged causal attention for prompt portions on the tcgen05 tensor cores (head size 128,
 // bfloat16): S = Q K^T and O += P V are tcgen05.mma with the accumulators in tensor memory,
-// K and V pages come in by TMA, and the softmax runs in registers between the two.
+// Q, K and V come in by TMA, and the softmax runs in registers between the two products.
 //
-// A CTA owns one tile of 128 query rows: the G query heads that share a kv head, for 128 / G
-// consecutive tokens of one request (row r = token r / G, head r % G), so K and V are read
-// once for the whole group. It walks the request's keys in tiles of 128.
+// A work item is one tile of 128 query rows and one kv head: the G query heads that share the
+// kv head, for 128 / G consecutive tokens of one request (row r = token r / G, head r % G), so
+// K and V are read once for the whole group. An item walks the request's keys in tiles of 128.
+// One persistent CTA per SM draws items from a counter (see the kernel below for its warps).
 //
-//   warp 0      producer: asks TMA for the pages of the next K and V tiles, one page per lane
-//               (a page is two boxes of page_size rows x 64 columns, 128-byte swizzle; the
-//               pages of a tile lie one after the other in shared memory, which is the
-//               K-major layout for K and the MN-major layout for V that the tensor core wants);
-//   warp 1      issuer: one lane issues S_j = Q K_j^T (8 k-steps) into tensor memory and, once
-//               the softmax has written P_j, O += P_j V_j with P read from tensor memory (two
-//               products of 64 output columns, 8 k-steps each);
-//   warps 2-9   softmax: two threads per row, one for keys 0..63 of the tile and one for keys
-//               64..127 (warps 2-5 and 6-9). Each reads its half row of S (64 float32), masks,
-//               takes the maximum, swaps it with its partner through shared memory, writes
-//               P = exp2(S * scale - m) as bfloat16 over the first half of the S buffer, and
-//               keeps its part of the row sum. The running maximum is only moved when
-//               some row of the warp has grown by more than 2^8 since it was set; then the
-//               rows of O in tensor memory are rescaled. (The result is the same: the factor
-//               cancels in O / l; only the range of P changes, and 2^8 is far from overflow.)
+// The softmax: two threads per row, one for keys 0..63 of the tile and one for keys 64..127.
+// Each reads its half row of S (64 float32), masks, takes the maximum, swaps it with its
+// partner through shared memory, writes P = exp2(S * scale - m) as bfloat16 over the first
+// half of the S buffer, and keeps its part of the row sum. The running maximum is only moved
+// when some row of the warp has grown by more than 2^8 since it was set; then the rows of O
+// in tensor memory are rescaled. (The result is the same: the factor cancels in O / l; only
+// the range of P changes, and 2^8 is far from overflow.)
 //
-// Tensor memory: 256 columns a CTA, S 0..127 and O 128..255; P_j lies over S_j. Shared memory:
-// one tile each of Q, K and V (96 KB). Two CTAs share an SM: inside a CTA the product, the
-// softmax and the second product of a key tile follow one another, and the other CTA's work
-// (and its start and its end) fills the gaps. MEASURED on B200, 2048-token prompt of 32/8
-// heads: 262 us for the mma.sync kernel; 136 us for one CTA per SM with two S buffers and one
-// softmax thread per row; 100 us with two threads per row; 91 us in this form; 78 us for
-// the persistent form further down. Per key tile
-// the softmax needs about 2000 cycles of an SM (the special-function unit alone 1024: 128 x 128
-// exponentials at 16 a cycle) against 1024 for the two products.
 // Rows of V that no query may read (past the request's end in its last page, before the
 // window) are zeroed in shared memory before P V: P is zero there, but the cache may hold
 // anything, NaN included. Keys of K in such rows give S values that the mask replaces.
+//
+// MEASURED on B200, 2048-token prompt of 32/8 heads (CUDA events, warm): 262 us for the
+// mma.sync kernel this replaced; 136 us for one CTA per item with two S buffers and one softmax
+// thread per row; 100 us with two threads per row; 91 us with two such CTAs per SM; 78 us
+// persistent with everything double-buffered; 74.5 us with items drawn only when there is
+// room for them; 65 us with Q by TMA (529 TFLOP/s; an 8192-token prompt 608 us, 904 TFLOP/s).
+// Timed inside the kernel with the global timer on that prompt: a key tile takes 1.45 us
+// (the special-function unit alone needs 1024 cycles, 0.53 us, for a tile's 128 x 128
+// exponentials, as long as its two products take), an item 2.5 us more (0.4 us to its first
+// S, 0.5 us for its last product, 1.6 us to scale and store O). Tried and not kept: a cubic
+// on the FMA pipe for every second or fourth exponential (issue-bound: 81.5 and 76.9 us
+// against 77.6); two softmax groups of four warps with an S and an O each (107 us).
 //
 // Every wait has a time limit (about two seconds): it records a code, the CTA stops issuing,
 // frees its tensor memory and returns. No cluster, no multicast.
@@ -47,8 +43,6 @@
 #define AT_BM 128
 #define AT_BN 128
 #define AT_DH 128
-#define AT_THREADS 320
-#define AT_SOFTMAX_THREADS 256
 #define AT_WAIT_CYCLES 4000000000ll
 #define AT_BLOCK_BYTES (128 * 64 * 2)          // 128 rows x 64 columns of bf16
 #define AT_TILE_BYTES (2 * AT_BLOCK_BYTES)     // a Q, K or V tile: two column halves
@@ -90,6 +84,11 @@ __device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity, int code
         }
     }
     return true;
+}
+// A box of the query rows: coordinates (column in the half, half, head, token)
+__device__ __forceinline__ void at_tma_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(at_smem(dst)), "l"(map), "r"(at_smem(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 __device__ __forceinline__ void at_tma_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -181,307 +180,6 @@ __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
     return *(uint32_t*)&v;
 }
 
-// error codes: 1 producer, 2 issuer, 3 softmax
-__global__ void __launch_bounds__(AT_THREADS, 2)
-attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                            const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
-                            long long out_stride, int page_size, int page_shift,
-                            const int* __restrict__ block_tables, int max_blocks,
-                            const int* __restrict__ positions, const int* __restrict__ seq_ids,
-                            const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok, int H,
-                            int Hkv, float scale_log2, int window) {
-    extern __shared__ unsigned char at_raw[];
-    unsigned char* base = (unsigned char*)(((uintptr_t)at_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* sQ = base;                                   // [2 halves][128 rows][128 B]
-    unsigned char* sK = sQ + AT_TILE_BYTES;                     // [2 halves][128][128 B]
-    unsigned char* sV = sK + AT_TILE_BYTES;                     // [2 halves][128][128 B]
-    uint64_t* bars = (uint64_t*)(sV + AT_TILE_BYTES);
-    uint64_t* k_full = bars;            // one phase per key tile each
-    uint64_t* k_empty = bars + 1;
-    uint64_t* v_full = bars + 2;
-    uint64_t* v_empty = bars + 3;
-    uint64_t* s_full = bars + 4;
-    uint64_t* p_full = bars + 5;
-    uint64_t* o_done = bars + 6;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 13);
-    float* s_xm = (float*)(bars + 14);  // [2 tile parities][2 halves][128 rows] row maxima
-    float* s_xl = s_xm + 512;           // [2 halves][128 rows] row sums at the end
-    int* s_pages = (int*)(s_xl + 256);  // [AT_PAGES_CAP]
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // later tiles of a request read more keys: they start first
-    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
-    const int G = H / Hkv;
-    const int tok0 = tile_tok0[tile], ntok = tile_ntok[tile];
-    const int n_rows = ntok * G;
-    const int p0 = positions[tok0];
-    if (p0 < 0) {                              // a request that brings nothing: zeros out
-        for (int i = tid; i < n_rows * AT_DH; i += AT_THREADS) {
-            const int r = i / AT_DH, d = i % AT_DH;
-            out[(size_t)(tok0 + r / G) * out_stride + (size_t)(kvh * G + r % G) * AT_DH + d] = __float2bfloat16_rn(0.f);
-        }
-        return;
-    }
-    const int* bt = block_tables + (size_t)seq_ids[tok0] * max_blocks;
-    const int p_last = p0 + ntok - 1;
-    const int key_lo = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
-    const int key_hi = p_last + 1;
-    const int t_lo = key_lo / AT_BN, t_hi = (key_hi + AT_BN - 1) / AT_BN;
-    const int n_it = t_hi - t_lo;
-    const int pages_per_tile = AT_BN >> page_shift;
-    const int pg_lo = t_lo * pages_per_tile;
-
-    if (tid == 0) {
-        at_mbar_init(k_full, 1); at_mbar_init(k_empty, 1);
-        at_mbar_init(v_full, 1); at_mbar_init(v_empty, 1);
-        at_mbar_init(s_full, 1); at_mbar_init(p_full, 8);
-        at_mbar_init(o_done, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(at_smem(tmem_slot)), "r"(256u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    // this tile's slice of the block table
-    {
-        int pg_hi = t_hi * pages_per_tile;
-        if (pg_hi > max_blocks) pg_hi = max_blocks;
-        if (pg_hi - pg_lo > AT_PAGES_CAP) pg_hi = pg_lo + AT_PAGES_CAP;
-        for (int i = pg_lo + tid; i < pg_hi; i += AT_THREADS) s_pages[i - pg_lo] = bt[i];
-    }
-    // Q rows -> shared memory in the swizzled K-major layout; rows past the tile are zeros
-    for (int i = tid; i < AT_BM * 16; i += AT_THREADS) {
-        const int r = i >> 4, c = i & 15;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < n_rows)
-            v = *(const uint4*)(q + (size_t)(tok0 + r / G) * q_stride + (size_t)(kvh * G + r % G) * AT_DH + c * 8);
-        *(uint4*)(sQ + (c >> 3) * AT_BLOCK_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    at_fence_before();
-    __syncthreads();
-    at_fence_after();
-    const uint32_t tmem = *tmem_slot;
-    const uint32_t tm_s = tmem, tm_o = tmem + 128u;
-
-    if (warp == 0) {
-        auto page_of = [&](int pi) { return pi - pg_lo < AT_PAGES_CAP ? s_pages[pi - pg_lo] : bt[pi]; };
-        bool ok = true;
-        for (int it = 0; it < n_it; ++it) {
-            const uint32_t ph = (uint32_t)it & 1u;
-            const int j = t_lo + it;
-            // pages of this tile that hold a key some row may read
-            int first = j * pages_per_tile, last = first + pages_per_tile;      // [first, last)
-            while (first < last && (first + 1) * page_size <= key_lo) ++first;
-            while (last > first && (last - 1) * page_size >= key_hi) --last;
-            const uint32_t bytes = (uint32_t)(last - first) * (uint32_t)page_size * 256u;
-            ok = __all_sync(0xffffffffu, ok && at_wait(k_empty, ph ^ 1u, 1));
-            if (!ok) break;
-            if (lane == 0) at_expect_tx(k_full, bytes);
-            __syncwarp();
-            for (int pi = first + lane; pi < last; pi += 32) {
-                const int row = (page_of(pi) * Hkv + kvh) * page_size;
-                unsigned char* dst = sK + (pi - j * pages_per_tile) * page_size * 128;
-                at_tma_2d(dst, &map_k, 0, row, k_full);
-                at_tma_2d(dst + AT_BLOCK_BYTES, &map_k, 64, row, k_full);
-            }
-            ok = __all_sync(0xffffffffu, at_wait(v_empty, ph ^ 1u, 1));
-            if (!ok) break;
-            if (lane == 0) at_expect_tx(v_full, bytes);
-            __syncwarp();
-            for (int pi = first + lane; pi < last; pi += 32) {
-                const int row = (page_of(pi) * Hkv + kvh) * page_size;
-                unsigned char* dst = sV + (pi - j * pages_per_tile) * page_size * 128;
-                at_tma_2d(dst, &map_v, 0, row, v_full);
-                at_tma_2d(dst + AT_BLOCK_BYTES, &map_v, 64, row, v_full);
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            // float32 accumulate, bf16 x bf16, M = 128; S: N = 128, both K-major;
-            // O: N = 64 per product, B (V) MN-major
-            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) |
-                                      ((uint32_t)(128 >> 4) << 24);
-            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
-                                      ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            const uint64_t dq0 = at_desc(sQ), dq1 = at_desc(sQ + AT_BLOCK_BYTES);
-            const uint64_t dk0 = at_desc(sK), dk1 = at_desc(sK + AT_BLOCK_BYTES);
-            bool ok = true;
-            for (int it = 0; it < n_it && ok; ++it) {
-                const uint32_t ph = (uint32_t)it & 1u;
-                ok = at_wait(k_full, ph, 2);
-                if (!ok) break;
-                at_fence_after();
-                // S (and the P that lay over it) is free: the product that read P was issued
-                // before this one, and products run in the order they were issued
-#pragma unroll
-                for (int k = 0; k < 4; ++k) at_mma_ss(tm_s, dq0 + 2 * k, dk0 + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) at_mma_ss(tm_s, dq1 + 2 * k, dk1 + 2 * k, idesc_qk, 1u);
-                at_commit(k_empty);
-                at_commit(s_full);
-                ok = at_wait(p_full, ph, 2) && at_wait(v_full, ph, 2);
-                if (!ok) break;
-                at_fence_after();
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint64_t dv = at_desc(sV + h * AT_BLOCK_BYTES);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k)           // 16 keys = 2 groups of 8 rows = 2048 bytes
-                        at_mma_ts(tm_o + 64u * h, tm_s + 8u * k, dv + (uint64_t)(128 * k), idesc_pv,
-                                  (it > 0 || k > 0) ? 1u : 0u);
-                }
-                at_commit(v_empty);
-                at_commit(o_done);
-            }
-        }
-    } else {
-        const int quarter = warp & 3;              // the 32 lanes of tensor memory this warp may touch
-        const int half = (warp - 2) >> 2;          // keys 0..63 or 64..127 of every tile
-        const int row = quarter * 32 + lane;
-        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        const bool row_ok = row < n_rows;
-        const int pos = row_ok ? p0 + row / G : -1;
-        const int vis_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-        // the warp's rows: lowest position and highest window start, for the "no mask" test
-        const int warp_first = quarter * 32, warp_last = quarter * 32 + 31;
-        const bool warp_rows_ok = warp_last < n_rows;
-        const int warp_pos_min = p0 + warp_first / G;
-        const int warp_pos_max = p0 + (warp_last < n_rows ? warp_last : n_rows - 1) / G;
-        const int warp_vis_max = (window > 0 && warp_pos_max - window + 1 > 0) ? warp_pos_max - window + 1 : 0;
-        float m_used = -INFINITY, l = 0.f;
-        bool ok = true;
-        for (int it = 0; it < n_it; ++it) {
-            const uint32_t ph = (uint32_t)it & 1u;
-            const int kbase = (t_lo + it) * AT_BN + 64 * half;
-            if (ok) ok = at_wait(s_full, ph, 3);
-            at_fence_after();
-            float sc[64];
-            {
-                uint32_t r0[32], r1[32];
-                at_tmem_ld32(tm_s + lane_base + 64u * half, r0);
-                at_tmem_ld32(tm_s + lane_base + 64u * half + 32u, r1);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < 32; ++i) { sc[i] = __uint_as_float(r0[i]); sc[32 + i] = __uint_as_float(r1[i]); }
-            }
-            const bool full = warp_rows_ok && kbase + 63 <= warp_pos_min && kbase >= warp_vis_max;
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            if (full) {
-#pragma unroll
-                for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const int key = kbase + i;
-                    sc[i] = (key <= pos && key >= vis_lo) ? sc[i] : -INFINITY;
-                    mx4[i & 3] = fmaxf(mx4[i & 3], sc[i]);
-                }
-            }
-            // the scale is positive: the maximum of the scaled values is the scaled maximum
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
-            // the other half of the row: both threads of a row end up with the same maximum
-            float* xm = s_xm + (it & 1) * 256;
-            xm[half * 128 + row] = mx;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            mx = fmaxf(mx, xm[(half ^ 1) * 128 + row]);
-            const float m_new = fmaxf(m_used, mx);
-            const bool grow = m_new > m_used + 8.f || (m_used == -INFINITY && m_new != -INFINITY);
-            const bool rescale = __any_sync(0xffffffffu, grow);
-            float corr = 1.f;
-            if (rescale) {
-                corr = m_new == -INFINITY ? 1.f : exp2f(m_used - m_new);       // exp2(-inf) = 0 for a first value
-                m_used = m_new;
-            }
-            const float base_m = m_used == -INFINITY ? 0.f : m_used;
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            {
-                uint32_t r[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float a = at_ex2(fmaf(sc[2 * i], scale_log2, -base_m));
-                    const float b = at_ex2(fmaf(sc[2 * i + 1], scale_log2, -base_m));
-                    sum4[i & 3] += a + b;
-                    r[i] = at_pack(a, b);
-                }
-                at_tmem_st32(tm_s + lane_base + 32u * half, r);
-            }
-            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-            // rows of V that nobody may read: zeros (this thread's half of its row of the tile)
-            const int tile_lo = (t_lo + it) * AT_BN;
-            if (tile_lo + AT_BN > key_hi || tile_lo < key_lo) {
-                if (ok) ok = at_wait(v_full, ph, 3);
-                const int key = tile_lo + row;
-                if (key >= key_hi || key < key_lo) {
-                    unsigned char* vrow = sV + half * AT_BLOCK_BYTES + row * 128;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) *(uint4*)(vrow + c * 16) = make_uint4(0u, 0u, 0u, 0u);
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            }
-            if (it > 0) {
-                if (ok) ok = at_wait(o_done, (uint32_t)(it - 1) & 1u, 3);       // P_{it-1} V_{it-1} is in O
-                at_fence_after();
-                if (rescale) {
-                    uint32_t r[32];
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        at_tmem_ld32(tm_o + lane_base + 64u * half + 32u * c, r);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-                        at_tmem_st32(tm_o + lane_base + 64u * half + 32u * c, r);
-                    }
-                }
-            }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            at_fence_before();
-            // a wait that ran out: nothing is signalled any more (the issuer's own wait runs
-            // out in turn), but every thread keeps walking the loop, so that the barriers and
-            // the warp-wide loads and stores above stay matched
-            ok = __all_sync(0xffffffffu, ok);
-            if (lane == 0 && ok) at_arrive(p_full);
-        }
-        if (ok && n_it > 0) ok = at_wait(o_done, (uint32_t)(n_it - 1) & 1u, 3);
-        at_fence_after();
-        s_xl[half * 128 + row] = l;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        l += s_xl[(half ^ 1) * 128 + row];
-        // every lane takes part in the loads from tensor memory (they are warp-wide); only
-        // the rows of the tile are written
-        const bool warp_ok = __all_sync(0xffffffffu, ok);
-        if (warp_ok) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            bf16* dst = out + (size_t)(tok0 + (row_ok ? row : 0) / G) * out_stride +
-                        (size_t)(kvh * G + (row_ok ? row : 0) % G) * AT_DH + 64 * half;
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t r[32];
-                at_tmem_ld32(tm_o + lane_base + 64u * half + 32u * c, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row_ok) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint4 v;
-                        v.x = at_pack(__uint_as_float(r[8 * i]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
-                        v.y = at_pack(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
-                        v.z = at_pack(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
-                        v.w = at_pack(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
-                        *(uint4*)(dst + c * 32 + i * 8) = v;
-                    }
-                }
-            }
-        }
-    }
-    at_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-        at_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
-    }
-}
-
 // ------------------------------------------------------------------ persistent form
 // One CTA per SM walks work items (query tile, kv head) that it draws from a counter, longest
 // first. Inside the CTA everything is double-buffered, so the parts of neighbouring key tiles
@@ -490,15 +188,14 @@ attention_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 //                 issuer runs Q K^T one key tile ahead of the softmax, and starts the next
 //                 item while the softmax threads still write the last one's O out;
 //   shared memory  two Q tiles, two K tiles, two V tiles (192 KB);
-//   warp 0   draws the items (the next one while it loads this one), reads their sizes,
-//            copies the item's Q rows into shared memory and publishes a record of the item
-//            in a ring of four;
+//   warp 0   draws an item when a Q buffer is free, reads its sizes, asks TMA for its Q rows
+//            (two boxes) and publishes a record of the item in a ring of four;
 //   warps 12 and 10  follow the records and ask TMA for the K and for the V pages, a warp
 //            each, so that K runs ahead of V and neither waits for the next item's Q;
 //   warps 1 and 11  issue S = Q K^T and O += P V, a thread each (a thread starts a product
 //            about every 80 cycles); warps 2-9 softmax, two threads a row, as above.
-// The counter is a global of this library, set to zero on the stream before each launch:
-// launches of this kernel must not overlap (the engine issues them on one stream).
+// The counter is a global of this library (one per device): launches of this kernel on one
+// device must not overlap (the engine issues them on one stream).
 // A record (and its Q buffer) is only replaced when every reader has seen it: the products
 // with the item's Q have run, and the second issuer, the K and V warps and the eight softmax
 // warps have each read the record; so no waiter ever falls two phases behind a barrier.
@@ -510,11 +207,15 @@ struct ApItem {          // what warp 0 tells the others about an item
     int pad[6];
 };
 
-__device__ unsigned int ap_ticket = 0;      // set to zero on the stream before every launch
+// The counter the CTAs draw items from, and the count of CTAs that have finished: the last
+// CTA of a launch to finish sets both back to zero for the next launch (every CTA reaches its
+// end, whatever its waits did).
+__device__ unsigned int ap_ticket = 0;
+__device__ unsigned int ap_finished = 0;
 
 __global__ void __launch_bounds__(AP_THREADS, 1)
 attention_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                               const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                               const __grid_constant__ CUtensorMap map_q, bf16* __restrict__ out,
                                long long out_stride, int page_size, int page_shift,
                                const int* __restrict__ block_tables, int max_blocks,
                                const int* __restrict__ positions, const int* __restrict__ seq_ids,
@@ -548,6 +249,11 @@ attention_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_k, const 
     const int G = H / Hkv;
     const int n_items = n_tiles * Hkv;
     const int pages_per_tile = AT_BN >> page_shift;
+    const int q_box_rows = (AT_BM / G) * G;       // rows of a Q box: the tokens of a full tile x G heads
+    // rows of the Q buffers that no box writes (128 is no multiple of G) must not hold NaN
+    // bit patterns by chance: zero both buffers once
+    for (int i = tid; i < 2 * AT_TILE_BYTES / 16; i += AP_THREADS) ((uint4*)sQ)[i] = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 
     if (tid == 0) {
         for (int i = 0; i < 2; ++i) {
@@ -581,7 +287,6 @@ attention_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_k, const 
     if (warp == 0) {
         // ---------------------------------------------------------- items and Q
         bool ok = true;
-        // The next item is drawn, and its tile looked up, while this one is being loaded.
         auto draw = [&](int& item, int& tok0, int& ntok) {
             item = 0;
             if (lane == 0) item = (int)atomicAdd(&ap_ticket, 1u);
@@ -594,7 +299,6 @@ attention_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_k, const 
             }
         };
         int item, tok0, ntok;
-        draw(item, tok0, ntok);
         for (uint32_t n = 0; ok; ++n) {
             ApItem* rec = &ring[n & 3];
             const uint32_t qb = n & 1u, qph = (n >> 1) & 1u;
@@ -602,6 +306,13 @@ attention_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_k, const 
             // item two back have run and everybody has read its record
             ok = __all_sync(0xffffffffu, at_wait(&q_empty[qb], qph ^ 1u, 1));
             if (!ok) break;
+            // An item is drawn only now, when the CTA has room for it: the CTA then holds the
+            // item it computes and the one it loads, and no third. (Drawn one turn earlier, as
+            // this kernel did at first, two items lay reserved behind the running one; with
+            // three or four items a CTA on a 2048-token prompt that is nearly a fixed share
+            // each: the CTAs' loads ranged from 24 to 35 key tiles, and the last CTA ended
+            // 11 us after the median one, of 61.)
+            draw(item, tok0, ntok);
             if (item >= n_items) {
                 if (lane == 0) {
                     rec->valid = 0;
@@ -613,35 +324,31 @@ attention_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_k, const 
             const int n_rows = ntok * G;
             const int p0 = positions[tok0], seq = seq_ids[tok0];
             const int q_tok0 = tok0;
-            int item_next, tok0_next, ntok_next;
-            draw(item_next, tok0_next, ntok_next);
             const int p_last = p0 + ntok - 1;
             const int key_lo = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
             const int key_hi = p_last + 1;
             const int t_lo = key_lo / AT_BN, t_hi = (key_hi + AT_BN - 1) / AT_BN;
             const int n_it = p0 < 0 ? 0 : t_hi - t_lo;
-            if (n_it > 0) {
-                // Q rows -> shared memory in the swizzled K-major layout, all copies in flight at
-                // once; rows past the tile are zeros
-                unsigned char* dq = sQ + qb * AT_TILE_BYTES;
-#pragma unroll 8
-                for (int i = lane; i < AT_BM * 16; i += 32) {
-                    const int r = i >> 4, c = i & 15;
-                    const bool in = r < n_rows;
-                    const bf16* src = in ? q + (size_t)(q_tok0 + r / G) * q_stride + (size_t)(kvh * G + r % G) * AT_DH + c * 8 : q;
-                    const uint32_t to = at_smem(dq + (c >> 3) * AT_BLOCK_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4));
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(to), "l"(src), "r"(in ? 16 : 0) : "memory");
-                }
-                asm volatile("cp.async.wait_all;" ::: "memory");
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            }
-            __syncwarp();
             if (lane == 0) {
                 rec->valid = 1; rec->tok0 = q_tok0; rec->n_rows = n_rows; rec->p0 = p0; rec->n_it = n_it;
                 rec->t_lo = t_lo; rec->key_lo = key_lo; rec->key_hi = key_hi; rec->seq = seq; rec->kvh = kvh;
-                at_arrive(&q_full[qb]);
+                if (n_it > 0) {
+                    // The item's Q rows by TMA: two boxes (the two 64-column halves of the head
+                    // size) of G heads x the tile's tokens, which land in row order token * G +
+                    // head with the 128-byte swizzle the products read. A box always spans a full
+                    // tile's tokens: tokens past this tile's are other tokens' rows (their results
+                    // are never stored; rows are independent), tokens past the last are zeros.
+                    // (Copied by this warp with 2048 16-byte cp.async, the rows of the first item
+                    // took 8 us to arrive and those of later items 13 us, competing with the
+                    // softmax warps for issue slots: measured with the global timer.)
+                    unsigned char* dq = sQ + qb * AT_TILE_BYTES;
+                    at_expect_tx(&q_full[qb], 2u * (uint32_t)q_box_rows * 128u);
+                    at_tma_4d(dq, &map_q, 0, 0, kvh * G, q_tok0, &q_full[qb]);
+                    at_tma_4d(dq + AT_BLOCK_BYTES, &map_q, 0, 1, kvh * G, q_tok0, &q_full[qb]);
+                } else {
+                    at_arrive(&q_full[qb]);
+                }
             }
-            item = item_next; tok0 = tok0_next; ntok = ntok_next;
         }
     } else if (warp == 10 || warp == 12) {
         // ---------------------------------------------------------- V (warp 10), K (warp 12)
@@ -921,6 +628,11 @@ attention_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_k, const 
         at_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
+    if (tid == 0 && atomicAdd(&ap_finished, 1u) == gridDim.x - 1u) {
+        ap_ticket = 0;              // nobody draws any more: every CTA has seen the end of the items
+        ap_finished = 0;
+        __threadfence();
+    }
 }
 
 // ------------------------------------------------------------------------------ host
@@ -959,6 +671,51 @@ static const CUtensorMap* at_map_of(const void* pages, long long rows, int page_
     return &maps.emplace(key, map).first->second;
 }
 
+// The tensor map of a step's query rows, q [tokens, >= H * 128] bf16 with a row stride, seen
+// as (64 columns, 2 halves, H heads, tokens): a box is one half of G heads of a tile's tokens.
+// Kept by (address, stride, tokens, heads, group): a step's activations come back to the same
+// addresses step after step.
+static const CUtensorMap* at_map_q(const void* q, long long q_stride, int tokens, int H, int G) {
+    struct Key {
+        const void* q; long long stride; int tokens, H, G;
+        bool operator==(const Key& o) const {
+            return q == o.q && stride == o.stride && tokens == o.tokens && H == o.H && G == o.G;
+        }
+    };
+    struct Hash {
+        size_t operator()(const Key& k) const {
+            return (size_t)(uintptr_t)k.q * 0x9e3779b97f4a7c15ull ^ ((size_t)k.stride << 32) ^ ((size_t)k.tokens << 12) ^
+                   ((size_t)k.H << 6) ^ (size_t)k.G;
+        }
+    };
+    static std::mutex lock;
+    static std::unordered_map<Key, CUtensorMap, Hash> maps;
+    static AtEncodeFn encode = nullptr;
+    std::lock_guard<std::mutex> hold(lock);
+    if (!encode) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess ||
+            qr != cudaDriverEntryPointSuccess)
+            return nullptr;
+        encode = (AtEncodeFn)p;
+    }
+    const Key key{q, q_stride, tokens, H, G};
+    auto it = maps.find(key);
+    if (it != maps.end()) return &it->second;
+    CUtensorMap map;
+    const cuuint64_t dims[4] = {64, 2, (cuuint64_t)H, (cuuint64_t)tokens};
+    const cuuint64_t strides[3] = {128, 256, (cuuint64_t)q_stride * 2};
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)G, (cuuint32_t)(AT_BM / G)};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(q), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return nullptr;
+    if (maps.size() > 4096) maps.clear();
+    return &maps.emplace(key, map).first->second;
+}
+
 // 1 if this kernel takes the shape: head size 128, up to 16 query heads a kv head (a tile then
 // holds 128 / group tokens, rounded down), pages of 8, 16, 32, 64 or 128 tokens.
 TGO_API int tgo_attention_tc_supports(int dh, int group, int page_size) {
@@ -974,17 +731,17 @@ TGO_API int tgo_attention_tc_error(int* value) {
 }
 
 // Prompt portions: tiles of up to 128 / group consecutive tokens of one request each
-// (tile_tok0, tile_ntok). k_cache and v_cache: [n_pages, Hkv, page_size, 128] bf16.
-// persistent = 1: one CTA per SM that draws (tile, kv head) items from a counter;
-// 0: one CTA per item, two per SM.
-TGO_API int tgo_attention_tc_prefill(const void* q, long long q_stride, void* out, long long out_stride,
+// (tile_tok0, tile_ntok); q has n_tokens rows of q_stride elements, its first H * 128 columns
+// the heads. k_cache and v_cache: [n_pages, Hkv, page_size, 128] bf16.
+// One CTA per SM draws (tile, kv head) items from a counter.
+TGO_API int tgo_attention_tc_prefill(const void* q, long long q_stride, int n_tokens, void* out, long long out_stride,
                                      const void* k_cache, const void* v_cache, int n_pages, int page_size,
                                      const int* block_tables, int max_blocks, const int* positions,
                                      const int* seq_ids, const int* tile_tok0, const int* tile_ntok,
                                      int n_tiles, int H, int Hkv, int dh, float scale, int window,
-                                     int persistent, cudaStream_t stream) {
+                                     cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || H % Hkv || !tgo_attention_tc_supports(dh, H / Hkv, page_size) || n_pages <= 0 ||
+    if (n_tokens <= 0 || H <= 0 || Hkv <= 0 || H % Hkv || !tgo_attention_tc_supports(dh, H / Hkv, page_size) || n_pages <= 0 ||
         max_blocks <= 0 || window < 0 || Hkv > 65535 || !tile_tok0 || !tile_ntok || q_stride % 8 ||
         out_stride % 8 || ((uintptr_t)q % 16) || ((uintptr_t)out % 16) || ((uintptr_t)k_cache % 128) ||
         ((uintptr_t)v_cache % 128))
@@ -993,42 +750,33 @@ TGO_API int tgo_attention_tc_prefill(const void* q, long long q_stride, void* ou
     if (rows > 0x7fffffffll || (long long)n_tiles * Hkv > 0x7fffffffll) return TGO_E_BAD_ARG;
     const CUtensorMap* mk = at_map_of(k_cache, rows, page_size);
     const CUtensorMap* mv = at_map_of(v_cache, rows, page_size);
-    if (!mk || !mv) return TGO_E_BAD_ARG;
+    const CUtensorMap* mq = at_map_q(q, q_stride, n_tokens, H, H / Hkv);
+    if (!mk || !mv || !mq) return TGO_E_BAD_ARG;
     int shift = 0;
     while ((1 << shift) < page_size) ++shift;
     const float scale_log2 = scale * 1.4426950408889634f;
-    if (persistent) {
+    {
         constexpr size_t smem = 1024 + 6 * (size_t)AT_TILE_BYTES + 22 * 8 + 4 * sizeof(ApItem) +
                                 768 * sizeof(float) + 2 * AT_PAGES_CAP * sizeof(int);
-        static int sms = 0;
-        static unsigned int* ticket = nullptr;
-        if (!sms) {
-            cudaError_t e = cudaFuncSetAttribute(attention_tc_persistent_kernel,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-            int dev = 0;
-            if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
-            if ((e = cudaGetSymbolAddress((void**)&ticket, ap_ticket)) != cudaSuccess) return (int)e;
-            if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
-        }
-        cudaError_t e = cudaMemsetAsync(ticket, 0, sizeof(unsigned int), stream);
+        // per device: its SM count, and whether this kernel's attribute is set there
+        static int sms_of[64] = {};
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return (int)e;
+        if (dev < 0 || dev >= 64) return TGO_E_BAD_ARG;
+        if (!sms_of[dev]) {
+            e = cudaFuncSetAttribute(attention_tc_persistent_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            int n = 0;
+            if ((e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+            sms_of[dev] = n;
+        }
+        const int sms = sms_of[dev];
         const int items = n_tiles * Hkv;
         attention_tc_persistent_kernel<<<dim3(items < sms ? items : sms), AP_THREADS, smem, stream>>>(
-            *mk, *mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_size, shift, block_tables, max_blocks,
+            *mk, *mv, *mq, (bf16*)out, out_stride, page_size, shift, block_tables, max_blocks,
             positions, seq_ids, tile_tok0, tile_ntok, n_tiles, H, Hkv, scale_log2, window);
         return launch_status();
     }
-    constexpr size_t smem = 1024 + 3 * (size_t)AT_TILE_BYTES + 14 * 8 + 768 * sizeof(float) + AT_PAGES_CAP * sizeof(int);
-    static bool once = false;
-    if (!once) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tc_prefill_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        once = true;
-    }
-    attention_tc_prefill_kernel<<<dim3(n_tiles, Hkv), AT_THREADS, smem, stream>>>(
-        *mk, *mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_size, shift, block_tables, max_blocks,
-        positions, seq_ids, tile_tok0, tile_ntok, H, Hkv, scale_log2, window);
-    return launch_status();
 }

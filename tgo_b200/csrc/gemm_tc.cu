@@ -15,10 +15,10 @@
 //   warps 2..5         epilogue: tcgen05.ld of their 32-lane quarter of the accumulator,
 //                      32 columns at a time, then the stores.
 // Rows of A are rows of D and TMEM lanes; rows of B are columns of D and TMEM columns.
-// `transpose_out` stores D^T instead: with the weight matrix as A and a few activation rows
-// as B this is the decode orientation (weights on the 128-wide M axis, batch on N).
-// `splits` > 1 cuts K over gridDim.z CTAs, each writing a float32 partial tile; a second
-// kernel adds the partials in split order and applies the output form.
+// (The decode orientation, weights as A and a few activation rows as B with D stored
+// transposed, was built and measured for 9 to 64 rows: 104-124 us a layer of the 8B shape
+// against the library's 80-83, with K splits and a reduce kernel 3-8 % behind it in the
+// running model. It is not kept.)
 //
 // A second form of the kernel (DUAL) gives a CTA 256 rows: two accumulators fed by two A
 // tiles and one shared B tile per k-block, and four more epilogue warps. Per product it
@@ -52,7 +52,6 @@
 #define TC_OUT_BF16 0
 #define TC_OUT_F32 1
 #define TC_OUT_ADD_F32 2
-#define TC_OUT_PARTIAL 3      // float32 partial tile of a K split
 #define TC_OUT_SWIGLU 4       // silu(gate) * up of a gate/up matrix interleaved in eights, bfloat16
 
 __device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -137,47 +136,33 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 }
 
 // One thread's 32 consecutive accumulator columns (row `gm` of A, rows gn0.. of B) -> memory.
-template <int OMODE, bool TRANSPOSE>
+template <int OMODE>
 __device__ __forceinline__ void tc_store(const uint32_t (&r)[32], void* __restrict__ out, int gm, int gn0,
-                                         int rows_a, int rows_b, long long ld_out, int split) {
+                                         int rows_a, int rows_b, long long ld_out) {
     if (OMODE == TC_OUT_SWIGLU) {
-        if (!TRANSPOSE) {
-            // columns come as 8 gate, 8 up, 8 gate, 8 up: 16 outputs at column gn0 / 2
-            if (gm >= rows_a) return;
-            bf16* dst = (bf16*)out + (size_t)gm * ld_out + gn0 / 2;
+        // columns come as 8 gate, 8 up, 8 gate, 8 up: 16 outputs at column gn0 / 2
+        if (gm >= rows_a) return;
+        bf16* dst = (bf16*)out + (size_t)gm * ld_out + gn0 / 2;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                if (gn0 + 16 * h + 16 > rows_b) break;
-                uint32_t pk[4];
+        for (int h = 0; h < 2; ++h) {
+            if (gn0 + 16 * h + 16 > rows_b) break;
+            uint32_t pk[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float a = silu_mul(__uint_as_float(r[16 * h + 2 * j]), __uint_as_float(r[16 * h + 8 + 2 * j]));
-                    const float b = silu_mul(__uint_as_float(r[16 * h + 2 * j + 1]), __uint_as_float(r[16 * h + 9 + 2 * j]));
-                    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-                    pk[j] = *(uint32_t*)&v;
-                }
-                if ((ld_out & 7) == 0) *(uint4*)(dst + 8 * h) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                else
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) *(uint32_t*)(dst + 8 * h + 2 * j) = pk[j];
+            for (int j = 0; j < 4; ++j) {
+                const float a = silu_mul(__uint_as_float(r[16 * h + 2 * j]), __uint_as_float(r[16 * h + 8 + 2 * j]));
+                const float b = silu_mul(__uint_as_float(r[16 * h + 2 * j + 1]), __uint_as_float(r[16 * h + 9 + 2 * j]));
+                __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+                pk[j] = *(uint32_t*)&v;
             }
-        } else {
-            // rows of A come as 8 gate, 8 up: the up value sits eight lanes further on
-            const int within = gm & 15;
-            const int feature = (gm >> 4) * 8 + (within & 7);
+            if ((ld_out & 7) == 0) *(uint4*)(dst + 8 * h) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            else
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const float mine = __uint_as_float(r[j]);
-                const float up = __shfl_down_sync(0xffffffffu, mine, 8);
-                const int gn = gn0 + j;
-                if (within < 8 && gm + 8 < rows_a + 8 && gm < rows_a && gn < rows_b)
-                    ((bf16*)out)[(size_t)gn * ld_out + feature] = __float2bfloat16_rn(silu_mul(mine, up));
-            }
+                for (int j = 0; j < 4; ++j) *(uint32_t*)(dst + 8 * h + 2 * j) = pk[j];
         }
         return;
     }
     if (gm >= rows_a) return;
-    if (!TRANSPOSE && OMODE != TC_OUT_PARTIAL && gn0 + 32 <= rows_b && (ld_out & 7) == 0) {
+    if (gn0 + 32 <= rows_b && (ld_out & 7) == 0) {
         if (OMODE == TC_OUT_BF16) {
             uint4* dst = (uint4*)((bf16*)out + (size_t)gm * ld_out + gn0);
 #pragma unroll
@@ -214,11 +199,7 @@ __device__ __forceinline__ void tc_store(const uint32_t (&r)[32], void* __restri
         const int gn = gn0 + j;
         if (gn >= rows_b) break;
         const float v = __uint_as_float(r[j]);
-        size_t at;
-        if (OMODE == TC_OUT_PARTIAL)
-            at = ((size_t)split * (TRANSPOSE ? rows_b : rows_a) + (TRANSPOSE ? gn : gm)) * ld_out + (TRANSPOSE ? gm : gn);
-        else
-            at = TRANSPOSE ? (size_t)gn * ld_out + gm : (size_t)gm * ld_out + gn;
+        const size_t at = (size_t)gm * ld_out + gn;
         if (OMODE == TC_OUT_BF16) ((bf16*)out)[at] = __float2bfloat16_rn(v);
         else if (OMODE == TC_OUT_ADD_F32) ((float*)out)[at] += v;
         else ((float*)out)[at] = v;
@@ -228,11 +209,11 @@ __device__ __forceinline__ void tc_store(const uint32_t (&r)[32], void* __restri
 // Persistent: the grid is at most one CTA per SM and each CTA walks tiles blockIdx.x,
 // blockIdx.x + gridDim.x, ... The accumulator is double-buffered in TMEM (2 x BN columns), so
 // the epilogue of one tile runs while the next tile's products are issued.
-template <int OMODE, bool TRANSPOSE, bool DUAL>
+template <int OMODE, bool DUAL>
 __global__ void __launch_bounds__(DUAL ? TC_THREADS + 128 : TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               void* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out, int splits,
-               int kb_per_split, int* __restrict__ err, int BN, int tail_splits,
+               void* __restrict__ out, int rows_a, int rows_b, int K, long long ld_out,
+               int* __restrict__ err, int BN, int tail_splits,
                float* __restrict__ tail_ws, int* __restrict__ tail_flags) {
     // DUAL: a CTA's tile is 256 rows, two 128-row halves that share every B tile in shared
     // memory (a third fewer operand bytes per product: one SM cannot be fed the 48 KB that a
@@ -262,7 +243,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // whole tiles in full rounds, then the tiles of the last round cut tail_splits ways
     const int whole = tail_splits > 1 ? n_tiles / (int)gridDim.x * (int)gridDim.x : n_tiles;
     const int n_tail = n_tiles - whole;
-    const int total = tail_splits > 1 ? whole + n_tail * tail_splits : n_tiles * splits;
+    const int total = tail_splits > 1 ? whole + n_tail * tail_splits : n_tiles;
     constexpr int EPI_WARPS = DUAL ? 8 : 4;
 
     if (threadIdx.x == 0) {
@@ -293,10 +274,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             kb_hi = (int)((long long)(split + 1) * kb_total / tail_splits);
         } else {
             tail = -1;
-            split = w / n_tiles;
-            tile = w % n_tiles;
-            kb_lo = split * kb_per_split;
-            kb_hi = kb_lo + kb_per_split < kb_total ? kb_lo + kb_per_split : kb_total;
+            split = 0;
+            tile = w;
+            kb_lo = 0;
+            kb_hi = kb_total;
         }
         const int group = tile / per_group, within = tile % per_group;
         const int group_m = tiles_m - group * TC_GROUP_M < TC_GROUP_M ? tiles_m - group * TC_GROUP_M : TC_GROUP_M;
@@ -312,19 +293,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
                 int split, m0, n0, kb_lo, n_kb, tail;
                 locate(w, split, m0, n0, kb_lo, n_kb, tail);
-                // Decode orientation: A is the weight matrix, read once from DRAM, and its row
-                // pitch is often a power of two, so CTAs that all walk K from the same end
-                // keep hitting the same few memory channels together (measured: the busiest
-                // channel carried twice the traffic of the idlest). Each tile starts its walk
-                // somewhere else; the sum over k takes another order, fixed per tile.
-                const int rot = TRANSPOSE && n_kb > 1 ? (int)(((unsigned)(m0 / TC_BM) * 13u + (unsigned)split * 5u) % (unsigned)n_kb) : 0;
                 for (int i = 0; i < n_kb; ++i, ++it) {
                     const int s = it % STAGES;
                     ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, err, 1);
                     if (!ok) break;
                     mbar_expect_tx(&full[s], (uint32_t)STAGE);
                     unsigned char* st = base + (size_t)s * STAGE;
-                    const int kb = kb_lo + (i + rot < n_kb ? i + rot : i + rot - n_kb);
+                    const int kb = kb_lo + i;
                     tma_load_2d(st, &map_a, kb * TC_BK, m0, &full[s]);
                     if (DUAL) tma_load_2d(st + TC_A_BYTES, &map_a, kb * TC_BK, m0 + TC_BM, &full[s]);
                     tma_load_2d(st + (DUAL ? 2 : 1) * TC_A_BYTES, &map_b, kb * TC_BK, n0, &full[s]);
@@ -446,7 +421,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                 }
                 if (ok && n_kb > 0)
-                    tc_store<OMODE, TRANSPOSE>(r, out, m0 + row, n0 + c * 32, rows_a, n_edge, ld_out, split);
+                    tc_store<OMODE>(r, out, m0 + row, n0 + c * 32, rows_a, n_edge, ld_out);
             }
             // the accumulator may be overwritten: one arrival per epilogue warp
             tc_fence_before();
@@ -471,21 +446,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
-    }
-}
-
-// out = sum over splits of partial[s] (in split order), in the wanted output form.
-template <int OMODE>
-__global__ void gemm_tc_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out,
-                                      long long n, int splits) {
-    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    for (; i < n; i += stride) {
-        float s = 0.f;
-        for (int k = 0; k < splits; ++k) s += partial[(size_t)k * n + i];
-        if (OMODE == TC_OUT_BF16) ((bf16*)out)[i] = __float2bfloat16_rn(s);
-        else if (OMODE == TC_OUT_ADD_F32) ((float*)out)[i] += s;
-        else ((float*)out)[i] = s;
     }
 }
 
@@ -556,11 +516,11 @@ static int tc_sms() {
     return 148;
 }
 
-template <int OMODE, bool TRANSPOSE, bool DUAL>
+template <int OMODE, bool DUAL>
 static int tc_launch(int BN, const CUtensorMap& ma, const CUtensorMap& mb, void* out, int rows_a, int rows_b, int K,
-                     long long ld_out, int splits, int kb_per_split, int* err, cudaStream_t stream,
-                     int tail_splits, float* tail_ws, int* tail_flags) {
-    auto kern = gemm_tc_kernel<OMODE, TRANSPOSE, DUAL>;
+                     long long ld_out, int* err, cudaStream_t stream, int tail_splits, float* tail_ws,
+                     int* tail_flags) {
+    auto kern = gemm_tc_kernel<OMODE, DUAL>;
     const size_t smem = TC_SMEM_TOTAL;
     static bool sized = false;            // per instance of this template
     if (!sized) {
@@ -568,33 +528,31 @@ static int tc_launch(int BN, const CUtensorMap& ma, const CUtensorMap& mb, void*
         if (e != cudaSuccess) return (int)e;
         sized = true;
     }
-    const int total = ((rows_b + BN - 1) / BN) * ((rows_a + (DUAL ? 2 : 1) * TC_BM - 1) / ((DUAL ? 2 : 1) * TC_BM)) * splits;
+    const int total = ((rows_b + BN - 1) / BN) * ((rows_a + (DUAL ? 2 : 1) * TC_BM - 1) / ((DUAL ? 2 : 1) * TC_BM));
     const int sms = tc_sms();
     // with a cut last round the kernel derives the rounds from the grid: it has to be `sms`
-    const dim3 grid(tail_splits > 1 ? tc_sms() : total < sms ? total : sms);
-    kern<<<grid, DUAL ? TC_THREADS + 128 : TC_THREADS, smem, stream>>>(ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, BN,
+    const dim3 grid(tail_splits > 1 ? sms : total < sms ? total : sms);
+    kern<<<grid, DUAL ? TC_THREADS + 128 : TC_THREADS, smem, stream>>>(ma, mb, out, rows_a, rows_b, K, ld_out, err, BN,
                                                                        tail_splits, tail_ws, tail_flags);
     return launch_status();
 }
 
-template <bool TRANSPOSE, bool DUAL = false>
+template <bool DUAL>
 static int tc_dispatch(int BN, const CUtensorMap& ma, const CUtensorMap& mb, void* out, int rows_a, int rows_b, int K,
-                       long long ld_out, int omode, int splits, int kb_per_split, int* err, cudaStream_t s,
-                       int tail_splits = 1, float* tail_ws = nullptr, int* tail_flags = nullptr) {
+                       long long ld_out, int omode, int* err, cudaStream_t s, int tail_splits, float* tail_ws,
+                       int* tail_flags) {
 #define TC_CASE(mode) \
-    return tc_launch<mode, TRANSPOSE, DUAL>(BN, ma, mb, out, rows_a, rows_b, K, ld_out, splits, kb_per_split, err, s, \
-                                            tail_splits, tail_ws, tail_flags)
+    return tc_launch<mode, DUAL>(BN, ma, mb, out, rows_a, rows_b, K, ld_out, err, s, tail_splits, tail_ws, tail_flags)
     switch (omode) {
         case TC_OUT_BF16: TC_CASE(TC_OUT_BF16);
         case TC_OUT_F32: TC_CASE(TC_OUT_F32);
         case TC_OUT_ADD_F32: TC_CASE(TC_OUT_ADD_F32);
-        case TC_OUT_SWIGLU: TC_CASE(TC_OUT_SWIGLU);
-        default: TC_CASE(TC_OUT_PARTIAL);
+        default: TC_CASE(TC_OUT_SWIGLU);
     }
 #undef TC_CASE
 }
 
-// For tests and tuning: the tile of the non-transposed product is rows x width instead of
+// For tests and tuning: the tile of the product is rows x width instead of
 // the cost model's choice (rows 128 or 256; 0 gives the choice back). The width has to be
 // one the instruction takes with 128 rows: a multiple of 16 from 16 to 256. tail: 0 leaves
 // the cut of the last round to the shape, 1 forbids it. Not for use while other threads
@@ -610,7 +568,7 @@ TGO_API int tgo_gemm_tc_force_tile(int rows, int width, int tail) {
     return 0;
 }
 
-// What the last non-transposed product ran as: rows and width of its tiles and the number
+// What the last product of this process ran as (one thread at a time launches products): rows and width of its tiles and the number
 // of parts its last round's tiles were cut into.
 static int g_last_rows = 0, g_last_width = 0, g_last_cut = 0;
 TGO_API void tgo_gemm_tc_last_plan(int* rows, int* width, int* cut) {
@@ -632,100 +590,70 @@ static int tc_tail_splits(long long tiles, int kb_total, int sms) {
     return s < 2 ? 1 : s;
 }
 
-// out[M, N] (row-major, leading dimension N) = x[M, K] . w[N, K]^T.
-//   transpose == 0: x is the A operand (rows on the 128-wide axis): prefill, many rows.
-//   transpose == 1: w is the A operand and x the B operand (M <= 256 rows padded to a
-//                   multiple of 16): decode, few rows; the tile is stored transposed.
+// out[M, N] (row-major, leading dimension N) = x[M, K] . w[N, K]^T; x is the A operand (its
+// rows on the 128-wide axis): prompt portions, many rows.
 // omode: 0 bfloat16, 1 float32, 2 add into float32, 4 w is a gate/up matrix with rows
-// interleaved in eights and out is silu(gate) * up, bfloat16 [M, N / 2] (no splits).
-// splits > 1: K is cut; `workspace` must hold splits * M * N floats.
+// interleaved in eights and out is silu(gate) * up, bfloat16 [M, N / 2].
 // tail_ws, tail_flags: tgo_gemm_tc_tail_floats() floats and tgo_gemm_tc_tail_flags() zeroed
-// ints of this device for the cut of the last round (splits == 1); without them the last
-// round is not cut. The kernel leaves the flags zero.
+// ints of this device for the cut of the last round; without them the last round is not cut.
+// The kernel leaves the flags zero. One product at a time per device may use them.
 // err: one int on the device that a timed-out wait sets.
 TGO_API int tgo_gemm_tc(const void* x, const void* w, void* out, int M, int N, int K, int omode,
-                        int transpose, int splits, float* workspace, float* tail_ws, int* tail_flags,
-                        int* err, cudaStream_t stream) {
+                        float* tail_ws, int* tail_flags, int* err, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 || omode < 0 || omode == TC_OUT_PARTIAL || omode > TC_OUT_SWIGLU || splits < 1 ||
-        (splits > 1 && (!workspace || omode == TC_OUT_SWIGLU)) || (omode == TC_OUT_SWIGLU && N % 16) ||
-        ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
+    if (K <= 0 || K % 8 || omode < 0 || omode == 3 || omode > TC_OUT_SWIGLU ||
+        (omode == TC_OUT_SWIGLU && N % 16) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
         return TGO_E_BAD_ARG;
     const long long ld = omode == TC_OUT_SWIGLU ? N / 2 : N;
     const int kb_total = (K + TC_BK - 1) / TC_BK;
-    if (splits > kb_total) splits = kb_total;
-    const int kb_per_split = (kb_total + splits - 1) / splits;
-    splits = (kb_total + kb_per_split - 1) / kb_per_split;
-    const int om = splits > 1 ? TC_OUT_PARTIAL : omode;
-    void* dst = splits > 1 ? (void*)workspace : out;
     CUtensorMap ma, mb;
     int rc;
-    if (!transpose) {
-        // Tile shape. The CTAs walk the tiles in rounds, and a round lasts as long as a whole
-        // tile however few tiles it has, unless it is the last and its tiles are cut along K.
-        // A k-block of a tile costs the larger of its products (2 cycles a column for 128
-        // rows) and of bringing its operands in (an SM is fed about 70 bytes a cycle:
-        // measured, a 128 x 256 tile's 48 KB keep the tensor pipe at 73 %). A tile of 256
-        // rows (two accumulators over one B tile) needs a third fewer bytes per product.
-        // Among 128 or 256 rows and widths in multiples of 32 (the kernel takes multiples of
-        // 16, but a sweep over twelve products of three model sizes at 512 to 4096 rows found
-        // the widths between to cost as much as the next multiple of 32 or more), the
-        // cheapest by this count wins.
-        const int sms = tc_sms();
-        const bool may_cut = splits == 1 && tail_ws && tail_flags && g_forced_tail != 1;
-        int bn = N >= 256 ? 256 : 128;
-        bool dual = false;
-        if (g_forced_rows && om != TC_OUT_PARTIAL) {
-            bn = g_forced_width;
-            dual = g_forced_rows == 256;
-        } else if (N >= 256 && om != TC_OUT_PARTIAL) {
-            double best = -1.0;
-            for (int rows = 128; rows <= 256; rows += 128) {
-                if (rows == 256 && M <= 128) break;
-                const long long tiles_m = (M + rows - 1) / rows;
-                for (int width = 256; width >= 64; width -= 32) {
-                    const long long tiles = tiles_m * ((N + width - 1) / width);
-                    const double math = 2.0 * width * (rows / 128);
-                    const double feed = ((rows / 128) * 16384.0 + 128.0 * width) / 70.0;
-                    const double per_kb = math > feed ? math : feed;
-                    // + the epilogue, which a 256-row tile cannot hide behind the next tile
-                    const double fixed = (rows == 256 ? 12.0 * width : 0.0) + 2000.0;
-                    const int cut = may_cut ? tc_tail_splits(tiles, kb_total, sms) : 1;
-                    double cost;
-                    if (cut > 1)        // + the parts' way through the workspace: written, waited for,
-                                        // read (fitted to measured differences between cut and uncut)
-                        cost = (double)(tiles / sms) * (per_kb * kb_total + fixed) +
-                               per_kb * ((kb_total + cut - 1) / cut) + fixed + cut * rows * width * 4.0 / 35.0 + 8000.0;
-                    else
-                        cost = (double)((tiles + sms - 1) / sms) * (per_kb * kb_total + fixed);
-                    if (best < 0 || cost < best) { best = cost; bn = width; dual = rows == 256; }
-                }
+    // Tile shape. The CTAs walk the tiles in rounds, and a round lasts as long as a whole
+    // tile however few tiles it has, unless it is the last and its tiles are cut along K.
+    // A k-block of a tile costs the larger of its products (2 cycles a column for 128
+    // rows) and of bringing its operands in (an SM is fed about 70 bytes a cycle:
+    // measured, a 128 x 256 tile's 48 KB keep the tensor pipe at 73 %). A tile of 256
+    // rows (two accumulators over one B tile) needs a third fewer bytes per product.
+    // Among 128 or 256 rows and widths in multiples of 32 (the kernel takes multiples of
+    // 16, but a sweep over twelve products of three model sizes at 512 to 4096 rows found
+    // the widths between to cost as much as the next multiple of 32 or more), the
+    // cheapest by this count wins.
+    const int sms = tc_sms();
+    const bool may_cut = tail_ws && tail_flags && g_forced_tail != 1;
+    int bn = N >= 256 ? 256 : 128;
+    bool dual = false;
+    if (g_forced_rows) {
+        bn = g_forced_width;
+        dual = g_forced_rows == 256;
+    } else if (N >= 256) {
+        double best = -1.0;
+        for (int rows = 128; rows <= 256; rows += 128) {
+            if (rows == 256 && M <= 128) break;
+            const long long tiles_m = (M + rows - 1) / rows;
+            for (int width = 256; width >= 64; width -= 32) {
+                const long long tiles = tiles_m * ((N + width - 1) / width);
+                const double math = 2.0 * width * (rows / 128);
+                const double feed = ((rows / 128) * 16384.0 + 128.0 * width) / 70.0;
+                const double per_kb = math > feed ? math : feed;
+                // + the epilogue, which a 256-row tile cannot hide behind the next tile
+                const double fixed = (rows == 256 ? 12.0 * width : 0.0) + 2000.0;
+                const int cut = may_cut ? tc_tail_splits(tiles, kb_total, sms) : 1;
+                double cost;
+                if (cut > 1)        // + the parts' way through the workspace: written, waited for,
+                                    // read (fitted to measured differences between cut and uncut)
+                    cost = (double)(tiles / sms) * (per_kb * kb_total + fixed) +
+                           per_kb * ((kb_total + cut - 1) / cut) + fixed + cut * rows * width * 4.0 / 35.0 + 8000.0;
+                else
+                    cost = (double)((tiles + sms - 1) / sms) * (per_kb * kb_total + fixed);
+                if (best < 0 || cost < best) { best = cost; bn = width; dual = rows == 256; }
             }
         }
-        const long long tiles = (long long)((M + (dual ? 2 : 1) * TC_BM - 1) / ((dual ? 2 : 1) * TC_BM)) * ((N + bn - 1) / bn);
-        const int cut = may_cut && om != TC_OUT_PARTIAL ? tc_tail_splits(tiles, kb_total, sms) : 1;
-        g_last_rows = dual ? 256 : 128; g_last_width = bn; g_last_cut = cut;
-        if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
-        if ((rc = make_map(&mb, w, N, K, bn))) return rc;
-        rc = dual ? tc_dispatch<false, true>(bn, ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream, cut, tail_ws, tail_flags)
-                  : tc_dispatch<false, false>(bn, ma, mb, dst, M, N, K, ld, om, splits, kb_per_split, err, stream, cut, tail_ws, tail_flags);
-    } else {
-        if (M > 256) return TGO_E_BAD_ARG;
-        const int bn = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
-        // the 128-row tiles of the weight matrix seldom fill the SMs a whole number of times
-        // (192 tiles of a gate/up matrix: a round and 44): the last round is cut along K
-        const bool may_cut = splits == 1 && tail_ws && tail_flags && g_forced_tail != 1;
-        const int cut = may_cut ? tc_tail_splits((N + TC_BM - 1) / TC_BM, kb_total, tc_sms()) : 1;
-        if ((rc = make_map(&ma, w, N, K, TC_BM))) return rc;
-        if ((rc = make_map(&mb, x, M, K, bn))) return rc;
-        // A = w (N rows), B = x (M rows); D^T is stored: out[m, n], leading dimension N
-        rc = tc_dispatch<true>(bn, ma, mb, dst, N, M, K, ld, om, splits, kb_per_split, err, stream, cut, tail_ws, tail_flags);
     }
-    if (rc || splits == 1) return rc;
-    const long long n = (long long)M * N;
-    const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
-    if (omode == TC_OUT_BF16) gemm_tc_reduce_kernel<TC_OUT_BF16><<<blocks, 256, 0, stream>>>(workspace, out, n, splits);
-    else if (omode == TC_OUT_F32) gemm_tc_reduce_kernel<TC_OUT_F32><<<blocks, 256, 0, stream>>>(workspace, out, n, splits);
-    else gemm_tc_reduce_kernel<TC_OUT_ADD_F32><<<blocks, 256, 0, stream>>>(workspace, out, n, splits);
-    return launch_status();
+    const long long tiles = (long long)((M + (dual ? 2 : 1) * TC_BM - 1) / ((dual ? 2 : 1) * TC_BM)) * ((N + bn - 1) / bn);
+    const int cut = may_cut ? tc_tail_splits(tiles, kb_total, sms) : 1;
+    g_last_rows = dual ? 256 : 128; g_last_width = bn; g_last_cut = cut;
+    if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
+    if ((rc = make_map(&mb, w, N, K, bn))) return rc;
+    return dual ? tc_dispatch<true>(bn, ma, mb, out, M, N, K, ld, omode, err, stream, cut, tail_ws, tail_flags)
+                : tc_dispatch<false>(bn, ma, mb, out, M, N, K, ld, omode, err, stream, cut, tail_ws, tail_flags);
 }

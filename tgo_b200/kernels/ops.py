@@ -412,9 +412,6 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_h
             "attention_flash_combine")
 
 
-TC_ATTENTION_PERSISTENT = True   # one CTA per SM drawing items, or one CTA per item
-
-
 def attention_tc_supports(head_dim: int, group: int, page_size: int) -> bool:
     return bool(load_library("attention_tc").tgo_attention_tc_supports(c_int(head_dim), c_int(group),
                                                                        c_int(page_size)))
@@ -443,11 +440,11 @@ def attention_tc_prefill(q: torch.Tensor, out: torch.Tensor, num_heads: int, num
     assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
     lib = load_library("attention_tc")
     _check(lib.tgo_attention_tc_prefill(
-        _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+        _ptr(q), c_ll(q.stride(0)), c_int(q.shape[0]), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
         c_int(k_cache.shape[0]), c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]),
         _ptr(positions), _ptr(seq_ids), _ptr(tile_tok0), _ptr(tile_ntok), c_int(tile_tok0.numel()),
         c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_float(scale), c_int(window),
-        c_int(1 if TC_ATTENTION_PERSISTENT else 0), _stream()), "attention_tc_prefill",
+        _stream()), "attention_tc_prefill",
         f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads}, page_size={page_size})")
 
 
@@ -535,14 +532,13 @@ def _tc_tail_buffers(device):
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
-            transpose: Optional[bool] = None, splits: int = 1, gated: bool = False) -> None:
+            gated: bool = False) -> None:
     """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, float32
-    accumulation in tensor memory, TMA-fed). out: bfloat16 or float32, or float32 that the
-    product is added to. transpose: the weight rows take the 128-wide axis and x (at most
-    256 rows) the other (decode); default: when x has at most 64 rows. splits > 1 cuts K
-    over that many CTAs per tile and adds the float32 partials in order. gated: w is a
-    gate/up matrix with rows interleaved in eights and out is silu(gate) * up, bfloat16
-    [M, N / 2]."""
+    accumulation in tensor memory, TMA-fed); for many rows. out: bfloat16 or float32, or
+    float32 that the product is added to. gated: w is a gate/up matrix with rows interleaved
+    in eights and out is silu(gate) * up, bfloat16 [M, N / 2]. One thread at a time launches
+    these (the forced tile and the last plan below are process-wide, the workspace of the
+    last round's cut is one per device)."""
     _need_cuda(x, w, out)
     M, K = x.shape
     N = w.shape[0]
@@ -550,7 +546,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     assert x.is_contiguous() and w.is_contiguous() and out.is_contiguous()
     assert out.shape == ((M, N // 2) if gated else (M, N))
     if gated:
-        assert out.dtype == torch.bfloat16 and N % 16 == 0 and splits == 1
+        assert out.dtype == torch.bfloat16 and N % 16 == 0
         omode = 4
     elif accumulate:
         assert out.dtype == torch.float32
@@ -558,19 +554,15 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     else:
         omode = 0 if out.dtype == torch.bfloat16 else 1
         assert out.dtype in (torch.bfloat16, torch.float32)
-    if transpose is None:
-        transpose = M <= 64
-    ws = torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None
     lib = load_library("gemm_tc")
-    tail_ws, tail_flags = (None, None) if splits > 1 else _tc_tail_buffers(x.device)
+    tail_ws, tail_flags = _tc_tail_buffers(x.device)
     _check(lib.tgo_gemm_tc(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_int(omode),
-                           c_int(1 if transpose else 0), c_int(splits), _ptr(ws), _ptr(tail_ws),
-                           _ptr(tail_flags), _ptr(gemm_tc_error_flag(x.device)), _stream()), "gemm_tc",
-           f"(M={M}, N={N}, K={K})")
+                           _ptr(tail_ws), _ptr(tail_flags), _ptr(gemm_tc_error_flag(x.device)),
+                           _stream()), "gemm_tc", f"(M={M}, N={N}, K={K})")
 
 
 def gemm_tc_force_tile(rows: int = 0, width: int = 0, cut_last_round: bool = True) -> None:
-    """For tests and tuning: `gemm_tc` (not transposed) runs tiles of rows x width (rows 128
+    """For tests and tuning: `gemm_tc` runs tiles of rows x width (rows 128
     or 256; width a multiple of 16 up to 256) instead of choosing; 0 gives the choice back.
     cut_last_round False: the tiles of the last round are not cut along K."""
     lib = load_library("gemm_tc")
@@ -579,7 +571,7 @@ def gemm_tc_force_tile(rows: int = 0, width: int = 0, cut_last_round: bool = Tru
 
 
 def gemm_tc_last_plan() -> tuple:
-    """(rows, width, parts) of the last non-transposed `gemm_tc`: its tile and into how many
+    """(rows, width, parts) of the last `gemm_tc`: its tile and into how many
     parts along K the tiles of its last round were cut (1: not cut)."""
     lib = load_library("gemm_tc")
     r, w, c = c_int(0), c_int(0), c_int(0)
