@@ -284,12 +284,14 @@ def main():
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES),
                     help="with --only: the 14B or 32B shape of the baseline record instead of the 8B one")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="with --only decode: prompt length")
-    ap.add_argument("--only", default="", choices=["", "prefill", "decode", "serve", "check"],
+    ap.add_argument("--rows", default="256,512,1024,2048", help="with --only products: row counts")
+    ap.add_argument("--only", default="", choices=["", "prefill", "decode", "serve", "check", "products"],
                     help="run just the 2,048-token prefill, just the decode steps, the "
                          "continuous-batching workload, or the exactness check at real layer "
                          "sizes (float32 against bfloat16, alone against cut and mixed; 4 layers "
-                         "unless --layers says otherwise), and print a short line instead of "
-                         "the contract line")
+                         "unless --layers says otherwise), or the four matrix products of a layer "
+                         "at the --rows row counts against the library product, and print a "
+                         "short line instead of the contract line")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -313,6 +315,11 @@ def main():
         if not args.layers:
             config["num_hidden_layers"] = 4
         return exactness_check(config, seed, args.shape)
+    if args.only == "products":
+        from tgo_b200.engine.measure import measure_products
+        for rec in measure_products(config, [int(r) for r in args.rows.split(",") if r]):
+            print(json.dumps({k: (round(v, 1) if isinstance(v, float) else v) for k, v in rec.items()}))
+        return 0
     model = tgo_b200.open_random(config, seed=seed, dtype="bfloat16", sigma=0.02, gain_sigma=0.05)
     peaks = load_peaks()
     if args.only == "prefill":

@@ -114,7 +114,8 @@ __device__ __forceinline__ uint64_t umma_desc(const void* tile) {
 // the width that wastes the least of the GPU for the shape at hand).
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
 #define TC_RING_BYTES (200 * 1024)
-#define TC_SMEM_TOTAL ((size_t)TC_RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/)
+#define TC_STAGE_OUT_BYTES 2048            // per epilogue warp: 32 rows x 64 bytes of output on their way out
+#define TC_SMEM_TOTAL ((size_t)TC_RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 8 * TC_STAGE_OUT_BYTES)
 __host__ __device__ __forceinline__ int tc_stage_bytes(int bn, bool dual = false) {
     return (dual ? 2 : 1) * TC_A_BYTES + bn * TC_BK * 2;
 }
@@ -132,7 +133,54 @@ __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(_
 __device__ __forceinline__ float silu_mul(float g, float u) {
     g = bf16_round(g);      // as when the product is stored before the gate is applied
     u = bf16_round(u);
-    return g / (1.f + expf(-g)) * u;
+    // 2^x and 1/x of the special-function unit (relative error about 2^-22; the result is
+    // rounded to bfloat16): the library routines cost ten times the instructions, and a
+    // 256 x 224 tile has 28672 of these
+    return __fdividef(g, 1.f + __expf(-g)) * u;
+}
+
+__device__ __forceinline__ void tc_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tc_tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t tc_pack(uint32_t lo, uint32_t hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(lo), __uint_as_float(hi));
+    return *(uint32_t*)&v;
+}
+
+// A warp's 32 rows x 64 bytes of bfloat16 output (each lane holds its row's four 16-byte
+// pieces) -> memory through the warp's staging buffer, so that a store instruction writes 8
+// rows x 64 contiguous bytes instead of 32 rows x 16: a quarter of the cache lines per
+// instruction. (Each thread storing its own row, a 256 x 192 tile took 5.8 us to leave, a
+// seventh of the tile's time, with the tensor core idle: measured with the global timer.)
+// dst: the warp's first row at the pieces' first column; rows_ok rows of the warp exist.
+__device__ __forceinline__ void tc_store_staged(unsigned char* stage, const uint4 (&v)[4], bf16* dst,
+                                                long long ld_out, int rows_ok, int lane) {
+    const uint32_t sbase = tc_smem(stage);
+    const int swz = (lane >> 1) & 3;
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sbase + (uint32_t)(lane * 64 + ((q ^ swz) << 4))),
+                     "r"(v[q].x), "r"(v[q].y), "r"(v[q].z), "r"(v[q].w) : "memory");
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int e = i * 32 + lane, row = e >> 2, q = e & 3;
+        uint4 x;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w)
+                     : "r"(sbase + (uint32_t)(row * 64 + ((q ^ ((row >> 1) & 3)) << 4))) : "memory");
+        if (row < rows_ok) *(uint4*)(dst + (size_t)row * ld_out + q * 8) = x;
+    }
+    __syncwarp();
 }
 
 // One thread's 32 consecutive accumulator columns (row `gm` of A, rows gn0.. of B) -> memory.
@@ -230,6 +278,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t* acc_full = empty + STAGES;       // [2]
     uint64_t* acc_empty = acc_full + 2;        // [2]
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    unsigned char* stage_out = base + TC_RING_BYTES + 256;      // [8 epilogue warps][TC_STAGE_OUT_BYTES]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // Tile order: the A-row tiles of one group of TC_GROUP_M run first over a B tile, so the
@@ -381,6 +430,111 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // a tile that is not a multiple of 32 wide: its last group of columns is cut at the
             // tile's edge (what lies beyond belongs to the next tile)
             const int n_edge = n0 + BN < rows_b ? n0 + BN : rows_b;
+            const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * ACC_COLS + (uint32_t)(half * 256);
+            // The usual tile (whole, bfloat16 or gated output, rows of the output 16-byte
+            // aligned): the loads from tensor memory run one group of columns ahead of the
+            // stores, and the stores go through the warp's staging buffer. MEASURED (global
+            // timer, 2048 rows of the 8B shapes): a 256 x 192 tile's way out 5.8 -> 3.1 us of
+            // its 42, a gated 256 x 224 tile's 9.8 -> 6.0 us of its 48 (a 256-row tile fills
+            // tensor memory, so the tensor core idles meanwhile, and every SM writes its tile
+            // at the same moment: 14 MB at once). Tried and not kept: copying the whole slice
+            // out of tensor memory into registers (rounded to bfloat16: up to 128 registers a
+            // thread), giving tensor memory back at once and storing while the next tile runs;
+            // the kernel then spills (its ten warps get 168 registers each, and with three
+            // warpgroups and setmaxnreg the compiler spilled more), and was slower: q/k/v
+            // 92.8 us against 85.9, gate/up 320 against 285.
+            if ((OMODE == TC_OUT_BF16 || OMODE == TC_OUT_SWIGLU) && tail < 0 && (ld_out & 7) == 0 && ok && n_kb > 0) {
+                unsigned char* stage = stage_out + (warp - 2) * TC_STAGE_OUT_BYTES;
+                const int row0 = m0 + half * TC_BM + quarter * 32;             // the warp's first row
+                const int rows_ok = rows_a - row0 < 32 ? rows_a - row0 : 32;   // may be <= 0
+                const int n_chunks = (BN + 31) / 32;
+                uint32_t ra[32], rb[32];
+                if (OMODE == TC_OUT_BF16) {
+                    tc_tmem_ld32(tacc, ra);
+#pragma unroll 1
+                    for (int c = 0; c < n_chunks; c += 2) {
+                        tc_tmem_wait_ld();
+                        if (c + 1 < n_chunks) tc_tmem_ld32(tacc + (uint32_t)((c + 1) * 32), rb);
+                        {
+                            const int gn0 = n0 + c * 32;
+                            if (gn0 + 32 <= n_edge) {
+                                uint4 v[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q)
+                                    v[q] = make_uint4(tc_pack(ra[8 * q], ra[8 * q + 1]), tc_pack(ra[8 * q + 2], ra[8 * q + 3]),
+                                                      tc_pack(ra[8 * q + 4], ra[8 * q + 5]), tc_pack(ra[8 * q + 6], ra[8 * q + 7]));
+                                tc_store_staged(stage, v, (bf16*)out + (size_t)row0 * ld_out + gn0, ld_out, rows_ok, lane);
+                            } else {
+                                tc_store<OMODE>(ra, out, m0 + row, gn0, rows_a, n_edge, ld_out);
+                            }
+                        }
+                        if (c + 1 < n_chunks) {
+                            tc_tmem_wait_ld();
+                            if (c + 2 < n_chunks) tc_tmem_ld32(tacc + (uint32_t)((c + 2) * 32), ra);
+                            const int gn0 = n0 + (c + 1) * 32;
+                            if (gn0 + 32 <= n_edge) {
+                                uint4 v[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q)
+                                    v[q] = make_uint4(tc_pack(rb[8 * q], rb[8 * q + 1]), tc_pack(rb[8 * q + 2], rb[8 * q + 3]),
+                                                      tc_pack(rb[8 * q + 4], rb[8 * q + 5]), tc_pack(rb[8 * q + 6], rb[8 * q + 7]));
+                                tc_store_staged(stage, v, (bf16*)out + (size_t)row0 * ld_out + gn0, ld_out, rows_ok, lane);
+                            } else {
+                                tc_store<OMODE>(rb, out, m0 + row, gn0, rows_a, n_edge, ld_out);
+                            }
+                        }
+                    }
+                } else {
+                    // gated: two groups of 32 accumulator columns (8 gate, 8 up, ...) make 32
+                    // outputs, 64 bytes a row; the next two groups are loaded while these leave
+                    tc_tmem_ld32(tacc, ra);
+                    if (n_chunks > 1) tc_tmem_ld32(tacc + 32u, rb);
+#pragma unroll 1
+                    for (int c = 0; c < n_chunks; c += 2) {
+                        tc_tmem_wait_ld();
+                        const int gn0 = n0 + c * 32;
+                        const bool pair = c + 1 < n_chunks && gn0 + 64 <= n_edge;
+                        uint4 v[4];
+                        if (pair) {
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                uint32_t pk[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float a = silu_mul(__uint_as_float(ra[16 * h + 2 * j]), __uint_as_float(ra[16 * h + 8 + 2 * j]));
+                                    const float b = silu_mul(__uint_as_float(ra[16 * h + 2 * j + 1]), __uint_as_float(ra[16 * h + 9 + 2 * j]));
+                                    __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+                                    pk[j] = *(uint32_t*)&t;
+                                }
+                                v[h] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            }
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                uint32_t pk[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float a = silu_mul(__uint_as_float(rb[16 * h + 2 * j]), __uint_as_float(rb[16 * h + 8 + 2 * j]));
+                                    const float b = silu_mul(__uint_as_float(rb[16 * h + 2 * j + 1]), __uint_as_float(rb[16 * h + 9 + 2 * j]));
+                                    __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+                                    pk[j] = *(uint32_t*)&t;
+                                }
+                                v[2 + h] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            }
+                        } else {
+                            tc_store<OMODE>(ra, out, m0 + row, gn0, rows_a, n_edge, ld_out);
+                            if (c + 1 < n_chunks) tc_store<OMODE>(rb, out, m0 + row, gn0 + 32, rows_a, n_edge, ld_out);
+                        }
+                        if (c + 2 < n_chunks) tc_tmem_ld32(tacc + (uint32_t)((c + 2) * 32), ra);
+                        if (c + 3 < n_chunks) tc_tmem_ld32(tacc + (uint32_t)((c + 3) * 32), rb);
+                        if (pair)
+                            tc_store_staged(stage, v, (bf16*)out + (size_t)row0 * ld_out + gn0 / 2, ld_out, rows_ok, lane);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                continue;
+            }
 #pragma unroll 1
             for (int c = 0; c < (BN + 31) / 32; ++c) {
                 uint32_t r[32];

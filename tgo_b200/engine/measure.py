@@ -178,3 +178,49 @@ def measure_decode(loaded, batch: int, prompt_len: int, tokens: int, warmup: int
             "p99_ms": rank(0.99), "bytes_per_step": nbytes,
             "gbs": nbytes / (ms_per_step * 1e-3) / 1e9, "gpu_launches": launches,
             "h2d_bytes_per_step": 0, "final_context": ctx[0]}
+
+
+def measure_products(config: dict, rows_list, repeats: int = 20) -> List[dict]:
+    """The four matrix products of one layer of `config` (q/k/v, o, gate/up with the gate
+    applied, down) at each row count, timed warm with CUDA events: this package's kernel for
+    that row count (`ops.linear` / `ops.gated_linear`, whichever kernel they pick), the
+    tcgen05 kernel forced, and the library product (for gate/up: plus this package's gate
+    kernel, which the library product needs after it). Weights and inputs are seeded random."""
+    d, f = config["hidden_size"], config["intermediate_size"]
+    H, Hkv = config["num_attention_heads"], config.get("num_key_value_heads", config["num_attention_heads"])
+    dh = config.get("head_dim", d // H)
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(1)
+    shapes = [("qkv", (H + 2 * Hkv) * dh, d, False), ("o", d, H * dh, False),
+              ("gate_up", 2 * f, d, True), ("down", d, f, False)]
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(repeats):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / repeats * 1e3
+    out = []
+    for name, N, K, gated in shapes:
+        w = (torch.randn(N, K, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        for M in rows_list:
+            x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+            y = torch.empty(M, N // 2 if gated else N, dtype=torch.bfloat16, device=dev)
+            rec = {"product": name, "rows": M, "N": N, "K": K, "gflop": 2.0 * M * N * K / 1e9}
+            rec["ours_us"] = timed((lambda: ops.gated_linear(x, w, True)) if gated else (lambda: ops.linear(x, w)))
+            if M > ops.SKINNY_MAX_ROWS * 8:
+                rec["tcgen05_us"] = timed(lambda: ops.gemm_tc(x, w, y, gated=gated))
+                rec["tile"] = "x".join(str(v) for v in ops.gemm_tc_last_plan())
+
+            def library():
+                gu = torch.mm(x, w.t())
+                if gated:
+                    ops.swiglu(gu, y, True)
+            rec["library_us"] = timed(library)
+            out.append(rec)
+    return out

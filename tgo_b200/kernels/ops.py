@@ -231,6 +231,9 @@ def _skinny_ok(x, w) -> bool:
 #   1025..    gemm_tc (tcgen05 + TMEM + TMA)                   3-17 % behind the library per
 #             product at 2048 rows, and it applies the gate in its epilogue
 TC_MIN_ROWS = 1025
+TC_MIN_ROWS_GATED = 1024   # the gate/up product with the gate in its epilogue: from here on it beats
+                           # the library product followed by the gate kernel (149.6 against 154.8 us
+                           # at 1024 rows of the 8B shape, 286 against 319 at 2048)
 USE_TC = True            # False: the library product for every size above 8 rows
 
 
@@ -241,10 +244,10 @@ def product_regime(rows: int) -> int:
     return 0 if rows <= SKINNY_MAX_ROWS else 1 if rows < TC_MIN_ROWS else 2
 
 
-def _tc_ok(x, w) -> bool:
+def _tc_ok(x, w, min_rows: Optional[int] = None) -> bool:
     return USE_TC and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and \
-        x.shape[0] >= TC_MIN_ROWS and w.shape[1] % 8 == 0 and x.is_contiguous() and \
-        w.is_contiguous() and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+        x.shape[0] >= (TC_MIN_ROWS if min_rows is None else min_rows) and w.shape[1] % 8 == 0 and \
+        x.is_contiguous() and w.is_contiguous() and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
 
 
 def _dense(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
@@ -307,7 +310,7 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool) ->
         out = torch.empty((M, f), dtype=torch.bfloat16, device=x.device)
         gemm_skinny(x, w_gate_up, out, gated=True)
         return out
-    if interleaved and _tc_ok(x, w_gate_up) and f % 8 == 0:
+    if interleaved and _tc_ok(x, w_gate_up, min(TC_MIN_ROWS, TC_MIN_ROWS_GATED)) and f % 8 == 0:
         out = torch.empty((M, f), dtype=torch.bfloat16, device=x.device)
         gemm_tc(x, w_gate_up, out, gated=True)
         return out
