@@ -223,13 +223,14 @@ def _skinny_ok(x, w) -> bool:
         x.shape[0] <= SKINNY_MAX_ROWS and w.shape[1] % 8 == 0
 
 
-# Which kernel multiplies, by the number of rows (measured in CUDA graphs on B200):
+# Which kernel multiplies, by the number of rows (measured on B200 with the 8B shapes,
+# `python bench.py --only products`):
 #   1..8      gemm_skinny (weight streaming, mma.sync)        8-16 % faster than the library
-#   9..1024   the library product (cuBLASLt through torch.mm)  the tcgen05 kernel is 3-8 % behind
-#             it per product up to 64 rows (decode orientation), 1.5-2.5 x at 256-512 rows and
-#             7-36 % at 1024: too few tiles for 148 SMs and no balancing of the last round
-#   1025..    gemm_tc (tcgen05 + TMEM + TMA)                   3-17 % behind the library per
-#             product at 2048 rows, and it applies the gate in its epilogue
+#   9..1024   the library product (cuBLASLt through torch.mm)  the tcgen05 kernel is behind it on
+#             q/k/v, o and down here (at 1024 rows 43 / 32 / 101 us against 37 / 26 / 75: too few
+#             tiles for 148 SMs)
+#   1025..    gemm_tc (tcgen05 + TMEM + TMA)                   at 2048 rows q/k/v 81 us (library 71),
+#             o 48 (49), down 145 (144), gate/up with the gate 286 (library and gate kernel 319)
 TC_MIN_ROWS = 1025
 TC_MIN_ROWS_GATED = 1024   # the gate/up product with the gate in its epilogue: from here on it beats
                            # the library product followed by the gate kernel (149.6 against 154.8 us
