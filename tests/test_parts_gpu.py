@@ -450,3 +450,26 @@ def test_layer_run_twice_and_borrowed_cache_on_the_gpu(tmp_path, dtype):
                          tiny.repeated_layers_reference(pc, pw, toks, plain.round_bfloat16))
     tiny.note(f"run_twice/{dtype}", float(np.abs(got - want).max()), tol)
     assert np.abs(got - want).max() <= tol
+
+
+def test_toy_model_through_the_bench_command(toy_registered, tmp_path):
+    """`tgo bench` on the toy architecture: its foreign parts count no flops and read no cache
+    by their own account, and the measurement still runs and adds up what the package's parts
+    report (nothing in the measuring code knows a mixer's or a feed-forward's fields)."""
+    import io
+    import json
+
+    from tgo_b200 import cli
+    raw = dict(architectures=["ToyForTests"], width=48, vocab=90, inner=80, eps=1e-5, decay=0.75,
+               mixer="test_decay", experts=3)
+    d = tiny.make_model_dir(tmp_path / "toy", raw, seed=2, sigma=0.15)
+    out, err, rec = io.StringIO(), io.StringIO(), tmp_path / "rec.json"
+    rc = cli.main(["bench", "--tokens", "6", "--prompt-tokens", "12", "--warmup", "2", "--context", "64",
+                   "--batch", "1,3", "--page-size", "8", "--json", str(rec), d], out=out, err=err)
+    assert rc == 0, err.getvalue()
+    got = json.loads(rec.read_text())
+    assert got["decode"]["tokens_per_s"] > 0 and set(got["decode_by_batch"]) == {"1", "3"}
+    # layer 1 of the toy is the package's attention and feed-forward: their flops are counted
+    attention = 2 * 12 * 48 * (64 + 64) + 2 * 12 * 64 * 48 + 4 * 64 * (12 * 13 // 2)
+    feed_forward = 2 * 12 * 48 * 3 * 80
+    assert got["prefill"]["flops"] == attention + feed_forward + 2 * 48 * 90
