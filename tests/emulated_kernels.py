@@ -136,13 +136,21 @@ def argmax(logits, out):
         out[r] = plain.argmax_lowest(logits[r].numpy())
 
 
-def sample(logits, temperature, top_k, top_p, draws, out):
+def sample(logits, temperature, top_k, top_p, draws, out, report=None, logprob=None,
+           top_ids=None, top_logprobs=None):
     import plain_qwen3 as plain
     for r in range(logits.shape[0]):
         ids, w, total = plain.policy_distribution(
             logits[r].numpy(), temperature=float(temperature[r]), top_k=int(top_k[r]),
             top_p=float(top_p[r]))
         out[r] = plain.walk(ids, w, total, float(draws[r]))
+        if report is not None and int(report[r]) >= 0:
+            lp, top = plain.token_logprobs(ids, w, total, int(out[r]), int(report[r]),
+                                           logits.shape[1])
+            logprob[r] = lp
+            for j, (i, v) in enumerate(top):
+                top_ids[r, j] = i
+                top_logprobs[r, j] = v
 
 
 def logits_adjust(row, bias_ids, bias, ids, counts, repetition, presence, frequency):

@@ -293,11 +293,15 @@ def penalize(logits, history, rep=1.0, presence=0.0, frequency=0.0, window=0):
 
 
 def policy_distribution(logits, history=(), temperature=0.0, top_k=0, top_p=0.0,
-                        rep=1.0, presence=0.0, frequency=0.0, window=0, bias=None):
+                        rep=1.0, presence=0.0, frequency=0.0, window=0, bias=None,
+                        exact_totals=False):
     """(ids ascending, float32 weights, float32 total) the draw is taken against:
     bias -> penalties -> (T == 0: argmax) -> /T -> top-k on the weights by
     (value, lower id) -> top-p prefix that reaches p of the total -> ascending ids
-    (sample/stages.go:74-146, 216-241, 251-324)."""
+    (sample/stages.go:74-146, 216-241, 251-324). The totals are single ascending float32
+    sums as there; with exact_totals they are float64 sums rounded once, for comparing an
+    implementation that sums in another order (over 150k terms the single float32 sum is
+    itself 1e-4 off, enough to move the nucleus's edge by a token)."""
     logits = np.array(logits, dtype=np.float32)
     for i, b in (bias or {}).items():
         logits[i] += np.float32(b)
@@ -307,22 +311,19 @@ def policy_distribution(logits, history=(), temperature=0.0, top_k=0, top_p=0.0,
     logits = logits / np.float32(temperature)
     m = logits[argmax_lowest(logits)]
     allw = np.exp((logits - m).astype(np.float64)).astype(np.float32)
-    if top_k <= 0 and top_p <= 0:
+    def sum32(xs):
+        if exact_totals:
+            return np.float32(np.sum(np.asarray(xs, np.float64)))
         total = np.float32(0)
-        for x in allw:
+        for x in xs:
             total = np.float32(total + x)
-        return list(range(len(allw))), allw, total
+        return total
+    if top_k <= 0 and top_p <= 0:
+        return list(range(len(allw))), allw, sum32(allw)
     n = min(top_k if top_k > 0 else 128, len(allw))
     order = sorted(range(len(allw)), key=lambda i: (-allw[i], i))[:n]
     wts = [allw[i] for i in order]
-    if top_k > 0:
-        total = np.float32(0)
-        for x in wts:
-            total = np.float32(total + x)
-    else:
-        total = np.float32(0)
-        for x in allw:
-            total = np.float32(total + x)
+    total = sum32(wts) if top_k > 0 else sum32(allw)
     if top_p > 0:
         target = np.float32(total * np.float32(top_p))
         acc, cnt = np.float32(0), 0
@@ -346,6 +347,27 @@ def walk(ids, weights, total, u):
             return i
         last = i
     return last
+
+
+def token_logprobs(ids, weights, total, token, n_top, vocab):
+    """(ln p(token), [(id, ln p)] for the n_top most likely tokens) of the distribution
+    policy_distribution returned: a kept token's share is its float32 weight over the
+    float32 total, every other token has probability zero and so -inf; the alternatives
+    descend by (probability, lower id), so once the kept tokens are used up the lowest
+    unkept ids follow (decode.go:263-318, sample/sample.go:155-176)."""
+    share = {i: np.float32(np.float32(x) / np.float32(total)) for i, x in zip(ids, weights)}
+
+    def ln(i):
+        q = float(share.get(i, 0.0))
+        return float(np.log(q)) if q > 0 else -np.inf
+    n = min(n_top, vocab)
+    order = sorted(share, key=lambda i: (-share[i], i))[:n]
+    i = 0
+    while len(order) < n:
+        if i not in share:
+            order.append(i)
+        i += 1
+    return ln(token), [(i, ln(i)) for i in order]
 
 
 def greedy_generate(cfg, w, prompt, n_new):

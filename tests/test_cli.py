@@ -133,10 +133,13 @@ def test_policy_refusals_and_draw_stream():
     for bad in (Policy(temperature=float("nan")), Policy(top_k=129), Policy(top_p=1.5),
                 Policy(repetition_penalty=-1), Policy(penalty_window=-2),
                 Policy(logit_bias={10: 1.0}), Policy(logit_bias={1: float("inf")}),
-                Policy(presence_penalty=float("nan")), Policy(max_tokens=-1)):
+                Policy(presence_penalty=float("nan")), Policy(max_tokens=-1),
+                Policy(top_logprobs=3), Policy(logprobs=True, top_logprobs=129),
+                Policy(logprobs=True, top_logprobs=-1)):
         with pytest.raises(ValueError):
             bad.check(10)
     Policy(logit_bias={1: float("-inf")}).check(10)        # banning a token is allowed
+    Policy(logprobs=True, top_logprobs=128).check(10)
     a, b = DrawStream(5), DrawStream(5)
     xs = [a.next() for _ in range(100)]
     assert xs == [b.next() for _ in range(100)] and xs != [DrawStream(6).next() for _ in range(100)]

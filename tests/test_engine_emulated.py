@@ -128,6 +128,44 @@ def test_generate_greedy_and_seeded_sampling(emulated, tmp_path):
             seq.append(tok)
 
 
+def test_logprobs_through_generate_and_session(emulated, tmp_path):
+    """Policy.logprobs: one TokenProb per generated token, of the distribution after the
+    policy; the tokens are the same with and without the report (logprobs_test.go:62-183)."""
+    from tgo_b200.sampling.policy import DrawStream, Policy
+    cfg, run = tiny.TINIES["B"]
+    d = tiny.make_model_dir(tmp_path / "b", cfg, seed=7, sigma=0.25)
+    loaded = cpu_model(d, cfg)
+    pc, pw = plain.load_model_dir(d)
+    prompts = list(tiny.random_requests(384, [9, 40], seed=4).values())
+    quiet = Policy(temperature=0.8, top_k=8, seed=7, max_tokens=4)
+    asked = Policy(temperature=0.8, top_k=8, seed=7, max_tokens=4, logprobs=True, top_logprobs=8)
+    out = loaded.generate(prompts, [asked, quiet], slots=2, chunk=16, page_size=8)
+    first, second = loaded.last_requests
+    assert out[0] == loaded.generate(prompts[:1], quiet, slots=1, page_size=8)[0]
+    assert second.logprobs == [] and len(first.logprobs) == 4
+    draws, seq = DrawStream(7), list(prompts[0])
+    for tok, tp in zip(out[0], first.logprobs):
+        logits = plain.forward(pc, pw, seq)[-1].astype(np.float32)
+        ids, w, total = plain.policy_distribution(logits, temperature=0.8, top_k=8)
+        assert tok == plain.walk(ids, w, total, draws.next()) == tp.id
+        lp, top = plain.token_logprobs(ids, w, total, tok, 8, 384)
+        assert abs(tp.logprob - lp) < 1e-5 and np.isfinite(tp.logprob)
+        assert [a.id for a in tp.top] == [i for i, _ in top] and not tp.top[0].top
+        assert abs(sum(np.exp(a.logprob) for a in tp.top) - 1) < 1e-5
+        seq.append(tok)
+    # greedy through a session: ln 1 at the argmax, -inf for every alternative after it
+    s = loaded.new_session(context=64, page_size=8)
+    assert s.logprobs() == []
+    seen = 0
+    for tok in s.complete(prompts[0], Policy(max_tokens=3, logprobs=True, top_logprobs=2)):
+        (tp,) = s.logprobs()
+        assert tp.id == tok and tp.logprob == 0 and tp.top[0].id == tok
+        assert tp.top[1].logprob == -np.inf
+        seen += 1
+    assert seen == 3
+    assert list(s.complete(prompts[0], Policy(max_tokens=2))) and s.logprobs() == []
+
+
 def test_session_and_context_limits(emulated, tmp_path):
     from tgo_b200.engine.session import ContextExhausted
     from tgo_b200.sampling.policy import Policy

@@ -107,6 +107,39 @@ def test_seeded_temperature_sampling_follows_the_plain_walk(lively):
             seq.append(tok)
 
 
+def test_logprobs_of_generated_tokens(lively):
+    """Policy.logprobs through generate and a session on the device: the same tokens with
+    and without the report, each drawn token's share of its kept set against the plain
+    distribution, the alternatives descending and summing to one over the kept set, and
+    ln 1 at temperature 0 (specs/030-logprobs.md section 6 of the reference)."""
+    import tgo_b200
+    from tgo_b200.sampling.policy import Policy
+    d, cfg, run, pc, pw = lively["B"]
+    model = tgo_b200.open(d, dtype="float32")
+    prompts = list(tiny.random_requests(cfg["vocab_size"], [9, 40], seed=9).values())
+    quiet = Policy(temperature=0.8, top_k=8, seed=7, max_tokens=6)
+    asked = Policy(temperature=0.8, top_k=8, seed=7, max_tokens=6, logprobs=True, top_logprobs=8)
+    got = model.generate(prompts, [asked, quiet], slots=2, chunk=16, page_size=8)
+    first, second = model.last_requests
+    assert got[0] == model.generate(prompts[:1], quiet, slots=1, page_size=8)[0]
+    assert second.logprobs == [] and [tp.id for tp in first.logprobs] == got[0]
+    seq = list(prompts[0])
+    for tok, tp in zip(got[0], first.logprobs):
+        logits = plain.forward(pc, pw, seq)[-1].astype(np.float32)
+        ids, w, total = plain.policy_distribution(logits, temperature=0.8, top_k=8)
+        lp, _ = plain.token_logprobs(ids, w, total, tok, 0, cfg["vocab_size"])
+        assert tok in ids and abs(tp.logprob - lp) < 1e-3           # the engine's float32 logits
+        lps = [a.logprob for a in tp.top]
+        assert len(lps) == 8 and lps == sorted(lps, reverse=True) and sorted(a.id for a in tp.top) == ids
+        assert abs(sum(np.exp(v) for v in lps) - 1) < 1e-5
+        seq.append(tok)
+    s = model.new_session(context=64, page_size=8)
+    for tok in s.complete(prompts[1], Policy(max_tokens=3, logprobs=True, top_logprobs=3)):
+        (tp,) = s.logprobs()
+        assert (tp.id, tp.logprob, tp.top[0].id) == (tok, 0.0, tok)
+        assert [a.logprob for a in tp.top[1:]] == [-np.inf, -np.inf]
+
+
 def test_scheduler_entry_points(lively):
     """admit / step / feed / finish by hand, as the reference's callers use them."""
     import tgo_b200

@@ -455,6 +455,64 @@ def test_sample_matches_plain(V, policy):
         assert lo - slack <= target <= cdf[i] + slack, (r, got, want)
 
 
+@pytest.mark.parametrize("V", [300, 151936])
+@pytest.mark.parametrize("policy", [dict(temperature=0.8), dict(temperature=1.3, top_k=40),
+                                    dict(temperature=0.7, top_p=0.9),
+                                    dict(temperature=1.0, top_k=3, top_p=0.99),
+                                    dict(temperature=0.0)])
+def test_sample_reports_the_distribution_it_drew_from(V, policy):
+    """The report of sample: the drawn token's share of the kept weights and the most likely
+    alternatives, against the plain distribution in float64; rows that ask for nothing stay
+    untouched, and asking changes no draw."""
+    import plain_qwen3 as plain
+    n = 6
+    logits = rnd(n, V, scale=3.0, seed=V + 1)
+    logits[2, 17] = logits[2, 5] = logits[2].max() + 1          # a tie at the top: lower id first
+    draws = [0.0, 0.13, 0.5, 0.77, 0.999, 0.31]
+    wants = [0, 5, 128, -1, 1, 20]
+    args = (logits, torch.full((n,), policy.get("temperature", 0.0), device=DEV),
+            torch.full((n,), policy.get("top_k", 0), dtype=torch.int32, device=DEV),
+            torch.full((n,), policy.get("top_p", 0.0), device=DEV), torch.tensor(draws, device=DEV))
+    quiet = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops().sample(*args, quiet)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    lp = torch.full((n,), 7.0, device=DEV)
+    top_ids = torch.full((n, 128), -1, dtype=torch.int32, device=DEV)
+    top_lp = torch.full((n, 128), 7.0, device=DEV)
+    ops().sample(*args, out, torch.tensor(wants, dtype=torch.int32, device=DEV), lp, top_ids, top_lp)
+    assert out.tolist() == quiet.tolist()
+    host = logits.cpu().numpy()
+    for r, w_ in enumerate(wants):
+        if w_ < 0:
+            assert float(lp[r]) == 7.0 and int(top_ids[r, 0]) == -1
+            continue
+        # the oracle's totals are float64 sums: the plain single ascending float32 sum is
+        # itself 1e-4 off over 150k terms, the device's (per thread, then over the threads in
+        # order) about 1e-6
+        ids, w, total = plain.policy_distribution(host[r], exact_totals=True, **policy)
+        got = int(out[r])
+        want_lp, want_top = plain.token_logprobs(ids, w, total, got, w_, V)
+        assert got in ids and np.isfinite(float(lp[r]))          # a drawn token is a kept one
+        assert abs(float(lp[r]) - want_lp) < 2e-5, (r, float(lp[r]), want_lp)
+        k = min(w_, V)
+        got_ids, got_lp = top_ids[r, :k].tolist(), top_lp[r, :k].tolist()
+        assert int(top_ids[r, k]) == -1 if k < 128 else True
+        assert all(a >= b for a, b in zip(got_lp, got_lp[1:])), r
+        for j, ((i, v), gi, gv) in enumerate(zip(want_top, got_ids, got_lp)):
+            if v == -np.inf:
+                assert gv == -np.inf and gi == i, (r, j)
+            else:
+                assert abs(gv - v) < 2e-5, (r, j, gv, v)
+                # equal ids, but for neighbours whose float32 weights are within rounding
+                assert gi == i or abs(host[r][gi] - host[r][i]) < 1e-5 * abs(host[r][i]), (r, j)
+        if r == 2 and w_ >= 2 and policy.get("temperature", 0.0) > 0:
+            assert got_ids[:2] == [5, 17]
+        if policy.get("top_k", 0) and k >= policy["top_k"]:
+            kept = min(policy["top_k"], len(ids))
+            assert abs(sum(math.exp(v) for v in got_lp[:kept]) - 1) < 1e-4
+            assert all(v == -np.inf for v in got_lp[kept:])
+
+
 def test_logits_adjust_matches_plain():
     import plain_qwen3 as plain
     V = 500

@@ -103,6 +103,26 @@ def test_sampling_order_and_ties():
     assert ids == [1]                      # penalties come before the greedy branch
 
 
+def test_token_logprobs_describe_the_distribution_drawn_from():
+    """The rows of the reference's table of logprob tests that need no device
+    (specs/030-logprobs.md section 6, logprobs_test.go:22-143)."""
+    logits = np.array([2.0, 1.0, 0.5, -1.0, 1.0], dtype=np.float32)
+    ids, w, total = plain.policy_distribution(logits, temperature=0.8, top_k=3)
+    lp, top = plain.token_logprobs(ids, w, total, 1, 5, 5)
+    e = np.exp((logits[[0, 1, 4]].astype(np.float64) - 2.0) / 0.8)
+    assert abs(lp - math.log(e[1] / e.sum())) < 1e-6             # its share of the kept set
+    assert [i for i, _ in top] == [0, 1, 4, 2, 3]                # ties and unkept: lower id first
+    assert abs(sum(math.exp(v) for _, v in top[:3]) - 1) < 1e-6 and top[3][1] == -np.inf
+    assert plain.token_logprobs(ids, w, total, 3, 0, 5) == (-np.inf, [])
+    ids, w, total = plain.policy_distribution(logits, temperature=0.0)
+    lp, top = plain.token_logprobs(ids, w, total, 0, 3, 5)
+    assert lp == 0 and top == [(0, 0.0), (1, -np.inf), (2, -np.inf)]     # greedy: one at the argmax
+    ids, w, total = plain.policy_distribution(logits, temperature=1.0)
+    lp, top = plain.token_logprobs(ids, w, total, 3, 9, 5)
+    z = np.exp(logits.astype(np.float64) - 2.0)
+    assert abs(lp - math.log(z[3] / z.sum())) < 1e-6 and len(top) == 5
+
+
 def test_tiny_forward_is_causal_and_tied(tmp_path):
     import tiny
     cfg, run = tiny.TINIES["A"]

@@ -119,7 +119,9 @@ class LoadedModel:
                  reserve: Optional[int] = None):
         """Run every prompt (lists of token ids) to completion with continuous batching;
         returns the generated ids per prompt, in order. `policy` is one Policy for all or
-        one per prompt; its max_tokens must be positive."""
+        one per prompt; its max_tokens must be positive. The requests stay in
+        `last_requests`; a policy with logprobs finds a TokenProb per generated token in its
+        request's `.logprobs`."""
         from .engine.scheduler import Request, Runner
         from .sampling.policy import Policy
         from .sampling.sampler import sample_rows
@@ -146,6 +148,7 @@ class LoadedModel:
             runner.submit(r)
         runner.run()
         self.last_runner = runner
+        self.last_requests = requests        # each with .logprobs, for policies that ask
         return [r.output for r in requests]
 
 

@@ -208,12 +208,40 @@ __device__ void block_prefix_i(int mine, int* part, int* seg, int* total) {
     __syncthreads();
 }
 
+// Entries have..want-1 of a row's alternatives: the lowest ids that are not among
+// listed[0..n_listed), each with -inf. These are tokens the policy gave no chance; among
+// equal shares the lower id comes first (decode.go:293-318). Ids below 2 * SM_MAXC suffice,
+// since at most SM_MAXC are listed and at most SM_MAXC are wanted. Every thread calls it.
+__device__ void fill_masked(int have, int want, const int* listed, int n_listed, int V,
+                            int* ipart, int* iseg, int* itotal,
+                            int* __restrict__ ids_out, float* __restrict__ lp_out) {
+    const int t = threadIdx.x;
+    int open_id = 0;
+    if (t < 2 * SM_MAXC && t < V) {
+        open_id = 1;
+        for (int j = 0; j < n_listed; ++j)
+            if (listed[j] == t) { open_id = 0; break; }
+    }
+    block_prefix_i(open_id, ipart, iseg, itotal);
+    if (open_id) {
+        const int at = have + ipart[t];
+        if (at < want) { ids_out[at] = t; lp_out[at] = -INFINITY; }
+    }
+}
+
 // ------------------------------------------------------------------------- sampler
+// With lp_n given, a row r with lp_n[r] >= 0 also reports the distribution it was drawn
+// from, after every stage of the policy (decode.go:263-318, sample/sample.go:155-176):
+// lp_out[r] = ln of the drawn token's share of the kept weights, and the lp_n[r] (at most
+// top_stride) most likely tokens, descending by (share, lower id), in top_ids / top_lp;
+// a token outside the kept set has -inf, and at temperature 0 every token but the argmax.
+// The draw is the same with and without the report.
 __global__ void __launch_bounds__(SM_THREADS)
 sample_kernel(const float* __restrict__ logits, long long stride, int V,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ draws,
-              int* __restrict__ out) {
+              int* __restrict__ out, const int* __restrict__ lp_n, float* __restrict__ lp_out,
+              int* __restrict__ top_ids, float* __restrict__ top_lp, int top_stride) {
     __shared__ Best bscratch[33];
     __shared__ float part[SM_THREADS];
     __shared__ float seg[32];
@@ -227,14 +255,29 @@ sample_kernel(const float* __restrict__ logits, long long stride, int V,
     __shared__ float cw[SM_MAXC], sw[SM_MAXC];
     __shared__ int cid[SM_MAXC], sid[SM_MAXC];
     __shared__ int n_cand, n_kept;
+    __shared__ int single_s;
 
     const int r = blockIdx.x, t = threadIdx.x;
     const float* row = logits + (size_t)r * stride;
     const float T = temperature[r];
     const float u = draws[r];
+    int want = lp_n ? lp_n[r] : -1;           // < 0: no report for this row
+    if (want > top_stride) want = top_stride;
+    if (want > V) want = V;
+    int* const alt_ids = top_ids ? top_ids + (size_t)r * top_stride : nullptr;
+    float* const alt_lp = top_lp ? top_lp + (size_t)r * top_stride : nullptr;
     if (T == 0.f) {
         const Best b = block_argmax(row, V, 1.f, bscratch);
-        if (t == 0) out[r] = b.i;
+        if (t == 0) {
+            out[r] = b.i;
+            if (want >= 0) lp_out[r] = 0.f;
+            if (want > 0) { alt_ids[0] = b.i; alt_lp[0] = 0.f; }
+            single_s = b.i;
+        }
+        if (want > 1) {
+            __syncthreads();
+            fill_masked(1, want, &single_s, 1, V, ipart, iseg, &itotal_s, alt_ids, alt_lp);
+        }
         return;
     }
     const float m = block_argmax(row, V, T, bscratch).v;     // max of logits / T
@@ -250,7 +293,8 @@ sample_kernel(const float* __restrict__ logits, long long stride, int V,
     block_prefix_f(mine, part, seg, &total_s);
     const float total_all = total_s;
 
-    if (k_req <= 0 && p_req <= 0.f) {
+    const bool all_kept = k_req <= 0 && p_req <= 0.f;
+    if (all_kept) {
         if (t == 0) result_s = V - 1;
         __syncthreads();
         const float target = u * total_all;
@@ -266,12 +310,17 @@ sample_kernel(const float* __restrict__ logits, long long stride, int V,
             result_s = pick;
         }
         __syncthreads();
-        if (t == 0) out[r] = result_s;
-        return;
+        if (t == 0) {
+            out[r] = result_s;
+            if (want >= 0) lp_out[r] = logf(expf(row[result_s] / T - m) / total_all);
+        }
+        if (want <= 0) return;
+        // the alternatives are the `want` largest of the whole vocabulary: selected below
     }
 
     // ---- the k largest weights by (weight, lower id): radix select on the float bits
-    const int k = k_req > 0 ? (k_req < V ? k_req : V) : (SM_MAXC < V ? SM_MAXC : V);
+    const int k = all_kept ? want
+                : k_req > 0 ? (k_req < V ? k_req : V) : (SM_MAXC < V ? SM_MAXC : V);
     if (t == 0) { sel_prefix = 0u; sel_remaining = (unsigned)k; }
     for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
@@ -334,6 +383,10 @@ sample_kernel(const float* __restrict__ logits, long long stride, int V,
         sid[rank] = cid[t];
     }
     __syncthreads();
+    if (all_kept) {
+        if (t < nc && t < want) { alt_ids[t] = sid[t]; alt_lp[t] = logf(sw[t] / total_all); }
+        return;
+    }
     if (t == 0) {
         float total;
         if (k_req > 0) {
@@ -355,6 +408,11 @@ sample_kernel(const float* __restrict__ logits, long long stride, int V,
     }
     __syncthreads();
     const int kept = n_kept;
+    if (want > 0) {
+        if (t < kept && t < want) { alt_ids[t] = sid[t]; alt_lp[t] = logf(sw[t] / total_s); }
+        if (want > kept)
+            fill_masked(kept, want, sid, kept, V, ipart, iseg, &itotal_s, alt_ids, alt_lp);
+    }
     // ascending by id
     if (t < kept) {
         int rank = 0;
@@ -368,20 +426,28 @@ sample_kernel(const float* __restrict__ logits, long long stride, int V,
         const float target = u * total_s;
         float acc = 0.f;
         int pick = kept > 0 ? cid[kept - 1] : 0;
+        float w_pick = kept > 0 ? cw[kept - 1] : 0.f;
         for (int j = 0; j < kept; ++j) {
             acc += cw[j];
-            if (acc > target) { pick = cid[j]; break; }
+            if (acc > target) { pick = cid[j]; w_pick = cw[j]; break; }
         }
         out[r] = pick;
+        if (want >= 0) lp_out[r] = logf(w_pick / total_s);
     }
 }
 
+// lp_n null: no row reports. Else lp_out has n floats and, if top_stride > 0, top_ids and
+// top_lp have n * top_stride entries (top_stride at most 128).
 TGO_API int tgo_sample(const float* logits, long long stride, int n, int V,
                        const float* temperature, const int* top_k, const float* top_p,
-                       const float* draws, int* out, cudaStream_t stream) {
+                       const float* draws, int* out, const int* lp_n, float* lp_out,
+                       int* top_ids, float* top_lp, int top_stride, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (V <= 0) return TGO_E_BAD_ARG;
+    if (lp_n && (!lp_out || top_stride < 0 || top_stride > SM_MAXC ||
+                 (top_stride > 0 && (!top_ids || !top_lp)))) return TGO_E_BAD_ARG;
     sample_kernel<<<n, SM_THREADS, 0, stream>>>(logits, stride, V, temperature, top_k, top_p,
-                                                draws, out);
+                                                draws, out, lp_n, lp_out, top_ids, top_lp,
+                                                lp_n ? top_stride : 0);
     return launch_status();
 }

@@ -276,6 +276,7 @@ class Request:
     finish_reason: str = ""
     evictions: int = 0
     sampler: object = None
+    logprobs: list = field(default_factory=list)    # TokenProb per sampled token, if asked
 
 
 class Runner:
@@ -345,6 +346,7 @@ class Runner:
                 tok = int(tok)
                 if tok in self.stop_ids:
                     req.finished, req.finish_reason = True, "stop"
+                    del req.logprobs[len(req.output):]       # parallel to the output
                 else:
                     req.output.append(tok)
                     if req.policy.max_tokens > 0 and len(req.output) >= req.policy.max_tokens:

@@ -27,6 +27,13 @@ class Session:
         self.engine = Engine(loaded.model, page_size=page_size, max_tokens=context, num_slots=1)
         self._n = 0
         self.usage = {"prompt_tokens": 0, "completion_tokens": 0}
+        self._last_probs: list = []
+
+    def logprobs(self) -> list:
+        """The tokens the last step of `complete` produced, as TokenProb (normally one);
+        empty unless the policy asks for logprobs (the reference's Stream.LogProbs,
+        decode.go:328-345). Valid until the next token is drawn."""
+        return self._last_probs
 
     def complete(self, prompt: Sequence[int], policy: Optional[Policy] = None) -> Iterator[int]:
         """Yield generated token ids until a stop id, the token budget or the context's end."""
@@ -56,8 +63,12 @@ class Session:
                 last = o + len(part) == len(prompt)
                 logits = eng.step([StepEntry(rid, part, [len(part) - 1] if last else [])])
             for _ in range(budget):
-                tok = int(sample_batch(logits, [policy], [draws.next()], [history]).item())
+                reports: list = []
+                tok = int(sample_batch(logits, [policy], [draws.next()], [history],
+                                       reports).item())
+                self._last_probs = [r for r in reports if r is not None]
                 if tok in self.stop_ids:
+                    self._last_probs = []
                     return
                 history.append(tok)
                 self.usage["completion_tokens"] += 1

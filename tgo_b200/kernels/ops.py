@@ -471,20 +471,39 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
-           top_p: torch.Tensor, draws: torch.Tensor, out: torch.Tensor) -> None:
+           top_p: torch.Tensor, draws: torch.Tensor, out: torch.Tensor,
+           report: Optional[torch.Tensor] = None, logprob: Optional[torch.Tensor] = None,
+           top_ids: Optional[torch.Tensor] = None, top_logprobs: Optional[torch.Tensor] = None
+           ) -> None:
     """Per row: temperature 0 -> argmax; else the softmax of logits / temperature, cut to the
     top_k largest (0: no cut) and to the top_p nucleus (0: no cut), walked in ascending id
-    order to draws[r] * total."""
-    _need_cuda(logits, temperature, top_k, top_p, draws, out)
+    order to draws[r] * total.
+
+    With `report` (int32 per row; negative: nothing for this row), a row also writes ln of
+    the drawn token's share of the distribution it was drawn from into logprob[r], and its
+    report[r] most likely tokens, descending, into top_ids[r] and top_logprobs[r] (both
+    [rows, at most 128]; a token the policy left no chance has -inf)."""
+    _need_cuda(logits, temperature, top_k, top_p, draws, out, report, logprob, top_ids,
+               top_logprobs)
     n, V = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32
     assert draws.dtype == torch.float32 and top_k.dtype == torch.int32 and out.dtype == torch.int32
     assert temperature.numel() == top_k.numel() == top_p.numel() == draws.numel() == n
+    width = 0
+    if report is not None:
+        assert report.dtype == torch.int32 and report.numel() == n
+        assert logprob is not None and logprob.dtype == torch.float32 and logprob.numel() == n
+        if top_ids is not None:
+            width = top_ids.shape[1]
+            assert top_ids.dtype == torch.int32 and top_logprobs.dtype == torch.float32
+            assert top_ids.shape == top_logprobs.shape == (n, width)
+            assert top_ids.is_contiguous() and top_logprobs.is_contiguous()
     lib = load_library("sampling")
     _check(lib.tgo_sample(_ptr(logits), c_ll(logits.stride(0)), c_int(n), c_int(V),
                           _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(draws), _ptr(out),
-                          _stream()), "sample")
+                          _ptr(report), _ptr(logprob), _ptr(top_ids), _ptr(top_logprobs),
+                          c_int(width), _stream()), "sample")
 
 
 def logits_adjust(row: torch.Tensor, bias_ids: Optional[torch.Tensor],

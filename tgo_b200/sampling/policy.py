@@ -11,7 +11,7 @@ from __future__ import annotations
 import math
 import struct
 from dataclasses import dataclass, field
-from typing import Dict
+from typing import Dict, List
 
 TOP_MAX = 128                 # most candidates either truncation keeps (sample/sample.go:47)
 MAX_DRAW = 0.99999994         # the largest float32 below one (sample/sample.go:194)
@@ -29,6 +29,8 @@ class Policy:
     logit_bias: Dict[int, float] = field(default_factory=dict)
     seed: int = 0
     max_tokens: int = 0               # 0: until the context is full
+    logprobs: bool = False            # report each drawn token's log probability
+    top_logprobs: int = 0             # and this many alternatives a step (needs logprobs)
 
     def check(self, vocab: int) -> None:
         t = self.temperature
@@ -51,6 +53,12 @@ class Policy:
             raise ValueError(f"policy: penalty window {self.penalty_window} is negative")
         if self.max_tokens < 0:
             raise ValueError(f"policy: max_tokens {self.max_tokens} is negative")
+        n = self.top_logprobs
+        if n < 0 or n > TOP_MAX:
+            raise ValueError(f"policy: top_logprobs is {n}; zero for none or 1..{TOP_MAX}")
+        if n > 0 and not self.logprobs:
+            raise ValueError("policy: top_logprobs is set and logprobs is not; the alternatives "
+                             "come with the drawn token's own number")
         for i, b in self.logit_bias.items():
             if not (0 <= int(i) < vocab):
                 raise ValueError(f"policy: logit bias id {i} is outside the vocabulary of {vocab}")
@@ -65,6 +73,18 @@ class Policy:
     def edits_logits(self) -> bool:
         return bool(self.logit_bias) or self.repetition_penalty not in (0.0, 1.0) or \
             self.presence_penalty != 0 or self.frequency_penalty != 0
+
+
+@dataclass
+class TokenProb:
+    """One token and what the distribution it was drawn from gave it, after every stage of
+    the policy (stream.go:57-88): `logprob` is ln of its share of the kept weights, -inf for a
+    token the policy left no chance (outside the top-k or the nucleus, or any token but the
+    argmax at temperature 0). `top` holds the policy's top_logprobs most likely tokens of
+    the same distribution, descending, ties to the lower id; it is empty inside those."""
+    id: int
+    logprob: float
+    top: List["TokenProb"] = field(default_factory=list)
 
 
 _MASK = (1 << 64) - 1
