@@ -534,8 +534,14 @@ def test_logits_adjust_matches_plain():
 # ------------------------------------------------------------- weight-streaming GEMM
 
 
+# at most 8 rows, 256 or more rows of W and a K that is a multiple of 2048 go to the persistent
+# form (one CTA an SM, x staged in shared memory) unless x is too large for that (8 x 12288);
+# the rest to the form of one CTA a 16-row tile
 @pytest.mark.parametrize("M,N,K", [(1, 16, 64), (3, 50, 96), (8, 257, 224), (9, 64, 4096),
-                                   (16, 100, 1000), (17, 33, 72), (40, 48, 512), (64, 130, 264)])
+                                   (16, 100, 1000), (17, 33, 72), (40, 48, 512), (64, 130, 264),
+                                   (1, 256, 2048), (5, 4099, 2048), (8, 6144, 520), (7, 300, 72),
+                                   (8, 2500, 4096), (2, 1000, 12288), (8, 304, 12288),
+                                   (3, 777, 6144)])
 def test_gemm_skinny(M, N, K):
     x = rnd(M, K, dtype=torch.bfloat16, seed=1)
     w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
@@ -549,12 +555,16 @@ def test_gemm_skinny(M, N, K):
     h2 = h.clone()
     ops().gemm_skinny(x, w, h2, accumulate=True)
     assert torch.allclose(h2, h + want, rtol=1e-4, atol=1e-3)
-    # a row's result does not depend on the rows beside it
+    # a row's result does not depend on the rows beside it (bit for bit while the same form of
+    # the kernel takes both: the two forms cut K differently)
     out_all = torch.empty(M, N, dtype=torch.float32, device=DEV)
     ops().gemm_skinny(x, w, out_all)
     out_one = torch.empty(1, N, dtype=torch.float32, device=DEV)
     ops().gemm_skinny(x[M - 1:M].contiguous(), w, out_one)
-    assert torch.equal(out_one[0], out_all[M - 1])
+    if ops().folds_norm(M, N, K) == ops().folds_norm(1, N, K):
+        assert torch.equal(out_one[0], out_all[M - 1])
+    else:
+        assert torch.allclose(out_one[0], out_all[M - 1], rtol=1e-4, atol=1e-3)
 
 
 def interleave8(gate, up):
@@ -562,7 +572,8 @@ def interleave8(gate, up):
     return torch.stack([gate.view(f // 8, 8, d), up.view(f // 8, 8, d)], dim=1).reshape(2 * f, d)
 
 
-@pytest.mark.parametrize("M,f,K", [(2, 224, 64), (8, 128, 96), (16, 1000, 264)])
+@pytest.mark.parametrize("M,f,K", [(2, 224, 64), (8, 128, 96), (16, 1000, 264), (8, 1000, 2048),
+                                   (3, 688, 4096)])
 def test_gemm_skinny_gated_output(M, f, K):
     """A gate/up matrix with rows interleaved in eights: the kernel applies the gate itself."""
     x = rnd(M, K, dtype=torch.bfloat16, seed=4)
@@ -583,6 +594,49 @@ def test_gemm_skinny_gated_output(M, f, K):
     # and gated_linear picks either
     got = ops().gated_linear(x, w, True)
     assert torch.allclose(got.float(), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 2048), (5, 4099, 2048), (8, 6144, 4096), (8, 1008, 4096),
+                                   (3, 304, 8192), (2, 320, 6144)])
+def test_gemm_skinny_with_the_norm_folded_in(M, N, K):
+    """RMSNorm of the float32 stream made while the product stages its rows: against the
+    norm kernel followed by the product, and against float64."""
+    o = ops()
+    assert o.folds_norm(M, N, K) and not o.folds_norm(8, 4096, 12288) and not o.folds_norm(2, 64, 2048)
+    assert not o.folds_norm(8, 5120, 5120) and o.folds_norm(4, 4096, 12288)
+    h = rnd(M, K, scale=3.0, seed=11)
+    h[M - 1, 5] = 400.0                                        # a row with its own scale
+    gain = 1 + rnd(K, scale=0.2, seed=12)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=13)
+    lazy = o.NormedRows(h, gain, 1e-5, torch.bfloat16)
+    x = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
+    o.add_rmsnorm(h, None, gain, 1e-5, x)
+    hd = h.double()
+    exact = (hd * torch.rsqrt((hd * hd).mean(1, keepdim=True) + 1e-5) * gain.double())
+    want = exact.to(torch.bfloat16).double() @ w.double().t()
+    for dt in (torch.bfloat16, torch.float32):
+        sep = torch.empty(M, N, dtype=dt, device=DEV)
+        o.gemm_skinny(x, w, sep)
+        got = torch.empty(M, N, dtype=dt, device=DEV)
+        o.gemm_skinny_normed(lazy, w, got)
+        # the two norms add their squares in another order: a row of x may differ by one
+        # bfloat16 step in a few places
+        tol = 2e-2 if dt == torch.bfloat16 else 2e-3
+        assert torch.allclose(got.double(), want, rtol=tol, atol=tol * want.abs().max().item())
+        assert torch.allclose(got.float(), sep.float(), rtol=tol, atol=tol * want.abs().max().item())
+        assert torch.equal(o.linear(lazy, w, dt), got)          # linear folds it the same way
+    assert torch.equal(lazy.rows(), x)                          # and what does not fold asks for the rows
+    # a row's result does not depend on the rows beside it
+    one = torch.empty(1, N, dtype=torch.float32, device=DEV)
+    o.gemm_skinny_normed(o.NormedRows(h[M - 1:].contiguous(), gain, 1e-5, torch.bfloat16), w, one)
+    assert torch.equal(one[0], got[M - 1])
+    if N % 16 == 0:
+        gated = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+        o.gemm_skinny_normed(lazy, w, gated, gated=True)
+        sep = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+        o.gemm_skinny(x, w, sep, gated=True)
+        assert torch.allclose(gated.float(), sep.float(), rtol=3e-2, atol=3e-2 * sep.float().abs().max().item())
+        assert torch.equal(o.gated_linear(lazy, w, True), gated)
 
 
 # ------------------------------------------------------------------ tcgen05 product

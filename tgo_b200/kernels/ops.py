@@ -217,6 +217,61 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate:
                                c_int(omode), _stream()), "gemm_skinny", f"(M={M}, N={N}, K={K})")
 
 
+class NormedRows:
+    """RMSNorm(h) * gain for a few rows of the float32 stream, not computed yet: a
+    weight-streaming product that takes it makes the rows while it stages them (one kernel
+    fewer between two products of a decode step); anything else asks for `rows()`. Carries
+    the shape, dtype and device of the rows it stands for."""
+
+    def __init__(self, h: torch.Tensor, gain: torch.Tensor, eps: float, dtype: torch.dtype):
+        self.h, self.gain, self.eps, self.dtype = h, gain, eps, dtype
+        self.shape, self.device = h.shape, h.device
+        self._rows: Optional[torch.Tensor] = None
+
+    def rows(self) -> torch.Tensor:
+        if self._rows is None:
+            self._rows = torch.empty(self.shape, dtype=self.dtype, device=self.device)
+            add_rmsnorm(self.h, None, self.gain, self.eps, self._rows)
+        return self._rows
+
+
+def rows_of(x) -> torch.Tensor:
+    """x itself, or the rows a NormedRows stands for."""
+    return x.rows() if isinstance(x, NormedRows) else x
+
+
+_folds = {}
+
+
+def folds_norm(M: int, N: int, K: int) -> bool:
+    """Whether the weight-streaming product of these sizes can take its rows as NormedRows."""
+    key = (M, N, K)
+    if key not in _folds:
+        _folds[key] = bool(load_library("gemm_skinny").tgo_gemm_skinny_folds_norm(
+            c_int(M), c_int(N), c_int(K)))
+    return _folds[key]
+
+
+def gemm_skinny_normed(x: NormedRows, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+    """gemm_skinny with RMSNorm(x.h) * x.gain as its rows (at most 8), the norm folded into
+    the product: out bfloat16 or float32 [M, N], or, `gated`, silu(gate) * up [M, N / 2]."""
+    _need_cuda(x.h, x.gain, w, out)
+    M, N, K = x.shape[0], w.shape[0], w.shape[1]
+    assert x.h.dtype == torch.float32 and x.h.is_contiguous() and x.h.shape[1] == K
+    assert w.dtype == torch.bfloat16 and w.is_contiguous() and out.is_contiguous()
+    assert x.gain.dtype == torch.float32 and x.gain.numel() == K
+    if gated:
+        assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2) and N % 16 == 0
+        omode = 3
+    else:
+        assert out.dtype in (torch.bfloat16, torch.float32) and out.shape == (M, N)
+        omode = 0 if out.dtype == torch.bfloat16 else 1
+    lib = load_library("gemm_skinny")
+    _check(lib.tgo_gemm_skinny_normed(_ptr(x.h), _ptr(x.gain), c_float(x.eps), _ptr(w), _ptr(out),
+                                      c_int(M), c_int(N), c_int(K), c_int(omode), _stream()),
+           "gemm_skinny_normed", f"(M={M}, N={N}, K={K})")
+
+
 def _skinny_ok(x, w) -> bool:
     dt = x.dtype
     return dt == torch.bfloat16 and w.dtype == torch.bfloat16 and \
@@ -281,6 +336,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     keeps the accumulator's width (the logits).
     """
     out_dtype = out_dtype or x.dtype
+    if isinstance(x, NormedRows):
+        M, N = x.shape[0], w.shape[0]
+        if residual is None and _skinny_ok(x, w) and folds_norm(M, N, w.shape[1]):
+            out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+            gemm_skinny_normed(x, w, out)
+            return out
+        x = x.rows()
     if _skinny_ok(x, w):
         M, N = x.shape[0], w.shape[0]
         if residual is not None:
@@ -307,6 +369,12 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool) ->
     rows then the up rows, or (`interleaved`) eight gate rows and the eight matching up rows
     in turn, which lets the bfloat16 kernels apply the gate in their epilogue."""
     M, f = x.shape[0], w_gate_up.shape[0] // 2
+    if isinstance(x, NormedRows):
+        if interleaved and _skinny_ok(x, w_gate_up) and folds_norm(M, 2 * f, w_gate_up.shape[1]):
+            out = torch.empty((M, f), dtype=torch.bfloat16, device=x.device)
+            gemm_skinny_normed(x, w_gate_up, out, gated=True)
+            return out
+        x = x.rows()
     if interleaved and _skinny_ok(x, w_gate_up):
         out = torch.empty((M, f), dtype=torch.bfloat16, device=x.device)
         gemm_skinny(x, w_gate_up, out, gated=True)

@@ -255,13 +255,15 @@ class GQAAttention(Part):
         return 2.0 * self.Hkv * self.dh * width * reach
 
     # ---- compute
-    def forward(self, x: torch.Tensor, ctx, cache: LayerCache, residual=None):
+    lazy_rows = True        # x may come as ops.NormedRows; its first product folds the norm in
+
+    def forward(self, x, ctx, cache: LayerCache, residual=None):
         """With `residual` (the float32 stream) the result may be added to it, and None is
         then returned; otherwise the result is returned for the caller to add."""
         H, Hkv, dh = self.H, self.Hkv, self.dh
         qw, kw = H * dh, Hkv * dh
         if cache.writable:
-            qkv = ops.linear(x, self.w_qkv)
+            qkv = ops.linear(x, self.w_qkv)           # x may be ops.NormedRows: folded in there
             q, k, v = qkv[:, :qw], qkv[:, qw:qw + kw], qkv[:, qw + kw:]
         else:
             q, k, v = ops.linear(x, self.w_q), None, None

@@ -10,6 +10,9 @@ Interfaces (duck-typed; `Part` only supplies the defaults):
   norm            forward(h, delta, out_dtype, rows=None) -> normed rows
                   h is the float32 residual stream [T, d]; delta, if given, is added
                   to it first (and stays added); rows selects rows instead of all.
+                  A forward that also takes `lazy=False` may, when asked, hand on rows it
+                  has not computed (`ops.NormedRows`: the stream, the gain and eps) for the
+                  consumer's first product to make while it reads them.
   position        `apply(q, k, ctx, num_heads, num_kv_heads, head_dim)` in place; and, if the
                   class sets `fusable = True`, `rotary(ctx)` -> (table [T, rotary_dim] of
                   cosines then sines, or None; rotary_dim), which lets the mixer do a
@@ -19,6 +22,9 @@ Interfaces (duck-typed; `Part` only supplies the defaults):
                   also takes `residual=None` may add its result into that float32 tensor
                   itself and return None (or return the result as usual).
   feed-forward    forward(x, ctx) -> [T, d]; `residual` as for the mixer.
+                  A mixer or feed-forward whose class sets `lazy_rows = True` accepts x as
+                  `ops.NormedRows` (it passes x to `ops.linear` / `ops.gated_linear`, or asks
+                  `ops.rows_of(x)` for the tensor); without it a part always gets a tensor.
   block           forward(h, pending, ctx, cache) -> (h, pending): `pending` is a delta
                   not yet added to h, so the add can be fused into the next norm.
 

@@ -27,6 +27,12 @@ class PreNormResidual(Part):
         # a part whose forward takes `residual` may add its result to the stream itself
         self._mixer_adds = "residual" in inspect.signature(self.mixer.forward).parameters
         self._ffn_adds = "residual" in inspect.signature(self.feed_forward.forward).parameters
+        # a part with `lazy_rows` set takes its input as ops.NormedRows (a norm it may fold
+        # into its first product), if the norm knows how to hand that on
+        self._lazy1 = getattr(self.mixer, "lazy_rows", False) and \
+            "lazy" in inspect.signature(self.norm1.forward).parameters
+        self._lazy2 = getattr(self.feed_forward, "lazy_rows", False) and \
+            "lazy" in inspect.signature(self.norm2.forward).parameters
 
     def parts(self):
         return [self.norm1, self.mixer, self.norm2, self.feed_forward]
@@ -59,12 +65,14 @@ class PreNormResidual(Part):
         return offered(self.mixer, "cache_bytes_read")(context_len, width)
 
     def forward(self, h, pending, ctx, cache):
-        n = self.norm1.forward(h, pending, ctx.act_dtype)
+        n = self.norm1.forward(h, pending, ctx.act_dtype, lazy=True) if self._lazy1 else \
+            self.norm1.forward(h, pending, ctx.act_dtype)
         if self._mixer_adds:
             a = self.mixer.forward(n, ctx, cache, residual=h)
         else:
             a = self.mixer.forward(n, ctx, cache)
-        n = self.norm2.forward(h, a, ctx.act_dtype)
+        n = self.norm2.forward(h, a, ctx.act_dtype, lazy=True) if self._lazy2 else \
+            self.norm2.forward(h, a, ctx.act_dtype)
         if self._ffn_adds:
             return h, self.feed_forward.forward(n, ctx, residual=h)
         return h, self.feed_forward.forward(n, ctx)

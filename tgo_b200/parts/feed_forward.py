@@ -60,7 +60,9 @@ class SwiGLU(Part):
     def flops(self, extents, first_positions, writes_cache: bool = True) -> float:
         return 2.0 * sum(extents) * self.hidden * 3 * self.inter
 
-    def forward(self, x: torch.Tensor, ctx, residual=None):
+    lazy_rows = True        # x may come as ops.NormedRows; the gate/up product folds the norm in
+
+    def forward(self, x, ctx, residual=None):
         """With `residual` (the float32 stream) the result may be added to it, and None is
         then returned; otherwise the result is returned for the caller to add."""
         act = ops.gated_linear(x, self.w_gate_up, self.interleaved)
