@@ -305,6 +305,57 @@ def test_attention_decode_split(H, Hkv, dh, ps, window):
         assert torch.allclose(out.float().cpu(), want, **tol(torch.bfloat16)), n_splits
 
 
+@pytest.mark.parametrize("H,Hkv,ps", [(32, 8, 16), (3, 3, 32), (16, 2, 8), (16, 1, 64), (12, 2, 16)])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("norm,rotate", [(True, True), (False, True), (True, False)])
+def test_attention_decode_fused_equals_the_two_kernels(H, Hkv, ps, window, norm, rotate):
+    """The decode kernel that norms, rotates and stores the step's own q, k and v itself gives
+    the bits of qk_norm_rope_cache followed by the decode kernel: in the attention's result
+    and in the cache. The requests' own positions lie at the start, the end and the middle of
+    a tile of 64 keys and of a page, and in every split."""
+    dh = 128
+    o = ops()
+    extents, firsts = [1, 1, 1, 1, 1, 1], [0, 63, 64, 700, 255, 130]
+    case = paged_case(extents, firsts, H, Hkv, dh, ps, torch.bfloat16, seed=H + ps)
+    T = len(extents)
+    g = torch.Generator().manual_seed(5)
+    qkv = (torch.randn(T, (H + 2 * Hkv) * dh, generator=g) * 2).to(torch.bfloat16).to(DEV)
+    qw, kw = H * dh, Hkv * dh
+    q_gain = (1 + 0.3 * torch.randn(dh, generator=g)).to(DEV) if norm else None
+    k_gain = (1 + 0.3 * torch.randn(dh, generator=g)).to(DEV) if norm else None
+    rope = None
+    if rotate:
+        inv = torch.tensor([10000.0 ** (-2 * i / dh) for i in range(dh // 2)], dtype=torch.float64, device=DEV)
+        rope = o.rope_table(case["pos"], inv)
+    slots = torch.empty(T, dtype=torch.int32)
+    for t in range(T):
+        pos = firsts[t]
+        slots[t] = int(case["bt"][t, pos // ps]) * ps + pos % ps
+    slots = slots.to(DEV)
+    scale = 1 / math.sqrt(dh)
+    # the two kernels
+    a = qkv.clone()
+    kc1, vc1 = case["kc"].clone(), case["vc"].clone()
+    o.qk_norm_rope_cache(a[:, :qw], a[:, qw:qw + kw], a[:, qw + kw:], H, Hkv, dh, q_gain, k_gain, 1e-6,
+                         rope, dh if rotate else 0, slots, kc1, vc1, ps)
+    for n_splits in (1, 3, 8):
+        want = torch.zeros(T, qw, dtype=torch.bfloat16, device=DEV)
+        o.attention_flash(a[:, :qw], want, H, Hkv, dh, kc1, vc1, ps, case["bt"], case["pos"], case["seq"],
+                          None, None, scale, window, n_splits=n_splits)
+        b = qkv.clone()
+        kc2, vc2 = case["kc"].clone(), case["vc"].clone()
+        assert o.decode_attention_fuses(b[:, :qw], dh, H // Hkv, ps, kc2, vc2, dh if rotate else 0)
+        got = torch.zeros(T, qw, dtype=torch.bfloat16, device=DEV)
+        o.attention_decode_fused(b[:, :qw], b[:, qw:qw + kw], b[:, qw + kw:], got, H, Hkv, dh, q_gain,
+                                 k_gain, 1e-6, rope, slots, kc2, vc2, ps, case["bt"], case["pos"],
+                                 case["seq"], scale, window, n_splits=n_splits)
+        bits = lambda t: t.view(torch.int16)               # unwritten rows of the cache hold NaN
+        assert torch.equal(bits(kc2), bits(kc1)) and torch.equal(bits(vc2), bits(vc1)), n_splits
+        assert torch.equal(bits(got), bits(want)), n_splits
+        assert torch.equal(b, qkv)                         # the raw rows are left as they came
+    assert o.attention_decode_tma_error() == 0
+
+
 @pytest.mark.parametrize("far", [0, 15, 16, 63, 64, 127, 128, 499])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("dh", [64, 128])

@@ -12,6 +12,13 @@
 // not masked in V by the copy as cp.async's zero fill did: the warp that owns such keys
 // writes zeros over its V rows before it multiplies (P is zero there, the cache may hold NaN).
 //
+// Fused form (DtFuse): the kernel also does what a kernel before it did for a decode step: it
+// takes the raw q rows, norms and rotates them into shared memory itself, and the one CTA of a
+// (token, kv head) whose keys include the token's own position norms and rotates the new k,
+// writes it and the new v to their row of the cache, and lays both over that row of the tile
+// that TMA brought (a stale row of the page). The arithmetic is that of
+// qk_norm_rope_cache_dh128_kernel, operation for operation, so both ways give the same bits.
+//
 // Every mbarrier wait has a time limit (about two seconds), after which a flag is set and the
 // CTA runs to its end without waiting again.
 #include <cuda.h>
@@ -69,6 +76,54 @@ __device__ __forceinline__ uint32_t dt_at(int r, int c) {
     return (uint32_t)((c >> 3) * DT_HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4));
 }
 
+struct DtFuse {
+    const bf16* k_new;          // this step's raw k rows [T, k_stride] and v rows, by token
+    long long k_stride;
+    const bf16* v_new;
+    long long v_stride;
+    const float* q_gain;        // per-head RMSNorm gains [128], or null for no norm
+    const float* k_gain;
+    float eps;
+    const float* rope;          // [T, 128]: 64 cosines then 64 sines of each token, or null
+    const int* slots;           // cache row (page * page_size + offset) of each token; < 0: none
+    bf16* k_cache;              // null: not fused, q comes normed and rotated, the cache written
+    bf16* v_cache;
+};
+
+// One head vector of 128 channels by a warp, lane l holding channels 4l .. 4l+3: RMSNorm with
+// `gain` (if given), then the half-split rotation by the token's cosines and sines (if given),
+// the partner channel i +- 64 sitting 16 lanes away. Returns the four values as bfloat16.
+__device__ __forceinline__ uint2 dt_norm_rope(const bf16* __restrict__ vec, const float* __restrict__ gain,
+                                              float eps, const float* __restrict__ cs, int lane) {
+    const uint2 raw = *(const uint2*)(vec + 4 * lane);
+    const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x);
+    const float2 b = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
+    float x[4] = {a.x, a.y, b.x, b.y};
+    if (gain) {
+        float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+        ss = warp_sum(ss);
+        const float scale = rsqrtf(ss / 128.f + eps);
+        const float4 g = *(const float4*)(gain + 4 * lane);
+        x[0] = (x[0] * scale) * g.x; x[1] = (x[1] * scale) * g.y;
+        x[2] = (x[2] * scale) * g.z; x[3] = (x[3] * scale) * g.w;
+    }
+    if (cs) {
+        const int i0 = 4 * (lane & 15);
+        const float4 c = *(const float4*)(cs + i0), sn = *(const float4*)(cs + 64 + i0);
+        const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
+            x[e] = lane < 16 ? x[e] * cc[e] - other * sv[e] : other * sv[e] + x[e] * cc[e];
+        }
+    }
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]), hi = __floats2bfloat162_rn(x[2], x[3]);
+    uint2 out;
+    out.x = *(const uint32_t*)&lo;
+    out.y = *(const uint32_t*)&hi;
+    return out;
+}
+
 template <bool KEYS_ON_M>
 __global__ void __launch_bounds__(DT_THREADS, DT_MIN_BLOCKS)
 flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -78,7 +133,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ positions, const int* __restrict__ seq_ids, int H,
                         int Hkv, float scale_log2, int window, int n_splits,
                         float* __restrict__ part_o, float* __restrict__ part_ml,
-                        const int* __restrict__ tok_list) {
+                        const int* __restrict__ tok_list, const DtFuse fz) {
     constexpr int DH = DT_DH, KS = DH / 16, CH = DH / 8, LDQ = DH + 8;
     extern __shared__ unsigned char dt_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)dt_raw + 1023) & ~(uintptr_t)1023);
@@ -136,15 +191,53 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = tid; i < 16 * CH; i += DT_THREADS) {
-        const int r = i / CH, c = i % CH;
-        const bool ok = r < G;
-        cp_async16(sq + r * LDQ + c * 8,
-                   ok ? q + (size_t)tok * q_stride + (size_t)(kvh * G + r) * DH + c * 8 : q, ok);
+    // fused form: the iteration and the warp that hold the token's own key, and its new row
+    int it_own = -1, warp_own = -1;
+    uint2 k_own = make_uint2(0u, 0u), v_own = make_uint2(0u, 0u);
+    if (fz.k_cache) {
+        const float* cs = fz.rope ? fz.rope + (size_t)tok * DH : nullptr;
+        if (warp < 4) {
+            for (int r = warp; r < 16; r += 4) {
+                uint2 row = make_uint2(0u, 0u);
+                if (r < G)
+                    row = dt_norm_rope(q + (size_t)tok * q_stride + (size_t)(kvh * G + r) * DH, fz.q_gain,
+                                       fz.eps, cs, lane);
+                *(uint2*)(sq + r * LDQ + 4 * lane) = row;
+            }
+            if (n_it > 0 && p >= t_lo * DT_BN && p < t_hi * DT_BN) {
+                it_own = p / DT_BN - t_lo;
+                warp_own = (p & (DT_BN - 1)) >> 4;
+                if (warp == warp_own) {
+                    k_own = dt_norm_rope(fz.k_new + (size_t)tok * fz.k_stride + (size_t)kvh * DH, fz.k_gain,
+                                         fz.eps, cs, lane);
+                    v_own = *(const uint2*)(fz.v_new + (size_t)tok * fz.v_stride + (size_t)kvh * DH + 4 * lane);
+                    const int row = fz.slots[tok];
+                    if (row >= 0) {
+                        const int page = row >> page_shift, off = row - (page << page_shift);
+                        const size_t at = (((size_t)page * Hkv + kvh) * page_size + off) * DH + 4 * lane;
+                        *(uint2*)(fz.k_cache + at) = k_own;
+                        *(uint2*)(fz.v_cache + at) = v_own;
+                    }
+                }
+            }
+        }
+    } else {
+        for (int i = tid; i < 16 * CH; i += DT_THREADS) {
+            const int r = i / CH, c = i % CH;
+            const bool ok = r < G;
+            cp_async16(sq + r * LDQ + c * 8,
+                       ok ? q + (size_t)tok * q_stride + (size_t)(kvh * G + r) * DH + c * 8 : q, ok);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
     }
-    cp_async_commit();
-    cp_async_wait<0>();
     __syncthreads();
+    // the token's own key and value over the row of the tile that the copy brought
+    auto lay_own = [&](uint32_t tile, uint2 row) {
+        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(tile + dt_at(p & (DT_BN - 1), lane >> 1) + (lane & 1) * 8),
+                     "r"(row.x), "r"(row.y) : "memory");
+        __syncwarp();
+    };
 
     if (warp == 4) {
         // ------------------------------------------------------------- producer
@@ -215,6 +308,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             const uint32_t kt = smem_u32(ring + s * DT_STAGE_BYTES);
             const uint32_t vt = kt + DT_TILE_BYTES;
             const int my_key0 = tile * DT_BN + warp * 16;
+            if (it == it_own && warp == warp_own) lay_own(kt, k_own);
             float sc[4] = {0.f, 0.f, 0.f, 0.f};       // keys g, g+8 x heads 2t, 2t+1
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
@@ -248,6 +342,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             if (ok) ok = dt_wait(smem_u32(&bars[2 * DT_STAGES + s]), ph);        // V
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            if (it == it_own && warp == warp_own) lay_own(vt, v_own);
             if (my_key0 + 16 > key_hi || my_key0 < key_lo) {       // V rows nobody may read: zeros
                 for (int i = lane; i < 16 * 16; i += 32) {
                     const int r = i >> 4, c = i & 15;
@@ -295,6 +390,10 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             const uint32_t kt = smem_u32(ring + s * DT_STAGE_BYTES);
             const uint32_t vt = kt + DT_TILE_BYTES;
             const int my_key0 = t * DT_BN + warp * 16;
+            if (it == it_own && warp == warp_own) {
+                lay_own(kt, k_own);
+                lay_own(vt, v_own);
+            }
             // this warp's V rows that nobody may read: zeros (P is zero there; the page may hold anything)
             if (my_key0 + 16 > key_hi || my_key0 < key_lo) {
                 for (int i = lane; i < 16 * 16; i += 32) {
@@ -499,12 +598,12 @@ TGO_API int tgo_attention_decode_tma_error(int* value) {
 // One token per request (token t is request seq_ids[t] at positions[t]); n_splits CTAs per
 // (token, kv head) write partial results to part_o [T, H, n_splits, 128] and part_ml
 // [T, H, n_splits, 2] for flash_combine_kernel when n_splits > 1.
-TGO_API int tgo_attention_decode_tma(const void* q, long long q_stride, void* out, long long out_stride,
-                                     const void* k_cache, const void* v_cache, int n_pages, int page_size,
-                                     const int* block_tables, int max_blocks, const int* positions,
-                                     const int* seq_ids, int T, int H, int Hkv, int dh, float scale,
-                                     int window, int n_splits, float* part_o, float* part_ml,
-                                     const int* tok_list, cudaStream_t stream) {
+static int dt_launch(const void* q, long long q_stride, void* out, long long out_stride,
+                     const void* k_cache, const void* v_cache, int n_pages, int page_size,
+                     const int* block_tables, int max_blocks, const int* positions,
+                     const int* seq_ids, int T, int H, int Hkv, int dh, float scale,
+                     int window, int n_splits, float* part_o, float* part_ml,
+                     const int* tok_list, const DtFuse& fz, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv || !tgo_attention_decode_tma_supports(dh, H / Hkv, page_size) ||
         n_pages <= 0 || max_blocks <= 0 || window < 0 || n_splits < 1 || n_splits > 65535 || Hkv > 65535 ||
@@ -534,9 +633,50 @@ TGO_API int tgo_attention_decode_tma(const void* q, long long q_stride, void* ou
         return tgo_launch_pdl(flash_decode_tma_kernel<true>, dim3(T, Hkv, n_splits), dim3(DT_THREADS), smem, stream,
                               *mk, *mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_size, shift,
                               block_tables, max_blocks, positions, seq_ids, H, Hkv, scale * 1.4426950408889634f,
-                              window, n_splits, part_o, part_ml, tok_list);
+                              window, n_splits, part_o, part_ml, tok_list, fz);
     return tgo_launch_pdl(flash_decode_tma_kernel<false>, dim3(T, Hkv, n_splits), dim3(DT_THREADS), smem, stream,
                           *mk, *mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_size, shift,
                           block_tables, max_blocks, positions, seq_ids, H, Hkv, scale * 1.4426950408889634f,
-                          window, n_splits, part_o, part_ml, tok_list);
+                          window, n_splits, part_o, part_ml, tok_list, fz);
+}
+
+TGO_API int tgo_attention_decode_tma(const void* q, long long q_stride, void* out, long long out_stride,
+                                     const void* k_cache, const void* v_cache, int n_pages, int page_size,
+                                     const int* block_tables, int max_blocks, const int* positions,
+                                     const int* seq_ids, int T, int H, int Hkv, int dh, float scale,
+                                     int window, int n_splits, float* part_o, float* part_ml,
+                                     const int* tok_list, cudaStream_t stream) {
+    DtFuse none = {};
+    return dt_launch(q, q_stride, out, out_stride, k_cache, v_cache, n_pages, page_size, block_tables,
+                     max_blocks, positions, seq_ids, T, H, Hkv, dh, scale, window, n_splits, part_o,
+                     part_ml, tok_list, none, stream);
+}
+
+// The fused form: q holds the raw query rows of the step's T tokens (every token, no list);
+// k_new and v_new their raw key and value rows; the kernel norms (gains of 128 floats, or
+// null for none) and rotates (rope [T, 128], cosines then sines, or null) q and k, writes k and
+// v to the cache rows slots[t], and attends over the cache including that row.
+TGO_API int tgo_attention_decode_tma_fused(const void* q, long long q_stride, void* out, long long out_stride,
+                                           void* k_cache, void* v_cache, int n_pages, int page_size,
+                                           const int* block_tables, int max_blocks, const int* positions,
+                                           const int* seq_ids, int T, int H, int Hkv, int dh, float scale,
+                                           int window, int n_splits, float* part_o, float* part_ml,
+                                           const void* k_new, long long k_stride, const void* v_new,
+                                           long long v_stride, const float* q_gain, const float* k_gain,
+                                           float eps, const float* rope, const int* slots,
+                                           cudaStream_t stream) {
+    if (!k_new || !v_new || !slots || !k_cache || !v_cache || k_stride % 4 || v_stride % 4 ||
+        ((uintptr_t)k_new % 8) || ((uintptr_t)v_new % 8) || q_stride % 4 || ((uintptr_t)q % 8) ||
+        (q_gain && (uintptr_t)q_gain % 16) || (k_gain && (uintptr_t)k_gain % 16) ||
+        (rope && (uintptr_t)rope % 16))
+        return TGO_E_BAD_ARG;
+    DtFuse fz;
+    fz.k_new = (const bf16*)k_new; fz.k_stride = k_stride;
+    fz.v_new = (const bf16*)v_new; fz.v_stride = v_stride;
+    fz.q_gain = q_gain; fz.k_gain = k_gain; fz.eps = eps;
+    fz.rope = rope; fz.slots = slots;
+    fz.k_cache = (bf16*)k_cache; fz.v_cache = (bf16*)v_cache;
+    return dt_launch(q, q_stride, out, out_stride, k_cache, v_cache, n_pages, page_size, block_tables,
+                     max_blocks, positions, seq_ids, T, H, Hkv, dh, scale, window, n_splits, part_o,
+                     part_ml, nullptr, fz, stream);
 }

@@ -425,6 +425,59 @@ def attention_decode_tma_error() -> int:
     return int(value.value)
 
 
+FUSE_DECODE_QK = True        # decode steps at head size 128: q/k-norm, rotation and cache write
+                             # inside the attention kernel instead of in a kernel before it
+
+
+def decode_attention_fuses(q: torch.Tensor, head_dim: int, group: int, page_size: int,
+                           k_cache: torch.Tensor, v_cache: torch.Tensor, rotary_dim: int) -> bool:
+    """Whether attention_decode_fused takes this layer: bfloat16, the TMA decode kernel's
+    shapes, and a rotation of the whole head or none."""
+    return FUSE_DECODE_QK and USE_TMA_DECODE and q.dtype == torch.bfloat16 and \
+        rotary_dim in (0, head_dim) and k_cache.dim() == 4 and k_cache.is_contiguous() and \
+        v_cache.is_contiguous() and k_cache.dtype == torch.bfloat16 and \
+        attention_decode_tma_supports(head_dim, group, page_size)
+
+
+def attention_decode_fused(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor,
+                           num_heads: int, num_kv_heads: int, head_dim: int,
+                           q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
+                           rope: Optional[torch.Tensor], slots: torch.Tensor, k_cache: torch.Tensor,
+                           v_cache: torch.Tensor, page_size: int, block_tables: torch.Tensor,
+                           positions: torch.Tensor, seq_ids: torch.Tensor, scale: float, window: int,
+                           n_splits: int = 1) -> None:
+    """A decode step's qk_norm_rope_cache and attention_flash in one kernel (head size 128):
+    q, k, v are the raw rows of the step's tokens, one a request; q and k are normed (gains, or
+    None) and rotated (`rope` [T, 128] from rope_table, or None) as qk_norm_rope_cache does,
+    bit for bit, k and v are stored at `slots` of the cache, and every token attends over its
+    request's keys including its own. q is left as it came."""
+    _need_cuda(q, k, v, out, q_gain, k_gain, rope, slots, k_cache, v_cache, block_tables, positions,
+               seq_ids)
+    T = q.shape[0]
+    assert q.dtype == k.dtype == v.dtype == out.dtype == k_cache.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and out.stride(1) == 1
+    assert k.shape[0] == v.shape[0] == T and slots.dtype == torch.int32 and slots.numel() == T
+    assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
+    if rope is not None:
+        assert rope.dtype == torch.float32 and rope.shape == (T, head_dim) and rope.is_contiguous()
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty((T, num_heads, n_splits, head_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((T, num_heads, n_splits, 2), dtype=torch.float32, device=q.device)
+    _check(load_library("attention_decode_tma").tgo_attention_decode_tma_fused(
+        _ptr(q), c_ll(q.stride(0)), _ptr(out), c_ll(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+        c_int(k_cache.shape[0]), c_int(page_size), _ptr(block_tables), c_int(block_tables.shape[1]),
+        _ptr(positions), _ptr(seq_ids), c_int(T), c_int(num_heads), c_int(num_kv_heads),
+        c_int(head_dim), c_float(scale), c_int(window), c_int(n_splits), _ptr(part_o), _ptr(part_ml),
+        _ptr(k), c_ll(k.stride(0)), _ptr(v), c_ll(v.stride(0)), _ptr(q_gain), _ptr(k_gain),
+        c_float(eps), _ptr(rope), _ptr(slots), _stream()),
+        "attention_decode_tma_fused", f"(head_dim={head_dim}, heads={num_heads}/{num_kv_heads})")
+    if n_splits > 1:
+        _check(load_library("attention_flash").tgo_attention_flash_combine(
+            _ptr(part_o), _ptr(part_ml), _ptr(out), c_ll(out.stride(0)), c_int(T), c_int(num_heads),
+            c_int(head_dim), c_int(n_splits), _stream()), "attention_flash_combine")
+
+
 def attention_flash(q: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int,
                     head_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_size: int,
                     block_tables: torch.Tensor, positions: torch.Tensor, seq_ids: torch.Tensor,

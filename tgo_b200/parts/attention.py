@@ -270,6 +270,16 @@ class GQAAttention(Part):
         fused = self.position is None or getattr(self.position, "fusable", False)
         rope, rot = self.position.rotary(ctx) if (fused and self.position is not None) \
             else (None, 0)
+        if fused and k is not None and ctx.decode_only and ops.decode_attention_fuses(
+                q, dh, H // Hkv, cache.page_size, cache.k, cache.v, rot if rope is not None else 0):
+            # a decode step at head size 128: the attention kernel norms, rotates and stores
+            a = torch.empty((x.shape[0], qw), dtype=q.dtype, device=q.device)
+            ops.attention_decode_fused(
+                q, k, v, a, H, Hkv, dh, self.q_gain, self.k_gain, self.eps, rope, cache.slots,
+                cache.k, cache.v, cache.page_size, cache.block_tables, ctx.positions, ctx.seq_ids,
+                self.scale, self.window or 0,
+                n_splits=decode_splits(ctx, Hkv, self.window or 0, q.device))
+            return ops.linear(a, self.w_o, residual=residual)
         if fused:
             ops.qk_norm_rope_cache(q, k, v, H, Hkv, dh, self.q_gain, self.k_gain, self.eps,
                                    rope, rot, cache.slots if k is not None else None,
