@@ -222,7 +222,6 @@ static int gs_launch(const bf16* x, const bf16* w, void* y, int M, int N, int K,
 // of 5.9; o 9.6 with a loop of 3.8: between a kernel's start and its first product lie 4 us
 // (index arithmetic and first instructions 0.9, x and the first weights 2 to 3) whatever the
 // form, and that, 13 kernels a layer, is what holds a decode step at 0.63 of the HBM rate.
-// Asking for the weights before x made x wait behind them (2.7 us instead of 1.9).
 #define GP_WARPS 16
 #define GP_UNROLL 4
 #define GP_SET_K (32 * GP_UNROLL)
@@ -365,58 +364,72 @@ gemm_stream_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void*
         if (++c_set == n_sets) { c_set = 0; flush(c_tile); ++c_tile; }
     };
 
-    // x first, then the weights: the copies of x queue behind whatever this SM has asked for
-    // before them, and behind a first round of weights they took 2.7 us to arrive instead of
-    // under 1. (Asking for weights before the wait would gain nothing here: a kernel of the
-    // step starts when the one before it has ended.)
+    // The first weights before the wait for the kernel that makes x: they depend on nothing.
+    // Where the rows are made here from the float32 stream this matters most: every CTA reads
+    // the same 128 KB of it from the L2, 4.4 us during which HBM would stand idle (a decode step
+    // went from 3.43 to 3.29 ms at batch 1 and from 3.91 to 3.86 at batch 8); for rows given
+    // as bfloat16 the copies of x then queue behind the weights (2.7 us instead of 1.9), but the
+    // step still gains (3.29 to 3.27, 3.85 to 3.84).
+    load_w(a_lo, a_hi);
+    load_w(b_lo, b_hi);
     pdl_wait();
     if (NORM_IN && k_end - k_begin <= 256) {
-        // every row's piece in registers at once (the weights' registers are not in use yet):
-        // one trip to the L2 for all of them, not one a row
+        // four rows' pieces in registers at a time (both sets of weights are on their way):
+        // the sums of squares first, then the rows again (from the L1 now) to scale them
         const int cols4 = k_end > k_begin ? (k_end - k_begin) / 4 : 0;
-        float4 v[8][2];
+        auto load4 = [&](float4 (&v)[4][2], int m0) {
 #pragma unroll
-        for (int m = 0; m < 8; ++m)
+            for (int r = 0; r < 4; ++r)
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                const int c = lane + 32 * q;
-                v[m][q] = (m < M && c < cols4) ? *(const float4*)(hsrc + (size_t)m * K + k_begin + 4 * c)
-                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int q = 0; q < 2; ++q) {
+                    const int c = lane + 32 * q, m = m0 + r;
+                    v[r][q] = (m < M && c < cols4) ? *(const float4*)(hsrc + (size_t)m * K + k_begin + 4 * c)
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+        };
+        for (int m0 = 0; m0 < M; m0 += 4) {
+            float4 v[4][2];
+            load4(v, m0);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                float ss = 0.f;
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+                    ss += v[r][q].x * v[r][q].x + v[r][q].y * v[r][q].y + v[r][q].z * v[r][q].z + v[r][q].w * v[r][q].w;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0) ssq[(m0 + r) * GP_WARPS + warp] = ss;
             }
+        }
+        __syncthreads();
         float4 gn[2];
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
             const int c = lane + 32 * q;
             gn[q] = c < cols4 ? *(const float4*)(gain + k_begin + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
+        for (int m0 = 0; m0 < M; m0 += 4) {
+            float4 v[4][2];
+            load4(v, m0);
 #pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            float ss = 0.f;
+            for (int r = 0; r < 4; ++r) {
+                const int m = m0 + r;
+                if (m >= M) break;
+                float total = 0.f;
 #pragma unroll
-            for (int q = 0; q < 2; ++q)
-                ss += v[m][q].x * v[m][q].x + v[m][q].y * v[m][q].y + v[m][q].z * v[m][q].z + v[m][q].w * v[m][q].w;
+                for (int wv = 0; wv < GP_WARPS; ++wv) total += ssq[m * GP_WARPS + wv];
+                const float scale = rsqrtf(total / (float)K + eps);
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            if (lane == 0) ssq[m * GP_WARPS + warp] = ss;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int m = 0; m < 8; ++m) {
-            if (m >= M) break;
-            float total = 0.f;
-#pragma unroll
-            for (int wv = 0; wv < GP_WARPS; ++wv) total += ssq[m * GP_WARPS + wv];
-            const float scale = rsqrtf(total / (float)K + eps);
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                const int c = lane + 32 * q;
-                if (c >= cols4) continue;
-                __nv_bfloat162 lo2 = __floats2bfloat162_rn((v[m][q].x * scale) * gn[q].x, (v[m][q].y * scale) * gn[q].y);
-                __nv_bfloat162 hi2 = __floats2bfloat162_rn((v[m][q].z * scale) * gn[q].z, (v[m][q].w * scale) * gn[q].w);
-                uint2 pk;
-                pk.x = *(uint32_t*)&lo2;
-                pk.y = *(uint32_t*)&hi2;
-                *(uint2*)(xs + (size_t)m * xs_ld + k_begin + 4 * c) = pk;
+                for (int q = 0; q < 2; ++q) {
+                    const int c = lane + 32 * q;
+                    if (c >= cols4) continue;
+                    __nv_bfloat162 lo2 = __floats2bfloat162_rn((v[r][q].x * scale) * gn[q].x, (v[r][q].y * scale) * gn[q].y);
+                    __nv_bfloat162 hi2 = __floats2bfloat162_rn((v[r][q].z * scale) * gn[q].z, (v[r][q].w * scale) * gn[q].w);
+                    uint2 pk;
+                    pk.x = *(uint32_t*)&lo2;
+                    pk.y = *(uint32_t*)&hi2;
+                    *(uint2*)(xs + (size_t)m * xs_ld + k_begin + 4 * c) = pk;
+                }
             }
         }
     } else if (NORM_IN) {
@@ -467,8 +480,6 @@ gemm_stream_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void*
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     }
-    load_w(a_lo, a_hi);
-    load_w(b_lo, b_hi);
     if (!NORM_IN) asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     __syncwarp();
     for (int s = 0; s < total; s += 2) {
