@@ -77,6 +77,43 @@ def test_replay_with_the_tcgen05_product_from_65_rows(models, family, monkeypatc
     assert worst <= tol, f"{family}: error {worst:.3e} at {where}, allowed {tol:.3e}"
 
 
+# ------------------------------------------- the persistent decode products inside a model
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_through_the_persistent_products(tmp_path_factory, dtype):
+    """Tiny D (hidden, q width and intermediate size 2048, head size 128): 1, 3 and 8 requests
+    decoding together. In bfloat16 every product of those steps, the vocabulary product
+    included, takes the persistent form of the weight-streaming kernel, the two norms of a
+    layer are made inside the q/k/v and gate/up products, and the attention kernel norms,
+    rotates and stores the step's own q, k and v. The logits are the plain implementation's."""
+    import tgo_b200
+    from tgo_b200.kernels import ops
+    cfg, run = tiny.TINY_D, tiny.TINY_D_RUN
+    d = tiny.make_model_dir(tmp_path_factory.mktemp("schedD"), cfg, run["seed"], run["sigma"])
+    if dtype == "bfloat16":
+        for M in (1, 3, 8):
+            assert ops.folds_norm(M, 2048 + 2 * 512, 2048) and ops.folds_norm(M, 4096, 2048)
+            assert ops.folds_norm(M, 512, 2048)
+    reqs = tiny.random_requests(cfg["vocab_size"], [40, 23, 61, 17, 33, 50, 29, 45], seed=41)
+    want, rounded = tiny.plain_logits(d, reqs), tiny.plain_logits_rounded(d, reqs)
+    model = tgo_b200.open(d, dtype=dtype)
+    for live in (1, 3, 8):
+        some = {r: reqs[r] for r in list(reqs)[:live]}
+        trace = crowd_trace(some, 12)
+        eng = model.new_engine(page_size=run["page_size"], max_tokens=tiny.max_tokens_of(trace),
+                               num_slots=live)
+        launches = ops.LAUNCHES[0]
+        got = tiny.run_trace_engine(eng, trace)
+        eng.check_kernels()
+        sub = {r: want[r] for r in some}
+        assert {k[0] for k in got} == set(some) and len(got) == sum(len(t) for t in some.values())
+        worst, where, tol = tiny.compare(got, sub, cfg, dtype, f"persistent_products/{live}/{dtype}",
+                                         {r: rounded[r] for r in some})
+        assert worst <= tol, f"{live} live/{dtype}: error {worst:.3e} at {where}, allowed {tol:.3e}"
+        assert ops.LAUNCHES[0] > launches
+
+
 # ---------------------------------------------------------- many requests live together
 
 

@@ -15,6 +15,13 @@ kernels too. (The tcgen05 product starts above 1024 rows: tests/test_schedules_g
 Tiny C with a 1200-token request, and with the threshold lowered to 65 rows.)
 
   TINY_C      2    160     4    2   128       512      272   320   5e5    1e-5   no    40 (layer 0)  16
+
+A fourth, TINY_D, is wide instead of tiny where the decode kernels ask for it: hidden size,
+q width and intermediate size of 2048, so that at 1 to 8 rows every product of a layer and
+the vocabulary product take the persistent form of the weight-streaming kernel, with the two
+norms folded into the q/k/v and gate/up products (tests/test_schedules_gpu.py).
+
+  TINY_D      2   2048    16    4   128      2048     2048   512   1e6    1e-6   no    none          16
 """
 from __future__ import annotations
 
@@ -50,6 +57,13 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], hidden_size=160, num_hidden_la
 TINY_C_RUN = dict(seed=2, sigma=0.03, page_size=16)
 
 TINIES = {"A": (TINY_A, TINY_A_RUN), "B": (TINY_B, TINY_B_RUN), "C": (TINY_C, TINY_C_RUN)}
+
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], hidden_size=2048, num_hidden_layers=2,
+              num_attention_heads=16, num_key_value_heads=4, head_dim=128, intermediate_size=2048,
+              vocab_size=512, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False,
+              max_position_embeddings=512, attention_bias=False, sliding_window=None,
+              use_sliding_window=False)
+TINY_D_RUN = dict(seed=4, sigma=0.02, page_size=16)
 
 
 def make_model_dir(path, config, seed, sigma, gain_sigma=0.1):
