@@ -191,10 +191,14 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    __syncthreads();          // the pages and the barriers are there: the producer may start
     // fused form: the iteration and the warp that hold the token's own key, and its new row
     int it_own = -1, warp_own = -1;
     uint2 k_own = make_uint2(0u, 0u), v_own = make_uint2(0u, 0u);
-    if (fz.k_cache) {
+    // The four computing warps stage q (and in the fused form make it) while the fifth already
+    // asks for the first tiles; they meet at a barrier of their own.
+    if (warp == 4) {
+    } else if (fz.k_cache) {
         const float* cs = fz.rope ? fz.rope + (size_t)tok * DH : nullptr;
         if (warp < 4) {
             for (int r = warp; r < 16; r += 4) {
@@ -222,7 +226,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             }
         }
     } else {
-        for (int i = tid; i < 16 * CH; i += DT_THREADS) {
+        for (int i = tid; i < 16 * CH; i += 128) {
             const int r = i / CH, c = i % CH;
             const bool ok = r < G;
             cp_async16(sq + r * LDQ + c * 8,
@@ -231,7 +235,7 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         cp_async_commit();
         cp_async_wait<0>();
     }
-    __syncthreads();
+    if (warp < 4) asm volatile("bar.sync 1, 128;" ::: "memory");
     // the token's own key and value over the row of the tile that the copy brought
     auto lay_own = [&](uint32_t tile, uint2 row) {
         asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(tile + dt_at(p & (DT_BN - 1), lane >> 1) + (lane & 1) * 8),
