@@ -31,7 +31,9 @@
 // on the FMA pipe for every second or fourth exponential (issue-bound: 81.5 and 76.9 us
 // against 77.6); two softmax groups of four warps with an S and an O each (107 us); three S
 // buffers and one O buffer, so that Q K^T may run two key tiles ahead (66.5 us against 65.6,
-// 614 us against 614 at 8192 tokens: the softmax threads do not wait for the products).
+// 614 us against 614 at 8192 tokens: the softmax threads do not wait for the products); four
+// softmax threads a row, 32 keys each, sixteen softmax warps (68.5 us against 66.2, 651 against
+// 612 at 8192 tokens: nor do they lack warps to hide their own latency).
 //
 // Every wait has a time limit (about two seconds): it records a code, the CTA stops issuing,
 // frees its tensor memory and returns. No cluster, no multicast.
